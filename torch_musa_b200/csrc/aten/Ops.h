@@ -1,0 +1,41 @@
+// Shared declarations for the ATen operator layer.
+#pragma once
+
+#include "core/Device.h"
+#include "core/Stream.h"
+#include "kernels/b200_kernels.h"
+
+#include <ATen/core/Tensor.h>
+
+namespace b200 {
+namespace ops {
+
+inline bool on_device(const at::Tensor& t) { return t.defined() && t.device().type() == kDeviceType; }
+
+// dtype code shared with the kernel library, or -1 if the kernels do not cover the type
+inline int kdtype(at::ScalarType t) {
+  switch (t) {
+    case at::kFloat: return B200_F32;
+    case at::kBFloat16: return B200_BF16;
+    case at::kHalf: return B200_F16;
+    default: return -1;
+  }
+}
+
+// Strided and/or dtype-converting same-device copy on our own kernels. Returns false when the
+// configuration is not covered (caller then uses the generic route).
+bool try_native_cast_copy(const at::Tensor& src, const at::Tensor& dst, cudaStream_t stream);
+
+inline cudaStream_t current_raw_stream(const at::Tensor& t) { return get_current_stream(t.device().index()).stream(); }
+
+// Switch the tcgen05 GEMM off/on (off: every matmul goes to the library GEMM through the fallback).
+B200_EXPORT void set_tensor_core_gemm(bool on);
+B200_EXPORT bool tensor_core_gemm_enabled();
+
+// Counter of hand-written kernel launches (reported by the benchmark as its own-kernel launch count).
+B200_EXPORT void count_launch(int n = 1);
+B200_EXPORT int64_t launch_count();
+B200_EXPORT void reset_launch_count();
+
+}  // namespace ops
+}  // namespace b200

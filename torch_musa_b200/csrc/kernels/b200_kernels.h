@@ -1,0 +1,225 @@
+/* C ABI of libb200_kernels.so: every hand-written sm_100a kernel of the backend.
+ *
+ * Conventions: pointers are device pointers unless named host_*; every function
+ * enqueues work on `stream` and returns a cudaError_t value as int (0 = ok);
+ * nothing here allocates device memory unless its comment says so; `dtype` is one
+ * of the B200_* codes below.  Callable from C, ctypes and the C++ operator layer.
+ */
+#pragma once
+
+#include <cuda_runtime_api.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_API __attribute__((visibility("default")))
+
+enum { B200_F32 = 0, B200_BF16 = 1, B200_F16 = 2, B200_F64 = 3, B200_I32 = 4, B200_I64 = 5, B200_U8 = 6,
+       B200_BOOL = 7, B200_I8 = 8, B200_I16 = 9, B200_FP8_E4M3 = 10, B200_FP8_E5M2 = 11 };
+
+/* number of kernels launched by this library since load / last reset (host counter) */
+B200_API int64_t b200_launch_count(void);
+B200_API void b200_reset_launch_count(void);
+B200_API const char* b200_kernels_arch(void);
+
+/* ---------------------------------------------------------------- elementwise */
+enum {
+  B200_OP_ADD = 0, B200_OP_SUB, B200_OP_MUL, B200_OP_DIV, B200_OP_MAXIMUM, B200_OP_MINIMUM,
+  B200_OP_RELU = 32, B200_OP_GELU_ERF, B200_OP_GELU_TANH, B200_OP_SILU, B200_OP_SIGMOID, B200_OP_TANH,
+  B200_OP_EXP, B200_OP_LOG, B200_OP_NEG, B200_OP_ABS, B200_OP_SQRT, B200_OP_RSQRT, B200_OP_RECIPROCAL,
+  B200_OP_SQUARE, B200_OP_COPY,
+  /* backward forms: out = f(grad, x) as a binary op */
+  B200_OP_RELU_BWD = 64, B200_OP_GELU_ERF_BWD, B200_OP_GELU_TANH_BWD, B200_OP_SILU_BWD, B200_OP_SIGMOID_BWD,
+  B200_OP_TANH_BWD
+};
+/* out[i] = op(a[i], alpha*b[i]) (alpha only for ADD/SUB); contiguous, same dtype; b may be NULL with
+ * b_scalar used instead. */
+B200_API int b200_binary(int op, int dtype, void* out, const void* a, const void* b, double b_scalar, double alpha,
+                         int64_t n, cudaStream_t stream);
+B200_API int b200_unary(int op, int dtype, void* out, const void* a, int64_t n, cudaStream_t stream);
+/* dtype-converting / strided copy. ndim <= 8; strides in elements. */
+B200_API int b200_cast_copy(void* dst, int dst_dtype, const void* src, int src_dtype, int ndim, const int64_t* sizes,
+                            const int64_t* dst_strides, const int64_t* src_strides, cudaStream_t stream);
+B200_API int b200_fill(void* out, int dtype, double value, int64_t n, cudaStream_t stream);
+/* out = a + alpha * (t1 * t2) / out = a + alpha * (t1 / t2) */
+B200_API int b200_addcmul(int dtype, void* out, const void* a, const void* t1, const void* t2, double alpha, int div,
+                          int64_t n, cudaStream_t stream);
+/* busy-wait for `cycles` SM clock ticks, never longer than max_cycles (bounded) */
+B200_API int b200_sleep(int64_t cycles, cudaStream_t stream);
+
+/* ---------------------------------------------------------------- reductions */
+enum { B200_RED_SUM = 0, B200_RED_MEAN, B200_RED_MAX, B200_RED_MIN, B200_RED_SUMSQ, B200_RED_ABSMAX };
+/* reduce the last dimension: in [rows, cols] contiguous -> out [rows]; out dtype = in dtype (accumulation fp32) */
+B200_API int b200_reduce_rows(int op, int dtype, void* out, const void* in, int64_t rows, int64_t cols,
+                              cudaStream_t stream);
+/* reduce everything to one value: out[0] (fp32 if out_f32 else input dtype). `scratch` needs >= 4*1024 bytes. */
+B200_API int b200_reduce_all(int op, int dtype, void* out, int out_f32, const void* in, int64_t n, float* scratch,
+                             cudaStream_t stream);
+/* column reduction: in [rows, cols] -> out [cols] (sum over rows); out fp32 or in dtype */
+B200_API int b200_reduce_cols_sum(int dtype, void* out, int out_dtype, const void* in, int64_t rows, int64_t cols,
+                                  cudaStream_t stream);
+
+/* ---------------------------------------------------------------- normalisation */
+/* y = x * rstd * w ; rstd[rows] fp32.  residual (optional): x_in = x + residual, written to res_out. */
+B200_API int b200_rmsnorm_fwd(int dtype, void* y, float* rstd, const void* x, const void* w, const void* residual,
+                              void* res_out, int64_t rows, int64_t cols, float eps, cudaStream_t stream);
+/* dx (and optionally dw partial sums in dw_partial[nblocks, cols] fp32; pass NULL to skip) */
+B200_API int b200_rmsnorm_bwd(int dtype, void* dx, float* dw_partial, int* nblocks_out_host, const void* dy,
+                              const void* x, const void* w, const float* rstd, int64_t rows, int64_t cols,
+                              cudaStream_t stream);
+B200_API int b200_rmsnorm_bwd_partial_rows(int64_t rows, int64_t cols);
+B200_API int b200_layernorm_fwd(int dtype, void* y, float* mean, float* rstd, const void* x, const void* w,
+                                const void* b, int64_t rows, int64_t cols, float eps, cudaStream_t stream);
+B200_API int b200_layernorm_bwd(int dtype, void* dx, float* dw_partial, float* db_partial, const void* dy,
+                                const void* x, const void* w, const float* mean, const float* rstd, int64_t rows,
+                                int64_t cols, cudaStream_t stream);
+
+/* ---------------------------------------------------------------- softmax / loss */
+B200_API int b200_softmax_fwd(int dtype, void* y, const void* x, int64_t rows, int64_t cols, int log_softmax,
+                              cudaStream_t stream);
+/* dx from dy and y (softmax output or log-softmax output) */
+B200_API int b200_softmax_bwd(int dtype, void* dx, const void* dy, const void* y, int64_t rows, int64_t cols,
+                              int log_softmax, cudaStream_t stream);
+/* fused cross entropy: per-row loss (fp32) and log-sum-exp (fp32); rows with target == ignore_index give 0 */
+B200_API int b200_cross_entropy_fwd(int dtype, float* loss, float* lse, const void* logits, const int64_t* target,
+                                    int64_t rows, int64_t cols, int64_t ignore_index, float label_smoothing,
+                                    cudaStream_t stream);
+/* dlogits = (softmax - onehot) * grad_scale[row or scalar]; may run in place over logits */
+B200_API int b200_cross_entropy_bwd(int dtype, void* dlogits, const void* logits, const float* lse,
+                                    const int64_t* target, const float* grad_loss, int grad_is_scalar, float scale,
+                                    int64_t rows, int64_t cols, int64_t ignore_index, float label_smoothing,
+                                    cudaStream_t stream);
+/* vocab-parallel pieces: per-row (max, sumexp, target logit) over a vocab shard [vocab_start, vocab_start+cols) */
+B200_API int b200_online_softmax_stats(int dtype, float* stats3, const void* logits, const int64_t* target,
+                                       int64_t rows, int64_t cols, int64_t vocab_start, cudaStream_t stream);
+/* combine world x [rows,3] stats -> loss[rows]; writes softmax-gradient in place into the logits shard */
+B200_API int b200_vocab_parallel_ce_finish(int dtype, float* loss, void* logits_inout, const float* all_stats,
+                                           int world, const int64_t* target, int64_t rows, int64_t cols,
+                                           int64_t vocab_start, int64_t ignore_index, cudaStream_t stream);
+
+/* ---------------------------------------------------------------- fused LLM ops */
+/* rotary embedding on x [tokens, heads, dim] with cos/sin [tokens(or seq), dim/2] (fp32);
+ * position of token t is pos[t] if pos != NULL else (t % seq). interleaved: pairs (2i,2i+1) vs halves (i,i+d/2).
+ * backward == forward with conj=1. */
+B200_API int b200_rope(int dtype, void* out, const void* x, const float* cos, const float* sin, const int64_t* pos,
+                       int64_t tokens, int64_t seq, int heads, int dim, int64_t x_token_stride, int64_t x_head_stride,
+                       int interleaved, int conj, cudaStream_t stream);
+/* x [rows, 2*h] -> out [rows, h] = silu(x[:, :h]) * x[:, h:]  (gate_first=1) */
+B200_API int b200_swiglu_fwd(int dtype, void* out, const void* x, int64_t rows, int64_t h, cudaStream_t stream);
+B200_API int b200_swiglu_bwd(int dtype, void* dx, const void* dy, const void* x, int64_t rows, int64_t h,
+                             cudaStream_t stream);
+/* two-tensor form: out = silu(gate) * up */
+B200_API int b200_silu_mul_fwd(int dtype, void* out, const void* gate, const void* up, int64_t n, cudaStream_t stream);
+B200_API int b200_silu_mul_bwd(int dtype, void* dgate, void* dup, const void* dy, const void* gate, const void* up,
+                               int64_t n, cudaStream_t stream);
+
+/* ---------------------------------------------------------------- embedding */
+B200_API int b200_embedding_fwd(int dtype, void* out, const void* weight, const int64_t* idx, int64_t n, int64_t dim,
+                                int64_t vocab, cudaStream_t stream);
+/* dense backward, fp32 atomics into grad_weight_f32 [vocab, dim] (must be zeroed), skipping padding_idx */
+B200_API int b200_embedding_bwd_atomic(int dtype, float* grad_weight_f32, const void* grad_out, const int64_t* idx,
+                                       int64_t n, int64_t dim, int64_t vocab, int64_t padding_idx,
+                                       cudaStream_t stream);
+/* deterministic: indices pre-sorted (sorted_idx, perm); one warp group per segment */
+B200_API int b200_embedding_bwd_sorted(int dtype, void* grad_weight, const void* grad_out, const int64_t* sorted_idx,
+                                       const int64_t* perm, int64_t n, int64_t dim, int64_t vocab,
+                                       int64_t padding_idx, cudaStream_t stream);
+
+/* ---------------------------------------------------------------- dropout (Philox 4x32-10) */
+typedef struct {
+  uint64_t seed, offset;
+  const int64_t* seed_ptr;
+  const int64_t* offset_ptr;
+  uint64_t offset_intragraph;
+  int captured;
+} b200_philox_t;
+B200_API int b200_dropout_fwd(int dtype, void* out, uint8_t* mask, const void* x, int64_t n, float p,
+                              b200_philox_t rng, cudaStream_t stream);
+B200_API int b200_dropout_bwd(int dtype, void* dx, const void* dy, const uint8_t* mask, int64_t n, float scale,
+                              cudaStream_t stream);
+B200_API int b200_uniform(int dtype, void* out, int64_t n, double lo, double hi, b200_philox_t rng, cudaStream_t s);
+B200_API int b200_normal(int dtype, void* out, int64_t n, double mean, double std, b200_philox_t rng, cudaStream_t s);
+
+/* ---------------------------------------------------------------- multi-tensor apply */
+/* Lists are host arrays of device pointers; metadata travels in kernel parameter space. */
+typedef struct {
+  float lr, beta1, beta2, eps, weight_decay;
+  int adamw;        /* decoupled weight decay */
+  int amsgrad;
+  int maximize;
+  const float* lr_ptr;        /* device scalar overrides lr when non-NULL */
+  const float* grad_scale;    /* device scalar; grads are divided by it when non-NULL */
+  const float* found_inf;     /* device scalar; the step is skipped when *found_inf != 0 */
+} b200_adam_args_t;
+/* steps: device pointers to per-tensor fp32 step counters (incremented in kernel unless found_inf) */
+B200_API int b200_multi_tensor_adam(int n_tensors, int param_dtype, int grad_dtype, int state_dtype,
+                                    void* const* params, void* const* grads, void* const* exp_avg,
+                                    void* const* exp_avg_sq, void* const* max_exp_avg_sq, float* const* steps,
+                                    const int64_t* numels, b200_adam_args_t args, cudaStream_t stream);
+typedef struct {
+  float lr, momentum, dampening, weight_decay;
+  int nesterov, maximize, first_step;
+  const float* lr_ptr;
+  const float* grad_scale;
+  const float* found_inf;
+} b200_sgd_args_t;
+B200_API int b200_multi_tensor_sgd(int n_tensors, int param_dtype, int grad_dtype, void* const* params,
+                                   void* const* grads, void* const* momentum_bufs, const int64_t* numels,
+                                   b200_sgd_args_t args, cudaStream_t stream);
+/* per-tensor and global L2 norm. out_per_tensor [n] fp32 (may be NULL), out_total[1] fp32. scratch: (n*320+320) floats */
+B200_API int b200_multi_tensor_l2norm(int n_tensors, int dtype, void* const* tensors, const int64_t* numels,
+                                      float* out_total, float* out_per_tensor, float* scratch, cudaStream_t stream);
+B200_API size_t b200_multi_tensor_l2norm_scratch_floats(int n_tensors);
+/* x *= scale (device scalar scale_ptr or host scale); sets *found_inf=1 when a non-finite value is seen */
+B200_API int b200_multi_tensor_scale(int n_tensors, int dtype, void* const* tensors, const int64_t* numels,
+                                     const float* inv_scale_ptr, float host_scale, float* found_inf,
+                                     cudaStream_t stream);
+/* generic foreach binary with scalar: t = op(t, s) or t = t + alpha * u */
+B200_API int b200_multi_tensor_axpby(int n_tensors, int dtype, void* const* out, void* const* x, void* const* y,
+                                     const int64_t* numels, float a, float b, cudaStream_t stream);
+/* LAMB: stage 1 computes update in `update` list; stage 2 applies trust ratio per tensor */
+typedef struct {
+  float lr, beta1, beta2, eps, weight_decay, max_grad_norm;
+  int step, bias_correction, grad_averaging, adam_w_mode, use_nvlamb;
+  const float* global_grad_norm; /* device scalar */
+} b200_lamb_args_t;
+B200_API int b200_multi_tensor_lamb(int n_tensors, int dtype, void* const* params, void* const* grads,
+                                    void* const* exp_avg, void* const* exp_avg_sq, const int64_t* numels,
+                                    b200_lamb_args_t args, float* scratch, cudaStream_t stream);
+B200_API size_t b200_multi_tensor_lamb_scratch_floats(int n_tensors, const int64_t* numels);
+/* GradScaler bookkeeping: one thread */
+B200_API int b200_amp_update_scale(float* scale, int* growth_tracker, const float* found_inf, float growth,
+                                   float backoff, int growth_interval, cudaStream_t stream);
+
+/* ---------------------------------------------------------------- GEMM (tcgen05 + TMEM + TMA) */
+/* D[M,N] = alpha * A[M,K] x B^T + beta * C, with B given as [N,K] when trans_b == 0 layout code:
+ *   a_kmajor: A is row-major [M,K] (K contiguous); else A is stored [K,M] (M contiguous)
+ *   b_kmajor: B is stored [N,K] (K contiguous);    else B is stored [K,N] (N contiguous)
+ * lda/ldb/ldd are the leading (non-contiguous) strides in elements. dtype: BF16 or F16 inputs, fp32 accumulate,
+ * output dtype out_dtype (BF16/F16/F32). bias (optional, [N], out dtype or fp32) is added in the epilogue;
+ * epilogue act: 0 none, 1 relu, 2 gelu(erf), 3 silu. accumulate != 0: D += result (beta = 1).
+ * batch > 1 strides in elements (0 = broadcast). Returns cudaErrorNotSupported for shapes the kernel does not
+ * cover (caller falls back): K % 8 != 0 or unaligned leading strides.
+ */
+typedef struct {
+  int m, n, k;
+  int a_kmajor, b_kmajor;
+  int64_t lda, ldb, ldd;
+  int in_dtype, out_dtype;
+  int batch;
+  int64_t stride_a, stride_b, stride_d;
+  const void* bias; int bias_dtype;
+  int act;
+  int accumulate;
+  float alpha;
+} b200_gemm_desc_t;
+B200_API int b200_gemm(const b200_gemm_desc_t* desc, void* d, const void* a, const void* b, cudaStream_t stream);
+/* 1 when the running driver exposes the tensor-map encoder the kernel needs */
+B200_API int b200_gemm_available(void);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,585 @@
+// bf16/fp16 GEMM on the 5th-generation tensor cores.
+//
+//   D[M,N] (+)= alpha * A[M,K] * B[N,K]^T (+ bias) (act)
+//
+// One persistent CTA per SM walks 128x256 output tiles.  Six warps, three roles:
+//   warp 0   TMA producer: cp.async.bulk.tensor (no multicast) fills a 4-stage ring of
+//            128x64 A and 256x64 B tiles in 128B-swizzled shared memory;
+//   warp 1   MMA issuer: one elected lane issues tcgen05.mma (cta_group::1, kind::f16,
+//            M128 N256 K16) from shared-memory descriptors into one of two 256-column
+//            TMEM accumulators and releases ring slots with tcgen05.commit;
+//   warps 2-5 epilogue: tcgen05.ld the finished accumulator (each warp its 32 TMEM lanes),
+//            apply alpha / bias / activation / accumulate, convert, store 16-byte vectors.
+// The two TMEM accumulators let the epilogue of tile i overlap the main loop of tile i+1.
+// Either operand may be K-major or MN-major in memory (forward, dgrad and wgrad GEMMs
+// without explicit transposes): MN-major tiles are fetched as 64-element boxes and
+// described to the tensor core with the MN-major canonical layout.
+// Every mbarrier wait is bounded: on expiry the CTA records a status word, stops issuing
+// work, frees its TMEM and returns, so a broken pipeline can never hang the device.
+//
+// Parity: the reference sends mm/addmm/bmm to a closed vendor library
+// (reference torch_musa/csrc/aten/ops/Matmul.cpp:293-335,373-380).
+#include "common.cuh"
+
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+namespace b200k {
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int kStages = 4;
+constexpr int kAccStages = 2;
+constexpr int kThreads = 192;
+constexpr int kATileBytes = BM * BK * 2;  // 16 KB
+constexpr int kBTileBytes = BN * BK * 2;  // 32 KB
+constexpr int kStageBytes = kATileBytes + kBTileBytes;
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr uint32_t kTmemCols = 512;
+constexpr long long kWaitCycles = 4000000000ll;  // ~2 s: far beyond any legitimate wait
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait. Returns false when the wait gave up (abort flag set by anyone, or time-out).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try(bar, parity)) return true;
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while (!mbar_try(bar, parity)) {
+    if ((++spins & 0x3ff) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kWaitCycles) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1,
+                                            int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                         uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the mbarrier once every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (sm_100 format): 128-byte swizzle, version 1.
+//   bits [0,14)  start address >> 4      bits [16,30) leading byte offset >> 4
+//   bits [32,46) stride byte offset >> 4 bits [46,48) version = 1   bits [61,64) layout = 2 (SWIZZLE_128B)
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+struct Params {
+  int m, n, k;
+  int batch;
+  int tiles_m, tiles_n;
+  int64_t ldd;       // elements
+  int64_t stride_d;  // elements between batches
+  const void* bias;
+  int bias_f32;
+  int act;
+  int accumulate;
+  float alpha;
+  uint32_t idesc;
+  int* status;  // device word: set to 1 when a bounded wait expired
+};
+
+__device__ __forceinline__ float apply_act(float v, int act) {
+  switch (act) {
+    case 1: return v > 0.f ? v : 0.f;
+    case 2: return 0.5f * v * (1.f + erff(v * 0.70710678118654752f));
+    case 3: return v / (1.f + __expf(-v));
+    default: return v;
+  }
+}
+
+template <typename OutT>
+__device__ __forceinline__ void store_chunk(OutT* __restrict__ drow, const float (&v)[32], int ncols_valid, bool vec_ok) {
+  if (vec_ok && ncols_valid == 32) {
+    if constexpr (sizeof(OutT) == 2) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        Vec16<OutT> o;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o.v[e] = ToF<OutT>::from(v[q * 8 + e]);
+        st16(drow + q * 8, o);
+      }
+    } else {
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(drow) + q * 4) =
+            make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+    }
+  } else {
+#pragma unroll
+    for (int e = 0; e < 32; ++e)
+      if (e < ncols_valid) drow[e] = ToF<OutT>::from(v[e]);
+  }
+}
+
+template <typename OutT, bool A_KMAJOR, bool B_KMAJOR>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, OutT* __restrict__ d,
+            const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment is required by the 128-byte swizzle atoms.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem + kStages * kATileBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  uint64_t* full_bar = bars;                       // [kStages]
+  uint64_t* empty_bar = bars + kStages;            // [kStages]
+  uint64_t* tfull_bar = bars + 2 * kStages;        // [kAccStages]
+  uint64_t* tempty_bar = tfull_bar + kAccStages;   // [kAccStages]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + kAccStages);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int k_blocks = (p.k + BK - 1) / BK;
+  const int tiles_per_batch = p.tiles_m * p.tiles_n;
+  const int total_tiles = tiles_per_batch * p.batch;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int s = 0; s < kAccStages; ++s) {
+      mbar_init(&tfull_bar[s], 1);
+      mbar_init(&tempty_bar[s], 4);  // one arrival per epilogue warp
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int b = tile / tiles_per_batch;
+        const int r = tile - b * tiles_per_batch;
+        const int m0 = (r % p.tiles_m) * BM;
+        const int n0 = (r / p.tiles_m) * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(&full_bar[stage], kStageBytes);
+          uint8_t* sa = smem_a + stage * kATileBytes;
+          uint8_t* sb = smem_b + stage * kBTileBytes;
+          const int k0 = kb * BK;
+          if constexpr (A_KMAJOR) {
+            tma_load_3d(sa, &tmap_a, &full_bar[stage], k0, m0, b);
+          } else {
+            // MN-major: two 64(M) x 64(K) boxes, 8 KB each
+            tma_load_3d(sa, &tmap_a, &full_bar[stage], m0, k0, b);
+            tma_load_3d(sa + 8192, &tmap_a, &full_bar[stage], m0 + 64, k0, b);
+          }
+          if constexpr (B_KMAJOR) {
+            tma_load_3d(sb, &tmap_b, &full_bar[stage], k0, n0, b);
+          } else {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) tma_load_3d(sb + q * 8192, &tmap_b, &full_bar[stage], n0 + q * 64, k0, b);
+          }
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem_a + stage * kATileBytes);
+          const uint32_t sb = smem_u32(smem_b + stage * kBTileBytes);
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; ++kk) {
+            // K-major: 16 elements = 32 B inside the 128-byte swizzle row; SBO = 8 rows x 128 B.
+            // MN-major: 16 k-rows of 128 B = 2048 B; LBO = next 64-wide MN box (8 KB), SBO = 8 k-rows.
+            const uint64_t adesc = A_KMAJOR ? make_desc(sa + kk * 32, 16, 1024) : make_desc(sa + kk * 2048, 8192, 1024);
+            const uint64_t bdesc = B_KMAJOR ? make_desc(sb + kk * 32, 16, 1024) : make_desc(sb + kk * 2048, 8192, 1024);
+            umma_f16(tmem_d, adesc, bdesc, p.idesc, (kb | kk) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);  // slot reusable once these MMAs have read it
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(&tfull_bar[acc]);  // accumulator complete
+        if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const bool vec_ok = (p.ldd % (16 / (int)sizeof(OutT)) == 0) && ((reinterpret_cast<uintptr_t>(d) & 15) == 0) &&
+                        (p.stride_d % (16 / (int)sizeof(OutT)) == 0);
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      const int b = tile / tiles_per_batch;
+      const int r = tile - b * tiles_per_batch;
+      const int m0 = (r % p.tiles_m) * BM;
+      const int n0 = (r / p.tiles_m) * BN;
+      if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) break;
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      OutT* drow = d + (int64_t)b * p.stride_d + (int64_t)row * p.ldd + n0;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col0 = n0 + c * 32;
+        if (col0 >= p.n) break;  // uniform across the warp
+        uint32_t raw[32];
+        tmem_ld32(taddr + (uint32_t)(c * 32), raw);
+        tmem_ld_wait();
+        if (row < p.m) {
+          const int valid = min(32, p.n - col0);
+          float v[32];
+#pragma unroll
+          for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(raw[e]) * p.alpha;
+          if (p.bias) {
+            if (p.bias_f32) {
+              const float* bp = reinterpret_cast<const float*>(p.bias) + col0;
+#pragma unroll
+              for (int e = 0; e < 32; ++e) if (e < valid) v[e] += __ldg(bp + e);
+            } else {
+              const OutT* bp = reinterpret_cast<const OutT*>(p.bias) + col0;
+#pragma unroll
+              for (int e = 0; e < 32; ++e) if (e < valid) v[e] += ToF<OutT>::to(bp[e]);
+            }
+          }
+          if (p.act) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) v[e] = apply_act(v[e], p.act);
+          }
+          if (p.accumulate) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) if (e < valid) v[e] += ToF<OutT>::to(drow[c * 32 + e]);
+          }
+          store_chunk<OutT>(drow + c * 32, v, valid, vec_ok);
+        }
+      }
+      // all TMEM reads of this accumulator are complete (wait::ld above): hand it back
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+  if (threadIdx.x == 0 && *abort_flag && p.status) atomicExch(p.status, 1);
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess) {
+      (void)cudaGetLastError();
+      return (EncodeTiledFn) nullptr;
+    }
+    return (EncodeTiledFn)p;
+  }();
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr;
+  uint64_t d0, d1, d2, s1, s2;
+  uint32_t b0, b1;
+  int dtype;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && d0 == o.d0 && d1 == o.d1 && d2 == o.d2 && s1 == o.s1 && s2 == o.s2 && b0 == o.b0 &&
+           b1 == o.b1 && dtype == o.dtype;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    uint64_t h = (uint64_t)(uintptr_t)k.ptr * 0x9E3779B97F4A7C15ull;
+    h ^= k.d0 + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2);
+    h ^= k.d1 + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2);
+    h ^= k.s1 + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2);
+    h ^= ((uint64_t)k.b0 << 32 | k.b1) + (h << 6) + (h >> 2);
+    h ^= k.d2 * 31 + k.s2 * 17 + (uint64_t)k.dtype;
+    return (size_t)h;
+  }
+};
+
+// dims innermost-first: {inner, outer, batch}; strides in bytes for outer and batch; box {b0, b1, 1}
+bool make_map(CUtensorMap* out, const void* ptr, int dtype, uint64_t inner, uint64_t outer, uint64_t batch,
+              uint64_t outer_stride_bytes, uint64_t batch_stride_bytes, uint32_t box_inner, uint32_t box_outer) {
+  static std::mutex mu;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  MapKey key{ptr, inner, outer, batch, outer_stride_bytes, batch_stride_bytes, box_inner, box_outer, dtype};
+  {
+    std::lock_guard<std::mutex> g(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+      *out = it->second;
+      return true;
+    }
+  }
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return false;
+  cuuint64_t dims[3] = {inner, outer, batch};
+  cuuint64_t strides[2] = {outer_stride_bytes, batch_stride_bytes ? batch_stride_bytes : outer_stride_bytes * outer};
+  cuuint32_t box[3] = {box_inner, box_outer, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUtensorMapDataType dt = dtype == B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult r = enc(out, dt, 3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  std::lock_guard<std::mutex> g(mu);
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, *out);
+  return true;
+}
+
+int* status_word() {
+  // One pinned, device-mapped word per process: kernels write it only when a bounded wait expired.
+  static int* host = [] {
+    int* p = nullptr;
+    if (cudaHostAlloc((void**)&p, sizeof(int), cudaHostAllocMapped) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return (int*)nullptr;
+    }
+    *p = 0;
+    return p;
+  }();
+  return host;
+}
+
+template <typename OutT>
+int launch(const b200_gemm_desc_t* g, void* d, const void* a, const void* b, cudaStream_t stream) {
+  CUtensorMap ma, mb;
+  const uint64_t esz = 2;
+  const uint64_t batch = (uint64_t)std::max(g->batch, 1);
+  bool ok;
+  if (g->a_kmajor)
+    ok = make_map(&ma, a, g->in_dtype, (uint64_t)g->k, (uint64_t)g->m, batch, (uint64_t)g->lda * esz,
+                  (uint64_t)g->stride_a * esz, BK, BM);
+  else
+    ok = make_map(&ma, a, g->in_dtype, (uint64_t)g->m, (uint64_t)g->k, batch, (uint64_t)g->lda * esz,
+                  (uint64_t)g->stride_a * esz, 64, BK);
+  if (!ok) return (int)cudaErrorNotSupported;
+  if (g->b_kmajor)
+    ok = make_map(&mb, b, g->in_dtype, (uint64_t)g->k, (uint64_t)g->n, batch, (uint64_t)g->ldb * esz,
+                  (uint64_t)g->stride_b * esz, BK, BN);
+  else
+    ok = make_map(&mb, b, g->in_dtype, (uint64_t)g->n, (uint64_t)g->k, batch, (uint64_t)g->ldb * esz,
+                  (uint64_t)g->stride_b * esz, 64, BK);
+  if (!ok) return (int)cudaErrorNotSupported;
+
+  Params p;
+  p.m = g->m; p.n = g->n; p.k = g->k;
+  p.batch = (int)batch;
+  p.tiles_m = (g->m + BM - 1) / BM;
+  p.tiles_n = (g->n + BN - 1) / BN;
+  p.ldd = g->ldd;
+  p.stride_d = g->stride_d;
+  p.bias = g->bias;
+  p.bias_f32 = g->bias_dtype == B200_F32;
+  p.act = g->act;
+  p.accumulate = g->accumulate;
+  p.alpha = g->alpha;
+  // instruction descriptor: fp32 accumulate, A/B format, majors, N>>3, M>>4
+  const uint32_t fmt = g->in_dtype == B200_BF16 ? 1u : 0u;
+  p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((g->a_kmajor ? 0u : 1u) << 15) | ((g->b_kmajor ? 0u : 1u) << 16) |
+            ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+  int* host_status = status_word();
+  int* dev_status = nullptr;
+  if (host_status) {
+    if (cudaHostGetDevicePointer((void**)&dev_status, host_status, 0) != cudaSuccess) {
+      (void)cudaGetLastError();
+      dev_status = nullptr;
+    }
+  }
+  p.status = dev_status;
+
+  const int total = p.tiles_m * p.tiles_n * p.batch;
+  int dev = 0, sms = kSMs;
+  cudaGetDevice(&dev);
+  static int cached_sms[64] = {0};
+  if (dev < 64) {
+    if (!cached_sms[dev]) cudaDeviceGetAttribute(&cached_sms[dev], cudaDevAttrMultiProcessorCount, dev);
+    if (cached_sms[dev] > 0) sms = cached_sms[dev];
+  }
+  const int grid = std::min(total, sms);
+
+#define GEMM_GO(AK, BKM)                                                                                         \
+  do {                                                                                                           \
+    static bool attr_set = false;                                                                                \
+    auto kern = gemm_kernel<OutT, AK, BKM>;                                                                      \
+    if (!attr_set) {                                                                                             \
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);       \
+      if (e != cudaSuccess) return (int)e;                                                                       \
+      attr_set = true;                                                                                           \
+    }                                                                                                            \
+    kern<<<grid, kThreads, kSmemBytes, stream>>>(ma, mb, (OutT*)d, p);                                           \
+  } while (0)
+
+  if (g->a_kmajor && g->b_kmajor) GEMM_GO(true, true);
+  else if (g->a_kmajor && !g->b_kmajor) GEMM_GO(true, false);
+  else if (!g->a_kmajor && g->b_kmajor) GEMM_GO(false, true);
+  else GEMM_GO(false, false);
+#undef GEMM_GO
+  B200K_LAUNCH_RET();
+}
+
+}  // namespace
+}  // namespace b200k
+
+using namespace b200k;
+
+extern "C" {
+
+int b200_gemm_available(void) { return get_encode() != nullptr ? 1 : 0; }
+
+// Non-zero once any GEMM launch of this process gave up on a bounded wait (sticky until cleared).
+B200_API int b200_gemm_status(int clear) {
+  int* s = status_word();
+  if (!s) return 0;
+  int v = *(volatile int*)s;
+  if (clear) *(volatile int*)s = 0;
+  return v;
+}
+
+int b200_gemm(const b200_gemm_desc_t* g, void* d, const void* a, const void* b, cudaStream_t stream) {
+  if (g->m <= 0 || g->n <= 0 || std::max(g->batch, 1) <= 0) return 0;
+  if (g->k <= 0) return (int)cudaErrorNotSupported;
+  if (g->in_dtype != B200_BF16 && g->in_dtype != B200_F16) return (int)cudaErrorNotSupported;
+  // TMA: base 16-byte aligned, byte strides multiples of 16
+  auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (!al(a) || !al(b) || g->lda % 8 != 0 || g->ldb % 8 != 0) return (int)cudaErrorNotSupported;
+  if (g->batch > 1 && (g->stride_a % 8 != 0 || g->stride_b % 8 != 0)) return (int)cudaErrorNotSupported;
+  // a zero batch stride (broadcast operand) cannot be expressed as a tensor-map stride
+  if (g->batch > 1 && (g->stride_a == 0 || g->stride_b == 0)) return (int)cudaErrorNotSupported;
+  // the contiguous extent must cover at least one 16-byte unit
+  if ((g->a_kmajor ? g->k : g->m) < 8 || (g->b_kmajor ? g->k : g->n) < 8) return (int)cudaErrorNotSupported;
+  switch (g->out_dtype) {
+    case B200_BF16: return launch<__nv_bfloat16>(g, d, a, b, stream);
+    case B200_F16: return launch<__half>(g, d, a, b, stream);
+    case B200_F32: return launch<float>(g, d, a, b, stream);
+    default: return (int)cudaErrorNotSupported;
+  }
+}
+
+}  // extern "C"

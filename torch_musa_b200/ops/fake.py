@@ -1,0 +1,76 @@
+"""FakeTensor (meta) rules for the ``blackwell::`` operators so they trace under torch.compile /
+torch.export.  Parity: reference torch_musa/core/ops/register_fake_impl.py:10-42."""
+from __future__ import annotations
+
+import torch
+
+_lib = torch.library
+
+
+def _reg(name):
+    def deco(fn):
+        try:
+            _lib.register_fake(f"blackwell::{name}")(fn)
+        except RuntimeError:
+            pass  # already registered (re-import)
+        return fn
+    return deco
+
+
+@_reg("rope")
+def _(x, cos, sin, positions=None, interleaved=False, conj=False):
+    return torch.empty(x.shape, dtype=x.dtype, device=x.device)
+
+
+@_reg("swiglu")
+def _(x):
+    return x.new_empty(x.shape[:-1] + (x.shape[-1] // 2,))
+
+
+@_reg("swiglu_backward")
+def _(dy, x):
+    return torch.empty_like(x, memory_format=torch.contiguous_format)
+
+
+@_reg("silu_mul")
+def _(gate, up):
+    return torch.empty_like(gate, memory_format=torch.contiguous_format)
+
+
+@_reg("silu_mul_backward")
+def _(dy, gate, up):
+    return (torch.empty_like(gate, memory_format=torch.contiguous_format),
+            torch.empty_like(up, memory_format=torch.contiguous_format))
+
+
+@_reg("cross_entropy_fwd")
+def _(logits, target, ignore_index=-100, label_smoothing=0.0):
+    r = logits.new_empty((logits.shape[0],), dtype=torch.float32)
+    return r, torch.empty_like(r)
+
+
+@_reg("cross_entropy_bwd")
+def _(logits, lse, target, grad_loss, scale, ignore_index, label_smoothing):
+    return torch.empty_like(logits, memory_format=torch.contiguous_format)
+
+
+@_reg("online_softmax_stats")
+def _(logits, target, vocab_start):
+    return logits.new_empty((logits.shape[0], 3), dtype=torch.float32)
+
+
+@_reg("vocab_parallel_ce_finish")
+def _(logits, all_stats, target, vocab_start, ignore_index):
+    return logits.new_empty((logits.shape[0],), dtype=torch.float32)
+
+
+@_reg("rms_norm_residual")
+def _(x, residual, weight, eps):
+    stat = x.new_empty(x.shape[:-1] + (1,), dtype=torch.float32)
+    return torch.empty_like(x), torch.empty_like(x), stat
+
+
+@_reg("multi_tensor_l2norm")
+def _(tensors, per_tensor=False):
+    t = tensors[0]
+    return t.new_empty((1,), dtype=torch.float32), t.new_empty((len(tensors) if per_tensor else 0,), dtype=torch.float32)

@@ -1,0 +1,214 @@
+"""Functional forms of the fused operators (autograd included)."""
+from __future__ import annotations
+
+import math
+from typing import List, Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+
+def _on_device(t: torch.Tensor) -> bool:
+    return t.device.type == "blackwell"
+
+
+# ------------------------------------------------------------------------- RMSNorm
+def rms_norm(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float = 1e-6) -> torch.Tensor:
+    """``x * rsqrt(mean(x^2) + eps) * weight`` over the last dimension (fp32 statistics).
+
+    On the device this is ``aten::_fused_rms_norm`` (one kernel forward, one backward)."""
+    return F.rms_norm(x, (x.shape[-1],), weight, eps)
+
+
+class _RMSNormResidual(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, residual, weight, eps):
+        y, res, rstd = torch.ops.blackwell.rms_norm_residual(x, residual, weight, eps)
+        ctx.save_for_backward(res, weight, rstd)
+        return y, res
+
+    @staticmethod
+    def backward(ctx, dy, dres):
+        res, weight, rstd = ctx.saved_tensors
+        dx, dw = torch.ops.aten._fused_rms_norm_backward(dy.contiguous(), res, [res.shape[-1]], rstd, weight,
+                                                         [True, True])
+        if dres is not None:
+            dx = dx + dres
+        return dx, dx, dw, None
+
+
+def rms_norm_residual(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6):
+    """Fused ``h = x + residual; y = rms_norm(h)``; returns ``(y, h)`` (one pass over memory)."""
+    if _on_device(x):
+        return _RMSNormResidual.apply(x, residual, weight, eps)
+    h = x + residual
+    return rms_norm(h, weight, eps), h
+
+
+# ------------------------------------------------------------------------- RoPE
+def precompute_rope_cache(seq_len: int, head_dim: int, theta: float = 10000.0, device=None):
+    """fp32 ``cos``/``sin`` tables of shape [seq_len, head_dim // 2]."""
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32, device="cpu") / head_dim))
+    t = torch.arange(seq_len, dtype=torch.float32, device="cpu")
+    freqs = torch.outer(t, inv)
+    cos, sin = freqs.cos().contiguous(), freqs.sin().contiguous()
+    if device is not None:
+        cos, sin = cos.to(device), sin.to(device)
+    return cos, sin
+
+
+def _rope_reference(x, cos, sin, positions, interleaved, conj):
+    # x [B, S, H, D]; cos/sin [P, D/2]
+    B, S, H, D = x.shape
+    if positions is not None:
+        c = cos[positions.reshape(B, S)].unsqueeze(2)
+        s = sin[positions.reshape(B, S)].unsqueeze(2)
+    else:
+        c = cos[:S].view(1, S, 1, D // 2)
+        s = sin[:S].view(1, S, 1, D // 2)
+    if conj:
+        s = -s
+    xf = x.float()
+    if interleaved:
+        x0, x1 = xf[..., 0::2], xf[..., 1::2]
+        o0, o1 = x0 * c - x1 * s, x1 * c + x0 * s
+        out = torch.stack((o0, o1), dim=-1).flatten(-2)
+    else:
+        x0, x1 = xf[..., : D // 2], xf[..., D // 2:]
+        out = torch.cat((x0 * c - x1 * s, x1 * c + x0 * s), dim=-1)
+    return out.to(x.dtype)
+
+
+class _Rope(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, cos, sin, positions, interleaved):
+        ctx.save_for_backward(cos, sin, positions if positions is not None else torch.empty(0))
+        ctx.has_pos = positions is not None
+        ctx.interleaved = interleaved
+        return torch.ops.blackwell.rope(x, cos, sin, positions, interleaved, False)
+
+    @staticmethod
+    def backward(ctx, dy):
+        cos, sin, pos = ctx.saved_tensors
+        dx = torch.ops.blackwell.rope(dy, cos, sin, pos if ctx.has_pos else None, ctx.interleaved, True)
+        return dx, None, None, None, None
+
+
+def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, positions: Optional[torch.Tensor] = None,
+         interleaved: bool = False) -> torch.Tensor:
+    """Rotary position embedding of ``x`` [batch, seq, heads, head_dim].
+
+    ``interleaved=False`` rotates the two halves of the head dimension (Llama / NeoX layout),
+    ``True`` rotates adjacent pairs (GPT-J layout). Backward is the conjugate rotation."""
+    if _on_device(x):
+        return _Rope.apply(x, cos, sin, positions, interleaved)
+    return _rope_reference(x, cos, sin, positions, interleaved, False)
+
+
+# ------------------------------------------------------------------------- SwiGLU
+class _SwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        ctx.save_for_backward(x)
+        return torch.ops.blackwell.swiglu(x)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x,) = ctx.saved_tensors
+        return torch.ops.blackwell.swiglu_backward(dy, x)
+
+
+def swiglu(x: torch.Tensor) -> torch.Tensor:
+    """``silu(x[..., :h]) * x[..., h:]`` for a packed gate|up tensor."""
+    if _on_device(x):
+        return _SwiGLU.apply(x)
+    g, u = x.chunk(2, dim=-1)
+    return F.silu(g) * u
+
+
+gated_silu = swiglu
+
+
+class _SiluMul(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gate, up):
+        ctx.save_for_backward(gate, up)
+        return torch.ops.blackwell.silu_mul(gate, up)
+
+    @staticmethod
+    def backward(ctx, dy):
+        gate, up = ctx.saved_tensors
+        return torch.ops.blackwell.silu_mul_backward(dy, gate, up)
+
+
+def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """``silu(gate) * up`` in one kernel (two-tensor SwiGLU)."""
+    if _on_device(gate):
+        return _SiluMul.apply(gate, up)
+    return F.silu(gate) * up
+
+
+# ------------------------------------------------------------------------- cross entropy
+class _FusedCE(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, target, ignore_index, label_smoothing, reduction, inplace_backward):
+        loss_rows, lse = torch.ops.blackwell.cross_entropy_fwd(logits, target, ignore_index, label_smoothing)
+        n_valid = None
+        if reduction == "mean":
+            n_valid = (target != ignore_index).sum().clamp_min(1).to(torch.float32)
+            out = loss_rows.sum() / n_valid
+        elif reduction == "sum":
+            out = loss_rows.sum()
+        else:
+            out = loss_rows
+        ctx.save_for_backward(logits, lse, target, n_valid if n_valid is not None else torch.empty(0))
+        ctx.cfg = (ignore_index, label_smoothing, reduction, inplace_backward)
+        return out
+
+    @staticmethod
+    def backward(ctx, dloss):
+        logits, lse, target, n_valid = ctx.saved_tensors
+        ignore_index, ls, reduction, inplace = ctx.cfg
+        g = dloss.to(torch.float32)
+        if reduction == "mean":
+            g = g / n_valid
+        g = g.reshape(-1) if reduction == "none" else g.reshape(1)
+        if inplace and logits.is_contiguous():
+            dl = torch.ops.blackwell.cross_entropy_bwd_(logits, lse, target, g, 1.0, ignore_index, ls)
+        else:
+            dl = torch.ops.blackwell.cross_entropy_bwd(logits, lse, target, g, 1.0, ignore_index, ls)
+        return dl, None, None, None, None, None
+
+
+def fused_cross_entropy(logits: torch.Tensor, target: torch.Tensor, ignore_index: int = -100,
+                        label_smoothing: float = 0.0, reduction: str = "mean",
+                        inplace_backward: bool = False) -> torch.Tensor:
+    """Cross entropy over [T, V] logits that never materialises the probabilities.
+
+    Forward stores only the per-row log-sum-exp; backward regenerates softmax from it.
+    ``inplace_backward=True`` writes the gradient over the logits (saves T*V elements) --
+    only valid when nothing else needs the logits after the loss."""
+    if logits.dim() != 2:
+        logits = logits.reshape(-1, logits.shape[-1])
+        target = target.reshape(-1)
+    if _on_device(logits):
+        return _FusedCE.apply(logits, target, ignore_index, label_smoothing, reduction, inplace_backward)
+    return F.cross_entropy(logits.float(), target, ignore_index=ignore_index, label_smoothing=label_smoothing,
+                           reduction=reduction)
+
+
+# ------------------------------------------------------------------------- misc
+def multi_tensor_l2norm(tensors: List[torch.Tensor], per_tensor: bool = False):
+    """Global (and optionally per-tensor) L2 norm of a list of tensors in a few launches."""
+    if len(tensors) > 0 and _on_device(tensors[0]):
+        total, per = torch.ops.blackwell.multi_tensor_l2norm(list(tensors), per_tensor)
+        return (total, per) if per_tensor else (total, None)
+    per = torch.stack([t.float().norm(2) for t in tensors]) if tensors else torch.zeros(0)
+    return per.norm(2).reshape(1), (per if per_tensor else None)
+
+
+def scaled_dot_product_attention(q, k, v, attn_mask=None, dropout_p: float = 0.0, is_causal: bool = False,
+                                 scale: Optional[float] = None, enable_gqa: bool = False):
+    """``F.scaled_dot_product_attention``; on the device it is routed to the backend's attention kernels."""
+    return F.scaled_dot_product_attention(q, k, v, attn_mask=attn_mask, dropout_p=dropout_p, is_causal=is_causal,
+                                          scale=scale, enable_gqa=enable_gqa)
