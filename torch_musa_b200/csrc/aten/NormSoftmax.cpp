@@ -264,9 +264,7 @@ b200_philox_t philox_for(const at::Tensor& t, std::optional<at::Generator> gen, 
   at::Generator g = (gen.has_value() && gen->defined()) ? *gen : default_generator(t.device().index());
   auto* impl = at::check_generator<GeneratorImpl>(g);
   std::lock_guard<std::mutex> lock(impl->mutex_);
-  // each thread consumes one counter per 4 outputs; reserve the worst case over any launch geometry
-  uint64_t per_thread = (uint64_t)((n + 1023) / 1024 + 1) * 4;
-  PhiloxArgs a = impl->philox_args(per_thread);
+  PhiloxArgs a = impl->philox_args(b200_philox_increment(n));
   b200_philox_t r;
   r.seed = a.seed; r.offset = a.offset; r.seed_ptr = a.seed_ptr; r.offset_ptr = a.offset_ptr;
   r.offset_intragraph = a.offset_intragraph; r.captured = a.captured;

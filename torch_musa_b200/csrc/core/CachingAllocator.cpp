@@ -556,7 +556,15 @@ class DeviceAllocatorImpl {
     int e;
     {
       DeviceSwitch sw(be_->device_events ? device_ : -1);
-      e = be_->raw_alloc(&p, seg, device_, stream);
+      if (capturing_depth_ > 0 && be_->device_events) {
+        // A driver allocation is not a captured operation: step out of the capture's error mode for it.
+        cudaStreamCaptureMode mode = cudaStreamCaptureModeRelaxed;
+        cudaThreadExchangeStreamCaptureMode(&mode);
+        e = be_->raw_alloc(&p, seg, device_, stream);
+        cudaThreadExchangeStreamCaptureMode(&mode);
+      } else {
+        e = be_->raw_alloc(&p, seg, device_, stream);
+      }
     }
     if (e != 0) {
       if (be_->device_events) (void)cudaGetLastError();

@@ -205,6 +205,7 @@ PYBIND11_MODULE(_C, m) {
   m.def("_kernel_launch_count", [] { return b200_launch_count(); });
   m.def("_reset_kernel_launch_count", [] { b200_reset_launch_count(); });
   m.def("_gemm_available", [] { return b200_gemm_available() != 0; });
+  m.def("_gemm_status", [](bool clear) { return b200_gemm_status(clear ? 1 : 0); }, py::arg("clear") = false);
   m.def("_set_tensor_core_gemm", [](bool on) { ops::set_tensor_core_gemm(on); });
   m.def("_tensor_core_gemm_enabled", [] { return ops::tensor_core_gemm_enabled(); });
   m.def("_runtime_version", [] {
@@ -259,6 +260,13 @@ PYBIND11_MODULE(_C, m) {
   });
   m.def("_stream_is_capturing", [](int64_t id, int64_t dev) {
     return Graph::is_capturing(stream_from_c10(c10::Stream::unpack3(id, (c10::DeviceIndex)dev, kDeviceType)));
+  });
+
+  m.def("_event_elapsed_time", [](uintptr_t a, uintptr_t b) {
+    TORCH_CHECK(a && b, "Both events must be recorded before calculating elapsed time.");
+    float ms = 0.f;
+    B200_CUDA_CHECK(cudaEventElapsedTime(&ms, reinterpret_cast<cudaEvent_t>(a), reinterpret_cast<cudaEvent_t>(b)));
+    return ms;
   });
 
   // IPC-capable event (the generic torch.Event covers everything else)

@@ -219,6 +219,44 @@ typedef struct {
 B200_API int b200_gemm(const b200_gemm_desc_t* desc, void* d, const void* a, const void* b, cudaStream_t stream);
 /* 1 when the running driver exposes the tensor-map encoder the kernel needs */
 B200_API int b200_gemm_available(void);
+/* non-zero once any GEMM launch of this process gave up on a bounded pipeline wait (sticky; clear != 0 resets) */
+B200_API int b200_gemm_status(int clear);
+/* Philox counters one launch of the random kernels may consume per thread, for n outputs */
+B200_API uint64_t b200_philox_increment(int64_t n);
+
+/* ---------------------------------------------------------------- collectives over peer-mapped memory */
+/* Every rank's arena and signal pad as mapped in THIS process (index = rank). `status` is a host-mapped word
+ * the kernels set to non-zero when a bounded wait expired. Epochs must grow by at least 2 per call and be
+ * identical on all ranks for the same call; offsets are byte offsets into the arena, multiples of 16. */
+typedef struct {
+  void* bufs[16];
+  uint32_t* sigs[16];
+  int rank, world;
+  int* status;
+} b200_symm_t;
+B200_API int b200_comm_max_world(void);
+B200_API size_t b200_comm_signal_bytes(void);
+/* out = scale * sum_ranks(in), n elements (n % 8 == 0); arena use: n*sizeof(in) at in_off, n*sizeof(out) at out_off */
+B200_API int b200_comm_allreduce(const b200_symm_t* s, int in_dtype, int out_dtype, const void* in, void* out,
+                                 int64_t n, float scale, uint32_t epoch, int64_t in_off, int64_t out_off,
+                                 cudaStream_t stream);
+/* out [world * nbytes] = concat over ranks of in [nbytes] (nbytes % 16 == 0); arena use: nbytes at in_off */
+B200_API int b200_comm_allgather(const b200_symm_t* s, int dtype_bytes, const void* in, void* out, int64_t nbytes,
+                                 uint32_t epoch, int64_t in_off, cudaStream_t stream);
+/* out [n_out] = scale * sum_ranks(in_rank[rank*n_out : (rank+1)*n_out]); arena use: world*n_out*sizeof(in) */
+B200_API int b200_comm_reduce_scatter(const b200_symm_t* s, int in_dtype, int out_dtype, const void* in, void* out,
+                                      int64_t n_out, float scale, uint32_t epoch, int64_t in_off,
+                                      cudaStream_t stream);
+/* reduce-scatter whose epilogue is the AdamW step on the owner's fp32 shard (p32, m, v) and its bf16 copy p16 */
+B200_API int b200_comm_reduce_scatter_adamw(const b200_symm_t* s, int in_dtype, const void* in, float* p32, float* m,
+                                            float* v, void* p16, int64_t n_out, float scale, uint32_t epoch,
+                                            int64_t in_off, float lr, float beta1, float beta2, float eps, float wd,
+                                            const float* step_ptr, cudaStream_t stream);
+/* all-to-all with per-peer splits; all offsets/lengths in bytes, multiples of 16. peer_send_off[p] = offset of
+ * the slice destined to this rank inside peer p's input. */
+B200_API int b200_comm_alltoall(const b200_symm_t* s, const void* in, void* out, int64_t in_bytes,
+                                const int64_t* send_off, const int64_t* recv_off, const int64_t* recv_len,
+                                const int64_t* peer_send_off, uint32_t epoch, int64_t in_off, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

@@ -80,12 +80,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   return true;
 }
 
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
-      : "memory");
-}
 __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1,
                                             int c2) {
   asm volatile(
@@ -554,7 +548,7 @@ extern "C" {
 int b200_gemm_available(void) { return get_encode() != nullptr ? 1 : 0; }
 
 // Non-zero once any GEMM launch of this process gave up on a bounded wait (sticky until cleared).
-B200_API int b200_gemm_status(int clear) {
+int b200_gemm_status(int clear) {
   int* s = status_word();
   if (!s) return 0;
   int v = *(volatile int*)s;

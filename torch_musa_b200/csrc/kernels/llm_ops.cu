@@ -304,6 +304,14 @@ using namespace b200k;
 
 extern "C" {
 
+uint64_t b200_philox_increment(int64_t n) {
+  // one Philox call (4 outputs) per thread per grid-stride round; worst case is the smallest grid
+  int64_t quads = cdiv(n, 4);
+  int grid = grid_cap(quads);
+  int64_t rounds = cdiv(quads, (int64_t)grid * kThreads);
+  return (uint64_t)(rounds < 1 ? 1 : rounds) * 4;
+}
+
 int b200_rope(int dtype, void* out, const void* x, const float* cosv, const float* sinv, const int64_t* pos,
               int64_t tokens, int64_t seq, int heads, int dim, int64_t ts, int64_t hs, int interleaved, int conj,
               cudaStream_t stream) {

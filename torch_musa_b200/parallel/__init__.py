@@ -1,0 +1,5 @@
+"""Parallelism helpers built on the ``bccl`` backend: DDP communication hooks whose bucket all-reduce
+is the backend's fused peer-memory kernel, FSDP2 glue, tensor-parallel fused cross entropy."""
+from .ddp import fused_allreduce_hook, bf16_compress_fused_hook, wrap_ddp  # noqa: F401
+from . import fsdp  # noqa: F401
+from .loss import parallel_fused_cross_entropy  # noqa: F401
