@@ -132,7 +132,30 @@ def main():
     if par == "fsdp":
         dist.init_process_group(backend=backend, rank=rank, world_size=world, device_id=device if not ours else None)
 
-    from torch_musa_b200.models import Llama, LlamaConfig
+    if ours:
+        from torch_musa_b200.models import Llama, LlamaConfig
+    else:
+        # The stock arm must not load the blackwell backend (it would become the process's accelerator):
+        # load the model definition and its plain-PyTorch functional fallbacks straight from their files.
+        import importlib.util
+        import types
+
+        pkg = types.ModuleType("_stock_pkg"); pkg.__path__ = []
+        opsp = types.ModuleType("_stock_pkg.ops"); opsp.__path__ = []
+        sys.modules["_stock_pkg"], sys.modules["_stock_pkg.ops"] = pkg, opsp
+        modelsp = types.ModuleType("_stock_pkg.models"); modelsp.__path__ = []
+        sys.modules["_stock_pkg.models"] = modelsp
+
+        def _load(name, path):
+            spec = importlib.util.spec_from_file_location(name, os.path.join(ROOT, "torch_musa_b200", path))
+            mod = importlib.util.module_from_spec(spec)
+            sys.modules[name] = mod
+            spec.loader.exec_module(mod)
+            return mod
+
+        opsp.functional = _load("_stock_pkg.ops.functional", "ops/functional.py")
+        _llama = _load("_stock_pkg.models.llama", "models/llama.py")
+        Llama, LlamaConfig = _llama.Llama, _llama.LlamaConfig
 
     cfg = LlamaConfig(n_layers=args.layers, max_seq_len=args.seq)
     torch.manual_seed(1234)
@@ -162,11 +185,7 @@ def main():
                 p.normal_(0.0, 0.02)
             else:
                 p.fill_(1.0)
-        from torch_musa_b200.ops.functional import precompute_rope_cache
-
-        cos, sin = precompute_rope_cache(args.seq, cfg.head_dim, cfg.rope_theta)
-        model.rope_cos = cos.to(device)
-        model.rope_sin = sin.to(device)
+        model.init_rope_cache(device)
 
     opt = torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1, fused=True)
 

@@ -119,9 +119,22 @@ class Llama(nn.Module):
         self.layers = nn.ModuleList(Block(cfg) for _ in range(cfg.n_layers))
         self.norm = nn.RMSNorm(cfg.dim, eps=cfg.norm_eps)
         self.lm_head = nn.Linear(cfg.dim, cfg.vocab_size, bias=False)
-        cos, sin = BF.precompute_rope_cache(cfg.max_seq_len, cfg.head_dim, cfg.rope_theta)
+        if torch.empty(0).device.type == "meta":
+            # deferred initialisation: the tables are filled in after materialisation (see init_rope_cache)
+            cos = torch.empty(cfg.max_seq_len, cfg.head_dim // 2, dtype=torch.float32)
+            sin = torch.empty_like(cos)
+        else:
+            cos, sin = BF.precompute_rope_cache(cfg.max_seq_len, cfg.head_dim, cfg.rope_theta)
         self.register_buffer("rope_cos", cos, persistent=False)
         self.register_buffer("rope_sin", sin, persistent=False)
+
+    def init_rope_cache(self, device=None):
+        """(Re)compute the fp32 cos/sin tables, e.g. after ``to_empty`` of a meta-initialised model."""
+        cfg = self.cfg
+        cos, sin = BF.precompute_rope_cache(cfg.max_seq_len, cfg.head_dim, cfg.rope_theta)
+        device = device if device is not None else self.rope_cos.device
+        self.rope_cos = cos.to(device)
+        self.rope_sin = sin.to(device)
 
     def reset_parameters(self, std: float = 0.02, seed: Optional[int] = None):
         g = None
