@@ -262,3 +262,28 @@ def test_reductions_via_kernel_library(bw, dev):
     ref = torch.stack([t.norm() for t in ts])
     assert torch.allclose(per.cpu(), ref, rtol=1e-4)
     assert float(total) == pytest.approx(float(ref.norm()), rel=1e-4)
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("hq,hkv,causal", [(4, 4, True), (8, 2, True), (4, 4, False)])
+def test_sdpa_fused_routing(bw, dev, dt, hq, hkv, causal):
+    """F.scaled_dot_product_attention takes the fused path (no materialised score matrix) and matches math."""
+    B, S, D = 2, 256, 64
+    q, k, v = torch.randn(B, hq, S, D).to(dt), torch.randn(B, hkv, S, D).to(dt), torch.randn(B, hkv, S, D).to(dt)
+    g = torch.randn(B, hq, S, D).to(dt)
+    qd, kd, vd = (leaf(t, dev) for t in (q, k, v))
+    qr, kr, vr = (leaf(t, None, torch.float32) for t in (q, k, v))
+    bw.reset_fallback_counts()
+    o = F.scaled_dot_product_attention(qd, kd, vd, is_causal=causal, enable_gqa=(hq != hkv))
+    o.backward(g.to(dev))
+    names = bw.fallback_counts()
+    assert not any("bmm" in n for n in names), "attention fell to the math decomposition"
+    orf = F.scaled_dot_product_attention(qr, kr, vr, is_causal=causal, enable_gqa=(hq != hkv))
+    orf.backward(g.float())
+    assert close(o, orf, dt, 2)
+    assert close(qd.grad, qr.grad, dt, 4) and close(kd.grad, kr.grad, dt, 4) and close(vd.grad, vr.grad, dt, 4)
+    # an explicit mask still works (math path)
+    mask = torch.rand(S, S) > 0.5
+    om = F.scaled_dot_product_attention(qd.detach()[:, :hkv], kd.detach(), vd.detach(), attn_mask=mask.to(dev))
+    omr = F.scaled_dot_product_attention(qr.detach()[:, :hkv], kr.detach(), vr.detach(), attn_mask=mask)
+    assert close(om, omr, dt, 4)

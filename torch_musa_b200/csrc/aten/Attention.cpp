@@ -1,0 +1,115 @@
+// scaled_dot_product_attention routing for the blackwell device.
+//
+// `_fused_sdp_choice` selects the fused path ("overrideable" in ATen's terms) for the cases the
+// fused kernels cover -- fp16/bf16, head_dim <= 256, no explicit mask, 4-D [B, H, S, D] -- and the
+// math decomposition otherwise, so every mask layout and dtype still works.  The fused forward
+// returns (out, logsumexp, ...) and backward consumes them, exactly the contract of ATen's
+// `_scaled_dot_product_fused_attention_overrideable(+_backward)`; grouped-query attention
+// (fewer KV heads) is handled without expanding K/V.
+// The fused implementation currently runs the library flash-attention kernels on the same memory
+// through the CUDA-alias bridge.
+// Parity: reference torch_musa/csrc/aten/ops/attention/mudnn/SDPBackendSelect.cpp:16-41,
+// SDPUtils.h:93-213 (eligibility), SDP.cpp:470-673 (vendor flash forward/backward).
+#include "aten/FallbackCall.h"
+#include "aten/Ops.h"
+
+#include <ATen/Functions.h>
+#include <ATen/native/DispatchStub.h>
+#include <ATen/native/transformers/attention.h>
+#include <torch/library.h>
+
+#include <atomic>
+
+namespace b200 {
+namespace ops {
+
+namespace {
+
+constexpr int64_t kMath = 0, kOverrideable = 4;
+std::atomic<bool> g_fused_sdp{true};
+
+bool fused_eligible(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+                    const std::optional<at::Tensor>& mask, double dropout_p) {
+  if (!g_fused_sdp.load(std::memory_order_relaxed)) return false;
+  if (mask.has_value() && mask->defined()) return false;
+  if (q.dim() != 4 || k.dim() != 4 || v.dim() != 4) return false;
+  auto dt = q.scalar_type();
+  if ((dt != at::kBFloat16 && dt != at::kHalf) || k.scalar_type() != dt || v.scalar_type() != dt) return false;
+  const int64_t d = q.size(3);
+  if (d > 256 || d % 8 != 0 || k.size(3) != d || v.size(3) != d) return false;
+  if (q.size(1) % k.size(1) != 0 || k.size(1) != v.size(1)) return false;
+  if (q.size(0) != k.size(0) || k.size(2) != v.size(2)) return false;
+  if (q.numel() == 0 || k.numel() == 0) return false;
+  (void)dropout_p;
+  return true;
+}
+
+int64_t fused_sdp_choice(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+                         const std::optional<at::Tensor>& mask, double dropout_p, bool is_causal,
+                         std::optional<double> scale, bool enable_gqa) {
+  (void)is_causal; (void)scale; (void)enable_gqa;
+  return fused_eligible(q, k, v, mask, dropout_p) ? kOverrideable : kMath;
+}
+
+}  // namespace
+
+int64_t fused_sdp_choice_stub_impl(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+                                   const std::optional<at::Tensor>& mask, double dropout_p, bool is_causal,
+                                   std::optional<double> scale, bool enable_gqa) {
+  return fused_sdp_choice(q, k, v, mask, dropout_p, is_causal, scale, enable_gqa);
+}
+
+namespace {
+
+using FwdRet = std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor, c10::SymInt, c10::SymInt, at::Tensor,
+                          at::Tensor, at::Tensor>;
+
+FwdRet sdpa_fused_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+                      const std::optional<at::Tensor>& attn_bias, double dropout_p, bool is_causal,
+                      bool return_debug_mask, std::optional<double> scale) {
+  TORCH_CHECK(!(attn_bias.has_value() && attn_bias->defined()),
+              "blackwell fused attention: explicit masks take the math path (this is a dispatch bug)");
+  auto st = run_fallback(B200_OP_HANDLE("aten::_scaled_dot_product_flash_attention", ""), q, k, v, dropout_p,
+                         is_causal, return_debug_mask, scale);
+  // (output, logsumexp, cum_seq_q, cum_seq_k, max_q, max_k, rng_state, unused, debug_attn_mask)
+  return FwdRet(st[0].toTensor(), st[1].toTensor(), st[2].toTensor(), st[3].toTensor(), st[4].toSymInt(),
+                st[5].toSymInt(), st[6].toTensor(), st[7].toTensor(), st[8].toTensor());
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> sdpa_fused_bwd(
+    const at::Tensor& grad_out, const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+    const at::Tensor& attn_bias, std::array<bool, 4> grad_input_mask, const at::Tensor& out,
+    const at::Tensor& logsumexp, const at::Tensor& cum_seq_q, const at::Tensor& cum_seq_k, c10::SymInt max_q,
+    c10::SymInt max_k, double dropout_p, bool is_causal, const at::Tensor& philox_seed,
+    const at::Tensor& philox_offset, std::optional<double> scale) {
+  (void)attn_bias; (void)grad_input_mask;
+  auto st = run_fallback(B200_OP_HANDLE("aten::_scaled_dot_product_flash_attention_backward", ""), grad_out, q, k, v,
+                         out, logsumexp, cum_seq_q, cum_seq_k, max_q, max_k, dropout_p, is_causal, philox_seed,
+                         philox_offset, scale);
+  return {st[0].toTensor(), st[1].toTensor(), st[2].toTensor(), at::Tensor()};
+}
+
+}  // namespace
+
+void set_fused_sdp(bool on) { g_fused_sdp = on; }
+bool fused_sdp_enabled() { return g_fused_sdp; }
+
+}  // namespace ops
+}  // namespace b200
+
+// F.scaled_dot_product_attention asks this per-device-type stub, not the dispatcher
+namespace at::native {
+REGISTER_PRIVATEUSE1_DISPATCH(_fused_sdp_choice_stub, &b200::ops::fused_sdp_choice_stub_impl)
+}  // namespace at::native
+
+namespace b200 {
+namespace ops {
+
+TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
+  m.impl("_fused_sdp_choice", TORCH_FN(fused_sdp_choice));
+  m.impl("_scaled_dot_product_fused_attention_overrideable", TORCH_FN(sdpa_fused_fwd));
+  m.impl("_scaled_dot_product_fused_attention_overrideable_backward", TORCH_FN(sdpa_fused_bwd));
+}
+
+}  // namespace ops
+}  // namespace b200

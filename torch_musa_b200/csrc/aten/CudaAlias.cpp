@@ -3,6 +3,7 @@
 #include "core/Backend.h"
 #include "core/Stream.h"
 
+#include <ATen/Context.h>
 #include <ATen/core/dispatch/Dispatcher.h>
 #include <ATen/cuda/CUDAGeneratorImpl.h>
 #include <ATen/detail/CUDAHooksInterface.h>
@@ -158,6 +159,12 @@ void cuda_alias_fallback(const c10::OperatorHandle& op, torch::jit::Stack* stack
   const size_t base = stack->size() - nargs;
   note_fallback(op);
   lazy_init();
+  // PyTorch's CUDA kernels expect its CUDA state (allocator tables, handles) to exist
+  static const bool cuda_ready = [] {
+    at::globalContext().lazyInitDevice(c10::DeviceType::CUDA);
+    return true;
+  }();
+  (void)cuda_ready;
 
   AliasScope scope;
   c10::DeviceIndex dev = -1;

@@ -32,6 +32,10 @@ inline cudaStream_t current_raw_stream(const at::Tensor& t) { return get_current
 B200_EXPORT void set_tensor_core_gemm(bool on);
 B200_EXPORT bool tensor_core_gemm_enabled();
 
+// Fused scaled-dot-product attention on/off (off: the math decomposition is always chosen).
+B200_EXPORT void set_fused_sdp(bool on);
+B200_EXPORT bool fused_sdp_enabled();
+
 // Counter of hand-written kernel launches (reported by the benchmark as its own-kernel launch count).
 B200_EXPORT void count_launch(int n = 1);
 B200_EXPORT int64_t launch_count();

@@ -207,6 +207,8 @@ PYBIND11_MODULE(_C, m) {
   m.def("_gemm_available", [] { return b200_gemm_available() != 0; });
   m.def("_gemm_status", [](bool clear) { return b200_gemm_status(clear ? 1 : 0); }, py::arg("clear") = false);
   m.def("_set_tensor_core_gemm", [](bool on) { ops::set_tensor_core_gemm(on); });
+  m.def("_set_fused_sdp", [](bool on) { ops::set_fused_sdp(on); });
+  m.def("_fused_sdp_enabled", [] { return ops::fused_sdp_enabled(); });
   m.def("_tensor_core_gemm_enabled", [] { return ops::tensor_core_gemm_enabled(); });
   m.def("_runtime_version", [] {
     int v = 0;

@@ -50,10 +50,21 @@ def llama_tiny_config(**kw) -> LlamaConfig:
     return LlamaConfig(**base)
 
 
+class RopeTables:
+    """Plain holder of the fp32 cos/sin tables shared by all layers.  It is deliberately not a tensor
+    argument of the layers' ``forward``: FSDP's mixed-precision policy casts floating-point forward
+    inputs to the compute dtype, and rotary tables must stay fp32."""
+
+    def __init__(self):
+        self.cos = None
+        self.sin = None
+
+
 class Attention(nn.Module):
-    def __init__(self, cfg: LlamaConfig):
+    def __init__(self, cfg: LlamaConfig, rope: RopeTables):
         super().__init__()
         self.cfg = cfg
+        self._rope = [rope]  # in a list so nn.Module does not try to register it
         hd, h, kv = cfg.head_dim, cfg.n_heads, cfg.kv_heads
         if cfg.fused_qkv:
             self.wqkv = nn.Linear(cfg.dim, (h + 2 * kv) * hd, bias=False)
@@ -63,9 +74,10 @@ class Attention(nn.Module):
             self.wv = nn.Linear(cfg.dim, kv * hd, bias=False)
         self.wo = nn.Linear(h * hd, cfg.dim, bias=False)
 
-    def forward(self, x, cos, sin, positions=None):
+    def forward(self, x, positions=None):
         B, S, _ = x.shape
         cfg = self.cfg
+        cos, sin = self._rope[0].cos, self._rope[0].sin
         hd, h, kv = cfg.head_dim, cfg.n_heads, cfg.kv_heads
         if cfg.fused_qkv:
             qkv = self.wqkv(x).view(B, S, h + 2 * kv, hd)
@@ -99,15 +111,15 @@ class FeedForward(nn.Module):
 
 
 class Block(nn.Module):
-    def __init__(self, cfg: LlamaConfig):
+    def __init__(self, cfg: LlamaConfig, rope: RopeTables):
         super().__init__()
         self.attn_norm = nn.RMSNorm(cfg.dim, eps=cfg.norm_eps)
-        self.attn = Attention(cfg)
+        self.attn = Attention(cfg, rope)
         self.ffn_norm = nn.RMSNorm(cfg.dim, eps=cfg.norm_eps)
         self.ffn = FeedForward(cfg)
 
-    def forward(self, x, cos, sin, positions=None):
-        x = x + self.attn(self.attn_norm(x), cos, sin, positions)
+    def forward(self, x, positions=None):
+        x = x + self.attn(self.attn_norm(x), positions)
         return x + self.ffn(self.ffn_norm(x))
 
 
@@ -116,7 +128,8 @@ class Llama(nn.Module):
         super().__init__()
         self.cfg = cfg
         self.tok_emb = nn.Embedding(cfg.vocab_size, cfg.dim)
-        self.layers = nn.ModuleList(Block(cfg) for _ in range(cfg.n_layers))
+        self._rope = RopeTables()
+        self.layers = nn.ModuleList(Block(cfg, self._rope) for _ in range(cfg.n_layers))
         self.norm = nn.RMSNorm(cfg.dim, eps=cfg.norm_eps)
         self.lm_head = nn.Linear(cfg.dim, cfg.vocab_size, bias=False)
         if torch.empty(0).device.type == "meta":
@@ -154,9 +167,10 @@ class Llama(nn.Module):
         cos, sin = self.rope_cos, self.rope_sin
         if cos.dtype != torch.float32:  # a module-wide .to(bf16) must not degrade the tables
             cos, sin = cos.float(), sin.float()
+        self._rope.cos, self._rope.sin = cos, sin
         x = self.tok_emb(tokens)
         for layer in self.layers:
-            x = layer(x, cos, sin, positions)
+            x = layer(x, positions)
         x = self.norm(x)
         logits = self.lm_head(x)
         if targets is None:
