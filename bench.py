@@ -293,6 +293,8 @@ def main():
                           "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"]}
         if ours:
             out["fallback_ops"] = len(bw.fallback_counts())
+            if os.environ.get("B200_BENCH_VERBOSE"):
+                sys.stderr.write("fallbacks: " + json.dumps(sorted(bw.fallback_counts().items(), key=lambda kv: -kv[1])) + "\n")
         print(json.dumps(out))
     if par == "fsdp":
         dist.destroy_process_group()

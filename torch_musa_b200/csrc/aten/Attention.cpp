@@ -27,6 +27,8 @@ namespace {
 
 constexpr int64_t kMath = 0, kOverrideable = 4;
 std::atomic<bool> g_fused_sdp{true};
+// which kernel family serves the fused path: 0 = flash, 1 = cuDNN.  Fixed between a forward and its backward.
+std::atomic<int> g_sdp_impl{1};
 
 bool fused_eligible(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
                     const std::optional<at::Tensor>& mask, double dropout_p) {
@@ -69,6 +71,13 @@ FwdRet sdpa_fused_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor
                       bool return_debug_mask, std::optional<double> scale) {
   TORCH_CHECK(!(attn_bias.has_value() && attn_bias->defined()),
               "blackwell fused attention: explicit masks take the math path (this is a dispatch bug)");
+  if (g_sdp_impl.load() == 1 && q.size(1) == k.size(1) && q.size(3) <= 128) {
+    std::optional<at::Tensor> no_bias;
+    auto st = run_fallback(B200_OP_HANDLE("aten::_scaled_dot_product_cudnn_attention", ""), q, k, v, no_bias,
+                           /*compute_log_sumexp=*/true, dropout_p, is_causal, return_debug_mask, scale);
+    return FwdRet(st[0].toTensor(), st[1].toTensor(), st[2].toTensor(), st[3].toTensor(), st[4].toSymInt(),
+                  st[5].toSymInt(), st[6].toTensor(), st[7].toTensor(), st[8].toTensor());
+  }
   auto st = run_fallback(B200_OP_HANDLE("aten::_scaled_dot_product_flash_attention", ""), q, k, v, dropout_p,
                          is_causal, return_debug_mask, scale);
   // (output, logsumexp, cum_seq_q, cum_seq_k, max_q, max_k, rng_state, unused, debug_attn_mask)
@@ -82,7 +91,15 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> sdpa_fused_bwd(
     const at::Tensor& logsumexp, const at::Tensor& cum_seq_q, const at::Tensor& cum_seq_k, c10::SymInt max_q,
     c10::SymInt max_k, double dropout_p, bool is_causal, const at::Tensor& philox_seed,
     const at::Tensor& philox_offset, std::optional<double> scale) {
-  (void)attn_bias; (void)grad_input_mask;
+  (void)grad_input_mask;
+  if (g_sdp_impl.load() == 1 && q.size(1) == k.size(1) && q.size(3) <= 128) {
+    at::Tensor no_bias;
+    auto st = run_fallback(B200_OP_HANDLE("aten::_scaled_dot_product_cudnn_attention_backward", ""), grad_out, q, k, v,
+                           out, logsumexp, philox_seed, philox_offset, no_bias, cum_seq_q, cum_seq_k, max_q, max_k,
+                           dropout_p, is_causal, scale);
+    return {st[0].toTensor(), st[1].toTensor(), st[2].toTensor(), at::Tensor()};
+  }
+  (void)attn_bias;
   auto st = run_fallback(B200_OP_HANDLE("aten::_scaled_dot_product_flash_attention_backward", ""), grad_out, q, k, v,
                          out, logsumexp, cum_seq_q, cum_seq_k, max_q, max_k, dropout_p, is_causal, philox_seed,
                          philox_offset, scale);
@@ -92,6 +109,8 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> sdpa_fused_bwd(
 }  // namespace
 
 void set_fused_sdp(bool on) { g_fused_sdp = on; }
+void set_sdp_impl(int impl) { g_sdp_impl = impl; }
+int sdp_impl() { return g_sdp_impl; }
 bool fused_sdp_enabled() { return g_fused_sdp; }
 
 }  // namespace ops

@@ -35,6 +35,8 @@ B200_EXPORT bool tensor_core_gemm_enabled();
 // Fused scaled-dot-product attention on/off (off: the math decomposition is always chosen).
 B200_EXPORT void set_fused_sdp(bool on);
 B200_EXPORT bool fused_sdp_enabled();
+B200_EXPORT void set_sdp_impl(int impl);  // 0 flash-style, 1 cuDNN-style library kernels
+B200_EXPORT int sdp_impl();
 
 // Counter of hand-written kernel launches (reported by the benchmark as its own-kernel launch count).
 B200_EXPORT void count_launch(int n = 1);

@@ -208,6 +208,8 @@ PYBIND11_MODULE(_C, m) {
   m.def("_gemm_status", [](bool clear) { return b200_gemm_status(clear ? 1 : 0); }, py::arg("clear") = false);
   m.def("_set_tensor_core_gemm", [](bool on) { ops::set_tensor_core_gemm(on); });
   m.def("_set_fused_sdp", [](bool on) { ops::set_fused_sdp(on); });
+  m.def("_set_sdp_impl", [](int impl) { ops::set_sdp_impl(impl); });
+  m.def("_sdp_impl", [] { return ops::sdp_impl(); });
   m.def("_fused_sdp_enabled", [] { return ops::fused_sdp_enabled(); });
   m.def("_tensor_core_gemm_enabled", [] { return ops::tensor_core_gemm_enabled(); });
   m.def("_runtime_version", [] {

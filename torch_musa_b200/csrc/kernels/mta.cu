@@ -166,16 +166,33 @@ struct AdamFunctor {
     };
     const bool vec = al16(p) && al16(g) && al16(ea) && al16(es) && (!mx || al16(mx));
     const int64_t n4 = vec ? n / 4 : 0;
-    for (int64_t q = threadIdx.x; q < n4; q += kThreads) {
-      const int64_t i = q * 4;
-      float pf[4], gf[4], mf[4], vf[4], xf[4] = {0.f, 0.f, 0.f, 0.f};
-      load4(p + i, pf); load4(g + i, gf); load4(ea + i, mf); load4(es + i, vf);
-      if (mx) load4(mx + i, xf);
+    // 4 independent 4-element packets per thread per trip: all loads are issued before any math so that
+    // 16 x 16 B are in flight per thread (the step is pure HBM streaming: 16 B read + 12 B written per element)
+    constexpr int ILP = 4;
+    for (int64_t q0 = threadIdx.x; q0 < n4; q0 += (int64_t)kThreads * ILP) {
+      float pf[ILP][4], gf[ILP][4], mf[ILP][4], vf[ILP][4], xf[ILP][4];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) upd(pf[k], gf[k], mf[k], vf[k], xf[k]);
-      store4(p + i, pf); store4(ea + i, mf); store4(es + i, vf);
-      if (mx) store4(mx + i, xf);
-      if (a.grad_scale) store4(g + i, gf);
+      for (int u = 0; u < ILP; ++u) {
+        const int64_t q = q0 + (int64_t)u * kThreads;
+        if (q < n4) {
+          const int64_t i = q * 4;
+          load4(p + i, pf[u]); load4(g + i, gf[u]); load4(ea + i, mf[u]); load4(es + i, vf[u]);
+          if (mx) load4(mx + i, xf[u]);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < ILP; ++u) {
+        const int64_t q = q0 + (int64_t)u * kThreads;
+        if (q < n4) {
+          const int64_t i = q * 4;
+          if (!mx) { xf[u][0] = xf[u][1] = xf[u][2] = xf[u][3] = 0.f; }
+#pragma unroll
+          for (int k = 0; k < 4; ++k) upd(pf[u][k], gf[u][k], mf[u][k], vf[u][k], xf[u][k]);
+          store4(p + i, pf[u]); store4(ea + i, mf[u]); store4(es + i, vf[u]);
+          if (mx) store4(mx + i, xf[u]);
+          if (a.grad_scale) store4(g + i, gf[u]);
+        }
+      }
     }
     for (int64_t i = n4 * 4 + threadIdx.x; i < n; i += kThreads) {
       float pf = ToF<TP>::to(p[i]), gf = ToF<TG>::to(g[i]), mf = ToF<TS>::to(ea[i]), vf = ToF<TS>::to(es[i]);

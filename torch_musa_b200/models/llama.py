@@ -80,8 +80,8 @@ class Attention(nn.Module):
         cos, sin = self._rope[0].cos, self._rope[0].sin
         hd, h, kv = cfg.head_dim, cfg.n_heads, cfg.kv_heads
         if cfg.fused_qkv:
-            qkv = self.wqkv(x).view(B, S, h + 2 * kv, hd)
-            q, k, v = qkv[:, :, :h], qkv[:, :, h:h + kv], qkv[:, :, h + kv:]
+            # split (not slicing): its backward is one concatenation instead of three zero-fill + add passes
+            q, k, v = self.wqkv(x).view(B, S, h + 2 * kv, hd).split([h, kv, kv], dim=2)
         else:
             q = self.wq(x).view(B, S, h, hd)
             k = self.wk(x).view(B, S, kv, hd)
