@@ -530,3 +530,51 @@ int b200_amp_update_scale(float* scale, int* growth_tracker, const float* found_
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of the multi-tensor L2 norm (declared in b200_no_alloc.h).
+#include "b200_no_alloc.h"
+
+namespace {
+
+constexpr size_t kStaticScratchFloats = (size_t)B200_L2NORM_STATIC_MAX_TENSORS * (kNormSlots + 1) + 8;
+
+// Lives in the library image on every device that loads it; in host code this name is only a handle
+// for cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) float g_l2norm_static_scratch[kStaticScratchFloats];
+
+constexpr int kMaxStaticDevices = 64;
+float* g_static_scratch_addr[kMaxStaticDevices] = {nullptr};
+
+// Device address of the array on the current device (looked up once per device).
+int static_scratch_for_current_device(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxStaticDevices) return (int)cudaErrorInvalidDevice;
+  if (!g_static_scratch_addr[dev]) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_l2norm_static_scratch);
+    if (e != cudaSuccess) return (int)e;
+    g_static_scratch_addr[dev] = p;
+  }
+  *out = g_static_scratch_addr[dev];
+  return 0;
+}
+
+}  // namespace
+
+extern "C" int b200_multi_tensor_l2norm_static(int n, int dtype, void* const* tensors, const int64_t* numels,
+                                               float* out_total, float* out_per_tensor, cudaStream_t stream) {
+  if (n < 0 || n > B200_L2NORM_STATIC_MAX_TENSORS) return (int)cudaErrorInvalidValue;
+  if (n == 0) {
+    if (out_total) return (int)cudaMemsetAsync(out_total, 0, sizeof(float), stream);
+    return 0;
+  }
+  float* scratch = nullptr;
+  int e = static_scratch_for_current_device(&scratch);
+  if (e) return e;
+  B200K_DISPATCH_FLOAT(dtype, T,
+                       return b200k::l2norm_impl<T>(n, tensors, numels, out_total, out_per_tensor, scratch, stream));
+  return (int)cudaErrorNotSupported;
+}
