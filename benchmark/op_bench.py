@@ -1,0 +1,225 @@
+#!/usr/bin/env python
+"""Operator benchmark harness: times one hand-written operator on the blackwell device with CUDA
+events (warm-up, L2 flush between iterations) and reports achieved FLOP/s or bytes/s as a fraction of
+the measured peaks of this machine (MEASURED_PEAKS.json if present).
+
+  python benchmark/op_bench.py gemm --m 4096 --n 4096 --k 4096
+  python benchmark/op_bench.py rmsnorm --rows 4096 --cols 4096 [--backward]
+  python benchmark/op_bench.py softmax|cross_entropy --rows 4096 --cols 32000
+  python benchmark/op_bench.py swiglu --rows 4096 --cols 11008
+  python benchmark/op_bench.py adamw --numel 268435456
+  python benchmark/op_bench.py all            (a Llama-7B shaped sweep; one JSON line per case)
+
+Every case prints one JSON line: {"op", "shape", "dtype", "us", "tflops" | "gbs", "frac_of_measured", ...}.
+Parity: reference benchmark/operator_benchmark (harness + per-op FLOPs/bytes, README.md:35-227).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+import torch.nn.functional as F  # noqa: E402
+
+import torch_musa_b200 as bw  # noqa: E402
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "tflops": d["bf16_tflops"], "src": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1590.0, "src": "fallback"}
+
+
+_FLUSH = None
+
+
+def flush_l2(dev):
+    global _FLUSH
+    if _FLUSH is None:
+        _FLUSH = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # 2x the 126 MB L2
+    _FLUSH.zero_()
+
+
+def timeit(fn, dev, iters=20, warmup=5, flush=True):
+    for _ in range(warmup):
+        fn()
+    bw.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        if flush:
+            flush_l2(dev)
+        s, e = bw.Event(enable_timing=True), bw.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        e.synchronize()
+        total += s.elapsed_time(e)
+    return total / iters * 1e3  # us
+
+
+def report(op, shape, dt, us, flops=None, nbytes=None, **extra):
+    pk = peaks()
+    out = {"op": op, "shape": shape, "dtype": str(dt).replace("torch.", ""), "us": round(us, 2)}
+    if flops is not None:
+        tf = flops / us / 1e6
+        out["tflops"] = round(tf, 1)
+        out["frac_of_" + pk["src"]] = round(tf / pk["tflops"], 3)
+    if nbytes is not None:
+        gbs = nbytes / us / 1e3
+        out["gbs"] = round(gbs, 1)
+        out["frac_of_" + pk["src"]] = round(gbs / pk["hbm_gbs"], 3)
+    quiet = extra.pop("quiet", False)
+    out.update(extra)
+    if not quiet:
+        print(json.dumps(out), flush=True)
+    return out
+
+
+def bench_gemm(dev, m, n, k, dt=torch.bfloat16, layout="nt", iters=20, quiet=False):
+    a = torch.randn(m, k, device=dev, dtype=dt)
+    w = torch.randn(n, k, device=dev, dtype=dt)
+    if layout == "nt":      # y = x @ W^T (forward)
+        fn = lambda: a @ w.t()
+    elif layout == "nn":    # dx = dy @ W   (dgrad): [m,n] x [n,k]
+        g = torch.randn(m, n, device=dev, dtype=dt)
+        fn = lambda: g @ w
+    else:                   # dW = dy^T @ x (wgrad): [n,m] x [m,k]
+        g = torch.randn(m, n, device=dev, dtype=dt)
+        fn = lambda: g.t() @ a
+    us = timeit(fn, dev, iters)
+    return report("gemm_" + layout, [m, n, k], dt, us, flops=2.0 * m * n * k, launches=1, quiet=quiet)
+
+
+def bench_gemm_sweep(dev, iters=10):
+    """Every tile configuration on the Llama-7B GEMM shapes (forward / dgrad / wgrad), one line per case."""
+    out = []
+    shapes = [(4096, 4096, 4096), (4096, 12288, 4096), (4096, 22016, 4096), (4096, 4096, 11008), (4096, 32000, 4096),
+              (8192, 8192, 8192), (2048, 4096, 4096)]
+    for cfg in (1, 2, 3, 0):
+        prev = bw._C._gemm_force_config(cfg)
+        try:
+            for (m, n, k) in shapes:
+                for layout in ("nt", "nn", "tn"):
+                    r = bench_gemm(dev, m, n, k, layout=layout, iters=iters, quiet=True)
+                    r["config"] = cfg
+                    print(json.dumps(r), flush=True)
+                    out.append(r)
+        finally:
+            bw._C._gemm_force_config(prev)
+    return out
+
+
+def bench_rmsnorm(dev, rows, cols, dt=torch.bfloat16, backward=False):
+    x = torch.randn(rows, cols, device=dev, dtype=dt, requires_grad=backward)
+    w = torch.ones(cols, device=dev, dtype=dt, requires_grad=backward)
+    es = x.element_size()
+    if not backward:
+        us = timeit(lambda: F.rms_norm(x, (cols,), w, 1e-5), dev)
+        return report("rmsnorm_fwd", [rows, cols], dt, us, nbytes=2 * rows * cols * es)
+    y = F.rms_norm(x, (cols,), w, 1e-5)
+    g = torch.randn_like(y)
+    us = timeit(lambda: torch.autograd.grad(y, (x, w), g, retain_graph=True), dev)
+    return report("rmsnorm_bwd", [rows, cols], dt, us, nbytes=3 * rows * cols * es)
+
+
+def bench_softmax(dev, rows, cols, dt=torch.bfloat16):
+    x = torch.randn(rows, cols, device=dev, dtype=dt)
+    us = timeit(lambda: torch.softmax(x, -1), dev)
+    return report("softmax_fwd", [rows, cols], dt, us, nbytes=2 * rows * cols * x.element_size())
+
+
+def bench_ce(dev, rows, cols, dt=torch.bfloat16):
+    from torch_musa_b200.ops import fused_cross_entropy
+
+    x = torch.randn(rows, cols, device=dev, dtype=dt, requires_grad=True)
+    t = torch.randint(0, cols, (rows,), device="cpu").to(dev)
+
+    def fn():
+        loss = fused_cross_entropy(x, t)
+        loss.backward()
+        x.grad = None
+
+    us = timeit(fn, dev)
+    return report("fused_cross_entropy_fwd_bwd", [rows, cols], dt, us, nbytes=3 * rows * cols * x.element_size())
+
+
+def bench_swiglu(dev, rows, cols, dt=torch.bfloat16):
+    from torch_musa_b200.ops import swiglu
+
+    x = torch.randn(rows, 2 * cols, device=dev, dtype=dt)
+    us = timeit(lambda: swiglu(x), dev)
+    return report("swiglu_fwd", [rows, cols], dt, us, nbytes=3 * rows * cols * x.element_size())
+
+
+def bench_adamw(dev, numel):
+    p = torch.randn(numel, device=dev, requires_grad=True)
+    p.grad = torch.randn(numel, device=dev)
+    opt = torch.optim.AdamW([p], lr=1e-3, fused=True)
+    opt.step()
+    us = timeit(opt.step, dev, flush=False)
+    # read p, g, m, v; write p, m, v (fp32)
+    return report("fused_adamw", [numel], torch.float32, us, nbytes=28 * numel)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("op")
+    ap.add_argument("--m", type=int, default=4096)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--rows", type=int, default=4096)
+    ap.add_argument("--cols", type=int, default=4096)
+    ap.add_argument("--numel", type=int, default=1 << 28)
+    ap.add_argument("--layout", default="nt", choices=["nt", "nn", "tn"])
+    ap.add_argument("--dtype", default="bfloat16")
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--backward", action="store_true")
+    ap.add_argument("--gemm-config", type=int, default=None, help="pin the GEMM tile configuration (1, 2 or 3)")
+    a = ap.parse_args()
+    if a.gemm_config is not None:
+        bw._C._gemm_force_config(a.gemm_config)
+    dev = torch.device("blackwell:0")
+    dt = getattr(torch, a.dtype)
+    if a.op == "gemm":
+        bench_gemm(dev, a.m, a.n, a.k, dt, a.layout, a.iters)
+    elif a.op == "gemm_sweep":
+        bench_gemm_sweep(dev, a.iters)
+    elif a.op == "rmsnorm":
+        bench_rmsnorm(dev, a.rows, a.cols, dt, a.backward)
+    elif a.op == "softmax":
+        bench_softmax(dev, a.rows, a.cols, dt)
+    elif a.op == "cross_entropy":
+        bench_ce(dev, a.rows, a.cols, dt)
+    elif a.op == "swiglu":
+        bench_swiglu(dev, a.rows, a.cols, dt)
+    elif a.op == "adamw":
+        bench_adamw(dev, a.numel)
+    elif a.op == "all":
+        for (m, n, k) in [(4096, 12288, 4096), (4096, 4096, 4096), (4096, 22016, 4096), (4096, 4096, 11008),
+                          (4096, 32000, 4096)]:
+            for lay in ("nt", "nn", "tn"):
+                bench_gemm(dev, m, n, k, dt, lay)
+        bench_rmsnorm(dev, 4096, 4096, dt)
+        bench_rmsnorm(dev, 4096, 4096, dt, backward=True)
+        bench_rmsnorm(dev, 256, 1024, torch.float16)
+        bench_softmax(dev, 4096, 32000, dt)
+        bench_ce(dev, 4096, 32000, dt)
+        bench_swiglu(dev, 4096, 11008, dt)
+        bench_adamw(dev, 1 << 28)
+    else:
+        raise SystemExit(f"unknown op {a.op}")
+    st = bw._C._gemm_status()
+    if st:
+        raise SystemExit("a GEMM launch gave up on a bounded wait")
+
+
+if __name__ == "__main__":
+    main()
