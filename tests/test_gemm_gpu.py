@@ -58,6 +58,33 @@ def test_mm_all_layouts(bw, dev, m, n, k):
         assert ref_close(y, ref, k, dt), name
 
 
+@pytest.mark.parametrize("config", [1, 2])
+@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (136, 264, 136), (384, 392, 520), (1000, 3000, 264),
+                                   (4096, 4096, 512), (2048, 11008, 4096)])
+def test_mm_every_tile_config(bw, dev, m, n, k, config):
+    """Single-CTA 128x256 and SM-pair 256x256 tiles give the same product in all four layouts."""
+    dt = torch.bfloat16
+    a, b = torch.randn(m, k).to(dt), torch.randn(k, n).to(dt)
+    ref = a.float() @ b.float()
+    ad, bd = a.to(dev), b.to(dev)
+    at_d = a.t().contiguous().to(dev).t()
+    bt_d = b.t().contiguous().to(dev).t()
+    bias = torch.randn(n).to(dt)
+    prev = bw._C._gemm_force_config(config)
+    try:
+        for A, B, name in [(ad, bd, "A:K B:MN"), (ad, bt_d, "A:K B:K"), (at_d, bd, "A:MN B:MN"), (at_d, bt_d, "A:MN B:K")]:
+            bw.reset_kernel_launch_count()
+            y = A @ B
+            assert bw.kernel_launch_count() == 1, name
+            assert ref_close(y, ref, k, dt), f"{name} config {config}"
+        y = torch.addmm(bias.to(dev), ad, bd)
+        assert ref_close(y, ref + bias.float(), k, dt), f"addmm config {config}"
+    finally:
+        bw._C._gemm_force_config(prev)
+    bw.synchronize()
+    assert bw._C._gemm_status(False) == 0
+
+
 def test_linear_autograd(bw, dev):
     dt = torch.bfloat16
     x, w, b = torch.randn(384, 512).to(dt), torch.randn(768, 512).to(dt), torch.randn(768).to(dt)

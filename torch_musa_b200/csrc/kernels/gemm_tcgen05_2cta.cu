@@ -1,0 +1,412 @@
+// bf16/fp16 GEMM on paired SMs: tcgen05.mma.cta_group::2.
+//
+//   D[M,N] (+)= alpha * A[M,K] * B[N,K]^T (+ bias) (act)
+//
+// A cluster of two CTAs (one per SM of a pair) owns a 256 x BN output tile (BN = 256 in every shipped
+// instantiation; the kernel is written for any BN that is a multiple of 128).
+// Each CTA stages its own 128 rows of A and its own BN/2 rows of B in 128B-swizzled shared
+// memory; one elected thread of the leader CTA issues M256 x BN x K16 instructions that read
+// both CTAs' shared memory and write 128 accumulator lanes x BN columns into each CTA's TMEM.
+// Against the single-CTA kernel this halves the B traffic per SM (64 instead of 96 bytes of
+// operand per tensor-core clock).
+//
+// Roles per CTA (six warps): warp 0 TMA producer (its loads signal the leader's "full"
+// barrier; no cluster multicast is used on any load), warp 1 TMEM allocation and -- in the
+// leader only -- MMA issue, warps 2-5 epilogue for the CTA's own 128 rows.  Ring slots and
+// accumulators are released to both CTAs with one multicast tcgen05.commit; the epilogues of
+// both CTAs hand an accumulator back by arriving on the leader's barrier.
+// Every wait is bounded; the CTAs of a pair leave together through a cluster barrier so no
+// signal can target the shared memory of a CTA that is gone.
+//
+// Parity: the reference sends mm/addmm/bmm to a closed vendor library
+// (reference torch_musa/csrc/aten/ops/Matmul.cpp:293-335,373-380).
+#include "gemm_common.cuh"
+
+#include <algorithm>
+#include <atomic>
+#include <cstdlib>
+
+namespace b200k {
+namespace {
+using namespace gemmdev;
+
+constexpr int BM2 = 256;      // rows per cluster tile
+constexpr int BMH = 128;      // rows per CTA
+constexpr int BK = 64;
+constexpr int kThreads = 192;
+constexpr uint32_t kTmemCols = 512;
+
+template <int BN>
+struct Cfg {
+  static constexpr int kBHalf = BN / 2;                   // B rows staged by each CTA
+  static constexpr int kATile = BMH * BK * 2;             // 16 KB
+  static constexpr int kBTile = kBHalf * BK * 2;          // 16 KB / 8 KB
+  static constexpr int kStage = kATile + kBTile;
+  static constexpr int kStages = BN == 256 ? 6 : 8;       // 192 KB of ring either way
+  static constexpr int kAcc = (int)kTmemCols / BN;        // 2 / 4 accumulators
+  static constexpr int kSmem = kStages * kStage + 1024 /*alignment slack*/ + 512 /*barriers*/;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t cta_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(cta_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// barrier given as a shared::cluster address (possibly in the peer CTA)
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+// Tile load into this CTA's shared memory; completion bytes are credited to a barrier that may live in
+// the peer CTA (the pair's leader).
+__device__ __forceinline__ void tma_load_3d_pair(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr,
+                                                 int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// One arrival on the barrier at this shared-memory offset in every CTA of the mask, once all MMAs issued so
+// far by this thread have completed.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t cta_mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(smem_u32(bar)), "h"(cta_mask)
+      : "memory");
+}
+
+template <typename OutT, bool A_KMAJOR, bool B_KMAJOR, int BN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 OutT* __restrict__ d, const Params p) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  // Both CTAs of the pair must use identical shared-memory offsets: the dynamic segment starts at the same
+  // offset in every CTA of a launch, so the same round-up yields the same layout.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem + C::kStages * C::kATile;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStage);
+  uint64_t* full_bar = bars;                          // [kStages]  used in the leader
+  uint64_t* empty_bar = bars + C::kStages;            // [kStages]  one per CTA
+  uint64_t* tfull_bar = bars + 2 * C::kStages;        // [kAcc]     one per CTA
+  uint64_t* tempty_bar = tfull_bar + C::kAcc;         // [kAcc]     used in the leader
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + C::kAcc);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1;
+  const int n_pairs = gridDim.x >> 1;
+  const int k_blocks = (p.k + BK - 1) / BK;
+  const int tiles_per_batch = p.tiles_m * p.tiles_n;
+  const int total_tiles = tiles_per_batch * p.batch;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(&full_bar[s], 1);   // the leader's expect_tx arrival; bytes come from both CTAs
+      mbar_init(&empty_bar[s], 1);  // one multicast commit
+    }
+    for (int s = 0; s < C::kAcc; ++s) {
+      mbar_init(&tfull_bar[s], 1);
+      mbar_init(&tempty_bar[s], 8);  // four epilogue warps in each of the two CTAs
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // peer barriers initialised and peer TMEM allocated before anything is signalled
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      const uint32_t full0 = mapa_u32(smem_u32(&full_bar[0]), 0);  // the leader's ring of "full" barriers
+      for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
+        const int b = tile / tiles_per_batch;
+        const int r = tile - b * tiles_per_batch;
+        const int m0 = (r % p.tiles_m) * BM2 + (int)rank * BMH;
+        const int n0 = (r / p.tiles_m) * BN + (int)rank * C::kBHalf;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+          if (leader) mbar_expect_tx(&full_bar[stage], 2 * C::kStage);
+          const uint32_t fb = full0 + (uint32_t)stage * 8u;
+          uint8_t* sa = smem_a + stage * C::kATile;
+          uint8_t* sb = smem_b + stage * C::kBTile;
+          const int k0 = kb * BK;
+          if constexpr (A_KMAJOR) {
+            tma_load_3d_pair(sa, &tmap_a, fb, k0, m0, b);
+          } else {
+            tma_load_3d_pair(sa, &tmap_a, fb, m0, k0, b);
+            tma_load_3d_pair(sa + 8192, &tmap_a, fb, m0 + 64, k0, b);
+          }
+          if constexpr (B_KMAJOR) {
+            tma_load_3d_pair(sb, &tmap_b, fb, k0, n0, b);
+          } else {
+#pragma unroll
+            for (int q = 0; q < C::kBHalf / 64; ++q) tma_load_3d_pair(sb + q * 8192, &tmap_b, fb, n0 + q * 64, k0, b);
+          }
+          if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (leader && lane == 0) {
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
+        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem_a + stage * C::kATile);
+          const uint32_t sb = smem_u32(smem_b + stage * C::kBTile);
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; ++kk) {
+            const uint64_t adesc = A_KMAJOR ? make_desc(sa + kk * 32, 16, 1024) : make_desc(sa + kk * 2048, 8192, 1024);
+            const uint64_t bdesc = B_KMAJOR ? make_desc(sb + kk * 32, 16, 1024) : make_desc(sb + kk * 2048, 8192, 1024);
+            umma_f16_pair(tmem_d, adesc, bdesc, p.idesc, (kb | kk) != 0 ? 1u : 0u);
+          }
+          umma_commit_pair(&empty_bar[stage], 3);  // frees this slot in both CTAs
+          if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit_pair(&tfull_bar[acc], 3);  // accumulator complete in both CTAs
+        if (++acc == C::kAcc) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    const int q = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const uint32_t tempty0 = mapa_u32(smem_u32(&tempty_bar[0]), 0);
+    const bool vec_ok = (p.ldd % (16 / (int)sizeof(OutT)) == 0) && ((reinterpret_cast<uintptr_t>(d) & 15) == 0) &&
+                        (p.stride_d % (16 / (int)sizeof(OutT)) == 0);
+    for (int tile = pair; tile < total_tiles; tile += n_pairs) {
+      const int b = tile / tiles_per_batch;
+      const int r = tile - b * tiles_per_batch;
+      const int m0 = (r % p.tiles_m) * BM2 + (int)rank * BMH;
+      const int n0 = (r / p.tiles_m) * BN;
+      if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) break;
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      OutT* drow = d + (int64_t)b * p.stride_d + (int64_t)row * p.ldd + n0;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col0 = n0 + c * 32;
+        if (col0 >= p.n) break;  // uniform across the warp
+        uint32_t raw[32];
+        tmem_ld32(taddr + (uint32_t)(c * 32), raw);
+        tmem_ld_wait();
+        if (row < p.m) {
+          const int valid = min(32, p.n - col0);
+          float v[32];
+#pragma unroll
+          for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(raw[e]) * p.alpha;
+          if (p.bias) {
+            if (p.bias_f32) {
+              const float* bp = reinterpret_cast<const float*>(p.bias) + col0;
+#pragma unroll
+              for (int e = 0; e < 32; ++e) if (e < valid) v[e] += __ldg(bp + e);
+            } else {
+              const OutT* bp = reinterpret_cast<const OutT*>(p.bias) + col0;
+#pragma unroll
+              for (int e = 0; e < 32; ++e) if (e < valid) v[e] += ToF<OutT>::to(bp[e]);
+            }
+          }
+          if (p.act) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) v[e] = apply_act(v[e], p.act);
+          }
+          if (p.accumulate) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) if (e < valid) v[e] += ToF<OutT>::to(drow[c * 32 + e]);
+          }
+          store_chunk<OutT>(drow + c * 32, v, valid, vec_ok);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(tempty0 + (uint32_t)acc * 8u);  // hand the accumulator back to the leader
+      if (++acc == C::kAcc) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  // A CTA that gave up on a wait may still have tile loads in flight towards its shared memory: give them
+  // a bounded moment to land before the memory is released.
+  if (*abort_flag && threadIdx.x == 0) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // no CTA of the pair leaves while the other may still signal it
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+  if (threadIdx.x == 0 && *abort_flag && p.status) atomicExch(p.status, 1);
+}
+
+// ------------------------------------------------------------------ host side
+template <typename OutT, int BN>
+int launch_pair(const b200_gemm_desc_t* g, void* d, const void* a, const void* b, cudaStream_t stream) {
+  using C = Cfg<BN>;
+  CUtensorMap ma, mb;
+  const uint64_t esz = 2;
+  const uint64_t batch = (uint64_t)std::max(g->batch, 1);
+  bool ok;
+  if (g->a_kmajor)
+    ok = gemm_make_map(&ma, a, g->in_dtype, (uint64_t)g->k, (uint64_t)g->m, batch, (uint64_t)g->lda * esz,
+                       (uint64_t)g->stride_a * esz, BK, BMH);
+  else
+    ok = gemm_make_map(&ma, a, g->in_dtype, (uint64_t)g->m, (uint64_t)g->k, batch, (uint64_t)g->lda * esz,
+                       (uint64_t)g->stride_a * esz, 64, BK);
+  if (!ok) return (int)cudaErrorNotSupported;
+  if (g->b_kmajor)
+    ok = gemm_make_map(&mb, b, g->in_dtype, (uint64_t)g->k, (uint64_t)g->n, batch, (uint64_t)g->ldb * esz,
+                       (uint64_t)g->stride_b * esz, BK, C::kBHalf);
+  else
+    ok = gemm_make_map(&mb, b, g->in_dtype, (uint64_t)g->n, (uint64_t)g->k, batch, (uint64_t)g->ldb * esz,
+                       (uint64_t)g->stride_b * esz, 64, BK);
+  if (!ok) return (int)cudaErrorNotSupported;
+
+  Params p;
+  p.m = g->m; p.n = g->n; p.k = g->k;
+  p.batch = (int)batch;
+  p.tiles_m = (g->m + BM2 - 1) / BM2;
+  p.tiles_n = (g->n + BN - 1) / BN;
+  p.ldd = g->ldd;
+  p.stride_d = g->stride_d;
+  p.bias = g->bias;
+  p.bias_f32 = g->bias_dtype == B200_F32;
+  p.act = g->act;
+  p.accumulate = g->accumulate;
+  p.alpha = g->alpha;
+  // instruction descriptor: fp32 accumulate, A/B format, majors, N>>3, M>>4 (M counts both CTAs)
+  const uint32_t fmt = g->in_dtype == B200_BF16 ? 1u : 0u;
+  p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((g->a_kmajor ? 0u : 1u) << 15) | ((g->b_kmajor ? 0u : 1u) << 16) |
+            ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM2 >> 4) << 24);
+  p.status = gemm_status_word_device();
+
+  const int total = p.tiles_m * p.tiles_n * p.batch;
+  const int pairs = std::max(1, gemm_sm_count() / 2);
+  const int grid = 2 * std::min(total, pairs);
+
+#define GEMM2_GO(AK, BKM)                                                                                        \
+  do {                                                                                                           \
+    static bool attr_set = false;                                                                                \
+    auto kern = gemm_pair_kernel<OutT, AK, BKM, BN>;                                                             \
+    if (!attr_set) {                                                                                             \
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem);         \
+      if (e != cudaSuccess) return (int)e;                                                                       \
+      attr_set = true;                                                                                           \
+    }                                                                                                            \
+    kern<<<grid, kThreads, C::kSmem, stream>>>(ma, mb, (OutT*)d, p);                                             \
+  } while (0)
+
+  if (g->a_kmajor && g->b_kmajor) GEMM2_GO(true, true);
+  else if (g->a_kmajor && !g->b_kmajor) GEMM2_GO(true, false);
+  else if (!g->a_kmajor && g->b_kmajor) GEMM2_GO(false, true);
+  else GEMM2_GO(false, false);
+#undef GEMM2_GO
+  B200K_LAUNCH_RET();
+}
+
+// 0 = cost model, 1 = single CTA 128x256, 2 = SM pair 256x256
+std::atomic<int> g_forced_config{[] {
+  const char* e = std::getenv("B200_GEMM_CONFIG");
+  return e ? std::atoi(e) : 0;
+}()};
+
+inline long long ceil_div_ll(long long a, long long b) { return (a + b - 1) / b; }
+
+}  // namespace
+
+int gemm_forced_config_exchange(int c) { return g_forced_config.exchange(c); }
+
+// Chooses between the single-CTA 128x256 kernel (returns cudaErrorNotSupported so the caller runs it) and the
+// SM-pair kernel with 256x256 tiles.  The model is waves x per-wave cost; per wave the pair kernel is ~15% cheaper
+// (measured 1.42-1.54 against 1.22-1.43 PFLOP/s on 4096-row bf16 problems) because each SM reads half of B.
+// 256x128 pair tiles were measured too and rejected: an N=128 instruction is no faster per column than N=256,
+// so they ran at 0.7-0.98 PFLOP/s whatever the wave count.
+int gemm_launch_2cta(const b200_gemm_desc_t* g, void* d, const void* a, const void* b, cudaStream_t stream) {
+  const int forced = g_forced_config.load(std::memory_order_relaxed);
+  const long long batch = std::max(g->batch, 1);
+  const int sms = gemm_sm_count();
+  const int pairs = std::max(1, sms / 2);
+  int choice = forced;
+  if (choice == 0) {
+    choice = 1;
+    if (g->m > 128) {  // with M <= 128 the second CTA of a pair would only multiply padding
+      const long long t1 = ceil_div_ll(g->m, 128) * ceil_div_ll(g->n, 256) * batch;
+      const long long t2 = ceil_div_ll(g->m, 256) * ceil_div_ll(g->n, 256) * batch;
+      const double c1 = (double)ceil_div_ll(t1, sms) * 1.15;
+      const double c2 = (double)ceil_div_ll(t2, pairs);
+      if (c2 <= c1) choice = 2;
+    }
+  }
+  if (choice != 2) return (int)cudaErrorNotSupported;
+  switch (g->out_dtype) {
+    case B200_BF16: return launch_pair<__nv_bfloat16, 256>(g, d, a, b, stream);
+    case B200_F16: return launch_pair<__half, 256>(g, d, a, b, stream);
+    case B200_F32: return launch_pair<float, 256>(g, d, a, b, stream);
+    default: return (int)cudaErrorNotSupported;
+  }
+}
+
+}  // namespace b200k
+
+// Pins the tile configuration for every later launch of this process (0 returns to the cost model).
+extern "C" int b200_gemm_force_config(int config) {
+  if (config < 0 || config > 2) return -1;
+  return b200k::gemm_forced_config_exchange(config);
+}
