@@ -42,6 +42,8 @@ def parse():
     p.add_argument("--micro-batch", type=int, default=1)
     p.add_argument("--parallelism", default="auto", choices=["auto", "fsdp", "single"])
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--trace", default=None, help="debug: also run two extra steps under torch.profiler and write "
+                   "a chrome trace per rank to this path prefix (never inside the timed region)")
     return p.parse_args()
 
 
@@ -249,6 +251,15 @@ def main():
         e2e = {"ms_total": e2e_ms, "h2d": h2d // args.steps, "d2h": d2h // args.steps}
 
     clocks = sampler.stop() if rank == 0 else None
+
+    if args.trace:
+        from torch.profiler import ProfilerActivity, profile
+
+        with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA]) as prof:
+            for i in range(2):
+                step(dev_tokens[i % n_batches])
+            barrier()
+        prof.export_chrome_trace(f"{args.trace}.rank{rank}.json")
 
     # max over ranks
     if par == "fsdp" and world > 1:

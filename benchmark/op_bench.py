@@ -110,13 +110,13 @@ def bench_gemm_sweep(dev, iters=10, rounds=3):
             for layout in ("nt", "nn", "tn"):
                 best = {}
                 for _ in range(rounds):
-                    for cfg in (1, 2, 0):
+                    for cfg in (1, 2, 3, 0):
                         bw._C._gemm_force_config(cfg)
                         r = bench_gemm(dev, m, n, k, layout=layout, iters=iters, quiet=True)
                         if cfg not in best or r["us"] < best[cfg]["us"]:
                             best[cfg] = r
                 line = {"op": "gemm_" + layout, "shape": [m, n, k]}
-                for cfg, name in ((1, "single_128x256"), (2, "pair_256x256"), (0, "auto")):
+                for cfg, name in ((1, "single_128x256"), (2, "pair_static"), (3, "pair_dynamic"), (0, "auto")):
                     line[name] = best[cfg]["tflops"]
                 print(json.dumps(line), flush=True)
                 out.append(line)

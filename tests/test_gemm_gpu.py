@@ -58,7 +58,7 @@ def test_mm_all_layouts(bw, dev, m, n, k):
         assert ref_close(y, ref, k, dt), name
 
 
-@pytest.mark.parametrize("config", [1, 2])
+@pytest.mark.parametrize("config", [1, 2, 3])
 @pytest.mark.parametrize("m,n,k", [(256, 256, 64), (136, 264, 136), (384, 392, 520), (1000, 3000, 264),
                                    (4096, 4096, 512), (2048, 11008, 4096)])
 def test_mm_every_tile_config(bw, dev, m, n, k, config):

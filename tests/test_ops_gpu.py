@@ -287,3 +287,45 @@ def test_sdpa_fused_routing(bw, dev, dt, hq, hkv, causal):
     om = F.scaled_dot_product_attention(qd.detach()[:, :hkv], kd.detach(), vd.detach(), attn_mask=mask.to(dev))
     omr = F.scaled_dot_product_attention(qr.detach()[:, :hkv], kr.detach(), vr.detach(), attn_mask=mask)
     assert close(om, omr, dt, 4)
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_cat_and_strided_copy(bw, dev, dt):
+    """cat along every dim, the backward of split (one cat), and strided / converting copies on the row kernel."""
+    xs = [torch.randn(4, n, 64).to(dt) for n in (8, 24, 16)]
+    for d in (0, 1, 2, -1):
+        shapes = [x if d in (1,) else x[:, :8] for x in xs]
+        ref = torch.cat(shapes, dim=d)
+        bw.reset_kernel_launch_count()
+        out = torch.cat([s.to(dev) for s in shapes], dim=d)
+        assert bw.kernel_launch_count() >= len(shapes)
+        assert torch.equal(out.cpu(), ref)
+    # legacy: 1-D empty tensors are skipped
+    out = torch.cat([torch.empty(0, device=dev, dtype=dt), xs[0].to(dev)], dim=1)
+    assert torch.equal(out.cpu(), xs[0])
+    # split backward
+    w = leaf(torch.randn(16, 96), dev, dt)
+    a, b, c = w.view(16, 3, 32).split([1, 1, 1], dim=1)
+    (a.float().sum() + 2 * b.float().sum() + 3 * c.float().sum()).backward()
+    assert torch.equal(w.grad.float().cpu().view(16, 3, 32)[:, 2], torch.full((16, 32), 3.0))
+    # converting copy into a column block of a wider fp32 matrix (rows of 128 elements)
+    src = torch.randn(2, 128).to(dt)
+    dst = torch.zeros(2, 512, device=dev)
+    dst[:, 256:384].copy_(src.to(dev))
+    ref = torch.zeros(2, 512)
+    ref[:, 256:384] = src.float()
+    assert torch.equal(dst.cpu(), ref)
+
+
+@pytest.mark.parametrize("world", [1, 2, 8])
+def test_chunk_cat(bw, dev, world):
+    """The reduce-scatter copy-in: chunk r of every gradient goes to row r, bf16 -> fp32, with zero padding."""
+    grads = [torch.randn(64, 32), torch.randn(16, 8, 4), torch.randn(24), torch.randn(13, 16)]
+    grads16 = [g.to(torch.bfloat16) for g in grads]
+    ref = torch._chunk_cat(grads16, dim=0, num_chunks=world).float()
+    dg = [g.to(dev) for g in grads16]
+    out = torch._chunk_cat(dg, dim=0, num_chunks=world)
+    assert out.dtype == torch.bfloat16 and torch.equal(out.float().cpu(), ref)
+    out32 = torch.full(ref.shape, 7.0, device=dev)
+    torch._chunk_cat(dg, dim=0, num_chunks=world, out=out32)
+    assert torch.equal(out32.cpu(), ref)

@@ -221,8 +221,8 @@ B200_API int b200_gemm(const b200_gemm_desc_t* desc, void* d, const void* a, con
 B200_API int b200_gemm_available(void);
 /* non-zero once any GEMM launch of this process gave up on a bounded pipeline wait (sticky; clear != 0 resets) */
 B200_API int b200_gemm_status(int clear);
-/* Tile configuration for later launches: 0 cost model (default), 1 single-CTA 128x256, 2 SM-pair 256x256.
- * Returns the previous setting, -1 for an unknown value. */
+/* Tile configuration for later launches: 0 cost model (default), 1 single-CTA 128x256, 2 SM-pair 256x256 with
+ * the static tile schedule, 3 SM-pair 256x256 with the dynamic (cluster launch control) schedule.  Returns the previous setting, -1 for an unknown value. */
 B200_API int b200_gemm_force_config(int config);
 /* Philox counters one launch of the random kernels may consume per thread, for n outputs */
 B200_API uint64_t b200_philox_increment(int64_t n);

@@ -196,28 +196,84 @@ __global__ void __launch_bounds__(kThreads) cast_strided_kernel(D* __restrict__ 
   }
 }
 
+// Rows of contiguous elements (unit inner stride on both sides, everything 8-element aligned): one 8-element
+// vector per thread per trip; the outer index is decomposed once per vector, not per element.
+template <typename D, typename S>
+__global__ void __launch_bounds__(kThreads) cast_rows_kernel(D* __restrict__ dst, const S* __restrict__ src, CopyDims d,
+                                                             int64_t vec_per_row, int64_t nvec) {
+  constexpr int V = 8;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+    int64_t r = i / vec_per_row;
+    const int64_t c = (i - r * vec_per_row) * V;
+    int64_t od = c, os = c;
+#pragma unroll 1
+    for (int k = d.ndim - 2; k >= 0; --k) {
+      int64_t q = r / d.sizes[k];
+      int64_t x = r - q * d.sizes[k];
+      od += x * d.ds[k];
+      os += x * d.ss[k];
+      r = q;
+    }
+    S in[V];
+    D o[V];
+    *reinterpret_cast<uint4*>(in) = *reinterpret_cast<const uint4*>(src + os);
+    if constexpr (sizeof(S) == 4) *reinterpret_cast<uint4*>(in + 4) = *reinterpret_cast<const uint4*>(src + os + 4);
+#pragma unroll
+    for (int k = 0; k < V; ++k) o[k] = convert<D, S>(in[k]);
+    *reinterpret_cast<uint4*>(dst + od) = *reinterpret_cast<uint4*>(o);
+    if constexpr (sizeof(D) == 4) *reinterpret_cast<uint4*>(dst + od + 4) = *reinterpret_cast<uint4*>(o + 4);
+  }
+}
+
+// Drops size-1 dims and merges neighbours that are one stride pattern on both sides. Returns the new rank.
+inline int coalesce_dims(int ndim, const int64_t* sizes, const int64_t* ds, const int64_t* ss, CopyDims& out) {
+  int64_t sz[16], d[16], s_[16];
+  int n = 0;
+  for (int i = 0; i < ndim && n < 16; ++i) {
+    if (sizes[i] == 1) continue;
+    if (n > 0 && d[n - 1] == ds[i] * sizes[i] && s_[n - 1] == ss[i] * sizes[i]) {
+      sz[n - 1] *= sizes[i];
+      d[n - 1] = ds[i];
+      s_[n - 1] = ss[i];
+    } else {
+      sz[n] = sizes[i]; d[n] = ds[i]; s_[n] = ss[i];
+      ++n;
+    }
+  }
+  if (n == 0) { sz[0] = 1; d[0] = 1; s_[0] = 1; n = 1; }
+  if (n > 8) return -1;
+  out.ndim = n;
+  for (int i = 0; i < n; ++i) { out.sizes[i] = sz[i]; out.ds[i] = d[i]; out.ss[i] = s_[i]; }
+  return n;
+}
+
 template <typename D, typename S>
 int launch_cast(void* dst, const void* src, int ndim, const int64_t* sizes, const int64_t* ds, const int64_t* ss,
                 cudaStream_t s) {
   int64_t n = 1;
   for (int i = 0; i < ndim; ++i) n *= sizes[i];
   if (n == 0) return 0;
-  // contiguous?
-  bool contig = true;
-  int64_t e = 1;
-  for (int i = ndim - 1; i >= 0; --i) {
-    if (sizes[i] != 1 && (ds[i] != e || ss[i] != e)) contig = false;
-    e *= sizes[i];
-  }
-  if (contig && aligned16((const S*)src) && aligned16((const D*)dst)) {
+  if (ndim > 16) return (int)cudaErrorNotSupported;
+  CopyDims d;
+  if (coalesce_dims(ndim, sizes, ds, ss, d) < 0) return (int)cudaErrorNotSupported;
+  const bool al = aligned16((const S*)src) && aligned16((const D*)dst);
+  if (d.ndim == 1 && d.ds[0] == 1 && d.ss[0] == 1 && al) {
     int grid = grid_for(n / 8 + 1);
     cast_contig_kernel<D, S><<<grid, kThreads, 0, s>>>((D*)dst, (const S*)src, n);
     B200K_LAUNCH_RET();
   }
-  if (ndim > 8) return (int)cudaErrorNotSupported;
-  CopyDims d;
-  d.ndim = ndim;
-  for (int i = 0; i < ndim; ++i) { d.sizes[i] = sizes[i]; d.ds[i] = ds[i]; d.ss[i] = ss[i]; }
+  const int last = d.ndim - 1;
+  bool rows = al && d.ndim >= 2 && d.ds[last] == 1 && d.ss[last] == 1 && d.sizes[last] % 8 == 0 && d.sizes[last] >= 64;
+  // 32-byte alignment of every row start for 4-byte types, 16-byte for 2-byte types: 8-element granularity covers both
+  for (int i = 0; rows && i < last; ++i) rows = d.ds[i] % 8 == 0 && d.ss[i] % 8 == 0;
+  if (rows) {
+    const int64_t vec_per_row = d.sizes[last] / 8;
+    const int64_t nvec = n / 8;
+    int grid = grid_for(nvec);
+    cast_rows_kernel<D, S><<<grid, kThreads, 0, s>>>((D*)dst, (const S*)src, d, vec_per_row, nvec);
+    B200K_LAUNCH_RET();
+  }
   int grid = grid_for(n);
   cast_strided_kernel<D, S><<<grid, kThreads, 0, s>>>((D*)dst, (const S*)src, d, n);
   B200K_LAUNCH_RET();

@@ -15,6 +15,9 @@
 // leader only -- MMA issue, warps 2-5 epilogue for the CTA's own 128 rows.  Ring slots and
 // accumulators are released to both CTAs with one multicast tcgen05.commit; the epilogues of
 // both CTAs hand an accumulator back by arriving on the leader's barrier.
+// Tiles are handed out either statically (cluster i takes tiles i, i+74, ...) or by cluster launch control:
+// the grid asks for one cluster per tile and a scheduler warp of each running cluster cancels clusters that
+// have not started and takes their tiles, so SMs that are busy with another kernel simply get no tiles.
 // Every wait is bounded; the CTAs of a pair leave together through a cluster barrier so no
 // signal can target the shared memory of a CTA that is gone.
 //
@@ -33,7 +36,7 @@ using namespace gemmdev;
 constexpr int BM2 = 256;      // rows per cluster tile
 constexpr int BMH = 128;      // rows per CTA
 constexpr int BK = 64;
-constexpr int kThreads = 192;
+constexpr int kThreads = 224;  // TMA, MMA, 4 epilogue warps, tile scheduler
 constexpr uint32_t kTmemCols = 512;
 
 template <int BN>
@@ -103,10 +106,70 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t cta_mas
       : "memory");
 }
 
+// ---- cluster launch control: a running cluster asks the hardware for the coordinates of a cluster of this
+// grid that has not started yet and takes over its tile; the answer (16 bytes) is delivered to the same
+// shared-memory offset in both CTAs and credited to the mbarrier at the same offset in both.
+__device__ __forceinline__ void clc_try_cancel(void* response, uint64_t* bar) {
+  asm volatile(
+      "clusterlaunchcontrol.try_cancel.async.shared::cta.mbarrier::complete_tx::bytes.multicast::cluster::all.b128 [%0], [%1];"
+      ::"r"(smem_u32(response)), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void clc_decode(const void* response, uint32_t& first_ctaid_x, uint32_t& valid) {
+  uint32_t x = 0, y = 0, z = 0, v = 0;
+  asm volatile(
+      "{\n\t.reg .pred p1;\n\t.reg .b128 r;\n\t"
+      "ld.shared.b128 r, [%4];\n\t"
+      "clusterlaunchcontrol.query_cancel.is_canceled.pred.b128 p1, r;\n\t"
+      "selp.u32 %3, 1, 0, p1;\n\t"
+      "@p1 clusterlaunchcontrol.query_cancel.get_first_ctaid.v4.b32.b128 {%0, %1, %2, _}, r;\n\t}"
+      : "+r"(x), "+r"(y), "+r"(z), "+r"(v)
+      : "r"(smem_u32(response))
+      : "memory");
+  // the next answer is written through the async proxy: order this generic-proxy read before it
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  first_ctaid_x = x;
+  valid = v;
+}
+__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t bar_cluster_addr, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(bar_cluster_addr),
+               "r"(bytes)
+               : "memory");
+}
+
+constexpr int kClcStages = 3;
+constexpr int kClcConsumers = 12;  // leader: TMA, MMA, 4 epilogue warps, scheduler; peer: TMA, 4 epilogue warps
+
+// Per-role cursor over the ring of scheduler answers.
+struct TileCursor {
+  uint64_t* full;        // this CTA's "answer arrived" barriers
+  const uint4* resp;     // this CTA's copy of the answers
+  uint32_t empty0;       // shared::cluster address of the leader's "answer consumed" barriers
+  int stage;
+  uint32_t phase;
+};
+
+// Next tile of this cluster.  Static schedule: stride by the number of pairs.  Dynamic schedule: consume one
+// scheduler answer.  Returns false when there is no further tile or a bounded wait expired.
+__device__ __forceinline__ bool next_tile(TileCursor& c, int dynamic, int& tile, int stride, int total,
+                                          volatile int* abort_flag) {
+  if (!dynamic) {
+    tile += stride;
+    return tile < total;
+  }
+  if (!mbar_wait(&c.full[c.stage], c.phase, abort_flag)) return false;
+  uint32_t x, valid;
+  clc_decode(&c.resp[c.stage], x, valid);
+  mbar_arrive_cluster(c.empty0 + (uint32_t)c.stage * 8u);
+  if (++c.stage == kClcStages) { c.stage = 0; c.phase ^= 1; }
+  tile = (int)(x >> 1);
+  return valid != 0 && tile < total;
+}
+
 template <typename OutT, bool A_KMAJOR, bool B_KMAJOR, int BN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 OutT* __restrict__ d, const Params p) {
+                 OutT* __restrict__ d, const Params p, const int dynamic) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   // Both CTAs of the pair must use identical shared-memory offsets: the dynamic segment starts at the same
@@ -114,12 +177,17 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* smem_a = smem;
   uint8_t* smem_b = smem + C::kStages * C::kATile;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStage);
+  uint8_t* ctrl = smem + C::kStages * C::kStage;
+  uint4* clc_resp = reinterpret_cast<uint4*>(ctrl);                        // [kClcStages] 16-byte answers
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ctrl + 16 * kClcStages);
   uint64_t* full_bar = bars;                          // [kStages]  used in the leader
   uint64_t* empty_bar = bars + C::kStages;            // [kStages]  one per CTA
   uint64_t* tfull_bar = bars + 2 * C::kStages;        // [kAcc]     one per CTA
   uint64_t* tempty_bar = tfull_bar + C::kAcc;         // [kAcc]     used in the leader
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + C::kAcc);
+  uint64_t* clc_full = tempty_bar + C::kAcc;          // [kClcStages] one per CTA
+  uint64_t* clc_empty = clc_full + kClcStages;        // [kClcStages] used in the leader
+  uint64_t* throttle_bar = clc_empty + kClcStages;    // leader: the producer started another tile
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(throttle_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -142,6 +210,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       mbar_init(&tfull_bar[s], 1);
       mbar_init(&tempty_bar[s], 8);  // four epilogue warps in each of the two CTAs
     }
+    for (int s = 0; s < kClcStages; ++s) {
+      mbar_init(&clc_full[s], 1);
+      mbar_init(&clc_empty[s], kClcConsumers);
+    }
+    mbar_init(throttle_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     prefetch_tmap(&tmap_a);
     prefetch_tmap(&tmap_b);
@@ -156,6 +229,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  TileCursor cur;
+  cur.full = clc_full;
+  cur.resp = clc_resp;
+  cur.empty0 = mapa_u32(smem_u32(&clc_empty[0]), 0);
+  cur.stage = 0;
+  cur.phase = 0;
+
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (both CTAs)
     if (lane == 0) {
@@ -163,7 +243,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       uint32_t phase = 0;
       bool ok = true;
       const uint32_t full0 = mapa_u32(smem_u32(&full_bar[0]), 0);  // the leader's ring of "full" barriers
-      for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
+      int tile = pair;
+      bool more = tile < total_tiles;
+      while (more && ok) {
+        if (dynamic && leader) mbar_arrive(throttle_bar);  // lets the scheduler ask for the tile after this one
         const int b = tile / tiles_per_batch;
         const int r = tile - b * tiles_per_batch;
         const int m0 = (r % p.tiles_m) * BM2 + (int)rank * BMH;
@@ -189,6 +272,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
           if (++stage == C::kStages) { stage = 0; phase ^= 1; }
         }
+        if (!ok) break;
+        more = next_tile(cur, dynamic, tile, n_pairs, total_tiles, abort_flag);
       }
     }
     __syncwarp();
@@ -198,7 +283,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
-      for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
+      int tile = pair;
+      bool more = tile < total_tiles;
+      while (more && ok) {
         if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
@@ -219,6 +306,26 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         if (!ok) break;
         umma_commit_pair(&tfull_bar[acc], 3);  // accumulator complete in both CTAs
         if (++acc == C::kAcc) { acc = 0; acc_phase ^= 1; }
+        more = next_tile(cur, dynamic, tile, n_pairs, total_tiles, abort_flag);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 6) {
+    // ------------------------------------------------------------ tile scheduler (leader CTA, dynamic schedule)
+    if (dynamic && leader && lane == 0 && pair < total_tiles) {
+      const uint32_t peer_full0 = mapa_u32(smem_u32(&clc_full[0]), 1);
+      uint32_t tphase = 0;
+      bool valid = true;
+      // One query in flight at a time: a query may only follow an answer that named a tile.
+      while (valid) {
+        if (!mbar_wait(throttle_bar, tphase, abort_flag)) break;  // the producer has started the current tile
+        tphase ^= 1;
+        if (!mbar_wait(&clc_empty[cur.stage], cur.phase ^ 1, abort_flag)) break;  // every role has read the old answer
+        mbar_expect_tx(&clc_full[cur.stage], 16);
+        mbar_expect_tx_cluster(peer_full0 + (uint32_t)cur.stage * 8u, 16);
+        clc_try_cancel(&clc_resp[cur.stage], &clc_full[cur.stage]);
+        int unused_tile = 0;
+        valid = next_tile(cur, 1, unused_tile, 0, total_tiles, abort_flag);
       }
     }
     __syncwarp();
@@ -230,7 +337,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const uint32_t tempty0 = mapa_u32(smem_u32(&tempty_bar[0]), 0);
     const bool vec_ok = (p.ldd % (16 / (int)sizeof(OutT)) == 0) && ((reinterpret_cast<uintptr_t>(d) & 15) == 0) &&
                         (p.stride_d % (16 / (int)sizeof(OutT)) == 0);
-    for (int tile = pair; tile < total_tiles; tile += n_pairs) {
+    int tile = pair;
+    bool more = tile < total_tiles;
+    while (more) {
       const int b = tile / tiles_per_batch;
       const int r = tile - b * tiles_per_batch;
       const int m0 = (r % p.tiles_m) * BM2 + (int)rank * BMH;
@@ -278,6 +387,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(tempty0 + (uint32_t)acc * 8u);  // hand the accumulator back to the leader
       if (++acc == C::kAcc) { acc = 0; acc_phase ^= 1; }
+      // lane 0 reads the scheduler's answer for the whole warp
+      int next = tile;
+      int go = 0;
+      if (lane == 0) go = next_tile(cur, dynamic, next, n_pairs, total_tiles, abort_flag) ? 1 : 0;
+      tile = __shfl_sync(0xffffffffu, next, 0);
+      more = __shfl_sync(0xffffffffu, go, 0) != 0;
     }
   }
 
@@ -298,7 +413,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
 // ------------------------------------------------------------------ host side
 template <typename OutT, int BN>
-int launch_pair(const b200_gemm_desc_t* g, void* d, const void* a, const void* b, cudaStream_t stream) {
+int launch_pair(const b200_gemm_desc_t* g, void* d, const void* a, const void* b, cudaStream_t stream, int dynamic) {
   using C = Cfg<BN>;
   CUtensorMap ma, mb;
   const uint64_t esz = 2;
@@ -339,7 +454,9 @@ int launch_pair(const b200_gemm_desc_t* g, void* d, const void* a, const void* b
 
   const int total = p.tiles_m * p.tiles_n * p.batch;
   const int pairs = std::max(1, gemm_sm_count() / 2);
-  const int grid = 2 * std::min(total, pairs);
+  // static schedule: one resident cluster per SM pair strides over the tiles; dynamic schedule: one cluster
+  // per tile is requested and the clusters that run take over the tiles of those that have not started
+  const int grid = dynamic ? 2 * total : 2 * std::min(total, pairs);
 
 #define GEMM2_GO(AK, BKM)                                                                                        \
   do {                                                                                                           \
@@ -350,7 +467,7 @@ int launch_pair(const b200_gemm_desc_t* g, void* d, const void* a, const void* b
       if (e != cudaSuccess) return (int)e;                                                                       \
       attr_set = true;                                                                                           \
     }                                                                                                            \
-    kern<<<grid, kThreads, C::kSmem, stream>>>(ma, mb, (OutT*)d, p);                                             \
+    kern<<<grid, kThreads, C::kSmem, stream>>>(ma, mb, (OutT*)d, p, dynamic);                                            \
   } while (0)
 
   if (g->a_kmajor && g->b_kmajor) GEMM2_GO(true, true);
@@ -361,11 +478,19 @@ int launch_pair(const b200_gemm_desc_t* g, void* d, const void* a, const void* b
   B200K_LAUNCH_RET();
 }
 
-// 0 = cost model, 1 = single CTA 128x256, 2 = SM pair 256x256
+// 0 = cost model, 1 = single CTA 128x256, 2 = SM pair 256x256 static schedule, 3 = SM pair 256x256 dynamic schedule
 std::atomic<int> g_forced_config{[] {
   const char* e = std::getenv("B200_GEMM_CONFIG");
   return e ? std::atoi(e) : 0;
 }()};
+
+// The dynamic (cluster launch control) schedule is what the cost model picks unless B200_GEMM_DYNAMIC=0: with a
+// static schedule a CTA that cannot become resident (its SM is held by a communication kernel) keeps its share
+// of the tiles waiting, so one busy SM stretches the whole GEMM to the length of the other kernel.
+const bool g_dynamic_default = [] {
+  const char* e = std::getenv("B200_GEMM_DYNAMIC");
+  return !(e && e[0] == '0');
+}();
 
 inline long long ceil_div_ll(long long a, long long b) { return (a + b - 1) / b; }
 
@@ -391,14 +516,15 @@ int gemm_launch_2cta(const b200_gemm_desc_t* g, void* d, const void* a, const vo
       const long long t2 = ceil_div_ll(g->m, 256) * ceil_div_ll(g->n, 256) * batch;
       const double c1 = (double)ceil_div_ll(t1, sms) * 1.15;
       const double c2 = (double)ceil_div_ll(t2, pairs);
-      if (c2 <= c1) choice = 2;
+      if (c2 <= c1) choice = g_dynamic_default ? 3 : 2;
     }
   }
-  if (choice != 2) return (int)cudaErrorNotSupported;
+  if (choice != 2 && choice != 3) return (int)cudaErrorNotSupported;
+  const int dynamic = choice == 3 ? 1 : 0;
   switch (g->out_dtype) {
-    case B200_BF16: return launch_pair<__nv_bfloat16, 256>(g, d, a, b, stream);
-    case B200_F16: return launch_pair<__half, 256>(g, d, a, b, stream);
-    case B200_F32: return launch_pair<float, 256>(g, d, a, b, stream);
+    case B200_BF16: return launch_pair<__nv_bfloat16, 256>(g, d, a, b, stream, dynamic);
+    case B200_F16: return launch_pair<__half, 256>(g, d, a, b, stream, dynamic);
+    case B200_F32: return launch_pair<float, 256>(g, d, a, b, stream, dynamic);
     default: return (int)cudaErrorNotSupported;
   }
 }
@@ -407,6 +533,6 @@ int gemm_launch_2cta(const b200_gemm_desc_t* g, void* d, const void* a, const vo
 
 // Pins the tile configuration for every later launch of this process (0 returns to the cost model).
 extern "C" int b200_gemm_force_config(int config) {
-  if (config < 0 || config > 2) return -1;
+  if (config < 0 || config > 3) return -1;
   return b200k::gemm_forced_config_exchange(config);
 }
