@@ -1,0 +1,140 @@
+"""Convolution routing (1x1 on the tcgen05 GEMM, the rest on library kernels) and the hand-written
+channels-last batch-norm kernels, against fp32 CPU references."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+
+def rel_err(a, b):
+    a, b = a.float().cpu(), b.float().cpu()
+    return float((a - b).abs().max() / b.abs().max().clamp_min(1e-6))
+
+
+@pytest.mark.parametrize("cin,cout,hw", [(64, 256, 14), (256, 64, 7), (128, 128, 9)])
+def test_pointwise_conv_runs_on_gemm(bw, dev, cin, cout, hw):
+    dt = torch.bfloat16
+    x = torch.randn(4, cin, hw, hw).to(dt)
+    w = (torch.randn(cout, cin, 1, 1) * 0.05).to(dt)
+    g = torch.randn(4, cout, hw, hw).to(dt)
+    xr, wr = x.float().requires_grad_(), w.float().requires_grad_()
+    yr = F.conv2d(xr, wr)
+    yr.backward(g.float())
+    xd = x.to(dev).contiguous(memory_format=torch.channels_last).requires_grad_()
+    wd = w.to(dev).requires_grad_()
+    hits = bw._C._pointwise_conv_hits()
+    bw.reset_kernel_launch_count()
+    y = F.conv2d(xd, wd)
+    assert bw._C._pointwise_conv_hits() == hits + 1 and bw.kernel_launch_count() == 1
+    assert y.is_contiguous(memory_format=torch.channels_last) and y.shape == yr.shape
+    y.backward(g.to(dev).contiguous(memory_format=torch.channels_last))
+    assert rel_err(y, yr) < 2e-2
+    assert rel_err(xd.grad, xr.grad) < 2e-2
+    assert rel_err(wd.grad, wr.grad) < 2e-2
+
+
+@pytest.mark.parametrize("k,stride,pad,groups", [(3, 1, 1, 1), (3, 2, 1, 1), (1, 2, 0, 1), (7, 2, 3, 1), (3, 1, 1, 4)])
+def test_general_conv(bw, dev, k, stride, pad, groups):
+    dt = torch.bfloat16
+    cin = 16 if k != 7 else 3 * groups
+    x = torch.randn(2, cin, 20, 20).to(dt)
+    w = (torch.randn(32, cin // groups, k, k) * 0.1).to(dt)
+    b = torch.randn(32).to(dt)
+    xr, wr, br = x.float().requires_grad_(), w.float().requires_grad_(), b.float().requires_grad_()
+    yr = F.conv2d(xr, wr, br, stride, pad, 1, groups)
+    yr.sum().backward()
+    xd, wd, bd = x.to(dev).requires_grad_(), w.to(dev).requires_grad_(), b.to(dev).requires_grad_()
+    y = F.conv2d(xd, wd, bd, stride, pad, 1, groups)
+    y.sum().backward()
+    assert rel_err(y, yr) < 3e-2 and rel_err(xd.grad, xr.grad) < 3e-2
+    assert rel_err(wd.grad, wr.grad) < 3e-2 and rel_err(bd.grad, br.grad) < 3e-2
+
+
+@pytest.mark.parametrize("shape", [(8, 64, 14, 14), (4, 256, 7, 7), (3, 8, 5, 5), (64, 128)])
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_batch_norm_training(bw, dev, shape, dt):
+    C = shape[1]
+    x = (torch.randn(*shape) * 2 + 0.5).to(dt)
+    w, b = torch.rand(C) + 0.5, torch.randn(C)
+    g = torch.randn(*shape).to(dt)
+    rm, rv = torch.zeros(C), torch.ones(C)
+    xr, wr, br = x.float().requires_grad_(), w.clone().requires_grad_(), b.clone().requires_grad_()
+    rm_r, rv_r = rm.clone(), rv.clone()
+    yr = F.batch_norm(xr, rm_r, rv_r, wr, br, True, 0.1, 1e-5)
+    yr.backward(g.float())
+    fmt = torch.channels_last if len(shape) == 4 else torch.contiguous_format
+    xd = x.to(dev).contiguous(memory_format=fmt).requires_grad_()
+    wd, bd = w.to(dev).requires_grad_(), b.to(dev).requires_grad_()
+    rm_d, rv_d = rm.to(dev), rv.to(dev)
+    bw.reset_kernel_launch_count()
+    y = F.batch_norm(xd, rm_d, rv_d, wd, bd, True, 0.1, 1e-5)
+    assert bw.kernel_launch_count() == 2, "batch norm forward did not run on the two hand-written passes"
+    y.backward(g.to(dev).contiguous(memory_format=fmt))
+    tol = 2e-2 if dt == torch.bfloat16 else 4e-3
+    assert rel_err(y, yr) < tol
+    assert rel_err(xd.grad, xr.grad) < tol * 2
+    assert rel_err(wd.grad, wr.grad) < tol and rel_err(bd.grad, br.grad) < tol
+    assert rel_err(rm_d, rm_r) < 1e-3 and rel_err(rv_d, rv_r) < 1e-3
+    # evaluation mode uses the running statistics
+    ye = F.batch_norm(xd.detach(), rm_d, rv_d, wd.detach(), bd.detach(), False, 0.1, 1e-5)
+    yer = F.batch_norm(x.float(), rm_r, rv_r, w, b, False, 0.1, 1e-5)
+    assert rel_err(ye, yer) < tol
+
+
+@pytest.mark.parametrize("relu,residual", [(True, False), (True, True), (False, True)])
+def test_fused_batch_norm_act(bw, dev, relu, residual):
+    from torch_musa_b200.ops import batch_norm_act
+
+    dt, shape, C = torch.bfloat16, (8, 64, 10, 10), 64
+    x = torch.randn(*shape).to(dt)
+    r = torch.randn(*shape).to(dt) if residual else None
+    w, b, g = torch.rand(C) + 0.5, torch.randn(C) * 0.3, torch.randn(*shape).to(dt)
+    xr, wr, br = x.float().requires_grad_(), w.clone().requires_grad_(), b.clone().requires_grad_()
+    rr = r.float().requires_grad_() if residual else None
+    yr = F.batch_norm(xr, None, None, wr, br, True, 0.1, 1e-5)
+    if residual:
+        yr = yr + rr
+    if relu:
+        yr = F.relu(yr)
+    yr.backward(g.float())
+    cl = torch.channels_last
+    xd = x.to(dev).contiguous(memory_format=cl).requires_grad_()
+    rd = r.to(dev).contiguous(memory_format=cl).requires_grad_() if residual else None
+    wd, bd = w.to(dev).requires_grad_(), b.to(dev).requires_grad_()
+    bw.reset_kernel_launch_count()
+    y = batch_norm_act(xd, wd, bd, None, None, rd, True, 0.1, 1e-5, relu)
+    assert bw.kernel_launch_count() == 2
+    y.backward(g.to(dev).contiguous(memory_format=cl))
+    assert rel_err(y, yr) < 2e-2 and rel_err(xd.grad, xr.grad) < 4e-2
+    assert rel_err(wd.grad, wr.grad) < 2e-2 and rel_err(bd.grad, br.grad) < 2e-2
+    if residual:
+        assert rel_err(rd.grad, rr.grad) < 2e-2
+
+
+def test_resnet18_step_matches_cpu(bw, dev):
+    """One autocast training step of a small ResNet: loss and a first-layer gradient agree with fp32 CPU."""
+    from torch_musa_b200.models import resnet, resnet18
+
+    torch.manual_seed(0)
+    ref = resnet18(num_classes=10)
+    x, t = torch.randn(8, 3, 64, 64), torch.randint(0, 10, (8,))
+    fused = resnet.FUSED_BN_ACT
+    try:
+        resnet.FUSED_BN_ACT = None
+        loss_ref = F.cross_entropy(ref(x), t)
+        loss_ref.backward()
+    finally:
+        resnet.FUSED_BN_ACT = fused
+    import copy
+
+    m = copy.deepcopy(ref)
+    m.zero_grad()
+    m = m.to(dev).to(memory_format=torch.channels_last)
+    xd = x.to(dev).contiguous(memory_format=torch.channels_last)
+    with torch.autocast("blackwell", dtype=torch.bfloat16):
+        loss = F.cross_entropy(m(xd), t.to(dev))
+    loss.backward()
+    assert abs(float(loss) - float(loss_ref)) < 0.08, (float(loss), float(loss_ref))
+    g, gr = m.fc.weight.grad, ref.fc.weight.grad
+    assert rel_err(g, gr) < 0.15

@@ -38,6 +38,10 @@ B200_EXPORT bool fused_sdp_enabled();
 B200_EXPORT void set_sdp_impl(int impl);  // 0 flash-style, 1 cuDNN-style library kernels
 B200_EXPORT int sdp_impl();
 
+// 1x1 convolutions as GEMMs over the channels-last matrix view (off: every convolution uses the library route).
+B200_EXPORT void set_pointwise_conv_gemm(bool on);
+B200_EXPORT int64_t pointwise_conv_hits();
+
 // Counter of hand-written kernel launches (reported by the benchmark as its own-kernel launch count).
 B200_EXPORT void count_launch(int n = 1);
 B200_EXPORT int64_t launch_count();

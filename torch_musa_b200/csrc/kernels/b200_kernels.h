@@ -219,6 +219,21 @@ typedef struct {
 B200_API int b200_gemm(const b200_gemm_desc_t* desc, void* d, const void* a, const void* b, cudaStream_t stream);
 /* 1 when the running driver exposes the tensor-map encoder the kernel needs */
 B200_API int b200_gemm_available(void);
+
+/* ---- batch normalisation over a [P, C] channels-last matrix (bf16 / fp16 activations, fp32 statistics) ----
+ * sums is a [2*C] fp32 workspace the call zeroes itself. stats_mode 0: batch statistics from sums (training),
+ * 1: running statistics (inference). resid / dresid / y may be NULL when the residual / ReLU variants are off. */
+B200_API int b200_bn_stats(int dtype, const void* x, float* sums, int64_t P, int C, cudaStream_t stream);
+B200_API int b200_bn_apply(int dtype, const void* x, const void* resid, void* y, const float* sums, const float* w,
+                           const float* b, float* running_mean, float* running_var, float* save_mean,
+                           float* save_invstd, int64_t P, int C, float eps, float momentum, int relu, int stats_mode,
+                           cudaStream_t stream);
+B200_API int b200_bn_bwd_reduce(int dtype, const void* dy, const void* x, const void* y, const float* mean,
+                                const float* invstd, float* sums, int64_t P, int C, int relu, cudaStream_t stream);
+B200_API int b200_bn_bwd_apply(int dtype, const void* dy, const void* x, const void* y, const float* mean,
+                               const float* invstd, const float* w, const float* sums, void* dx, void* dresid,
+                               int64_t P, int C, int relu, cudaStream_t stream);
+
 /* non-zero once any GEMM launch of this process gave up on a bounded pipeline wait (sticky; clear != 0 resets) */
 B200_API int b200_gemm_status(int clear);
 /* Tile configuration for later launches: 0 cost model (default), 1 single-CTA 128x256, 2 SM-pair 256x256 with

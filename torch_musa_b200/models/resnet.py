@@ -15,6 +15,11 @@ import torch
 import torch.nn as nn
 
 
+# Hook for a fused "batch norm (+ residual) (+ ReLU)" implementation: f(bn_module, x, residual, relu) -> Tensor.
+# None (the default, and what a stand-alone import of this file gets) keeps the plain nn.Module composition.
+FUSED_BN_ACT = None
+
+
 def _conv3x3(cin: int, cout: int, stride: int = 1, groups: int = 1, dilation: int = 1) -> nn.Conv2d:
     return nn.Conv2d(cin, cout, 3, stride=stride, padding=dilation, groups=groups, bias=False, dilation=dilation)
 
@@ -41,14 +46,21 @@ class Bottleneck(nn.Module):
         self.stride = stride
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        f = FUSED_BN_ACT
         identity = x
-        out = self.relu(self.bn1(self.conv1(x)))
-        out = self.relu(self.bn2(self.conv2(out)))
-        out = self.bn3(self.conv3(out))
+        if f is None:
+            out = self.relu(self.bn1(self.conv1(x)))
+            out = self.relu(self.bn2(self.conv2(out)))
+            out = self.bn3(self.conv3(out))
+            if self.downsample is not None:
+                identity = self.downsample(x)
+            out += identity
+            return self.relu(out)
+        out = f(self.bn1, self.conv1(x), None, True)
+        out = f(self.bn2, self.conv2(out), None, True)
         if self.downsample is not None:
-            identity = self.downsample(x)
-        out += identity
-        return self.relu(out)
+            identity = f(self.downsample[1], self.downsample[0](x), None, False)
+        return f(self.bn3, self.conv3(out), identity, True)
 
 
 class BasicBlock(nn.Module):
@@ -115,7 +127,10 @@ class ResNet(nn.Module):
         return nn.Sequential(*layers)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        x = self.maxpool(self.relu(self.bn1(self.conv1(x))))
+        if FUSED_BN_ACT is not None:
+            x = self.maxpool(FUSED_BN_ACT(self.bn1, self.conv1(x), None, True))
+        else:
+            x = self.maxpool(self.relu(self.bn1(self.conv1(x))))
         x = self.layer4(self.layer3(self.layer2(self.layer1(x))))
         x = torch.flatten(self.avgpool(x), 1)
         return self.fc(x)

@@ -10,6 +10,7 @@ torch_patches/torch_nn_functional.py.patch, torch_nn_modules_activation.py.patch
 from .functional import (  # noqa: F401
     rms_norm,
     rms_norm_residual,
+    batch_norm_act,
     rope,
     precompute_rope_cache,
     swiglu,
@@ -19,5 +20,5 @@ from .functional import (  # noqa: F401
     multi_tensor_l2norm,
     scaled_dot_product_attention,
 )
-from .modules import RMSNorm, RoPE, SwishGLU, FusedCrossEntropyLoss  # noqa: F401
+from .modules import RMSNorm, RoPE, SwishGLU, FusedCrossEntropyLoss, BatchNormAct2d  # noqa: F401
 from . import fake  # noqa: F401  (FakeTensor / meta rules for torch.compile)

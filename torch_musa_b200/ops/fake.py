@@ -74,3 +74,19 @@ def _(x, residual, weight, eps):
 def _(tensors, per_tensor=False):
     t = tensors[0]
     return t.new_empty((1,), dtype=torch.float32), t.new_empty((len(tensors) if per_tensor else 0,), dtype=torch.float32)
+
+
+@_reg("batch_norm_act")
+def _(input, weight, bias, running_mean, running_var, residual, training, momentum, eps, relu):
+    c = input.shape[1]
+    n = c if training else 0
+    return (torch.empty_like(input), input.new_empty((n,), dtype=torch.float32),
+            input.new_empty((n,), dtype=torch.float32))
+
+
+@_reg("batch_norm_act_backward")
+def _(grad_out, input, out, weight, save_mean, save_invstd, relu, has_residual):
+    c = input.shape[1]
+    return (torch.empty_like(input), input.new_empty((c,), dtype=torch.float32),
+            input.new_empty((c,), dtype=torch.float32),
+            torch.empty_like(input) if has_residual else input.new_empty((0,)))

@@ -45,6 +45,62 @@ def rms_norm_residual(x: torch.Tensor, residual: torch.Tensor, weight: torch.Ten
     return rms_norm(h, weight, eps), h
 
 
+# ------------------------------------------------------------------------- BatchNorm (+residual) (+ReLU)
+class _BatchNormAct(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, running_mean, running_var, residual, training, momentum, eps, relu):
+        y, mean, invstd = torch.ops.blackwell.batch_norm_act(x, weight, bias, running_mean, running_var, residual,
+                                                             training, momentum, eps, relu)
+        ctx.relu, ctx.has_res, ctx.training = relu, residual is not None, training
+        ctx.save_for_backward(x, y if relu else None, weight, mean, invstd)
+        ctx.mark_non_differentiable(mean, invstd)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        if not ctx.training:
+            raise RuntimeError("batch_norm_act: backward through evaluation-mode statistics is not supported; "
+                               "use torch.nn.functional.batch_norm")
+        x, y, weight, mean, invstd = ctx.saved_tensors
+        dx, dw, db, dres = torch.ops.blackwell.batch_norm_act_backward(dy, x, y, weight, mean, invstd, ctx.relu,
+                                                                       ctx.has_res)
+        return (dx, dw if weight is not None else None, db if weight is not None else None, None, None,
+                dres if ctx.has_res else None, None, None, None, None)
+
+
+def _bn_act_fast(x, weight, bias, running_mean, running_var) -> bool:
+    if not _on_device(x) or x.dtype not in (torch.bfloat16, torch.float16):
+        return False
+    if x.dim() == 4:
+        if not x.is_contiguous(memory_format=torch.channels_last):
+            return False
+    elif x.dim() != 2 or not x.is_contiguous():
+        return False
+    if x.shape[1] % 8 != 0:
+        return False
+    return all(t is None or t.dtype == torch.float32 for t in (weight, bias, running_mean, running_var))
+
+
+def batch_norm_act(x: torch.Tensor, weight: Optional[torch.Tensor], bias: Optional[torch.Tensor],
+                   running_mean: Optional[torch.Tensor], running_var: Optional[torch.Tensor],
+                   residual: Optional[torch.Tensor] = None, training: bool = True, momentum: float = 0.1,
+                   eps: float = 1e-5, relu: bool = True) -> torch.Tensor:
+    """``act(batch_norm(x) + residual)`` with ``act`` = ReLU or identity.
+
+    On the device, for bf16/fp16 channels-last activations with fp32 parameters, the whole expression is one
+    statistics pass plus one fused normalise/affine/add/ReLU pass (and the mirrored two passes backward);
+    anywhere else it is the plain composition."""
+    if _bn_act_fast(x, weight, bias, running_mean, running_var) and (residual is None or (
+            residual.dtype == x.dtype and residual.shape == x.shape and residual.stride() == x.stride())):
+        if training or (running_mean is not None and running_var is not None and not torch.is_grad_enabled()):
+            return _BatchNormAct.apply(x, weight, bias, running_mean, running_var, residual, training, momentum, eps,
+                                       relu)
+    y = F.batch_norm(x, running_mean, running_var, weight, bias, training, momentum, eps)
+    if residual is not None:
+        y = y + residual
+    return F.relu(y) if relu else y
+
+
 # ------------------------------------------------------------------------- RoPE
 def precompute_rope_cache(seq_len: int, head_dim: int, theta: float = 10000.0, device=None):
     """fp32 ``cos``/``sin`` tables of shape [seq_len, head_dim // 2]."""

@@ -53,3 +53,29 @@ class FusedCrossEntropyLoss(nn.Module):
     def forward(self, logits: torch.Tensor, target: torch.Tensor):
         return BF.fused_cross_entropy(logits, target, self.ignore_index, self.label_smoothing, self.reduction,
                                       self.inplace_backward)
+
+
+class BatchNormAct2d(nn.BatchNorm2d):
+    """``BatchNorm2d`` with the following ReLU (and an optional residual add before it) fused into the same
+    kernel passes.  Parameters, buffers and state_dict keys are those of ``nn.BatchNorm2d``."""
+
+    def __init__(self, num_features: int, eps: float = 1e-5, momentum: float = 0.1, relu: bool = True, **kw):
+        super().__init__(num_features, eps=eps, momentum=momentum, **kw)
+        self.relu = relu
+
+    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        return bn_module_act(self, x, residual, self.relu)
+
+
+def bn_module_act(bn: nn.BatchNorm2d, x: torch.Tensor, residual: Optional[torch.Tensor] = None,
+                  relu: bool = True) -> torch.Tensor:
+    """Applies an existing ``nn.BatchNorm2d`` module followed by (+ residual) (ReLU) through the fused operator."""
+    training = bn.training or (bn.running_mean is None and bn.running_var is None)
+    momentum = 0.0 if bn.momentum is None else bn.momentum
+    if bn.training and bn.track_running_stats and bn.num_batches_tracked is not None:
+        bn.num_batches_tracked.add_(1)
+        if bn.momentum is None:
+            momentum = 1.0 / float(bn.num_batches_tracked)
+    return BF.batch_norm_act(x, bn.weight, bn.bias, bn.running_mean if (not bn.training or bn.track_running_stats) else None,
+                             bn.running_var if (not bn.training or bn.track_running_stats) else None, residual, training,
+                             momentum, bn.eps, relu)
