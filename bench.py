@@ -42,6 +42,9 @@ def parse():
     p.add_argument("--micro-batch", type=int, default=1)
     p.add_argument("--parallelism", default="auto", choices=["auto", "fsdp", "single"])
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--config", default="llama_fsdp", choices=["llama_fsdp", "resnet50_ddp"],
+                   help="llama_fsdp: the headline Llama-7B FSDP2 step; resnet50_ddp: ResNet-50 DDP images/s")
+    p.add_argument("--batch", type=int, default=256, help="resnet50_ddp: images per GPU")
     p.add_argument("--trace", default=None, help="debug: also run two extra steps under torch.profiler and write "
                    "a chrome trace per rank to this path prefix (never inside the timed region)")
     return p.parse_args()
@@ -99,11 +102,166 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
+def _load_by_path(name, rel):
+    """Loads one file of the package as a stand-alone module (the stock arm must not import the backend)."""
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location(name, os.path.join(ROOT, "torch_musa_b200", rel))
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def main_resnet(args):
+    """ResNet-50 DDP training throughput: bf16 autocast over fp32 master weights, channels-last, per-GPU batch
+    256 of 3x224x224 N(0,1) images, SGD momentum 0.9 (fused multi-tensor optimizer), 25 MB gradient buckets."""
+    import torch
+    import torch.distributed as dist
+    import torch.nn.functional as F
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29511")
+    ours = args.impl == "ours"
+    if ours:
+        import torch_musa_b200 as bw
+        from torch_musa_b200.models import resnet50
+
+        devmod, devtype, backend = bw, "blackwell", "bccl"
+    else:
+        devmod, devtype, backend = torch.cuda, "cuda", "nccl"
+        resnet50 = _load_by_path("_stock_resnet", "models/resnet.py").resnet50
+    device = torch.device(devtype, local_rank)
+    devmod.set_device(local_rank)
+    use_ddp = world > 1
+    if use_ddp:
+        dist.init_process_group(backend=backend, rank=rank, world_size=world, device_id=device if not ours else None)
+
+    torch.manual_seed(1234)
+    model = resnet50(1000).to(device).to(memory_format=torch.channels_last)
+    if use_ddp:
+        if ours:
+            from torch_musa_b200.parallel.ddp import wrap_ddp
+
+            net = wrap_ddp(model, device_ids=[local_rank], bucket_cap_mb=25, gradient_as_bucket_view=True)
+        else:
+            net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank], bucket_cap_mb=25,
+                                                            gradient_as_bucket_view=True)
+    else:
+        net = model
+    if ours:
+        from torch_musa_b200.optim import FusedSGD
+
+        opt = FusedSGD(model.parameters(), lr=0.1, momentum=0.9, weight_decay=1e-4)
+    else:
+        opt = torch.optim.SGD(model.parameters(), lr=0.1, momentum=0.9, weight_decay=1e-4, fused=True)
+
+    B = args.batch
+    gen = torch.Generator().manual_seed(1000 + rank)
+    n_batches = 2
+    host_x = [torch.randn(B, 3, 224, 224, generator=gen).pin_memory() for _ in range(n_batches)]
+    host_t = [torch.randint(0, 1000, (B,), generator=gen).pin_memory() for _ in range(n_batches)]
+    dev_x = [x.to(device).contiguous(memory_format=torch.channels_last) for x in host_x]
+    dev_t = [t.to(device) for t in host_t]
+
+    def step(x, t):
+        with torch.autocast(devtype, dtype=torch.bfloat16):
+            loss = F.cross_entropy(net(x), t)
+        loss.backward()
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        return loss
+
+    def barrier():
+        if use_ddp:
+            dist.barrier()
+        devmod.synchronize()
+
+    for i in range(args.warmup):
+        step(dev_x[i % n_batches], dev_t[i % n_batches])
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    if ours:
+        bw.reset_kernel_launch_count()
+    ev0, ev1 = devmod.Event(enable_timing=True), devmod.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for i in range(args.steps):
+        loss = step(dev_x[i % n_batches], dev_t[i % n_batches])
+    ev1.record()
+    barrier()
+    ms_total = ev0.elapsed_time(ev1)
+    launches = bw.kernel_launch_count() if ours else 0
+    final_loss = float(loss.detach().float().cpu())
+
+    e2e_ms, h2d, d2h = 0.0, 0, 0
+    if not args.no_e2e:
+        barrier()
+        ev2, ev3 = devmod.Event(enable_timing=True), devmod.Event(enable_timing=True)
+        ev2.record()
+        for i in range(args.steps):
+            x = host_x[i % n_batches].to(device, non_blocking=True).contiguous(memory_format=torch.channels_last)
+            t = host_t[i % n_batches].to(device, non_blocking=True)
+            h2d += x.numel() * x.element_size() + t.numel() * t.element_size()
+            lv = step(x, t).detach().float().cpu()
+            d2h += lv.numel() * lv.element_size()
+        ev3.record()
+        barrier()
+        e2e_ms = ev2.elapsed_time(ev3)
+    clocks = sampler.stop() if rank == 0 else None
+    if args.trace:
+        from torch.profiler import ProfilerActivity, profile
+
+        with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA]) as prof:
+            for i in range(2):
+                step(dev_x[i % n_batches], dev_t[i % n_batches])
+            barrier()
+        prof.export_chrome_trace(f"{args.trace}.rank{rank}.json")
+    if use_ddp:
+        t = torch.tensor([ms_total, e2e_ms], dtype=torch.float64).to(device).float()
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total, e2e_ms = float(t[0].cpu()), float(t[1].cpu())
+    ms_per_step = ms_total / args.steps
+    imgs = B * world
+    if rank == 0:
+        out = {
+            "metric": "resnet50_ddp_train_images_per_s", "value": imgs / (ms_per_step / 1e3), "unit": "images/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic (images N(0,1), labels uniform in [0,1000) from a seed; random-init weights)",
+            "impl": args.impl,
+            "config": {"model": "resnet-50 (torchvision layout, 1000 classes)", "global_batch": imgs,
+                       "image": "3x224x224", "parallelism": f"ddp{world}, 25 MB buckets" if use_ddp else "single device",
+                       "precision": "bf16 autocast, fp32 master weights, channels-last",
+                       "optimizer": "fused multi-tensor SGD momentum 0.9",
+                       "cache": "activations per step (several GB) are far larger than the 126 MB L2"},
+            "final_loss": final_loss, "gpu_launches": launches, "clocks": clocks,
+        }
+        if not args.no_e2e:
+            out["e2e"] = {"value": imgs / (e2e_ms / args.steps / 1e3), "unit": "images/s",
+                          "h2d_bytes_per_step": h2d // args.steps, "d2h_bytes_per_step": d2h // args.steps}
+        if ours:
+            out["fallback_ops"] = len(bw.fallback_counts())
+            if os.environ.get("B200_BENCH_VERBOSE"):
+                sys.stderr.write("fallbacks: " + json.dumps(sorted(bw.fallback_counts().items(), key=lambda kv: -kv[1])) + "\n")
+        print(json.dumps(out))
+    if use_ddp:
+        dist.destroy_process_group()
+    return 0
+
+
 def main():
     args = parse()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
         return 0
+    if args.config == "resnet50_ddp":
+        return main_resnet(args)
 
     import torch
     import torch.distributed as dist

@@ -91,6 +91,12 @@ bool run_gemm(const at::Tensor& out, const at::Tensor& a, const at::Tensor& b, c
   g.alpha = alpha;
   if (g.out_dtype < 0 || out.stride(nd - 1) != 1) return false;
   DeviceSwitch sw(out.device().index());
+  at::Tensor workspace;
+  if (const size_t ws = b200_gemm_workspace_bytes(&g)) {
+    workspace = at::empty({(int64_t)(ws / sizeof(float))}, out.options().dtype(at::kFloat));
+    g.workspace = workspace.mutable_data_ptr();
+    g.workspace_bytes = ws;
+  }
   int e = b200_gemm(&g, out.mutable_data_ptr(), A.t.const_data_ptr(), B.t.const_data_ptr(), current_raw_stream(out));
   if (e == (int)cudaErrorNotSupported) return false;
   B200_KERNEL_CALL(e);

@@ -215,8 +215,13 @@ typedef struct {
   int act;
   int accumulate;
   float alpha;
+  /* optional fp32 scratch for split-K (see b200_gemm_workspace_bytes); NULL / 0: never split */
+  void* workspace;
+  size_t workspace_bytes;
 } b200_gemm_desc_t;
 B200_API int b200_gemm(const b200_gemm_desc_t* desc, void* d, const void* a, const void* b, cudaStream_t stream);
+/* Scratch a split-K run of this problem wants (few output tiles, long K); 0 when the problem is not split. */
+B200_API size_t b200_gemm_workspace_bytes(const b200_gemm_desc_t* desc);
 /* 1 when the running driver exposes the tensor-map encoder the kernel needs */
 B200_API int b200_gemm_available(void);
 

@@ -131,7 +131,14 @@ struct Params {
   float alpha;
   uint32_t idesc;
   int* status;  // device word: set to 1 when a bounded wait expired
+  // split-K: tile index = split * (tiles * batch) + tile; split s covers k-blocks [s * kb_per_split, ...) and
+  // writes its partial product at d + s * split_stride
+  int splits;
+  int kb_per_split;
+  int64_t split_stride;
 };
+
+
 
 __device__ __forceinline__ float apply_act(float v, int act) {
   switch (act) {
@@ -169,12 +176,24 @@ __device__ __forceinline__ void store_chunk(OutT* __restrict__ drow, const float
 
 }  // namespace gemmdev
 
+// What the host decided for one problem: how many K-splits and which kernel family.
+struct GemmPlan {
+  int pair;          // 1: SM-pair kernel (256-row tiles), 0: single-CTA kernel (128-row tiles)
+  int dynamic;       // pair kernel: cluster-launch-control schedule
+  int splits;        // 1 = no split-K
+  int kb_per_split;
+};
+
 // host helpers implemented in gemm_tcgen05.cu
 bool gemm_make_map(CUtensorMap* out, const void* ptr, int dtype, uint64_t inner, uint64_t outer, uint64_t batch,
                    uint64_t outer_stride_bytes, uint64_t batch_stride_bytes, uint32_t box_inner, uint32_t box_outer);
 int* gemm_status_word_device();
 int gemm_sm_count();
 // 2-CTA (cta_group::2) variant; returns cudaErrorNotSupported when it does not apply
-int gemm_launch_2cta(const b200_gemm_desc_t* g, void* d, const void* a, const void* b, cudaStream_t stream);
+int gemm_launch_2cta(const b200_gemm_desc_t* g, void* d, const void* a, const void* b, cudaStream_t stream,
+                     const GemmPlan& plan);
+GemmPlan gemm_plan(const b200_gemm_desc_t* g);
+// sums the fp32 partial products of a split-K run and applies bias / activation / accumulate / output cast
+int gemm_splitk_reduce(const b200_gemm_desc_t* g, void* d, const float* ws, int splits, cudaStream_t stream);
 
 }  // namespace b200k

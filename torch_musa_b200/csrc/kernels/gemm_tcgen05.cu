@@ -60,7 +60,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   const int lane = threadIdx.x & 31;
   const int k_blocks = (p.k + BK - 1) / BK;
   const int tiles_per_batch = p.tiles_m * p.tiles_n;
-  const int total_tiles = tiles_per_batch * p.batch;
+  const int tiles_all_batches = tiles_per_batch * p.batch;
+  const int total_tiles = tiles_all_batches * p.splits;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -92,11 +93,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        const int b = tile / tiles_per_batch;
-        const int r = tile - b * tiles_per_batch;
+        const int split = tile / tiles_all_batches;
+        const int tb = tile - split * tiles_all_batches;
+        const int b = tb / tiles_per_batch;
+        const int r = tb - b * tiles_per_batch;
+        const int kb0 = split * p.kb_per_split;
+        const int kb1 = min(k_blocks, kb0 + p.kb_per_split);
         const int m0 = (r % p.tiles_m) * BM;
         const int n0 = (r / p.tiles_m) * BN;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
           mbar_expect_tx(&full_bar[stage], kStageBytes);
           uint8_t* sa = smem_a + stage * kATileBytes;
@@ -127,10 +132,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int kb0 = (tile / tiles_all_batches) * p.kb_per_split;
+        const int kb1 = min(k_blocks, kb0 + p.kb_per_split);
         if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(smem_a + stage * kATileBytes);
@@ -141,7 +148,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             // MN-major: 16 k-rows of 128 B = 2048 B; LBO = next 64-wide MN box (8 KB), SBO = 8 k-rows.
             const uint64_t adesc = A_KMAJOR ? make_desc(sa + kk * 32, 16, 1024) : make_desc(sa + kk * 2048, 8192, 1024);
             const uint64_t bdesc = B_KMAJOR ? make_desc(sb + kk * 32, 16, 1024) : make_desc(sb + kk * 2048, 8192, 1024);
-            umma_f16(tmem_d, adesc, bdesc, p.idesc, (kb | kk) != 0 ? 1u : 0u);
+            umma_f16(tmem_d, adesc, bdesc, p.idesc, (kb > kb0 || kk != 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);  // slot reusable once these MMAs have read it
           if (++stage == kStages) { stage = 0; phase ^= 1; }
@@ -160,14 +167,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     const bool vec_ok = (p.ldd % (16 / (int)sizeof(OutT)) == 0) && ((reinterpret_cast<uintptr_t>(d) & 15) == 0) &&
                         (p.stride_d % (16 / (int)sizeof(OutT)) == 0);
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-      const int b = tile / tiles_per_batch;
-      const int r = tile - b * tiles_per_batch;
+      const int split = tile / tiles_all_batches;
+      const int tb = tile - split * tiles_all_batches;
+      const int b = tb / tiles_per_batch;
+      const int r = tb - b * tiles_per_batch;
       const int m0 = (r % p.tiles_m) * BM;
       const int n0 = (r / p.tiles_m) * BN;
       if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) break;
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
-      OutT* drow = d + (int64_t)b * p.stride_d + (int64_t)row * p.ldd + n0;
+      OutT* drow = d + (int64_t)split * p.split_stride + (int64_t)b * p.stride_d + (int64_t)row * p.ldd + n0;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -306,7 +315,8 @@ int* status_word() {
 }
 
 template <typename OutT>
-int launch(const b200_gemm_desc_t* g, void* d, const void* a, const void* b, cudaStream_t stream) {
+int launch(const b200_gemm_desc_t* g, void* d, const void* a, const void* b, cudaStream_t stream,
+           const GemmPlan& plan) {
   CUtensorMap ma, mb;
   const uint64_t esz = 2;
   const uint64_t batch = (uint64_t)std::max(g->batch, 1);
@@ -351,8 +361,11 @@ int launch(const b200_gemm_desc_t* g, void* d, const void* a, const void* b, cud
     }
   }
   p.status = dev_status;
+  p.splits = plan.splits;
+  p.kb_per_split = plan.kb_per_split;
+  p.split_stride = (int64_t)g->m * g->n;
 
-  const int total = p.tiles_m * p.tiles_n * p.batch;
+  const int total = p.tiles_m * p.tiles_n * p.batch * p.splits;
   int dev = 0, sms = kSMs;
   cudaGetDevice(&dev);
   static int cached_sms[64] = {0};
@@ -424,8 +437,7 @@ int b200_gemm_status(int clear) {
   return v;
 }
 
-int b200_gemm(const b200_gemm_desc_t* g, void* d, const void* a, const void* b, cudaStream_t stream) {
-  if (g->m <= 0 || g->n <= 0 || std::max(g->batch, 1) <= 0) return 0;
+static int gemm_validate(const b200_gemm_desc_t* g, const void* a, const void* b) {
   if (g->k <= 0) return (int)cudaErrorNotSupported;
   if (g->in_dtype != B200_BF16 && g->in_dtype != B200_F16) return (int)cudaErrorNotSupported;
   // TMA: base 16-byte aligned, byte strides multiples of 16
@@ -436,20 +448,53 @@ int b200_gemm(const b200_gemm_desc_t* g, void* d, const void* a, const void* b, 
   if (g->batch > 1 && (g->stride_a == 0 || g->stride_b == 0)) return (int)cudaErrorNotSupported;
   // the contiguous extent must cover at least one 16-byte unit
   if ((g->a_kmajor ? g->k : g->m) < 8 || (g->b_kmajor ? g->k : g->n) < 8) return (int)cudaErrorNotSupported;
-  static const bool use_2cta = [] {
-    const char* e = std::getenv("B200_GEMM_2CTA");
-    return !(e && e[0] == '0');
-  }();
-  if (use_2cta) {
-    int e2 = gemm_launch_2cta(g, d, a, b, stream);
-    if (e2 != (int)cudaErrorNotSupported) return e2;
-  }
+  if (g->out_dtype != B200_BF16 && g->out_dtype != B200_F16 && g->out_dtype != B200_F32) return (int)cudaErrorNotSupported;
+  return 0;
+}
+
+static int gemm_dispatch(const b200_gemm_desc_t* g, void* d, const void* a, const void* b, cudaStream_t stream,
+                         const GemmPlan& plan) {
+  if (plan.pair) return gemm_launch_2cta(g, d, a, b, stream, plan);
   switch (g->out_dtype) {
-    case B200_BF16: return launch<__nv_bfloat16>(g, d, a, b, stream);
-    case B200_F16: return launch<__half>(g, d, a, b, stream);
-    case B200_F32: return launch<float>(g, d, a, b, stream);
+    case B200_BF16: return launch<__nv_bfloat16>(g, d, a, b, stream, plan);
+    case B200_F16: return launch<__half>(g, d, a, b, stream, plan);
+    case B200_F32: return launch<float>(g, d, a, b, stream, plan);
     default: return (int)cudaErrorNotSupported;
   }
+}
+
+// Bytes of fp32 scratch a split-K run of this problem wants (0: the problem is not split).  A caller that
+// passes less in desc->workspace simply gets the unsplit kernel.
+size_t b200_gemm_workspace_bytes(const b200_gemm_desc_t* g) {
+  if (g->m <= 0 || g->n <= 0 || g->k <= 0) return 0;
+  const GemmPlan plan = gemm_plan(g);
+  return plan.splits > 1 ? (size_t)plan.splits * (size_t)g->m * (size_t)g->n * sizeof(float) : 0;
+}
+
+int b200_gemm(const b200_gemm_desc_t* g, void* d, const void* a, const void* b, cudaStream_t stream) {
+  if (g->m <= 0 || g->n <= 0 || std::max(g->batch, 1) <= 0) return 0;
+  int v = gemm_validate(g, a, b);
+  if (v != 0) return v;
+  GemmPlan plan = gemm_plan(g);
+  if (plan.splits > 1) {
+    const size_t need = (size_t)plan.splits * (size_t)g->m * (size_t)g->n * sizeof(float);
+    if (g->workspace && g->workspace_bytes >= need && (reinterpret_cast<uintptr_t>(g->workspace) & 15) == 0) {
+      // every split writes its fp32 partial product; one pass sums them and applies the epilogue
+      b200_gemm_desc_t part = *g;
+      part.out_dtype = B200_F32;
+      part.ldd = g->n;
+      part.stride_d = 0;
+      part.bias = nullptr;
+      part.act = 0;
+      part.accumulate = 0;
+      int e = gemm_dispatch(&part, g->workspace, a, b, stream, plan);
+      if (e != 0) return e;
+      return gemm_splitk_reduce(g, d, (const float*)g->workspace, plan.splits, stream);
+    }
+    plan.splits = 1;
+    plan.kb_per_split = (g->k + BK - 1) / BK;
+  }
+  return gemm_dispatch(g, d, a, b, stream, plan);
 }
 
 }  // extern "C"

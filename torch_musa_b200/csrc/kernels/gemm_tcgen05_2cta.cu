@@ -198,7 +198,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int n_pairs = gridDim.x >> 1;
   const int k_blocks = (p.k + BK - 1) / BK;
   const int tiles_per_batch = p.tiles_m * p.tiles_n;
-  const int total_tiles = tiles_per_batch * p.batch;
+  const int tiles_all_batches = tiles_per_batch * p.batch;
+  const int total_tiles = tiles_all_batches * p.splits;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -247,11 +248,15 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       bool more = tile < total_tiles;
       while (more && ok) {
         if (dynamic && leader) mbar_arrive(throttle_bar);  // lets the scheduler ask for the tile after this one
-        const int b = tile / tiles_per_batch;
-        const int r = tile - b * tiles_per_batch;
+        const int split = tile / tiles_all_batches;
+        const int tb = tile - split * tiles_all_batches;
+        const int b = tb / tiles_per_batch;
+        const int r = tb - b * tiles_per_batch;
+        const int kb0 = split * p.kb_per_split;
+        const int kb1 = min(k_blocks, kb0 + p.kb_per_split);
         const int m0 = (r % p.tiles_m) * BM2 + (int)rank * BMH;
         const int n0 = (r / p.tiles_m) * BN + (int)rank * C::kBHalf;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
           if (leader) mbar_expect_tx(&full_bar[stage], 2 * C::kStage);
           const uint32_t fb = full0 + (uint32_t)stage * 8u;
@@ -286,10 +291,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int tile = pair;
       bool more = tile < total_tiles;
       while (more && ok) {
+        const int kb0 = (tile / tiles_all_batches) * p.kb_per_split;
+        const int kb1 = min(k_blocks, kb0 + p.kb_per_split);
         if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(smem_a + stage * C::kATile);
@@ -298,7 +305,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           for (int kk = 0; kk < BK / 16; ++kk) {
             const uint64_t adesc = A_KMAJOR ? make_desc(sa + kk * 32, 16, 1024) : make_desc(sa + kk * 2048, 8192, 1024);
             const uint64_t bdesc = B_KMAJOR ? make_desc(sb + kk * 32, 16, 1024) : make_desc(sb + kk * 2048, 8192, 1024);
-            umma_f16_pair(tmem_d, adesc, bdesc, p.idesc, (kb | kk) != 0 ? 1u : 0u);
+            umma_f16_pair(tmem_d, adesc, bdesc, p.idesc, (kb > kb0 || kk != 0) ? 1u : 0u);
           }
           umma_commit_pair(&empty_bar[stage], 3);  // frees this slot in both CTAs
           if (++stage == C::kStages) { stage = 0; phase ^= 1; }
@@ -340,14 +347,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     int tile = pair;
     bool more = tile < total_tiles;
     while (more) {
-      const int b = tile / tiles_per_batch;
-      const int r = tile - b * tiles_per_batch;
+      const int split = tile / tiles_all_batches;
+      const int tb = tile - split * tiles_all_batches;
+      const int b = tb / tiles_per_batch;
+      const int r = tb - b * tiles_per_batch;
       const int m0 = (r % p.tiles_m) * BM2 + (int)rank * BMH;
       const int n0 = (r / p.tiles_m) * BN;
       if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) break;
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
-      OutT* drow = d + (int64_t)b * p.stride_d + (int64_t)row * p.ldd + n0;
+      OutT* drow = d + (int64_t)split * p.split_stride + (int64_t)b * p.stride_d + (int64_t)row * p.ldd + n0;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -413,7 +422,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
 // ------------------------------------------------------------------ host side
 template <typename OutT, int BN>
-int launch_pair(const b200_gemm_desc_t* g, void* d, const void* a, const void* b, cudaStream_t stream, int dynamic) {
+int launch_pair(const b200_gemm_desc_t* g, void* d, const void* a, const void* b, cudaStream_t stream,
+                const GemmPlan& plan) {
+  const int dynamic = plan.dynamic;
   using C = Cfg<BN>;
   CUtensorMap ma, mb;
   const uint64_t esz = 2;
@@ -451,8 +462,11 @@ int launch_pair(const b200_gemm_desc_t* g, void* d, const void* a, const void* b
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((g->a_kmajor ? 0u : 1u) << 15) | ((g->b_kmajor ? 0u : 1u) << 16) |
             ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM2 >> 4) << 24);
   p.status = gemm_status_word_device();
+  p.splits = plan.splits;
+  p.kb_per_split = plan.kb_per_split;
+  p.split_stride = (int64_t)g->m * g->n;
 
-  const int total = p.tiles_m * p.tiles_n * p.batch;
+  const int total = p.tiles_m * p.tiles_n * p.batch * p.splits;
   const int pairs = std::max(1, gemm_sm_count() / 2);
   // static schedule: one resident cluster per SM pair strides over the tiles; dynamic schedule: one cluster
   // per tile is requested and the clusters that run take over the tiles of those that have not started
@@ -492,18 +506,24 @@ const bool g_dynamic_default = [] {
   return !(e && e[0] == '0');
 }();
 
+std::atomic<bool> g_splitk{[] {
+  const char* e = std::getenv("B200_GEMM_SPLITK");
+  return !(e && e[0] == '0');
+}()};
+
 inline long long ceil_div_ll(long long a, long long b) { return (a + b - 1) / b; }
 
 }  // namespace
 
 int gemm_forced_config_exchange(int c) { return g_forced_config.exchange(c); }
 
-// Chooses between the single-CTA 128x256 kernel (returns cudaErrorNotSupported so the caller runs it) and the
-// SM-pair kernel with 256x256 tiles.  The model is waves x per-wave cost; per wave the pair kernel is ~15% cheaper
-// (measured 1.42-1.54 against 1.22-1.43 PFLOP/s on 4096-row bf16 problems) because each SM reads half of B.
-// 256x128 pair tiles were measured too and rejected: an N=128 instruction is no faster per column than N=256,
-// so they ran at 0.7-0.98 PFLOP/s whatever the wave count.
-int gemm_launch_2cta(const b200_gemm_desc_t* g, void* d, const void* a, const void* b, cudaStream_t stream) {
+// Chooses the kernel family and the split-K factor.
+// Family: waves x per-wave cost; per wave the pair kernel is ~15% cheaper (measured 1.42-1.54 against 1.22-1.43
+// PFLOP/s on 4096-row bf16 problems) because each SM reads half of B.  256x128 pair tiles were measured too and
+// rejected: an N=128 instruction is no faster per column than N=256, so they ran at 0.7-0.98 PFLOP/s.
+// Split-K: when the output has fewer tiles than half the machine and K is long (weight gradients of
+// convolutions and of small linear layers: K = batch x pixels), K is cut so that every SM (pair) gets a slice.
+GemmPlan gemm_plan(const b200_gemm_desc_t* g) {
   const int forced = g_forced_config.load(std::memory_order_relaxed);
   const long long batch = std::max(g->batch, 1);
   const int sms = gemm_sm_count();
@@ -519,14 +539,76 @@ int gemm_launch_2cta(const b200_gemm_desc_t* g, void* d, const void* a, const vo
       if (c2 <= c1) choice = g_dynamic_default ? 3 : 2;
     }
   }
-  if (choice != 2 && choice != 3) return (int)cudaErrorNotSupported;
-  const int dynamic = choice == 3 ? 1 : 0;
+  GemmPlan plan;
+  plan.pair = choice == 2 || choice == 3;
+  plan.dynamic = choice == 3;
+  const int k_blocks = (g->k + BK - 1) / BK;
+  plan.splits = 1;
+  plan.kb_per_split = k_blocks;
+  if (batch == 1 && g_splitk.load(std::memory_order_relaxed)) {
+    const long long tiles = ceil_div_ll(g->m, plan.pair ? 256 : 128) * ceil_div_ll(g->n, 256);
+    const long long units = plan.pair ? pairs : sms;
+    if (tiles * 2 <= units && k_blocks >= 32) {
+      long long s = std::min<long long>(units / tiles, k_blocks / 8);
+      s = std::min<long long>(s, 256);
+      if (s > 1) {
+        plan.kb_per_split = (int)ceil_div_ll(k_blocks, s);
+        plan.splits = (int)ceil_div_ll(k_blocks, plan.kb_per_split);  // no empty split
+      }
+    }
+  }
+  return plan;
+}
+
+int gemm_launch_2cta(const b200_gemm_desc_t* g, void* d, const void* a, const void* b, cudaStream_t stream,
+                     const GemmPlan& plan) {
   switch (g->out_dtype) {
-    case B200_BF16: return launch_pair<__nv_bfloat16, 256>(g, d, a, b, stream, dynamic);
-    case B200_F16: return launch_pair<__half, 256>(g, d, a, b, stream, dynamic);
-    case B200_F32: return launch_pair<float, 256>(g, d, a, b, stream, dynamic);
+    case B200_BF16: return launch_pair<__nv_bfloat16, 256>(g, d, a, b, stream, plan);
+    case B200_F16: return launch_pair<__half, 256>(g, d, a, b, stream, plan);
+    case B200_F32: return launch_pair<float, 256>(g, d, a, b, stream, plan);
     default: return (int)cudaErrorNotSupported;
   }
+}
+
+// ------------------------------------------------------------------ split-K reduction
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float* __restrict__ ws, OutT* __restrict__ d, int m, int n, int64_t ldd, int splits,
+                     const void* __restrict__ bias, int bias_f32, int act, int accumulate) {
+  const int64_t total = (int64_t)m * n;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    float v = 0.f;
+    for (int s = 0; s < splits; ++s) v += ws[(int64_t)s * total + i];
+    const int64_t r = i / n;
+    const int c = (int)(i - r * n);
+    if (bias) v += bias_f32 ? reinterpret_cast<const float*>(bias)[c] : ToF<OutT>::to(reinterpret_cast<const OutT*>(bias)[c]);
+    if (act) v = apply_act(v, act);
+    OutT* o = d + r * ldd + c;
+    if (accumulate) v += ToF<OutT>::to(*o);
+    *o = ToF<OutT>::from(v);
+  }
+}
+
+int gemm_splitk_reduce(const b200_gemm_desc_t* g, void* d, const float* ws, int splits, cudaStream_t stream) {
+  const int64_t total = (int64_t)g->m * g->n;
+  const int grid = (int)std::min<int64_t>((total + 255) / 256, (int64_t)gemm_sm_count() * 8);
+  const int bias_f32 = g->bias_dtype == B200_F32;
+  switch (g->out_dtype) {
+    case B200_BF16:
+      splitk_reduce_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(ws, (__nv_bfloat16*)d, g->m, g->n, g->ldd, splits,
+                                                                    g->bias, bias_f32, g->act, g->accumulate);
+      break;
+    case B200_F16:
+      splitk_reduce_kernel<__half><<<grid, 256, 0, stream>>>(ws, (__half*)d, g->m, g->n, g->ldd, splits, g->bias,
+                                                             bias_f32, g->act, g->accumulate);
+      break;
+    case B200_F32:
+      splitk_reduce_kernel<float><<<grid, 256, 0, stream>>>(ws, (float*)d, g->m, g->n, g->ldd, splits, g->bias,
+                                                            bias_f32, g->act, g->accumulate);
+      break;
+    default: return (int)cudaErrorNotSupported;
+  }
+  B200K_LAUNCH_RET();
 }
 
 }  // namespace b200k
