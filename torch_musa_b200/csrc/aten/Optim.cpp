@@ -52,6 +52,15 @@ const float* opt_scalar(const std::optional<at::Tensor>& t, const char* what) {
   return t->data_ptr<float>();
 }
 
+// Same element order in memory: strides agree on every dimension that has more than one element (a
+// [C_out, C_in, 1, 1] weight is the same memory in the contiguous and the channels-last format).
+bool same_layout(const at::Tensor& a, const at::Tensor& b) {
+  if (a.sizes() != b.sizes()) return false;
+  for (int64_t d = 0; d < a.dim(); ++d)
+    if (a.size(d) > 1 && a.stride(d) != b.stride(d)) return false;
+  return true;
+}
+
 bool adam_fast(at::TensorList params, at::TensorList grads, at::TensorList ea, at::TensorList es, at::TensorList mx,
                at::TensorList steps, bool amsgrad) {
   if (params.empty()) return true;
@@ -62,8 +71,7 @@ bool adam_fast(at::TensorList params, at::TensorList grads, at::TensorList ea, a
   for (const auto& s : steps)
     if (!on_device(s) || s.scalar_type() != at::kFloat || s.numel() != 1) return false;
   for (size_t i = 0; i < params.size(); ++i) {
-    if (params[i].strides() != grads[i].strides() || params[i].strides() != ea[i].strides() ||
-        params[i].strides() != es[i].strides())
+    if (!same_layout(params[i], grads[i]) || !same_layout(params[i], ea[i]) || !same_layout(params[i], es[i]))
       return false;
   }
   return true;
@@ -130,10 +138,10 @@ bool sgd_fast(at::TensorList params, at::TensorList grads, at::TensorList bufs, 
   if (momentum != 0.0) {
     if (bufs.size() != params.size() || !dense_list(bufs)) return false;
     for (size_t i = 0; i < params.size(); ++i)
-      if (bufs[i].scalar_type() != params[i].scalar_type() || bufs[i].strides() != params[i].strides()) return false;
+      if (bufs[i].scalar_type() != params[i].scalar_type() || !same_layout(bufs[i], params[i])) return false;
   }
   for (size_t i = 0; i < params.size(); ++i)
-    if (params[i].strides() != grads[i].strides()) return false;
+    if (!same_layout(params[i], grads[i])) return false;
   return true;
 }
 
