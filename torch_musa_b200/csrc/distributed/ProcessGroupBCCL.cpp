@@ -425,6 +425,30 @@ bool ProcessGroupBCCL::try_fused_reduce_scatter(at::Tensor& out, at::Tensor& in,
   return true;
 }
 
+// Equal splits only: every rank can then compute every offset without an exchange of split tables.
+bool ProcessGroupBCCL::try_fused_alltoall_equal(at::Tensor& out, at::Tensor& in, cudaStream_t s, c10::DeviceIndex dev) {
+  if (!opts_->use_fused_collectives || size_ < 2 || coalescing_ > 0) return false;
+  const int64_t bytes = in.numel() * (int64_t)in.element_size();
+  if (bytes % (16 * size_) != 0 || bytes > opts_->fused_max_bytes || bytes < 1024 || out.numel() != in.numel()) return false;
+  auto sm = symmetric_memory(dev);
+  if (!sm->ok()) return false;
+  const int64_t chunk = bytes / size_;
+  std::vector<int64_t> send_off(size_), recv_off(size_), recv_len(size_), peer_send_off(size_);
+  for (int r = 0; r < size_; ++r) {
+    send_off[r] = r * chunk;
+    recv_off[r] = r * chunk;
+    recv_len[r] = chunk;
+    peer_send_off[r] = rank_ * chunk;
+  }
+  int64_t half = 0;
+  uint32_t epoch = sm->next_epoch(&half);
+  int e = b200_comm_alltoall(sm->desc(), in.const_data_ptr(), out.mutable_data_ptr(), bytes, send_off.data(),
+                             recv_off.data(), recv_len.data(), peer_send_off.data(), epoch, half, s);
+  TORCH_CHECK(e == 0, "bccl: fused all-to-all launch failed (", cudaGetErrorString((cudaError_t)e), ")");
+  ++fused_count_;
+  return true;
+}
+
 // ------------------------------------------------------------------ collectives
 c10::intrusive_ptr<c10d::Work> ProcessGroupBCCL::broadcast(std::vector<at::Tensor>& tensors,
                                                            const c10d::BroadcastOptions& o) {
@@ -600,7 +624,10 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupBCCL::alltoall_base(at::Tensor& out, 
   for (int r = 0; r < size_; ++r) { so[r] = a; ro[r] = b; a += sc[r]; b += rc[r]; }
   TORCH_CHECK(a == in.numel() && b == out.numel(), "bccl all_to_all_single: split sizes do not add up");
   const size_t esz = in.element_size();
+  const bool equal = in_splits.empty() && out_splits.empty();
+  const c10::DeviceIndex dev = in.device().index();
   return collective(c10d::OpType::ALLTOALL_BASE, "all_to_all_single", {in}, {out}, [&, esz](ncclComm_t comm, cudaStream_t s) {
+    if (equal && try_fused_alltoall_equal(out, in, s, dev)) return;
     BCCL_NCCL_CHECK(ncclGroupStart());
     for (int r = 0; r < size_; ++r) {
       if (sc[r]) BCCL_NCCL_CHECK(ncclSend(static_cast<const char*>(in.const_data_ptr()) + so[r] * esz, (size_t)sc[r],

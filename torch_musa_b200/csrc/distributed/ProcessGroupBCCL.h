@@ -188,6 +188,7 @@ class B200_EXPORT ProcessGroupBCCL final : public c10d::Backend {
   void check_tensor(const at::Tensor& t, const char* what) const;
   bool try_fused_allreduce(at::Tensor& t, const c10d::ReduceOp& op, cudaStream_t s, c10::DeviceIndex dev);
   bool try_fused_allgather(at::Tensor& out, at::Tensor& in, cudaStream_t s, c10::DeviceIndex dev);
+  bool try_fused_alltoall_equal(at::Tensor& out, at::Tensor& in, cudaStream_t s, c10::DeviceIndex dev);
   bool try_fused_reduce_scatter(at::Tensor& out, at::Tensor& in, const c10d::ReduceOp& op, cudaStream_t s,
                                 c10::DeviceIndex dev);
 

@@ -27,7 +27,8 @@ namespace b200k {
 namespace {
 
 constexpr int kMaxWorld = 16;
-constexpr int kMaxChannels = 64;       // CTAs per collective kernel
+constexpr int kMaxChannels = 128;      // CTAs per collective kernel
+constexpr int kUnroll = 4;             // packets in flight per thread: peer loads have microseconds of latency
 constexpr int kThreads = 512;
 constexpr long long kWaitCycles = 4000000000ll;  // ~2 s
 
@@ -79,8 +80,25 @@ __device__ __forceinline__ bool cta_exchange(const Peers& P, uint32_t e, int* sh
 template <typename T>
 __device__ __forceinline__ void copy_packets(T* __restrict__ dst, const T* __restrict__ src, int64_t npk) {
   constexpr int V = Vec16<T>::N;
-  for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < npk; v += (int64_t)gridDim.x * blockDim.x)
-    st16(dst + v * V, ld16(src + v * V));
+  constexpr int U = 2 * kUnroll;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; v + (U - 1) * stride < npk; v += U * stride) {
+    Vec16<T> r[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) r[u] = ld16(src + (v + u * stride) * V);
+#pragma unroll
+    for (int u = 0; u < U; ++u) st16(dst + (v + u * stride) * V, r[u]);
+  }
+  for (; v < npk; v += stride) st16(dst + v * V, ld16(src + v * V));
+}
+
+// 8-element packet load converted to fp32 and added into acc
+template <typename TI>
+__device__ __forceinline__ void load_packet(const TI* __restrict__ p, TI (&tmp)[8]) {
+#pragma unroll
+  for (int q = 0; q < 8 * (int)sizeof(TI) / 16; ++q)
+    *reinterpret_cast<uint4*>(tmp + q * (16 / sizeof(TI))) = *reinterpret_cast<const uint4*>(p + q * (16 / sizeof(TI)));
 }
 
 template <typename TO, int V>
@@ -129,27 +147,41 @@ __global__ void __launch_bounds__(kThreads) allreduce_kernel(Peers P, const TI* 
   // 2. reduce my slice from every peer, push the result to every peer's out region
   {
     const int64_t base = r * chunk, lim = min(chunk, npk - base);
-    for (int64_t v = g0; v < lim; v += gstride) {
-      const int64_t e = (base + v) * V;
-      float acc[V];
+    for (int64_t v0 = g0; v0 < lim; v0 += kUnroll * gstride) {
+      float acc[kUnroll][V];
 #pragma unroll
-      for (int k = 0; k < V; ++k) acc[k] = 0.f;
+      for (int u = 0; u < kUnroll; ++u)
+#pragma unroll
+        for (int k = 0; k < V; ++k) acc[u][k] = 0.f;
       for (int p = 0; p < W; ++p) {
         const int src = (r + p) % W;  // stagger peers so the W ranks do not hit one GPU at once
-        const TI* pin = reinterpret_cast<const TI*>(static_cast<const char*>(P.buf[src]) + in_off) + e;
-        TI tmp[V];
+        const TI* pin = reinterpret_cast<const TI*>(static_cast<const char*>(P.buf[src]) + in_off);
+        TI tmp[kUnroll][V];
 #pragma unroll
-        for (int q = 0; q < V * (int)sizeof(TI) / 16; ++q)
-          *reinterpret_cast<uint4*>(tmp + q * (16 / sizeof(TI))) = *reinterpret_cast<const uint4*>(pin + q * (16 / sizeof(TI)));
+        for (int u = 0; u < kUnroll; ++u) {
+          const int64_t v = v0 + u * gstride;
+          if (v < lim) load_packet(pin + (base + v) * V, tmp[u]);
+        }
 #pragma unroll
-        for (int k = 0; k < V; ++k) acc[k] += ToF<TI>::to(tmp[k]);
+        for (int u = 0; u < kUnroll; ++u) {
+          if (v0 + u * gstride < lim) {
+#pragma unroll
+            for (int k = 0; k < V; ++k) acc[u][k] += ToF<TI>::to(tmp[u][k]);
+          }
+        }
       }
 #pragma unroll
-      for (int k = 0; k < V; ++k) acc[k] *= scale;
-      for (int p = 0; p < W; ++p) {
-        const int dst = (r + p) % W;
-        TO* pout = reinterpret_cast<TO*>(static_cast<char*>(P.buf[dst]) + out_off) + e;
-        store_acc<TO, V>(pout, acc);
+      for (int u = 0; u < kUnroll; ++u) {
+        const int64_t v = v0 + u * gstride;
+        if (v < lim) {
+#pragma unroll
+          for (int k = 0; k < V; ++k) acc[u][k] *= scale;
+          for (int p = 0; p < W; ++p) {
+            const int dst = (r + p) % W;
+            TO* pout = reinterpret_cast<TO*>(static_cast<char*>(P.buf[dst]) + out_off) + (base + v) * V;
+            store_acc<TO, V>(pout, acc[u]);
+          }
+        }
       }
     }
   }
@@ -213,30 +245,46 @@ __global__ void __launch_bounds__(kThreads) reduce_scatter_kernel(Peers P, const
     }
   }
   if (!cta_exchange(P, epoch, &sh_ok)) return;
-  for (int64_t v = g0; v < npk; v += gstride) {
-    const int64_t e = ((int64_t)r * npk + v) * V;
-    float acc[V];
+  for (int64_t v0 = g0; v0 < npk; v0 += kUnroll * gstride) {
+    float acc[kUnroll][V];
     {
-      TI tmp[V];
+      TI tmp[kUnroll][V];
 #pragma unroll
-      for (int q = 0; q < V * (int)sizeof(TI) / 16; ++q)
-        *reinterpret_cast<uint4*>(tmp + q * (16 / sizeof(TI))) = *reinterpret_cast<const uint4*>(in + e + q * (16 / sizeof(TI)));
+      for (int u = 0; u < kUnroll; ++u) {
+        const int64_t v = v0 + u * gstride;
+        if (v < npk) load_packet(in + ((int64_t)r * npk + v) * V, tmp[u]);
+      }
 #pragma unroll
-      for (int k = 0; k < V; ++k) acc[k] = ToF<TI>::to(tmp[k]);
+      for (int u = 0; u < kUnroll; ++u)
+#pragma unroll
+        for (int k = 0; k < V; ++k) acc[u][k] = (v0 + u * gstride < npk) ? ToF<TI>::to(tmp[u][k]) : 0.f;
     }
     for (int p = 1; p < W; ++p) {
       const int src = (r + p) % W;
-      const TI* pin = reinterpret_cast<const TI*>(static_cast<const char*>(P.buf[src]) + in_off) + e;
-      TI tmp[V];
+      const TI* pin = reinterpret_cast<const TI*>(static_cast<const char*>(P.buf[src]) + in_off);
+      TI tmp[kUnroll][V];
 #pragma unroll
-      for (int q = 0; q < V * (int)sizeof(TI) / 16; ++q)
-        *reinterpret_cast<uint4*>(tmp + q * (16 / sizeof(TI))) = *reinterpret_cast<const uint4*>(pin + q * (16 / sizeof(TI)));
+      for (int u = 0; u < kUnroll; ++u) {
+        const int64_t v = v0 + u * gstride;
+        if (v < npk) load_packet(pin + ((int64_t)r * npk + v) * V, tmp[u]);
+      }
 #pragma unroll
-      for (int k = 0; k < V; ++k) acc[k] += ToF<TI>::to(tmp[k]);
+      for (int u = 0; u < kUnroll; ++u) {
+        if (v0 + u * gstride < npk) {
+#pragma unroll
+          for (int k = 0; k < V; ++k) acc[u][k] += ToF<TI>::to(tmp[u][k]);
+        }
+      }
     }
 #pragma unroll
-    for (int k = 0; k < V; ++k) acc[k] *= scale;
-    store_acc<TO, V>(out + v * V, acc);
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t v = v0 + u * gstride;
+      if (v < npk) {
+#pragma unroll
+        for (int k = 0; k < V; ++k) acc[u][k] *= scale;
+        store_acc<TO, V>(out + v * V, acc[u]);
+      }
+    }
   }
 }
 
