@@ -2,6 +2,10 @@
 // (flight recorder, fused-path switch, test hooks) and symmetric-memory views.
 #include "distributed/ProcessGroupBCCL.h"
 #include "distributed/SymmetricMemory.h"
+#include "aten/Ops.h"
+#include "core/Backend.h"
+
+#include <ATen/Functions.h>
 
 #include <pybind11/chrono.h>
 #include <torch/csrc/utils/pybind.h>
@@ -23,7 +27,92 @@ void init_distributed_bindings(py::module& m) {
       .def("take_status", &SymmetricMemory::take_status)
       .def("local_tensor", [](SymmetricMemory& s, int64_t off, std::vector<int64_t> sizes, at::ScalarType dt) {
         return s.local_tensor(off, sizes, dt);
+      })
+      .def_property_readonly("size_bytes", [](SymmetricMemory& s) { return (int64_t)(2 * s.half_bytes()); })
+      // ---- expert-parallel token exchange (kernels/moe.cu); all on the device's current stream
+      .def("moe_count", [](SymmetricMemory& s, const at::Tensor& idx, int64_t E) {
+        TORCH_CHECK(ops::on_device(idx) && idx.scalar_type() == at::kInt && idx.is_contiguous(), "idx: int32 device tensor");
+        DeviceSwitch sw(idx.device().index());
+        at::Tensor slot = at::empty_like(idx);
+        at::Tensor counts = at::empty({E}, idx.options());
+        B200_KERNEL_CALL(b200_moe_count(idx.const_data_ptr<int>(), slot.data_ptr<int>(), counts.data_ptr<int>(),
+                                        idx.numel(), (int)E, ops::current_raw_stream(idx)));
+        return std::make_tuple(slot, counts);
+      })
+      .def("moe_dispatch", [](SymmetricMemory& s, const at::Tensor& x, const at::Tensor& idx, const at::Tensor& slot,
+                              const at::Tensor& counts, int64_t E, int64_t cap_rows, int64_t recv_off,
+                              int64_t counts_off) {
+        TORCH_CHECK(s.ok(), "symmetric memory is not usable: ", s.why_not());
+        TORCH_CHECK(ops::on_device(x) && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.is_contiguous(),
+                    "moe_dispatch: x must be a contiguous bf16 [tokens, d] device tensor");
+        TORCH_CHECK(idx.dim() == 2 && idx.size(0) == x.size(0) && idx.scalar_type() == at::kInt && idx.is_contiguous() &&
+                    slot.sizes() == idx.sizes() && counts.numel() == E, "moe_dispatch: bad index tensors");
+        const int T = (int)x.size(0), K = (int)idx.size(1), d = (int)x.size(1);
+        TORCH_CHECK(recv_off >= 0 && recv_off + cap_rows * d * 2 <= (int64_t)(2 * s.half_bytes()) &&
+                    counts_off + (int64_t)s.world() * E * 4 <= (int64_t)(2 * s.half_bytes()),
+                    "moe_dispatch: receive buffer outside the arena");
+        DeviceSwitch sw(x.device().index());
+        at::Tensor pos = at::empty_like(idx);
+        at::Tensor recv_counts = at::empty({E / s.world()}, idx.options());
+        const uint32_t epoch = s.next_epoch(nullptr);
+        B200_KERNEL_CALL(b200_moe_dispatch(s.desc(), x.const_data_ptr(), idx.const_data_ptr<int>(),
+                                           slot.const_data_ptr<int>(), counts.const_data_ptr<int>(), pos.data_ptr<int>(),
+                                           recv_counts.data_ptr<int>(), T, K, d, (int)E, cap_rows, recv_off, counts_off,
+                                           epoch, ops::current_raw_stream(x)));
+        return std::make_tuple(pos, recv_counts);
+      })
+      .def("moe_gather", [](SymmetricMemory& s, const at::Tensor& idx, const at::Tensor& pos,
+                            const std::optional<at::Tensor>& w, int64_t d, int64_t E, int64_t src_off) {
+        TORCH_CHECK(s.ok(), "symmetric memory is not usable: ", s.why_not());
+        TORCH_CHECK(idx.dim() == 2 && idx.scalar_type() == at::kInt && pos.sizes() == idx.sizes() &&
+                    pos.scalar_type() == at::kInt && idx.is_contiguous() && pos.is_contiguous(), "moe_gather: bad indices");
+        TORCH_CHECK(!w || (w->scalar_type() == at::kFloat && w->sizes() == idx.sizes() && w->is_contiguous()),
+                    "moe_gather: weights must be fp32 [tokens, k]");
+        DeviceSwitch sw(idx.device().index());
+        at::Tensor out = at::empty({idx.size(0), d}, idx.options().dtype(at::kBFloat16));
+        const uint32_t epoch = s.next_epoch(nullptr);
+        B200_KERNEL_CALL(b200_moe_gather(s.desc(), out.mutable_data_ptr(), idx.const_data_ptr<int>(),
+                                         pos.const_data_ptr<int>(), w ? w->const_data_ptr<float>() : nullptr,
+                                         (int)idx.size(0), (int)idx.size(1), (int)d, (int)E, src_off, epoch,
+                                         ops::current_raw_stream(idx)));
+        return out;
+      })
+      .def("moe_scatter", [](SymmetricMemory& s, const at::Tensor& x, const at::Tensor& idx, const at::Tensor& pos,
+                             const std::optional<at::Tensor>& w, int64_t E, int64_t dst_off) {
+        TORCH_CHECK(s.ok(), "symmetric memory is not usable: ", s.why_not());
+        TORCH_CHECK(ops::on_device(x) && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.is_contiguous(),
+                    "moe_scatter: x must be a contiguous bf16 [tokens, d] device tensor");
+        TORCH_CHECK(idx.dim() == 2 && idx.size(0) == x.size(0) && pos.sizes() == idx.sizes(), "moe_scatter: bad indices");
+        TORCH_CHECK(!w || (w->scalar_type() == at::kFloat && w->sizes() == idx.sizes() && w->is_contiguous()),
+                    "moe_scatter: weights must be fp32 [tokens, k]");
+        DeviceSwitch sw(x.device().index());
+        const uint32_t epoch = s.next_epoch(nullptr);
+        B200_KERNEL_CALL(b200_moe_scatter(s.desc(), x.const_data_ptr(), idx.const_data_ptr<int>(),
+                                          pos.const_data_ptr<int>(), w ? w->const_data_ptr<float>() : nullptr,
+                                          (int)x.size(0), (int)idx.size(1), (int)x.size(1), (int)E, dst_off, epoch,
+                                          ops::current_raw_stream(x)));
+      })
+      .def("moe_gather_dot", [](SymmetricMemory& s, const at::Tensor& grad, const at::Tensor& idx, const at::Tensor& pos,
+                                int64_t E, int64_t src_off) {
+        TORCH_CHECK(s.ok(), "symmetric memory is not usable: ", s.why_not());
+        TORCH_CHECK(ops::on_device(grad) && grad.scalar_type() == at::kBFloat16 && grad.dim() == 2 && grad.is_contiguous(),
+                    "moe_gather_dot: grad must be a contiguous bf16 [tokens, d] device tensor");
+        DeviceSwitch sw(grad.device().index());
+        at::Tensor dw = at::empty(idx.sizes(), idx.options().dtype(at::kFloat));
+        B200_KERNEL_CALL(b200_moe_gather_dot(s.desc(), grad.const_data_ptr(), idx.const_data_ptr<int>(),
+                                             pos.const_data_ptr<int>(), dw.data_ptr<float>(), (int)grad.size(0),
+                                             (int)idx.size(1), (int)grad.size(1), (int)E, src_off,
+                                             ops::current_raw_stream(grad)));
+        return dw;
       });
+
+  // A stand-alone arena of `bytes` bytes mapped across the ranks that share `store` (world 1: no mapping).
+  m.def("_create_symmetric_memory", [](c10::intrusive_ptr<c10d::Store> store, const std::string& key, int rank,
+                                       int world, int device, int64_t bytes) {
+    lazy_init();
+    return std::make_shared<SymmetricMemory>(std::move(store), key, rank, world, (c10::DeviceIndex)device,
+                                             (size_t)((bytes + 1) / 2 + 255) / 256 * 256);
+  });
 
   m.def("_create_process_group", [](c10::intrusive_ptr<c10d::Store> store, int rank, int size,
                                     std::chrono::milliseconds timeout, py::object pg_options) {

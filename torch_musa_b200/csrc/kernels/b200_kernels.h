@@ -281,6 +281,22 @@ B200_API int b200_comm_alltoall(const b200_symm_t* s, const void* in, void* out,
                                 const int64_t* send_off, const int64_t* recv_off, const int64_t* recv_len,
                                 const int64_t* peer_send_off, uint32_t epoch, int64_t in_off, cudaStream_t stream);
 
+/* ---------------------------------------------------------------- expert-parallel MoE token exchange (bf16 rows)
+ * E experts, E / world per rank in rank order; idx / slot / pos are int32 [T*K]; receive buffers hold cap_rows
+ * rows of d elements at a byte offset of every rank's arena; counts_off points at world*E int32 of scratch in the
+ * arena. Epochs as for the collectives (each call consumes two). */
+B200_API int b200_moe_count(const int* idx, int* slot, int* counts, int64_t n_pairs, int E, cudaStream_t stream);
+B200_API int b200_moe_dispatch(const b200_symm_t* s, const void* x, const int* idx, const int* slot,
+                               const int* counts_local, int* pos, int* recv_counts, int T, int K, int d, int E,
+                               int64_t cap_rows, int64_t recv_off, int64_t counts_off, uint32_t epoch,
+                               cudaStream_t stream);
+B200_API int b200_moe_gather(const b200_symm_t* s, void* out, const int* idx, const int* pos, const float* w, int T,
+                             int K, int d, int E, int64_t src_off, uint32_t epoch, cudaStream_t stream);
+B200_API int b200_moe_scatter(const b200_symm_t* s, const void* x, const int* idx, const int* pos, const float* w,
+                              int T, int K, int d, int E, int64_t dst_off, uint32_t epoch, cudaStream_t stream);
+B200_API int b200_moe_gather_dot(const b200_symm_t* s, const void* grad, const int* idx, const int* pos, float* dw,
+                                 int T, int K, int d, int E, int64_t src_off, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
