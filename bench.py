@@ -42,7 +42,7 @@ def parse():
     p.add_argument("--micro-batch", type=int, default=1)
     p.add_argument("--parallelism", default="auto", choices=["auto", "fsdp", "single"])
     p.add_argument("--no-e2e", action="store_true")
-    p.add_argument("--config", default="llama_fsdp", choices=["llama_fsdp", "resnet50_ddp"],
+    p.add_argument("--config", default="llama_fsdp", choices=["llama_fsdp", "resnet50_ddp", "moe_ep"],
                    help="llama_fsdp: the headline Llama-7B FSDP2 step; resnet50_ddp: ResNet-50 DDP images/s")
     p.add_argument("--batch", type=int, default=256, help="resnet50_ddp: images per GPU")
     p.add_argument("--trace", default=None, help="debug: also run two extra steps under torch.profiler and write "
@@ -255,6 +255,172 @@ def main_resnet(args):
     return 0
 
 
+def _stock_package():
+    """Loads the model files under a throw-away package name so that the stock arm never imports the backend."""
+    import types
+
+    for name in ("_stock_pkg", "_stock_pkg.ops", "_stock_pkg.models", "_stock_pkg.parallel"):
+        if name not in sys.modules:
+            m = types.ModuleType(name)
+            m.__path__ = []
+            sys.modules[name] = m
+    sys.modules["_stock_pkg.ops"].functional = _load_by_path("_stock_pkg.ops.functional", "ops/functional.py")
+    llama = _load_by_path("_stock_pkg.models.llama", "models/llama.py")
+    moe = _load_by_path("_stock_pkg.models.moe", "models/moe.py")
+    pmoe = _load_by_path("_stock_pkg.parallel.moe", "parallel/moe.py")
+    return llama, moe, pmoe
+
+
+def main_moe(args):
+    """Mixtral-style MoE decoder, expert parallel over all ranks: 8 layers, d 4096, 8 SwiGLU experts of 14336,
+    top-2 router, 8192 tokens per GPU, bf16 parameters and activations, fused AdamW; forward + backward + step."""
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29511")
+    ours = args.impl == "ours"
+    if ours:
+        import torch_musa_b200 as bw
+        from torch_musa_b200.models import MoEConfig, MoETransformer
+        from torch_musa_b200.parallel import moe as pmoe
+
+        devmod, devtype, backend = bw, "blackwell", "bccl"
+    else:
+        devmod, devtype, backend = torch.cuda, "cuda", "nccl"
+        _, moe_mod, pmoe = _stock_package()
+        MoEConfig, MoETransformer = moe_mod.MoEConfig, moe_mod.MoETransformer
+    device = torch.device(devtype, local_rank)
+    devmod.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group(backend=backend, rank=rank, world_size=world, device_id=device if not ours else None)
+
+    B, S = 2, 4096
+    cfg = MoEConfig(n_layers=args.layers if args.layers != 32 else 8, max_seq_len=S)
+    torch.manual_seed(1234)
+    with torch.device(device):
+        model = MoETransformer(cfg, ep_world=world).to(torch.bfloat16)
+    with torch.no_grad():
+        for p in model.parameters():
+            if p.dim() >= 2:
+                p.normal_(0.0, 0.02)
+    if ours:
+        exchange = pmoe.make_expert_exchange(cfg.n_experts, cfg.dim, B * S, cfg.top_k, slots=cfg.n_layers, device=device,
+                                             capacity_factor=cfg.capacity_factor)
+    else:
+        exchange = pmoe.ReferenceExpertExchange(cfg.n_experts)
+    model.set_exchange(exchange)
+    replicated = model.replicated_parameters()
+    experts = model.expert_parameters()
+    opt = torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1, fused=True)
+
+    gen = torch.Generator().manual_seed(1000 + rank)
+    n_batches = 4
+    host_tokens = [torch.randint(0, cfg.vocab_size, (B, S + 1), generator=gen).pin_memory() for _ in range(n_batches)]
+    dev_tokens = [t.to(device) for t in host_tokens]
+
+    def sync_grads():
+        if world == 1:
+            return
+        grads = [p.grad for p in replicated if p.grad is not None]
+        flat = torch.cat([g.reshape(-1) for g in grads])
+        dist.all_reduce(flat, op=dist.ReduceOp.AVG)
+        off = 0
+        for g in grads:
+            g.copy_(flat[off:off + g.numel()].view_as(g))
+            off += g.numel()
+        torch._foreach_mul_([p.grad for p in experts if p.grad is not None], 1.0 / world)
+
+    def step(tok):
+        loss = model(tok[:, :-1], tok[:, 1:])
+        loss.backward()
+        sync_grads()
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        return loss
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        devmod.synchronize()
+
+    for i in range(args.warmup):
+        step(dev_tokens[i % n_batches])
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    if ours:
+        bw.reset_kernel_launch_count()
+    ev0, ev1 = devmod.Event(enable_timing=True), devmod.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for i in range(args.steps):
+        loss = step(dev_tokens[i % n_batches])
+    ev1.record()
+    barrier()
+    ms_total = ev0.elapsed_time(ev1)
+    launches = bw.kernel_launch_count() if ours else 0
+    final_loss = float(loss.detach().float().cpu())
+    e2e_ms, h2d, d2h = 0.0, 0, 0
+    if not args.no_e2e:
+        barrier()
+        ev2, ev3 = devmod.Event(enable_timing=True), devmod.Event(enable_timing=True)
+        ev2.record()
+        for i in range(args.steps):
+            tok = host_tokens[i % n_batches].to(device, non_blocking=True)
+            h2d += tok.numel() * tok.element_size()
+            lv = step(tok).detach().float().cpu()
+            d2h += lv.numel() * lv.element_size()
+        ev3.record()
+        barrier()
+        e2e_ms = ev2.elapsed_time(ev3)
+    clocks = sampler.stop() if rank == 0 else None
+    if args.trace:
+        from torch.profiler import ProfilerActivity, profile
+
+        with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA]) as prof:
+            for i in range(2):
+                step(dev_tokens[i % n_batches])
+            barrier()
+        prof.export_chrome_trace(f"{args.trace}.rank{rank}.json")
+    if ours:
+        exchange.check()
+    if world > 1:
+        t = torch.tensor([ms_total, e2e_ms], dtype=torch.float64).to(device).float()
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total, e2e_ms = float(t[0].cpu()), float(t[1].cpu())
+    ms_per_step = ms_total / args.steps
+    toks = B * S * world
+    if rank == 0:
+        out = {
+            "metric": "moe_ep_train_tokens_per_s", "value": toks / (ms_per_step / 1e3), "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic (token ids uniform in [0,32000) from a seed; random-init weights)", "impl": args.impl,
+            "config": {"model": f"mixtral-style moe ({cfg.n_layers}L d4096 h32/kv8, 8 experts x ffn14336, top-2)",
+                       "global_batch": B * world, "seq_len": S, "tokens_per_gpu": B * S,
+                       "parallelism": f"ep{world} ({cfg.n_experts // world} expert(s) per GPU), replicated attention/router",
+                       "expert_gemm": "bf16", "optimizer": "fused AdamW lr 3e-4 on bf16 parameters",
+                       "cache": "weights and activations per step are far larger than the 126 MB L2"},
+            "final_loss": final_loss, "gpu_launches": launches, "clocks": clocks,
+        }
+        if not args.no_e2e:
+            out["e2e"] = {"value": toks / (e2e_ms / args.steps / 1e3), "unit": "tokens/s",
+                          "h2d_bytes_per_step": h2d // args.steps, "d2h_bytes_per_step": d2h // args.steps}
+        if ours:
+            out["fallback_ops"] = len(bw.fallback_counts())
+            if os.environ.get("B200_BENCH_VERBOSE"):
+                sys.stderr.write("fallbacks: " + json.dumps(sorted(bw.fallback_counts().items(), key=lambda kv: -kv[1])) + "\n")
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
 def main():
     args = parse()
     if args.impl == "reference":
@@ -262,6 +428,8 @@ def main():
         return 0
     if args.config == "resnet50_ddp":
         return main_resnet(args)
+    if args.config == "moe_ep":
+        return main_moe(args)
 
     import torch
     import torch.distributed as dist

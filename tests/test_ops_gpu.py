@@ -329,3 +329,19 @@ def test_chunk_cat(bw, dev, world):
     out32 = torch.full(ref.shape, 7.0, device=dev)
     torch._chunk_cat(dg, dim=0, num_chunks=world, out=out32)
     assert torch.equal(out32.cpu(), ref)
+
+
+def test_mixed_device_arguments_raise(bw, dev):
+    """A host tensor among the arguments of a hand-written operator is rejected on the host, before any launch."""
+    from torch_musa_b200 import ops as BO
+
+    x = torch.randn(1, 4, 2, 8, device=dev, dtype=torch.bfloat16)
+    cos, sin = BO.precompute_rope_cache(4, 8)          # host tables
+    with pytest.raises(RuntimeError, match="same device"):
+        torch.ops.blackwell.rope(x, cos, sin)
+    h = torch.randn(4, 16, device=dev, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="same device"):
+        F.rms_norm(h, (16,), torch.ones(16, dtype=torch.bfloat16))
+    with pytest.raises(RuntimeError, match="same device"):
+        torch.ops.blackwell.cross_entropy_fwd(h.float(), torch.zeros(4, dtype=torch.long))
+    bw.synchronize()

@@ -62,6 +62,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> bn_forward(const at::Tensor& x, c
   at::Tensor save_mean, save_invstd, sums;
   const void* rp = nullptr;
   if (defined(resid)) {
+    check_devices("batch_norm_act", x, *resid);
     TORCH_CHECK(resid->sizes() == x.sizes() && resid->strides() == x.strides() && resid->scalar_type() == x.scalar_type(),
                 "batch_norm_act: the residual must have the layout and dtype of the input");
     rp = resid->const_data_ptr();
@@ -94,6 +95,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> bn_backward(const at:
   const Mat m = as_matrix(x);
   auto stream = current_raw_stream(x);
   const int dt = kdtype(x.scalar_type());
+  check_devices("batch_norm_backward", x, dy_in, y, w, mean, invstd);
   at::Tensor dy = dy_in;
   if (dy.scalar_type() != x.scalar_type()) dy = dy.to(x.scalar_type());
   if (dy.strides() != x.strides()) {

@@ -28,6 +28,7 @@ inline void check_fast(const at::Tensor& t, const char* what) {
 at::Tensor rope(const at::Tensor& x, const at::Tensor& cos, const at::Tensor& sin,
                 const std::optional<at::Tensor>& positions, bool interleaved, bool conj) {
   check_fast(x, "rope");
+  check_devices("rope", x, cos, sin, positions);
   TORCH_CHECK(x.dim() == 4, "rope: x must be [batch, seq, heads, head_dim], got ", x.sizes());
   const int64_t B = x.size(0), S = x.size(1), H = x.size(2), D = x.size(3);
   TORCH_CHECK(cos.scalar_type() == at::kFloat && sin.scalar_type() == at::kFloat && cos.is_contiguous() &&
@@ -69,6 +70,7 @@ at::Tensor swiglu(const at::Tensor& x) {
 
 at::Tensor swiglu_backward(const at::Tensor& dy, const at::Tensor& x) {
   check_fast(x, "swiglu_backward");
+  check_devices("swiglu_backward", x, dy);
   at::Tensor xc = x.contiguous(), dyc = dy.contiguous();
   const int64_t h = x.size(-1) / 2, rows = h ? x.numel() / (2 * h) : 0;
   at::Tensor dx = at::empty_like(xc);
@@ -80,6 +82,7 @@ at::Tensor swiglu_backward(const at::Tensor& dy, const at::Tensor& x) {
 
 at::Tensor silu_mul(const at::Tensor& gate, const at::Tensor& up) {
   check_fast(gate, "silu_mul");
+  check_devices("silu_mul", gate, up);
   TORCH_CHECK(gate.sizes() == up.sizes() && gate.scalar_type() == up.scalar_type(), "silu_mul: shape/dtype mismatch");
   at::Tensor g = gate.contiguous(), u = up.contiguous();
   at::Tensor out = at::empty_like(g);
@@ -91,6 +94,7 @@ at::Tensor silu_mul(const at::Tensor& gate, const at::Tensor& up) {
 
 std::tuple<at::Tensor, at::Tensor> silu_mul_backward(const at::Tensor& dy, const at::Tensor& gate, const at::Tensor& up) {
   check_fast(gate, "silu_mul_backward");
+  check_devices("silu_mul_backward", gate, dy, up);
   at::Tensor g = gate.contiguous(), u = up.contiguous(), d = dy.contiguous();
   at::Tensor dg = at::empty_like(g), du = at::empty_like(u);
   DeviceSwitch sw(g.device().index());
@@ -103,6 +107,7 @@ std::tuple<at::Tensor, at::Tensor> silu_mul_backward(const at::Tensor& dy, const
 std::tuple<at::Tensor, at::Tensor> cross_entropy_fwd(const at::Tensor& logits, const at::Tensor& target,
                                                      int64_t ignore_index, double label_smoothing) {
   check_fast(logits, "cross_entropy_fwd");
+  check_devices("cross_entropy_fwd", logits, target);
   TORCH_CHECK(logits.dim() == 2 && target.dim() == 1 && target.size(0) == logits.size(0) &&
                   target.scalar_type() == at::kLong && on_device(target),
               "cross_entropy_fwd: expected logits [T, V] and int64 target [T] on the device");
@@ -121,6 +126,7 @@ at::Tensor cross_entropy_bwd_impl(const at::Tensor& logits, const at::Tensor& ls
                                   const std::optional<at::Tensor>& grad_loss, double scale, int64_t ignore_index,
                                   double label_smoothing, bool inplace) {
   check_fast(logits, "cross_entropy_bwd");
+  check_devices("cross_entropy_bwd", logits, lse, target, grad_loss);
   TORCH_CHECK(!inplace || logits.is_contiguous(), "cross_entropy_bwd_: logits must be contiguous");
   at::Tensor x = logits.contiguous(), t = target.contiguous();
   const int64_t rows = x.size(0), cols = x.size(1);
@@ -155,6 +161,7 @@ at::Tensor& cross_entropy_bwd_(at::Tensor& logits, const at::Tensor& lse, const 
 
 at::Tensor online_softmax_stats(const at::Tensor& logits, const at::Tensor& target, int64_t vocab_start) {
   check_fast(logits, "online_softmax_stats");
+  check_devices("online_softmax_stats", logits, target);
   at::Tensor x = logits.contiguous(), t = target.contiguous();
   at::Tensor stats = at::empty({x.size(0), 3}, x.options().dtype(at::kFloat));
   DeviceSwitch sw(x.device().index());
@@ -167,6 +174,7 @@ at::Tensor online_softmax_stats(const at::Tensor& logits, const at::Tensor& targ
 at::Tensor vocab_parallel_ce_finish(at::Tensor& logits, const at::Tensor& all_stats, const at::Tensor& target,
                                     int64_t vocab_start, int64_t ignore_index) {
   check_fast(logits, "vocab_parallel_ce_finish");
+  check_devices("vocab_parallel_ce_finish", logits, all_stats, target);
   TORCH_CHECK(logits.is_contiguous() && all_stats.is_contiguous() && all_stats.scalar_type() == at::kFloat &&
                   all_stats.dim() == 3 && all_stats.size(1) == logits.size(0) && all_stats.size(2) == 3,
               "vocab_parallel_ce_finish: all_stats must be contiguous float32 [world, T, 3]");
@@ -183,6 +191,7 @@ at::Tensor vocab_parallel_ce_finish(at::Tensor& logits, const at::Tensor& all_st
 std::tuple<at::Tensor, at::Tensor, at::Tensor> rms_norm_residual(const at::Tensor& x, const at::Tensor& residual,
                                                                  const at::Tensor& weight, double eps) {
   check_fast(x, "rms_norm_residual");
+  check_devices("rms_norm_residual", x, residual, weight);
   TORCH_CHECK(x.sizes() == residual.sizes() && x.scalar_type() == residual.scalar_type() &&
                   weight.scalar_type() == x.scalar_type(),
               "rms_norm_residual: shape/dtype mismatch");

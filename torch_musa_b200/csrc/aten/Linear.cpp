@@ -59,6 +59,7 @@ bool gemm_eligible(const at::Tensor& a, const at::Tensor& b) {
   if (dt != b.scalar_type()) return false;
   if (dt != at::kBFloat16 && dt != at::kHalf) return false;
   if (a.is_conj() || b.is_conj() || a.is_neg() || b.is_neg()) return false;
+  if (!on_device(a) || !on_device(b) || a.device() != b.device()) return false;  // the generic route reports the mismatch
   return true;
 }
 
@@ -84,6 +85,8 @@ bool run_gemm(const at::Tensor& out, const at::Tensor& a, const at::Tensor& b, c
   g.stride_a = A.bstride;
   g.stride_b = B.bstride;
   g.stride_d = nd == 3 ? out.stride(0) : 0;
+  if (bias) check_devices("addmm", out, *bias);
+  check_devices("mm", out, a, b);
   g.bias = bias ? bias->const_data_ptr() : nullptr;
   g.bias_dtype = bias ? kdtype(bias->scalar_type()) : 0;
   g.act = act;

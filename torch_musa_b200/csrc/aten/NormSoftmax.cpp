@@ -28,6 +28,7 @@ int64_t prod(at::IntArrayRef v) {
 // --------------------------------------------------------------------- RMSNorm
 std::tuple<at::Tensor, at::Tensor> fused_rms_norm(const at::Tensor& input, at::IntArrayRef normalized_shape,
                                                   const std::optional<at::Tensor>& weight, std::optional<double> eps) {
+  check_devices("rms_norm", input, weight);
   const int64_t cols = prod(normalized_shape);
   const bool w_ok = !weight.has_value() || !weight->defined() ||
                     (weight->scalar_type() == input.scalar_type() && weight->is_contiguous());
@@ -56,6 +57,7 @@ std::tuple<at::Tensor, at::Tensor> fused_rms_norm_backward(const at::Tensor& gra
                                                            at::IntArrayRef normalized_shape, const at::Tensor& rstd,
                                                            const std::optional<at::Tensor>& weight,
                                                            std::array<bool, 2> mask) {
+  check_devices("rms_norm_backward", input, grad_out, rstd, weight);
   const int64_t cols = prod(normalized_shape);
   const bool has_w = weight.has_value() && weight->defined();
   const bool w_ok = !has_w || (weight->scalar_type() == input.scalar_type() && weight->is_contiguous());
@@ -95,6 +97,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> native_layer_norm(const at::Tenso
                                                                  c10::SymIntArrayRef normalized_shape_,
                                                                  const std::optional<at::Tensor>& weight,
                                                                  const std::optional<at::Tensor>& bias, double eps) {
+  check_devices("layer_norm", input, weight, bias);
   auto normalized_shape = C10_AS_INTARRAYREF_SLOW(normalized_shape_);
   const int64_t cols = prod(normalized_shape);
   const bool has_w = weight.has_value() && weight->defined(), has_b = bias.has_value() && bias->defined();
@@ -125,6 +128,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> native_layer_norm_backward(
     const at::Tensor& rstd, const std::optional<at::Tensor>& weight, const std::optional<at::Tensor>& bias,
     std::array<bool, 3> mask) {
   auto normalized_shape = C10_AS_INTARRAYREF_SLOW(normalized_shape_);
+  check_devices("layer_norm_backward", input, grad_out, mean, rstd, weight, bias);
   const int64_t cols = prod(normalized_shape);
   const bool has_w = weight.has_value() && weight->defined();
   const bool ok = (!has_w || (weight->scalar_type() == input.scalar_type() && weight->is_contiguous())) &&
@@ -189,6 +193,7 @@ at::Tensor _log_softmax(const at::Tensor& self, int64_t dim, bool h2f) { return 
 
 at::Tensor softmax_bwd_common(const at::Tensor& grad, const at::Tensor& out, int64_t dim, at::ScalarType in_dtype,
                               bool log) {
+  check_devices("softmax_backward", out, grad);
   const int64_t d = at::maybe_wrap_dim(dim, out.dim());
   if (fast(out) && grad.scalar_type() == out.scalar_type() && in_dtype == out.scalar_type() && out.dim() > 0 &&
       d == out.dim() - 1 && out.numel() > 0) {
@@ -288,6 +293,7 @@ std::tuple<at::Tensor, at::Tensor> native_dropout(const at::Tensor& input, doubl
 }
 
 at::Tensor native_dropout_backward(const at::Tensor& grad, const at::Tensor& mask, double scale) {
+  check_devices("native_dropout_backward", grad, mask);
   if (fast(grad) && grad.is_non_overlapping_and_dense() && mask.scalar_type() == at::kBool &&
       mask.sizes() == grad.sizes() && mask.strides() == grad.strides() && grad.numel() > 0) {
     at::Tensor dx = at::empty_strided(grad.sizes(), grad.strides(), grad.options());

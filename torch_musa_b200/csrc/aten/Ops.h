@@ -12,6 +12,20 @@ namespace ops {
 
 inline bool on_device(const at::Tensor& t) { return t.defined() && t.device().type() == kDeviceType; }
 
+// Every tensor argument whose pointer goes to a kernel must live on the device of the first one: a host pointer
+// dereferenced on the GPU is a memory fault, not an exception.  Undefined / absent tensors are skipped.
+inline void check_one_device(const char* op, const at::Tensor& ref, const at::Tensor& t) {
+  TORCH_CHECK(!t.defined() || t.device() == ref.device(), "Expected all tensors to be on the same device, but found at "
+              "least two devices, ", ref.device(), " and ", t.device(), "! (when checking arguments of ", op, ")");
+}
+inline void check_one_device(const char* op, const at::Tensor& ref, const std::optional<at::Tensor>& t) {
+  if (t.has_value()) check_one_device(op, ref, *t);
+}
+template <class... Ts>
+inline void check_devices(const char* op, const at::Tensor& ref, const Ts&... ts) {
+  (check_one_device(op, ref, ts), ...);
+}
+
 // dtype code shared with the kernel library, or -1 if the kernels do not cover the type
 inline int kdtype(at::ScalarType t) {
   switch (t) {

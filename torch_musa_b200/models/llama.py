@@ -164,6 +164,8 @@ class Llama(nn.Module):
 
     def forward(self, tokens: torch.Tensor, targets: Optional[torch.Tensor] = None, positions=None):
         B, S = tokens.shape
+        if self.rope_cos.device != tokens.device and self.rope_cos.device.type != "meta":
+            self.rope_cos, self.rope_sin = self.rope_cos.to(tokens.device), self.rope_sin.to(tokens.device)
         cos, sin = self.rope_cos, self.rope_sin
         if cos.dtype != torch.float32:  # a module-wide .to(bf16) must not degrade the tables
             cos, sin = cos.float(), sin.float()

@@ -134,6 +134,8 @@ class MoETransformer(nn.Module):
 
     def forward(self, tokens: torch.Tensor, targets: Optional[torch.Tensor] = None):
         B, S = tokens.shape
+        if self.rope_cos.device != tokens.device:   # buffers created on the host follow the tokens
+            self.rope_cos, self.rope_sin = self.rope_cos.to(tokens.device), self.rope_sin.to(tokens.device)
         self._rope.cos, self._rope.sin = self.rope_cos.float(), self.rope_sin.float()
         x = self.tok_emb(tokens)
         for layer in self.layers:
