@@ -4,6 +4,8 @@ vocabulary-parallel cross entropy, and failure detection driven from the host.""
 import pytest
 import torch
 
+import torch.distributed as dist
+
 from _dist_utils import run_ranks
 
 
@@ -87,3 +89,89 @@ def _failing_rank_body(rank, world):
 
 def test_missing_rank_is_detected_gloo():
     run_ranks(_failing_rank_body, 2, "gloo", timeout=120)
+
+
+def _tp_llama_body(rank, world):
+    from torch_musa_b200.models.llama import llama_tiny_config
+    from torch_musa_b200.models.llama_tp import TPLlama
+    cfg = llama_tiny_config(n_kv_heads=2)
+    torch.manual_seed(0)
+    full = TPLlama(cfg, 1)
+    torch.manual_seed(1)
+    tok = torch.randint(0, cfg.vocab_size, (2, 33))
+    loss_ref = full(tok[:, :-1], tok[:, 1:]); loss_ref.backward()
+    tp = TPLlama(cfg, world)
+    hd, h, kv = cfg.head_dim, cfg.n_heads, cfg.kv_heads
+    def rows(w, n_units, unit):  # take this rank's block of n_units/world units of `unit` rows
+        per = n_units // world
+        return w[rank * per * unit:(rank + 1) * per * unit]
+    with torch.no_grad():
+        tp.tok_emb.weight.copy_(full.tok_emb.weight); tp.norm.weight.copy_(full.norm.weight)
+        tp.lm_head.weight.copy_(rows(full.lm_head.weight, cfg.vocab_size, 1))
+        for a, b in zip(tp.layers, full.layers):
+            a.attn_norm.weight.copy_(b.attn_norm.weight); a.ffn_norm.weight.copy_(b.ffn_norm.weight)
+            W = b.attn.wqkv.weight
+            q, k, v = W[:h * hd], W[h * hd:(h + kv) * hd], W[(h + kv) * hd:]
+            a.attn.wqkv.weight.copy_(torch.cat([rows(q, h, hd), rows(k, kv, hd), rows(v, kv, hd)]))
+            per = h * hd // world
+            a.attn.wo.weight.copy_(b.attn.wo.weight[:, rank * per:(rank + 1) * per])
+            W13 = b.ffn.w13.weight; f = cfg.ffn_dim; pf = f // world
+            a.ffn.w13.weight.copy_(torch.cat([W13[rank * pf:(rank + 1) * pf], W13[f + rank * pf:f + (rank + 1) * pf]]))
+            a.ffn.w2.weight.copy_(b.ffn.w2.weight[:, rank * pf:(rank + 1) * pf])
+    loss = tp(tok[:, :-1], tok[:, 1:]); loss.backward()
+    for p in tp.replicated_parameters():
+        dist.all_reduce(p.grad)
+    assert abs(float(loss) - float(loss_ref)) < 1e-4, (float(loss), float(loss_ref))
+    assert torch.allclose(tp.tok_emb.weight.grad, full.tok_emb.weight.grad, atol=1e-5)
+    per = h * hd // world
+    if cfg.n_layers > 0: assert torch.allclose(tp.layers[0].attn.wo.weight.grad, full.layers[0].attn.wo.weight.grad[:, rank * per:(rank + 1) * per], atol=1e-5)
+    if cfg.n_layers > 1: assert torch.allclose(tp.layers[1].attn_norm.weight.grad, full.layers[1].attn_norm.weight.grad, atol=1e-5)
+
+
+
+def test_tensor_parallel_llama_matches_single_process():
+    """TP=2 Llama (column/row-parallel layers, sequence-parallel norms, vocabulary-parallel loss) over gloo:
+    loss and gradients equal the unsharded model's."""
+    run_ranks(_tp_llama_body, 2, "gloo")
+
+
+def _moe_ep_body(rank, world):
+    from torch_musa_b200.models import MoETransformer, moe_tiny_config
+    from torch_musa_b200.parallel.moe import ReferenceExpertExchange
+
+    cfg = moe_tiny_config()
+    torch.manual_seed(0)
+    full = MoETransformer(cfg, 1)
+    full.set_exchange(ReferenceExpertExchange.__new__(ReferenceExpertExchange))
+    solo = full.layers[0].moe._exchange[0]
+    solo.E, solo.group, solo.rank, solo.world, solo.E_local = cfg.n_experts, None, 0, 1, cfg.n_experts
+    ep = MoETransformer(cfg, world)
+    ep.set_exchange(ReferenceExpertExchange(cfg.n_experts))
+    n_local = cfg.n_experts // world
+    with torch.no_grad():
+        sd = {k: v for k, v in full.state_dict().items() if "experts" not in k}
+        ep.load_state_dict(sd, strict=False)
+        for a, b in zip(ep.layers, full.layers):
+            a.moe.experts.w13.copy_(b.moe.experts.w13[rank * n_local:(rank + 1) * n_local])
+            a.moe.experts.w2.copy_(b.moe.experts.w2[rank * n_local:(rank + 1) * n_local])
+    torch.manual_seed(7)
+    toks = torch.randint(0, cfg.vocab_size, (world, 2, 17))
+    # the unsharded model sees every rank's tokens; each EP rank its own
+    loss_ref = sum(full(toks[r][:, :-1], toks[r][:, 1:]) for r in range(world)) / world
+    loss_ref.backward()
+    loss = ep(toks[rank][:, :-1], toks[rank][:, 1:])
+    loss.backward()
+    total = loss.detach().clone()
+    dist.all_reduce(total)
+    assert abs(float(total) / world - float(loss_ref)) < 1e-4
+    g = ep.layers[0].moe.experts.w2.grad / world          # expert gradients: summed over source ranks already
+    gr = full.layers[0].moe.experts.w2.grad[rank * n_local:(rank + 1) * n_local]
+    assert torch.allclose(g, gr, atol=1e-5), (g - gr).abs().max()
+    rg = ep.layers[0].moe.router.weight.grad.clone()
+    dist.all_reduce(rg)
+    assert torch.allclose(rg / world, full.layers[0].moe.router.weight.grad, atol=1e-5)
+
+
+def test_expert_parallel_moe_matches_single_process():
+    """EP=2 MoE decoder with the sort + all_to_all exchange over gloo against the same model with all experts local."""
+    run_ranks(_moe_ep_body, 2, "gloo")
