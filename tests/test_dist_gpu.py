@@ -213,3 +213,50 @@ def _watchdog_body(rank, world):
 
 def test_watchdog_reports_timeout():
     run_ranks(_watchdog_body, 2, "bccl")
+
+
+def _fused_ag_matmul_body(rank, world):
+    import torch_musa_b200 as bw
+    from torch_musa_b200.parallel import tensor_parallel as TP
+    from torch_musa_b200.parallel.fused_tp import FusedTensorParallel
+
+    dev = torch.device("blackwell", rank)
+    ctx = FusedTensorParallel(max_shard_bytes=1024 * 1024 * 2, max_rows=4096, device=dev, copier_pairs=4)
+    for rows, K, N in [(256, 512, 384), (512, 1024, 512), (1024, 256, 136)]:
+        torch.manual_seed(100 + rank)
+        x = (torch.randn(rows, K) * 0.5).to(torch.bfloat16).to(dev)
+        torch.manual_seed(7)
+        w = (torch.randn(N, K) * 0.1).to(torch.bfloat16).to(dev)
+        x_full_ref = TP.all_gather_rows(x)
+        ref = (x_full_ref.float() @ w.float().t()).cpu()
+        for wt in (w, w.t().contiguous().t()):            # K-major and N-major weight layouts
+            out = ctx.ag_matmul(x, wt, None)
+            assert out is not None, "shape should be covered by the fused kernel"
+            y, x_full = out
+            assert torch.equal(x_full.cpu(), x_full_ref.cpu())
+            err = (y.float().cpu() - ref).abs().max() / ref.abs().max()
+            assert err < 2e-2, float(err)
+    # through autograd with the fused forward installed
+    ctx.install()
+    try:
+        x = (torch.randn(256, 512) * 0.5).to(torch.bfloat16).to(dev).requires_grad_()
+        w = (torch.randn(384, 512) * 0.1).to(torch.bfloat16).to(dev).requires_grad_()
+        before = ctx.calls
+        y = TP.ag_matmul(x, w)
+        y.float().pow(2).sum().backward()
+        assert ctx.calls == before + 1
+        TP.FUSED_AG_MATMUL = None
+        x2, w2 = x.detach().clone().requires_grad_(), w.detach().clone().requires_grad_()
+        y2 = TP.ag_matmul(x2, w2)
+        y2.float().pow(2).sum().backward()
+        assert torch.allclose(y.float(), y2.float(), atol=2e-2, rtol=2e-2)
+        assert torch.allclose(x.grad.float(), x2.grad.float(), atol=0.5, rtol=5e-2)
+        assert torch.allclose(w.grad.float(), w2.grad.float(), atol=0.5, rtol=5e-2)
+    finally:
+        ctx.uninstall()
+    bw.synchronize()
+    ctx.check()
+
+
+def test_fused_allgather_gemm_matches_unfused():
+    run_ranks(_fused_ag_matmul_body, 2, "bccl", env={"NCCL_NVLS_ENABLE": "0"})

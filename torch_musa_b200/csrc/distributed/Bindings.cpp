@@ -92,6 +92,45 @@ void init_distributed_bindings(py::module& m) {
                                           (int)x.size(0), (int)idx.size(1), (int)x.size(1), (int)E, dst_off, epoch,
                                           ops::current_raw_stream(x)));
       })
+      // all-gather -> GEMM in one launch (kernels/gemm_tcgen05_2cta.cu): y = gather_rows(x_shard) @ w^T
+      .def("gemm_allgather", [](SymmetricMemory& s, const at::Tensor& x_shard, const at::Tensor& w, int64_t shard_off,
+                                at::Tensor& flags, int64_t copier_pairs) {
+        TORCH_CHECK(s.ok(), "symmetric memory is not usable: ", s.why_not());
+        TORCH_CHECK(ops::on_device(x_shard) && x_shard.dim() == 2 && x_shard.is_contiguous() &&
+                    (x_shard.scalar_type() == at::kBFloat16 || x_shard.scalar_type() == at::kHalf),
+                    "gemm_allgather: x_shard must be a contiguous bf16/fp16 [rows, K] device tensor");
+        TORCH_CHECK(ops::on_device(w) && w.dim() == 2 && w.scalar_type() == x_shard.scalar_type() &&
+                    w.size(1) == x_shard.size(1) && w.device() == x_shard.device(), "gemm_allgather: w must be [N, K]");
+        TORCH_CHECK(ops::on_device(flags) && flags.scalar_type() == at::kInt && flags.is_contiguous(),
+                    "gemm_allgather: flags must be an int32 device tensor");
+        const int64_t rows = x_shard.size(0), K = x_shard.size(1), N = w.size(0), M = rows * s.world();
+        TORCH_CHECK(flags.numel() >= M / 256, "gemm_allgather: flags too short");
+        const int64_t shard_bytes = rows * K * (int64_t)x_shard.element_size();
+        TORCH_CHECK(shard_off >= 0 && shard_off + shard_bytes <= (int64_t)(2 * s.half_bytes()),
+                    "gemm_allgather: shard does not fit the arena");
+        DeviceSwitch sw(x_shard.device().index());
+        s.local_tensor(shard_off, {rows, K}, x_shard.scalar_type()).copy_(x_shard);
+        at::Tensor x_full = at::empty({M, K}, x_shard.options());
+        at::Tensor y = at::empty({M, N}, x_shard.options());
+        b200_gemm_desc_t g{};
+        g.m = (int)M; g.n = (int)N; g.k = (int)K;
+        g.a_kmajor = 1; g.lda = K;
+        if (w.stride(1) == 1 && w.stride(0) >= K) { g.b_kmajor = 1; g.ldb = w.stride(0); }
+        else if (w.stride(0) == 1 && w.stride(1) >= N) { g.b_kmajor = 0; g.ldb = w.stride(1); }
+        else TORCH_CHECK(false, "gemm_allgather: w must be dense in one of its two dimensions");
+        g.ldd = N;
+        g.in_dtype = ops::kdtype(x_shard.scalar_type());
+        g.out_dtype = g.in_dtype;
+        g.batch = 1;
+        g.alpha = 1.f;
+        const uint32_t epoch = s.next_epoch(nullptr);
+        int e = b200_gemm_allgather(&g, s.desc(), shard_off, x_full.mutable_data_ptr(),
+                                    reinterpret_cast<uint32_t*>(flags.data_ptr<int>()), epoch, (int)copier_pairs,
+                                    y.mutable_data_ptr(), w.const_data_ptr(), ops::current_raw_stream(x_shard));
+        TORCH_CHECK(e != (int)cudaErrorNotSupported, "gemm_allgather: shape not covered (M % (256*world), K % 64, alignment)");
+        B200_KERNEL_CALL(e);
+        return std::make_tuple(y, x_full);
+      })
       .def("moe_gather_dot", [](SymmetricMemory& s, const at::Tensor& grad, const at::Tensor& idx, const at::Tensor& pos,
                                 int64_t E, int64_t src_off) {
         TORCH_CHECK(s.ok(), "symmetric memory is not usable: ", s.why_not());

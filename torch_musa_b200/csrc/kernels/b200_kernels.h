@@ -281,6 +281,15 @@ B200_API int b200_comm_alltoall(const b200_symm_t* s, const void* in, void* out,
                                 const int64_t* send_off, const int64_t* recv_off, const int64_t* recv_len,
                                 const int64_t* peer_send_off, uint32_t epoch, int64_t in_off, cudaStream_t stream);
 
+/* all-gather -> GEMM in ONE launch: D[M, N] = rows gathered from every rank's shard [M / world, K] (at shard_off of
+ * its arena) times B[N, K]^T.  A few copier CTAs stream the peers' shards into a_full [M, K] (local) with bulk
+ * copies while the other clusters multiply the 256-row panels that have arrived (own shard first).  flags: local
+ * uint32 [M / 256], zeroed once, reused by every call; the call uses epochs `epoch` and `epoch + 1`.
+ * Needs M % (256 * world) == 0, K % 64 == 0, K-major contiguous A. */
+B200_API int b200_gemm_allgather(const b200_gemm_desc_t* desc, const b200_symm_t* s, int64_t shard_off, void* a_full,
+                                 uint32_t* flags, uint32_t epoch, int copier_pairs, void* d, const void* b,
+                                 cudaStream_t stream);
+
 /* ---------------------------------------------------------------- expert-parallel MoE token exchange (bf16 rows)
  * E experts, E / world per rank in rank order; idx / slot / pos are int32 [T*K]; receive buffers hold cap_rows
  * rows of d elements at a byte offset of every rank's arena; counts_off points at world*E int32 of scratch in the

@@ -176,6 +176,21 @@ __device__ __forceinline__ void store_chunk(OutT* __restrict__ drow, const float
 
 }  // namespace gemmdev
 
+// all-gather -> GEMM: the A operand [M, K] is assembled in local memory from the ranks' row shards by a few
+// copier CTAs of the same launch while the other clusters already multiply the panels that have arrived.
+struct AgParams {
+  int enabled;
+  int world, rank;
+  int copier_pairs;          // clusters (from pair index 0) that copy instead of multiplying
+  int panels_per_shard;      // 256-row panels in one rank's shard
+  int64_t panel_bytes;       // 256 * K * 2
+  const void* src[16];       // every rank's shard (peer-mapped; src[rank] is the local one)
+  void* dst;                 // local [M, K]
+  uint32_t* flags;           // local, one word per panel: epoch of the last call that completed it
+  uint32_t* sig[16];         // signal pads (peer-mapped), slot [copier CTA][source rank]
+  uint32_t epoch;            // this call: epoch = shards ready, epoch + 1 = peer finished pulling
+};
+
 // What the host decided for one problem: how many K-splits and which kernel family.
 struct GemmPlan {
   int pair;          // 1: SM-pair kernel (256-row tiles), 0: single-CTA kernel (128-row tiles)
@@ -191,7 +206,7 @@ int* gemm_status_word_device();
 int gemm_sm_count();
 // 2-CTA (cta_group::2) variant; returns cudaErrorNotSupported when it does not apply
 int gemm_launch_2cta(const b200_gemm_desc_t* g, void* d, const void* a, const void* b, cudaStream_t stream,
-                     const GemmPlan& plan);
+                     const GemmPlan& plan, const AgParams* ag = nullptr);
 GemmPlan gemm_plan(const b200_gemm_desc_t* g);
 // sums the fp32 partial products of a split-K run and applies bias / activation / accumulate / output cast
 int gemm_splitk_reduce(const b200_gemm_desc_t* g, void* d, const float* ws, int splits, cudaStream_t stream);

@@ -166,10 +166,108 @@ __device__ __forceinline__ bool next_tile(TileCursor& c, int dynamic, int& tile,
   return valid != 0 && tile < total;
 }
 
+// ---- all-gather copier: one thread per CTA streams 32 KB chunks peer HBM -> shared memory -> local HBM with
+// bulk copies (no multicast), five loads in flight, and publishes a panel flag when a 256-row panel is complete.
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void bulk_store_1d(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(smem_src)),
+               "r"(bytes)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_gpu_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// spins until (int)(*p - want) >= 0; false when the wait limit expired or another thread of the CTA gave up
+template <bool SYS>
+__device__ __forceinline__ bool wait_word(const uint32_t* p, uint32_t want, volatile int* abort_flag) {
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while ((int32_t)((SYS ? ld_acquire_sys_u32(p) : ld_acquire_gpu_u32(p)) - want) < 0) {
+    if ((++spins & 0xff) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kWaitCycles) { *abort_flag = 1; return false; }
+    }
+  }
+  return true;
+}
+
+constexpr int kAgRing = 6;            // 32 KB slots in the operand ring's shared memory
+constexpr uint32_t kAgChunk = 32768;
+
+__device__ void ag_copier(const AgParams& ag, uint8_t* ring, uint64_t* bars, volatile int* abort_flag) {
+  const int cc = blockIdx.x, n_cc = 2 * ag.copier_pairs;
+  const int W = ag.world, r = ag.rank;
+  // 1. tell every peer that my shard is complete (my earlier kernels have finished) and wait for theirs
+  __threadfence_system();
+  for (int peer = 0; peer < W; ++peer)
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(ag.sig[peer] + cc * 16 + r), "r"(ag.epoch) : "memory");
+  bool ok = true;
+  for (int peer = 0; peer < W && ok; ++peer) ok = wait_word<true>(ag.sig[r] + cc * 16 + peer, ag.epoch, abort_flag);
+  // 2. my panels, own shard first (the GEMM clusters consume panels in the same rotated order)
+  const int n_panels = ag.panels_per_shard * W;
+  const int chunks_per_panel = (int)(ag.panel_bytes / kAgChunk);
+  const int my_panels = ok ? (n_panels - cc + n_cc - 1) / n_cc : 0;
+  const long long total = (long long)my_panels * chunks_per_panel;
+  auto chunk_addr = [&](long long g, const char*& src, char*& dst, int& panel, bool& last) {
+    const int q = cc + (int)(g / chunks_per_panel) * n_cc;
+    const int i = (int)(g % chunks_per_panel);
+    panel = (q + r * ag.panels_per_shard) % n_panels;
+    const int owner = panel / ag.panels_per_shard;
+    src = static_cast<const char*>(ag.src[owner]) + (long long)(panel - owner * ag.panels_per_shard) * ag.panel_bytes +
+          (long long)i * kAgChunk;
+    dst = static_cast<char*>(ag.dst) + (long long)panel * ag.panel_bytes + (long long)i * kAgChunk;
+    last = i == chunks_per_panel - 1;
+  };
+  auto issue_load = [&](long long g) {
+    const char* src; char* dst; int panel; bool last;
+    chunk_addr(g, src, dst, panel, last);
+    const int s = (int)(g % kAgRing);
+    mbar_expect_tx(&bars[s], kAgChunk);
+    bulk_load_1d(ring + (size_t)s * kAgChunk, src, kAgChunk, &bars[s]);
+  };
+  long long issued = 0;
+  for (; issued < total && issued < kAgRing - 1; ++issued) issue_load(issued);
+  for (long long g = 0; g < total && ok; ++g) {
+    const int s = (int)(g % kAgRing);
+    if (!mbar_wait(&bars[s], (uint32_t)((g / kAgRing) & 1), abort_flag)) { ok = false; break; }
+    const char* src; char* dst; int panel; bool last;
+    chunk_addr(g, src, dst, panel, last);
+    bulk_store_1d(dst, ring + (size_t)s * kAgChunk, kAgChunk);
+    if (issued < total) {
+      // the slot of chunk g-1 is reused now: its store must have finished reading shared memory
+      asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+      issue_load(issued++);
+    }
+    if (last) {
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // the panel's bytes are in local memory
+      asm volatile("fence.proxy.async;" ::: "memory");
+      __threadfence();
+      asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(ag.flags + panel), "r"(ag.epoch) : "memory");
+    }
+  }
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  // 3. nobody's shard may be overwritten before every peer has finished pulling from it
+  for (int peer = 0; peer < W; ++peer)
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(ag.sig[peer] + cc * 16 + r), "r"(ag.epoch + 1) : "memory");
+  for (int peer = 0; peer < W && ok; ++peer) ok = wait_word<true>(ag.sig[r] + cc * 16 + peer, ag.epoch + 1, abort_flag);
+}
+
 template <typename OutT, bool A_KMAJOR, bool B_KMAJOR, int BN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 OutT* __restrict__ d, const Params p, const int dynamic) {
+                 OutT* __restrict__ d, const Params p, const int dynamic, const AgParams ag) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   // Both CTAs of the pair must use identical shared-memory offsets: the dynamic segment starts at the same
@@ -194,12 +292,17 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
-  const int pair = blockIdx.x >> 1;
-  const int n_pairs = gridDim.x >> 1;
+  const int n_copiers = ag.enabled ? ag.copier_pairs : 0;      // clusters [0, n_copiers) assemble the A operand
+  const bool copier = (int)(blockIdx.x >> 1) < n_copiers;
+  const int n_pairs = (int)(gridDim.x >> 1) - n_copiers;
   const int k_blocks = (p.k + BK - 1) / BK;
   const int tiles_per_batch = p.tiles_m * p.tiles_n;
   const int tiles_all_batches = tiles_per_batch * p.batch;
   const int total_tiles = tiles_all_batches * p.splits;
+  // a copier cluster multiplies nothing: giving it a first tile beyond the end idles all of its GEMM roles
+  const int pair = copier ? total_tiles : (int)(blockIdx.x >> 1) - n_copiers;
+  // with gathered A the m-tiles are visited own shard first, in the order the copiers deliver the panels
+  const int m_rot = ag.enabled ? ag.rank * ag.panels_per_shard : 0;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -239,7 +342,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (both CTAs)
-    if (lane == 0) {
+    if (copier) {
+      if (lane == 0) ag_copier(ag, smem_a, full_bar, abort_flag);
+    } else if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -254,8 +359,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int r = tb - b * tiles_per_batch;
         const int kb0 = split * p.kb_per_split;
         const int kb1 = min(k_blocks, kb0 + p.kb_per_split);
-        const int m0 = (r % p.tiles_m) * BM2 + (int)rank * BMH;
+        const int mt = ((r % p.tiles_m) + m_rot) % p.tiles_m;
+        const int m0 = mt * BM2 + (int)rank * BMH;
         const int n0 = (r / p.tiles_m) * BN + (int)rank * C::kBHalf;
+        if (ag.enabled) {
+          // the 256-row panel of this tile must have been assembled by a copier CTA of this launch
+          if (!wait_word<false>(ag.flags + mt, ag.epoch, abort_flag)) { ok = false; break; }
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
           if (leader) mbar_expect_tx(&full_bar[stage], 2 * C::kStage);
@@ -351,7 +462,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const int tb = tile - split * tiles_all_batches;
       const int b = tb / tiles_per_batch;
       const int r = tb - b * tiles_per_batch;
-      const int m0 = (r % p.tiles_m) * BM2 + (int)rank * BMH;
+      const int m0 = (((r % p.tiles_m) + m_rot) % p.tiles_m) * BM2 + (int)rank * BMH;
       const int n0 = (r / p.tiles_m) * BN;
       if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) break;
       tc_fence_after();
@@ -423,8 +534,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 // ------------------------------------------------------------------ host side
 template <typename OutT, int BN>
 int launch_pair(const b200_gemm_desc_t* g, void* d, const void* a, const void* b, cudaStream_t stream,
-                const GemmPlan& plan) {
-  const int dynamic = plan.dynamic;
+                const GemmPlan& plan, const AgParams* agp) {
+  AgParams ag{};
+  if (agp) ag = *agp;
+  const int dynamic = ag.enabled ? 0 : plan.dynamic;   // copier and GEMM clusters must all be resident: static grid
   using C = Cfg<BN>;
   CUtensorMap ma, mb;
   const uint64_t esz = 2;
@@ -470,7 +583,8 @@ int launch_pair(const b200_gemm_desc_t* g, void* d, const void* a, const void* b
   const int pairs = std::max(1, gemm_sm_count() / 2);
   // static schedule: one resident cluster per SM pair strides over the tiles; dynamic schedule: one cluster
   // per tile is requested and the clusters that run take over the tiles of those that have not started
-  const int grid = dynamic ? 2 * total : 2 * std::min(total, pairs);
+  int grid = dynamic ? 2 * total : 2 * std::min(total, pairs);
+  if (ag.enabled) grid = 2 * (ag.copier_pairs + std::min(total, std::max(1, pairs - ag.copier_pairs)));
 
 #define GEMM2_GO(AK, BKM)                                                                                        \
   do {                                                                                                           \
@@ -481,7 +595,7 @@ int launch_pair(const b200_gemm_desc_t* g, void* d, const void* a, const void* b
       if (e != cudaSuccess) return (int)e;                                                                       \
       attr_set = true;                                                                                           \
     }                                                                                                            \
-    kern<<<grid, kThreads, C::kSmem, stream>>>(ma, mb, (OutT*)d, p, dynamic);                                            \
+    kern<<<grid, kThreads, C::kSmem, stream>>>(ma, mb, (OutT*)d, p, dynamic, ag);                                            \
   } while (0)
 
   if (g->a_kmajor && g->b_kmajor) GEMM2_GO(true, true);
@@ -561,11 +675,11 @@ GemmPlan gemm_plan(const b200_gemm_desc_t* g) {
 }
 
 int gemm_launch_2cta(const b200_gemm_desc_t* g, void* d, const void* a, const void* b, cudaStream_t stream,
-                     const GemmPlan& plan) {
+                     const GemmPlan& plan, const AgParams* ag) {
   switch (g->out_dtype) {
-    case B200_BF16: return launch_pair<__nv_bfloat16, 256>(g, d, a, b, stream, plan);
-    case B200_F16: return launch_pair<__half, 256>(g, d, a, b, stream, plan);
-    case B200_F32: return launch_pair<float, 256>(g, d, a, b, stream, plan);
+    case B200_BF16: return launch_pair<__nv_bfloat16, 256>(g, d, a, b, stream, plan, ag);
+    case B200_F16: return launch_pair<__half, 256>(g, d, a, b, stream, plan, ag);
+    case B200_F32: return launch_pair<float, 256>(g, d, a, b, stream, plan, ag);
     default: return (int)cudaErrorNotSupported;
   }
 }
@@ -617,4 +731,39 @@ int gemm_splitk_reduce(const b200_gemm_desc_t* g, void* d, const float* ws, int 
 extern "C" int b200_gemm_force_config(int config) {
   if (config < 0 || config > 3) return -1;
   return b200k::gemm_forced_config_exchange(config);
+}
+
+// all-gather -> GEMM in one launch.  D[M, N] = gather_rows(A shards)[M, K] x B[N, K]^T with M = world * shard
+// rows; every rank's shard lives at `shard_off` of its arena; a_full [M, K] and flags [M / 256] are local
+// (flags persistent, zero-initialised once).  Consumes epochs `epoch` and `epoch + 1` of the arena's pad.
+extern "C" int b200_gemm_allgather(const b200_gemm_desc_t* g, const b200_symm_t* s, int64_t shard_off, void* a_full,
+                                   uint32_t* flags, uint32_t epoch, int copier_pairs, void* d, const void* b,
+                                   cudaStream_t stream) {
+  using namespace b200k;
+  if (!g->a_kmajor || g->batch > 1 || s->world < 2 || s->world > 16 || g->m % (256 * s->world) != 0 ||
+      g->k % 64 != 0 || g->lda != g->k || (shard_off & 15) || copier_pairs < 1 || copier_pairs > 16 ||
+      (reinterpret_cast<uintptr_t>(a_full) & 15))
+    return (int)cudaErrorNotSupported;
+  if (g->in_dtype != B200_BF16 && g->in_dtype != B200_F16) return (int)cudaErrorNotSupported;
+  if (copier_pairs * 2 >= gemm_sm_count() / 2) return (int)cudaErrorNotSupported;
+  AgParams ag{};
+  ag.enabled = 1;
+  ag.world = s->world;
+  ag.rank = s->rank;
+  ag.copier_pairs = copier_pairs;
+  ag.panels_per_shard = g->m / s->world / 256;
+  ag.panel_bytes = (int64_t)256 * g->k * 2;
+  for (int r = 0; r < s->world; ++r) {
+    ag.src[r] = static_cast<const char*>(s->bufs[r]) + shard_off;
+    ag.sig[r] = s->sigs[r];
+  }
+  ag.dst = a_full;
+  ag.flags = flags;
+  ag.epoch = epoch;
+  GemmPlan plan;
+  plan.pair = 1;
+  plan.dynamic = 0;
+  plan.splits = 1;
+  plan.kb_per_split = (g->k + BK - 1) / BK;
+  return gemm_launch_2cta(g, d, a_full, b, stream, plan, &ag);
 }

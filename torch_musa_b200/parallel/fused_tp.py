@@ -1,0 +1,64 @@
+"""Fused tensor-parallel primitives on the blackwell device.
+
+``FusedTensorParallel`` owns a peer-mapped arena for the activation shards and installs
+``tensor_parallel.FUSED_AG_MATMUL``: all-gather -> GEMM as ONE kernel launch -- a few CTAs stream the peers'
+row shards over NVLink (bulk copies peer HBM -> shared memory -> local HBM, no multicast) into the local
+[M, K] operand while the remaining SM pairs already run tcgen05 tiles on the 256-row panels that have
+arrived, own shard first.  Shapes the kernel does not cover (M % (256 * world), K % 64) fall back to
+all_gather + GEMM; the choice depends on shapes only, so every rank takes the same branch.
+Parity: the reference has no fused collective path; its FSDP/TP all-gathers are separate vendor-library
+calls (reference torch_musa/csrc/distributed/ProcessGroupMCCL.cpp:4678-4735).
+"""
+from __future__ import annotations
+
+import itertools
+
+import torch
+import torch.distributed as dist
+
+from . import tensor_parallel as TP
+
+_ids = itertools.count()
+
+
+class FusedTensorParallel:
+    def __init__(self, max_shard_bytes: int, max_rows: int, group=None, device=None, copier_pairs: int = 8):
+        import torch_musa_b200 as bw
+
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.device = torch.device(device if device is not None else f"blackwell:{bw.current_device()}")
+        self.max_shard_bytes = (int(max_shard_bytes) + 255) // 256 * 256
+        self.copier_pairs = copier_pairs
+        store = dist.distributed_c10d._get_default_store()
+        self.sm = bw._C._create_symmetric_memory(store, f"tp_arena/{next(_ids)}", self.rank, self.world,
+                                                 self.device.index or 0, self.max_shard_bytes)
+        if not self.sm.ok:
+            raise RuntimeError(f"tensor-parallel arena unavailable: {self.sm.why_not}")
+        self.flags = torch.zeros(max(1, max_rows // 256), dtype=torch.int32, device=self.device)
+        self.calls = 0
+
+    def ag_matmul(self, x_shard: torch.Tensor, w: torch.Tensor, group):
+        rows, K = x_shard.shape
+        M = rows * self.world
+        if (x_shard.dtype not in (torch.bfloat16, torch.float16) or w.dtype != x_shard.dtype or M % (256 * self.world)
+                or K % 64 or rows * K * x_shard.element_size() > self.max_shard_bytes or M // 256 > self.flags.numel()):
+            return None
+        y, x_full = self.sm.gemm_allgather(x_shard.contiguous(), w, 0, self.flags, self.copier_pairs)
+        self.calls += 1
+        return y, x_full
+
+    def install(self) -> "FusedTensorParallel":
+        TP.FUSED_AG_MATMUL = self.ag_matmul
+        return self
+
+    def uninstall(self) -> None:
+        if TP.FUSED_AG_MATMUL == self.ag_matmul:
+            TP.FUSED_AG_MATMUL = None
+
+    def check(self) -> None:
+        import torch_musa_b200 as bw
+
+        st = self.sm.take_status() or bw._C._gemm_status(True)
+        if st:
+            raise RuntimeError(f"a fused tensor-parallel kernel gave up on a bounded wait (status {st})")
