@@ -260,3 +260,45 @@ def _fused_ag_matmul_body(rank, world):
 
 def test_fused_allgather_gemm_matches_unfused():
     run_ranks(_fused_ag_matmul_body, 2, "bccl", env={"NCCL_NVLS_ENABLE": "0"})
+
+
+def _fused_matmul_rs_body(rank, world):
+    import torch_musa_b200 as bw
+    from torch_musa_b200.parallel import tensor_parallel as TP
+    from torch_musa_b200.parallel.fused_tp import FusedTensorParallel
+
+    dev = torch.device("blackwell", rank)
+    ctx = FusedTensorParallel(max_shard_bytes=1 << 21, max_rows=4096, device=dev, copier_pairs=4,
+                              max_partial_bytes=2048 * 1024 * 2, reducer_pairs=4)
+    for M, K, N in [(512, 256, 256), (1024, 520, 512), (2048, 136, 1024), (512, 256, 256)]:
+        torch.manual_seed(200 + rank)
+        x = (torch.randn(M, K) * 0.5).to(torch.bfloat16).to(dev)
+        w = (torch.randn(N, K) * 0.1).to(torch.bfloat16).to(dev)
+        ref = TP.reduce_scatter_rows((x.float() @ w.float().t())).cpu()
+        for wt in (w, w.t().contiguous().t()):
+            y = ctx.matmul_rs(x, wt, None)
+            assert y is not None
+            err = (y.float().cpu() - ref).abs().max() / ref.abs().max()
+            assert err < 3e-2, (M, K, N, float(err))
+    ctx.install()
+    try:
+        x = (torch.randn(512, 256) * 0.5).to(torch.bfloat16).to(dev).requires_grad_()
+        w = (torch.randn(256, 256) * 0.1).to(torch.bfloat16).to(dev).requires_grad_()
+        y = TP.matmul_rs(x, w)
+        y.float().pow(2).sum().backward()
+        assert ctx.rs_calls >= 9 and ctx.calls >= 1      # backward of matmul_rs ran the fused all-gather GEMM
+        TP.FUSED_AG_MATMUL = TP.FUSED_MATMUL_RS = None
+        x2, w2 = x.detach().clone().requires_grad_(), w.detach().clone().requires_grad_()
+        y2 = TP.matmul_rs(x2, w2)
+        y2.float().pow(2).sum().backward()
+        assert torch.allclose(y.float(), y2.float(), atol=3e-2, rtol=3e-2)
+        assert torch.allclose(x.grad.float(), x2.grad.float(), atol=0.5, rtol=5e-2)
+        assert torch.allclose(w.grad.float(), w2.grad.float(), atol=0.5, rtol=5e-2)
+    finally:
+        ctx.uninstall()
+    bw.synchronize()
+    ctx.check()
+
+
+def test_fused_gemm_reduce_scatter_matches_unfused():
+    run_ranks(_fused_matmul_rs_body, 2, "bccl", env={"NCCL_NVLS_ENABLE": "0"})

@@ -131,6 +131,42 @@ void init_distributed_bindings(py::module& m) {
         B200_KERNEL_CALL(e);
         return std::make_tuple(y, x_full);
       })
+      // GEMM -> reduce-scatter in one launch: y_shard = rows `rank` of sum_ranks(x_r @ w_r^T)
+      .def("gemm_reduce_scatter", [](SymmetricMemory& s, const at::Tensor& x, const at::Tensor& w, int64_t partial_off,
+                                     int64_t flag_off, int64_t reducer_pairs) {
+        TORCH_CHECK(s.ok(), "symmetric memory is not usable: ", s.why_not());
+        TORCH_CHECK(ops::on_device(x) && x.dim() == 2 && x.is_contiguous() &&
+                    (x.scalar_type() == at::kBFloat16 || x.scalar_type() == at::kHalf),
+                    "gemm_reduce_scatter: x must be a contiguous bf16/fp16 [M, K] device tensor");
+        TORCH_CHECK(ops::on_device(w) && w.dim() == 2 && w.scalar_type() == x.scalar_type() && w.size(1) == x.size(1) &&
+                    w.device() == x.device(), "gemm_reduce_scatter: w must be [N, K]");
+        const int64_t M = x.size(0), K = x.size(1), N = w.size(0), W = s.world();
+        TORCH_CHECK(M % W == 0, "gemm_reduce_scatter: rows must divide by the world size");
+        const int64_t flag_bytes = W * (M / 256 / W + 1) * (N / 256 + 1) * 2 * 4;
+        TORCH_CHECK(partial_off >= 0 && partial_off + M * N * 2 <= (int64_t)(2 * s.half_bytes()) &&
+                    flag_off + flag_bytes <= (int64_t)(2 * s.half_bytes()), "gemm_reduce_scatter: buffers exceed the arena");
+        DeviceSwitch sw(x.device().index());
+        at::Tensor y = at::empty({M / W, N}, x.options());
+        b200_gemm_desc_t g{};
+        g.m = (int)M; g.n = (int)N; g.k = (int)K;
+        g.a_kmajor = 1; g.lda = K;
+        if (w.stride(1) == 1 && w.stride(0) >= K) { g.b_kmajor = 1; g.ldb = w.stride(0); }
+        else if (w.stride(0) == 1 && w.stride(1) >= N) { g.b_kmajor = 0; g.ldb = w.stride(1); }
+        else TORCH_CHECK(false, "gemm_reduce_scatter: w must be dense in one of its two dimensions");
+        g.ldd = N;
+        g.in_dtype = ops::kdtype(x.scalar_type());
+        g.out_dtype = g.in_dtype;
+        g.batch = 1;
+        g.alpha = 1.f;
+        const uint32_t epoch = s.next_epoch(nullptr);
+        int e = b200_gemm_reduce_scatter(&g, s.desc(), partial_off, flag_off, epoch, (int)reducer_pairs,
+                                         y.mutable_data_ptr(), x.const_data_ptr(), w.const_data_ptr(),
+                                         ops::current_raw_stream(x));
+        TORCH_CHECK(e != (int)cudaErrorNotSupported,
+                    "gemm_reduce_scatter: shape not covered (M % (256*world), N % 256, K alignment, world <= 8)");
+        B200_KERNEL_CALL(e);
+        return y;
+      })
       .def("moe_gather_dot", [](SymmetricMemory& s, const at::Tensor& grad, const at::Tensor& idx, const at::Tensor& pos,
                                 int64_t E, int64_t src_off) {
         TORCH_CHECK(s.ok(), "symmetric memory is not usable: ", s.why_not());

@@ -290,6 +290,15 @@ B200_API int b200_gemm_allgather(const b200_gemm_desc_t* desc, const b200_symm_t
                                  uint32_t* flags, uint32_t epoch, int copier_pairs, void* d, const void* b,
                                  cudaStream_t stream);
 
+/* GEMM -> reduce-scatter in ONE launch: out[M / world, N] = row block `rank` of the sum over ranks of
+ * A_r[M, K_r] x B_r[N, K_r]^T.  Tiles go to a partial buffer in the arena (other ranks' panels first) and raise
+ * per-tile flags in the panel owner's arena; reducer CTAs of the same launch pull the finished panels from every
+ * rank with bulk copies, add them in fp32 and write the output.  flag table: world * (M/256/world) * (N/256) * 2
+ * uint32 at flag_off of every arena, zeroed once.  Needs M % (256 * world) == 0, N % 256 == 0, world <= 8. */
+B200_API int b200_gemm_reduce_scatter(const b200_gemm_desc_t* desc, const b200_symm_t* s, int64_t partial_off,
+                                      int64_t flag_off, uint32_t epoch, int reducer_pairs, void* out, const void* a,
+                                      const void* b, cudaStream_t stream);
+
 /* ---------------------------------------------------------------- expert-parallel MoE token exchange (bf16 rows)
  * E experts, E / world per rank in rank order; idx / slot / pos are int32 [T*K]; receive buffers hold cap_rows
  * rows of d elements at a byte offset of every rank's arena; counts_off points at world*E int32 of scratch in the

@@ -191,6 +191,23 @@ struct AgParams {
   uint32_t epoch;            // this call: epoch = shards ready, epoch + 1 = peer finished pulling
 };
 
+// GEMM -> reduce-scatter: every rank multiplies into a partial [M, N] buffer of its arena, visiting the row panels
+// of the other ranks first; per finished tile it raises a flag in the panel owner's arena.  A few reducer CTAs of
+// the same launch wait for the flags of their own panels from every source rank, pull the partial panels with bulk
+// copies into shared memory, sum them in fp32 and write this rank's [M / world, N] output rows.
+struct RsParams {
+  int enabled;
+  int world, rank;
+  int reducer_pairs;         // clusters (from pair index 0) that reduce instead of multiplying
+  int panels_per_shard;
+  int64_t panel_bytes;       // 256 * N * 2
+  const void* src[16];       // every rank's partial buffer (peer-mapped)
+  uint32_t* flag[16];        // every rank's flag table (peer-mapped): [source rank][panel in shard][n tile][cta of pair]
+  uint32_t* sig[16];         // signal pads for the trailing barrier
+  void* out;                 // local [M / world, N]
+  uint32_t epoch;
+};
+
 // What the host decided for one problem: how many K-splits and which kernel family.
 struct GemmPlan {
   int pair;          // 1: SM-pair kernel (256-row tiles), 0: single-CTA kernel (128-row tiles)
@@ -206,7 +223,7 @@ int* gemm_status_word_device();
 int gemm_sm_count();
 // 2-CTA (cta_group::2) variant; returns cudaErrorNotSupported when it does not apply
 int gemm_launch_2cta(const b200_gemm_desc_t* g, void* d, const void* a, const void* b, cudaStream_t stream,
-                     const GemmPlan& plan, const AgParams* ag = nullptr);
+                     const GemmPlan& plan, const AgParams* ag = nullptr, const RsParams* rs = nullptr);
 GemmPlan gemm_plan(const b200_gemm_desc_t* g);
 // sums the fp32 partial products of a split-K run and applies bias / activation / accumulate / output cast
 int gemm_splitk_reduce(const b200_gemm_desc_t* g, void* d, const float* ws, int splits, cudaStream_t stream);

@@ -264,10 +264,94 @@ __device__ void ag_copier(const AgParams& ag, uint8_t* ring, uint64_t* bars, vol
   for (int peer = 0; peer < W && ok; ++peer) ok = wait_word<true>(ag.sig[r] + cc * 16 + peer, ag.epoch + 1, abort_flag);
 }
 
+// ---- reduce-scatter reducer: all threads of the CTA.  Work items are 8 KB chunks of this rank's own panels;
+// per item one thread pulls the chunk from every source rank's partial buffer into shared memory with bulk
+// copies (two stages), then all threads add the `world` copies in fp32 and store bf16/fp16 output.
+constexpr uint32_t kRsChunk = 8192;
+
+template <typename OutT>
+__device__ void rs_reducer(const RsParams& rs, int tiles_n, uint8_t* stage_mem, uint64_t* bars, volatile int* abort_flag) {
+  const int cc = blockIdx.x, n_cc = 2 * rs.reducer_pairs;
+  const int W = rs.world, r = rs.rank;
+  const int chunks_per_panel = (int)(rs.panel_bytes / kRsChunk);
+  const long long n_items = (long long)rs.panels_per_shard * chunks_per_panel;
+  const uint32_t stage_bytes = (uint32_t)W * kRsChunk;
+  int waited_panel = -1;
+  auto wait_panel = [&](int p) {
+    // every tile of panel p from every source rank has been written (flags live in MY arena)
+    const uint32_t* base = rs.flag[r];
+    const int per_src = rs.panels_per_shard * tiles_n * 2;
+    for (int i = threadIdx.x; i < W * tiles_n * 2; i += blockDim.x) {
+      const int src = i / (tiles_n * 2), j = i - src * (tiles_n * 2);
+      wait_word<true>(base + src * per_src + p * tiles_n * 2 + j, rs.epoch, abort_flag);
+    }
+    __syncthreads();
+  };
+  auto issue = [&](long long item, int st) {
+    const int p = (int)(item / chunks_per_panel), c = (int)(item % chunks_per_panel);
+    const long long off = ((long long)(r * rs.panels_per_shard + p)) * rs.panel_bytes + (long long)c * kRsChunk;
+    asm volatile("fence.proxy.async;" ::: "memory");   // flag acquires (generic proxy) before the bulk reads
+    mbar_expect_tx(&bars[st], stage_bytes);
+    for (int s = 0; s < W; ++s) {
+      const int src = (r + s) % W;
+      bulk_load_1d(stage_mem + (size_t)st * stage_bytes + (size_t)s * kRsChunk, static_cast<const char*>(rs.src[src]) + off,
+                   kRsChunk, &bars[st]);
+    }
+  };
+  // item sequence of this CTA: cc, cc + n_cc, ...   (k-th item uses stage k & 1, phase (k >> 1) & 1)
+  long long k = 0;
+  long long first = cc;
+  if (first < n_items) {
+    const int p0 = (int)(first / chunks_per_panel);
+    wait_panel(p0);
+    waited_panel = p0;
+    if (threadIdx.x == 0 && !*abort_flag) issue(first, 0);
+  }
+  for (long long item = first; item < n_items; item += n_cc, ++k) {
+    if (*abort_flag) break;
+    const int st = (int)(k & 1);
+    const long long next = item + n_cc;
+    if (next < n_items) {
+      const int pn = (int)(next / chunks_per_panel);
+      if (pn != waited_panel) { wait_panel(pn); waited_panel = pn; }
+      if (threadIdx.x == 0 && !*abort_flag) issue(next, st ^ 1);   // stage st^1 was drained in the previous iteration
+    }
+    if (!mbar_wait(&bars[st], (uint32_t)((k >> 1) & 1), abort_flag)) break;
+    const int p = (int)(item / chunks_per_panel), c = (int)(item % chunks_per_panel);
+    OutT* out = reinterpret_cast<OutT*>(static_cast<char*>(rs.out) + (long long)p * rs.panel_bytes + (long long)c * kRsChunk);
+    const uint8_t* sm = stage_mem + (size_t)st * stage_bytes;
+    for (int v = threadIdx.x; v < (int)(kRsChunk / 16); v += blockDim.x) {
+      float acc[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+      for (int s = 0; s < W; ++s) {
+        const Vec16<OutT> x = *reinterpret_cast<const Vec16<OutT>*>(sm + (size_t)s * kRsChunk + (size_t)v * 16);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] += ToF<OutT>::to(x.v[e]);
+      }
+      Vec16<OutT> o;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o.v[e] = ToF<OutT>::from(acc[e]);
+      st16(out + (size_t)v * 8, o);
+    }
+    __syncthreads();   // the stage may be refilled
+  }
+  __syncthreads();
+  // peers may overwrite their partial buffers only after everybody has finished pulling
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    for (int peer = 0; peer < W; ++peer)
+      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(rs.sig[peer] + cc * 16 + r), "r"(rs.epoch + 1) : "memory");
+    bool ok = !*abort_flag;
+    for (int peer = 0; peer < W && ok; ++peer) ok = wait_word<true>(rs.sig[r] + cc * 16 + peer, rs.epoch + 1, abort_flag);
+  }
+  __syncthreads();
+}
+
 template <typename OutT, bool A_KMAJOR, bool B_KMAJOR, int BN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 OutT* __restrict__ d, const Params p, const int dynamic, const AgParams ag) {
+                 OutT* __restrict__ d, const Params p, const int dynamic, const AgParams ag, const RsParams rs) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   // Both CTAs of the pair must use identical shared-memory offsets: the dynamic segment starts at the same
@@ -292,7 +376,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
-  const int n_copiers = ag.enabled ? ag.copier_pairs : 0;      // clusters [0, n_copiers) assemble the A operand
+  // clusters [0, n_copiers) do not multiply: they assemble the A operand (all-gather) or reduce the partial
+  // products (reduce-scatter)
+  const int n_copiers = ag.enabled ? ag.copier_pairs : (rs.enabled ? rs.reducer_pairs : 0);
   const bool copier = (int)(blockIdx.x >> 1) < n_copiers;
   const int n_pairs = (int)(gridDim.x >> 1) - n_copiers;
   const int k_blocks = (p.k + BK - 1) / BK;
@@ -302,7 +388,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   // a copier cluster multiplies nothing: giving it a first tile beyond the end idles all of its GEMM roles
   const int pair = copier ? total_tiles : (int)(blockIdx.x >> 1) - n_copiers;
   // with gathered A the m-tiles are visited own shard first, in the order the copiers deliver the panels
-  const int m_rot = ag.enabled ? ag.rank * ag.panels_per_shard : 0;
+  // reduce-scatter: the other ranks' panels first (the next rank's first), the own panels last
+  const int m_rot = ag.enabled ? ag.rank * ag.panels_per_shard
+                               : (rs.enabled ? ((rs.rank + 1) % rs.world) * rs.panels_per_shard : 0);
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -340,10 +428,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   cur.stage = 0;
   cur.phase = 0;
 
+  if (copier && rs.enabled) rs_reducer<OutT>(rs, p.tiles_n, smem_a, full_bar, abort_flag);   // whole CTA
+
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (both CTAs)
     if (copier) {
-      if (lane == 0) ag_copier(ag, smem_a, full_bar, abort_flag);
+      if (lane == 0 && ag.enabled) ag_copier(ag, smem_a, full_bar, abort_flag);
     } else if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
@@ -503,6 +593,17 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           store_chunk<OutT>(drow + c * 32, v, valid, vec_ok);
         }
       }
+      if (rs.enabled) {
+        // this CTA's half of the tile is in the partial buffer: tell the owner of the row panel
+        __threadfence_system();
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps
+        if (warp == 2 && lane == 0) {
+          const int mt = ((r % p.tiles_m) + m_rot) % p.tiles_m;
+          const int owner = mt / rs.panels_per_shard, pin = mt - owner * rs.panels_per_shard;
+          uint32_t* f = rs.flag[owner] + (((size_t)rs.rank * rs.panels_per_shard + pin) * p.tiles_n + (r / p.tiles_m)) * 2 + rank;
+          asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(rs.epoch) : "memory");
+        }
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(tempty0 + (uint32_t)acc * 8u);  // hand the accumulator back to the leader
@@ -534,10 +635,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 // ------------------------------------------------------------------ host side
 template <typename OutT, int BN>
 int launch_pair(const b200_gemm_desc_t* g, void* d, const void* a, const void* b, cudaStream_t stream,
-                const GemmPlan& plan, const AgParams* agp) {
+                const GemmPlan& plan, const AgParams* agp, const RsParams* rsp) {
   AgParams ag{};
   if (agp) ag = *agp;
-  const int dynamic = ag.enabled ? 0 : plan.dynamic;   // copier and GEMM clusters must all be resident: static grid
+  RsParams rs{};
+  if (rsp) rs = *rsp;
+  const int dynamic = (ag.enabled || rs.enabled) ? 0 : plan.dynamic;   // helper and GEMM clusters must all be resident
   using C = Cfg<BN>;
   CUtensorMap ma, mb;
   const uint64_t esz = 2;
@@ -585,6 +688,7 @@ int launch_pair(const b200_gemm_desc_t* g, void* d, const void* a, const void* b
   // per tile is requested and the clusters that run take over the tiles of those that have not started
   int grid = dynamic ? 2 * total : 2 * std::min(total, pairs);
   if (ag.enabled) grid = 2 * (ag.copier_pairs + std::min(total, std::max(1, pairs - ag.copier_pairs)));
+  if (rs.enabled) grid = 2 * (rs.reducer_pairs + std::min(total, std::max(1, pairs - rs.reducer_pairs)));
 
 #define GEMM2_GO(AK, BKM)                                                                                        \
   do {                                                                                                           \
@@ -595,7 +699,7 @@ int launch_pair(const b200_gemm_desc_t* g, void* d, const void* a, const void* b
       if (e != cudaSuccess) return (int)e;                                                                       \
       attr_set = true;                                                                                           \
     }                                                                                                            \
-    kern<<<grid, kThreads, C::kSmem, stream>>>(ma, mb, (OutT*)d, p, dynamic, ag);                                            \
+    kern<<<grid, kThreads, C::kSmem, stream>>>(ma, mb, (OutT*)d, p, dynamic, ag, rs);                                            \
   } while (0)
 
   if (g->a_kmajor && g->b_kmajor) GEMM2_GO(true, true);
@@ -675,11 +779,11 @@ GemmPlan gemm_plan(const b200_gemm_desc_t* g) {
 }
 
 int gemm_launch_2cta(const b200_gemm_desc_t* g, void* d, const void* a, const void* b, cudaStream_t stream,
-                     const GemmPlan& plan, const AgParams* ag) {
+                     const GemmPlan& plan, const AgParams* ag, const RsParams* rs) {
   switch (g->out_dtype) {
-    case B200_BF16: return launch_pair<__nv_bfloat16, 256>(g, d, a, b, stream, plan, ag);
-    case B200_F16: return launch_pair<__half, 256>(g, d, a, b, stream, plan, ag);
-    case B200_F32: return launch_pair<float, 256>(g, d, a, b, stream, plan, ag);
+    case B200_BF16: return launch_pair<__nv_bfloat16, 256>(g, d, a, b, stream, plan, ag, rs);
+    case B200_F16: return launch_pair<__half, 256>(g, d, a, b, stream, plan, ag, rs);
+    case B200_F32: return launch_pair<float, 256>(g, d, a, b, stream, plan, ag, rs);
     default: return (int)cudaErrorNotSupported;
   }
 }
@@ -766,4 +870,40 @@ extern "C" int b200_gemm_allgather(const b200_gemm_desc_t* g, const b200_symm_t*
   plan.splits = 1;
   plan.kb_per_split = (g->k + BK - 1) / BK;
   return gemm_launch_2cta(g, d, a_full, b, stream, plan, &ag);
+}
+
+// GEMM -> reduce-scatter in one launch.  out[M / world, N] = rows `rank` of sum over ranks of A_r[M, K_r] x B_r[N, K_r]^T.
+// The partial product goes to `partial_off` of the arena ([M, N], output dtype), the flag table to `flag_off`
+// (world * M/256/world * N/256 * 2 words, zeroed once).  Consumes epochs `epoch` and `epoch + 1`.
+extern "C" int b200_gemm_reduce_scatter(const b200_gemm_desc_t* g, const b200_symm_t* s, int64_t partial_off,
+                                        int64_t flag_off, uint32_t epoch, int reducer_pairs, void* out, const void* a,
+                                        const void* b, cudaStream_t stream) {
+  using namespace b200k;
+  if (g->batch > 1 || s->world < 2 || s->world > 8 || g->m % (256 * s->world) != 0 || g->n % 256 != 0 ||
+      (partial_off & 1023) || (flag_off & 15) || reducer_pairs < 1 || reducer_pairs > 16 || g->ldd != g->n ||
+      g->bias || g->act || g->accumulate || (reinterpret_cast<uintptr_t>(out) & 15))
+    return (int)cudaErrorNotSupported;
+  if ((g->in_dtype != B200_BF16 && g->in_dtype != B200_F16) || g->out_dtype != g->in_dtype) return (int)cudaErrorNotSupported;
+  if (reducer_pairs * 2 >= gemm_sm_count() / 2) return (int)cudaErrorNotSupported;
+  RsParams rs{};
+  rs.enabled = 1;
+  rs.world = s->world;
+  rs.rank = s->rank;
+  rs.reducer_pairs = reducer_pairs;
+  rs.panels_per_shard = g->m / s->world / 256;
+  rs.panel_bytes = (int64_t)256 * g->n * 2;
+  for (int r = 0; r < s->world; ++r) {
+    rs.src[r] = static_cast<const char*>(s->bufs[r]) + partial_off;
+    rs.flag[r] = reinterpret_cast<uint32_t*>(static_cast<char*>(s->bufs[r]) + flag_off);
+    rs.sig[r] = s->sigs[r];
+  }
+  rs.out = out;
+  rs.epoch = epoch;
+  GemmPlan plan;
+  plan.pair = 1;
+  plan.dynamic = 0;
+  plan.splits = 1;
+  plan.kb_per_split = (g->k + BK - 1) / BK;
+  void* partial = static_cast<char*>(s->bufs[s->rank]) + partial_off;
+  return gemm_launch_2cta(g, partial, a, b, stream, plan, nullptr, &rs);
 }

@@ -22,21 +22,31 @@ _ids = itertools.count()
 
 
 class FusedTensorParallel:
-    def __init__(self, max_shard_bytes: int, max_rows: int, group=None, device=None, copier_pairs: int = 8):
+    FLAG_BYTES = 1 << 20
+
+    def __init__(self, max_shard_bytes: int, max_rows: int, group=None, device=None, copier_pairs: int = 8,
+                 max_partial_bytes: int = 0, reducer_pairs: int = 8):
         import torch_musa_b200 as bw
 
         self.group = group
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self.device = torch.device(device if device is not None else f"blackwell:{bw.current_device()}")
         self.max_shard_bytes = (int(max_shard_bytes) + 255) // 256 * 256
-        self.copier_pairs = copier_pairs
+        self.copier_pairs, self.reducer_pairs = copier_pairs, reducer_pairs
+        self.max_partial_bytes = (int(max_partial_bytes) + 1023) // 1024 * 1024
+        self.partial_off = (self.max_shard_bytes + 1023) // 1024 * 1024
+        self.flag_off = self.partial_off + self.max_partial_bytes
+        total = self.flag_off + self.FLAG_BYTES
         store = dist.distributed_c10d._get_default_store()
         self.sm = bw._C._create_symmetric_memory(store, f"tp_arena/{next(_ids)}", self.rank, self.world,
-                                                 self.device.index or 0, self.max_shard_bytes)
+                                                 self.device.index or 0, total)
         if not self.sm.ok:
             raise RuntimeError(f"tensor-parallel arena unavailable: {self.sm.why_not}")
         self.flags = torch.zeros(max(1, max_rows // 256), dtype=torch.int32, device=self.device)
-        self.calls = 0
+        self.sm.local_tensor(self.flag_off, [self.FLAG_BYTES // 4], torch.int32).zero_()
+        bw.synchronize()
+        dist.barrier(group)          # every rank's flag table is zero before anyone's kernel can raise a flag in it
+        self.calls = self.rs_calls = 0
 
     def ag_matmul(self, x_shard: torch.Tensor, w: torch.Tensor, group):
         rows, K = x_shard.shape
@@ -48,13 +58,28 @@ class FusedTensorParallel:
         self.calls += 1
         return y, x_full
 
+    def matmul_rs(self, x: torch.Tensor, w: torch.Tensor, group):
+        M, K = x.shape
+        N = w.shape[0]
+        flag_words = self.world * (M // 256 // self.world + 1) * (N // 256 + 1) * 2
+        if (x.dtype not in (torch.bfloat16, torch.float16) or w.dtype != x.dtype or M % (256 * self.world) or N % 256
+                or K % 8 or self.world > 8 or M * N * 2 > self.max_partial_bytes or flag_words * 4 > self.FLAG_BYTES):
+            return None
+        y = self.sm.gemm_reduce_scatter(x.contiguous(), w, self.partial_off, self.flag_off, self.reducer_pairs)
+        self.rs_calls += 1
+        return y
+
     def install(self) -> "FusedTensorParallel":
         TP.FUSED_AG_MATMUL = self.ag_matmul
+        if self.max_partial_bytes:
+            TP.FUSED_MATMUL_RS = self.matmul_rs
         return self
 
     def uninstall(self) -> None:
         if TP.FUSED_AG_MATMUL == self.ag_matmul:
             TP.FUSED_AG_MATMUL = None
+        if TP.FUSED_MATMUL_RS == self.matmul_rs:
+            TP.FUSED_MATMUL_RS = None
 
     def check(self) -> None:
         import torch_musa_b200 as bw
