@@ -42,7 +42,7 @@ def parse():
     p.add_argument("--micro-batch", type=int, default=1)
     p.add_argument("--parallelism", default="auto", choices=["auto", "fsdp", "single"])
     p.add_argument("--no-e2e", action="store_true")
-    p.add_argument("--config", default="llama_fsdp", choices=["llama_fsdp", "resnet50_ddp", "moe_ep"],
+    p.add_argument("--config", default="llama_fsdp", choices=["llama_fsdp", "resnet50_ddp", "moe_ep", "llama_tp"],
                    help="llama_fsdp: the headline Llama-7B FSDP2 step; resnet50_ddp: ResNet-50 DDP images/s")
     p.add_argument("--batch", type=int, default=256, help="resnet50_ddp: images per GPU")
     p.add_argument("--trace", default=None, help="debug: also run two extra steps under torch.profiler and write "
@@ -268,7 +268,157 @@ def _stock_package():
     llama = _load_by_path("_stock_pkg.models.llama", "models/llama.py")
     moe = _load_by_path("_stock_pkg.models.moe", "models/moe.py")
     pmoe = _load_by_path("_stock_pkg.parallel.moe", "parallel/moe.py")
+    sys.modules["_stock_pkg.parallel"].tensor_parallel = _load_by_path("_stock_pkg.parallel.tensor_parallel",
+                                                                       "parallel/tensor_parallel.py")
+    _load_by_path("_stock_pkg.parallel.loss", "parallel/loss.py")
+    sys.modules["_stock_pkg"].ops = sys.modules["_stock_pkg.ops"]
+    sys.modules["_stock_pkg"].parallel = sys.modules["_stock_pkg.parallel"]
     return llama, moe, pmoe
+
+
+def main_tp(args):
+    """Llama-7B architecture, tensor parallel over all ranks (column-parallel q/k/v/gate/up, row-parallel o/down,
+    sequence-parallel norms, vocabulary-parallel loss), bf16, one sequence of 2048 tokens per GPU in the batch
+    (batch 8 x 2048 at TP=8); forward + backward + fused AdamW step."""
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29511")
+    ours = args.impl == "ours"
+    if ours:
+        import torch_musa_b200 as bw
+        from torch_musa_b200.models.llama import LlamaConfig
+        from torch_musa_b200.models.llama_tp import TPLlama
+
+        devmod, devtype, backend = bw, "blackwell", "bccl"
+    else:
+        devmod, devtype, backend = torch.cuda, "cuda", "nccl"
+        llama_mod, _, _ = _stock_package()
+        LlamaConfig = llama_mod.LlamaConfig
+        TPLlama = _load_by_path("_stock_pkg.models.llama_tp", "models/llama_tp.py").TPLlama
+    device = torch.device(devtype, local_rank)
+    devmod.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group(backend=backend, rank=rank, world_size=world, device_id=device if not ours else None)
+
+    B, S = world, 2048
+    cfg = LlamaConfig(n_layers=args.layers, max_seq_len=S)
+    torch.manual_seed(1234)
+    with torch.device(device):
+        model = TPLlama(cfg, world).to(torch.bfloat16)
+    with torch.no_grad():
+        for p in model.parameters():
+            if p.dim() >= 2:
+                p.normal_(0.0, 0.02)
+    fused = None
+    if ours and world > 1:
+        from torch_musa_b200.parallel.fused_tp import FusedTensorParallel
+
+        T = B * S
+        fused = FusedTensorParallel(max_shard_bytes=T // world * cfg.dim * 2, max_rows=T, device=device,
+                                    max_partial_bytes=T * cfg.dim * 2).install()
+    opt = torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1, fused=True)
+    gen = torch.Generator().manual_seed(1000)          # every rank sees the same batch: tensor parallelism
+    n_batches = 4
+    host_tokens = [torch.randint(0, cfg.vocab_size, (B, S + 1), generator=gen).pin_memory() for _ in range(n_batches)]
+    dev_tokens = [t.to(device) for t in host_tokens]
+    partial_grad = model.replicated_parameters()
+
+    def step(tok):
+        loss = model(tok[:, :-1], tok[:, 1:])
+        loss.backward()
+        if world > 1:
+            flat = torch.cat([p.grad.reshape(-1) for p in partial_grad])
+            dist.all_reduce(flat)
+            off = 0
+            for p in partial_grad:
+                p.grad.copy_(flat[off:off + p.numel()].view_as(p.grad))
+                off += p.numel()
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        return loss
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        devmod.synchronize()
+
+    for i in range(args.warmup):
+        step(dev_tokens[i % n_batches])
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    if ours:
+        bw.reset_kernel_launch_count()
+    ev0, ev1 = devmod.Event(enable_timing=True), devmod.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for i in range(args.steps):
+        loss = step(dev_tokens[i % n_batches])
+    ev1.record()
+    barrier()
+    ms_total = ev0.elapsed_time(ev1)
+    launches = bw.kernel_launch_count() if ours else 0
+    final_loss = float(loss.detach().float().cpu())
+    e2e_ms, h2d, d2h = 0.0, 0, 0
+    if not args.no_e2e:
+        barrier()
+        ev2, ev3 = devmod.Event(enable_timing=True), devmod.Event(enable_timing=True)
+        ev2.record()
+        for i in range(args.steps):
+            tok = host_tokens[i % n_batches].to(device, non_blocking=True)
+            h2d += tok.numel() * tok.element_size()
+            lv = step(tok).detach().float().cpu()
+            d2h += lv.numel() * lv.element_size()
+        ev3.record()
+        barrier()
+        e2e_ms = ev2.elapsed_time(ev3)
+    clocks = sampler.stop() if rank == 0 else None
+    if args.trace:
+        from torch.profiler import ProfilerActivity, profile
+
+        with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA]) as prof:
+            for i in range(2):
+                step(dev_tokens[i % n_batches])
+            barrier()
+        prof.export_chrome_trace(f"{args.trace}.rank{rank}.json")
+    fused_calls = None
+    if fused is not None:
+        fused.check()
+        fused_calls = {"allgather_gemm": fused.calls, "gemm_reduce_scatter": fused.rs_calls}
+    if world > 1:
+        t = torch.tensor([ms_total, e2e_ms], dtype=torch.float64).to(device).float()
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total, e2e_ms = float(t[0].cpu()), float(t[1].cpu())
+    ms_per_step = ms_total / args.steps
+    toks = B * S
+    if rank == 0:
+        out = {
+            "metric": "llama7b_tp_train_tokens_per_s", "value": toks / (ms_per_step / 1e3), "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic (token ids uniform in [0,32000) from a seed; random-init weights)", "impl": args.impl,
+            "config": {"model": "llama-7b (32L d4096 h32 ffn11008 vocab32000)" if args.layers == 32 else f"llama-7b-dims-{args.layers}L (INVALID: reduced layers)",
+                       "global_batch": B, "seq_len": S,
+                       "parallelism": f"tp{world}: colwise q/k/v/gate/up, rowwise o/down, sequence-parallel norms, vocab-parallel loss",
+                       "optimizer": "fused AdamW lr 3e-4 on bf16 parameters", "fused_collective_calls": fused_calls,
+                       "cache": "weights and activations per step are far larger than the 126 MB L2"},
+            "final_loss": final_loss, "gpu_launches": launches, "clocks": clocks,
+        }
+        if not args.no_e2e:
+            out["e2e"] = {"value": toks / (e2e_ms / args.steps / 1e3), "unit": "tokens/s",
+                          "h2d_bytes_per_step": h2d // args.steps, "d2h_bytes_per_step": d2h // args.steps}
+        if ours:
+            out["fallback_ops"] = len(bw.fallback_counts())
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
 
 
 def main_moe(args):
@@ -430,6 +580,8 @@ def main():
         return main_resnet(args)
     if args.config == "moe_ep":
         return main_moe(args)
+    if args.config == "llama_tp":
+        return main_tp(args)
 
     import torch
     import torch.distributed as dist

@@ -298,25 +298,27 @@ __device__ void rs_reducer(const RsParams& rs, int tiles_n, uint8_t* stage_mem, 
                    kRsChunk, &bars[st]);
     }
   };
-  // item sequence of this CTA: cc, cc + n_cc, ...   (k-th item uses stage k & 1, phase (k >> 1) & 1)
-  long long k = 0;
-  long long first = cc;
-  if (first < n_items) {
-    const int p0 = (int)(first / chunks_per_panel);
-    wait_panel(p0);
-    waited_panel = p0;
-    if (threadIdx.x == 0 && !*abort_flag) issue(first, 0);
-  }
-  for (long long item = first; item < n_items; item += n_cc, ++k) {
+  // item sequence of this CTA: cc, cc + n_cc, ...; the k-th item uses stage k % NS with parity (k / NS) & 1 and is
+  // requested NS - 1 items ahead, so NS - 1 stages of peer reads are in flight while one stage is being summed
+  // up to 12 stages: bars[0..11] are the ring's "full" and "empty" barriers, adjacent in shared memory and all
+  // initialised with one expected arrival; a reducer CTA uses them for nothing else
+  const int NS = max(2, min(12, (int)(196608u / stage_bytes)));
+  const long long my_items = cc < n_items ? (n_items - cc + n_cc - 1) / n_cc : 0;
+  auto request = [&](long long k) {       // all threads: wait for the item's panel, then one thread issues the loads
+    const long long item = cc + k * n_cc;
+    const int pn = (int)(item / chunks_per_panel);
+    if (pn != waited_panel) { wait_panel(pn); waited_panel = pn; }
+    if (threadIdx.x == 0 && !*abort_flag) issue(item, (int)(k % NS));
+  };
+  long long requested = 0;
+  for (; requested < my_items && requested < NS - 1; ++requested) request(requested);
+  for (long long k = 0; k < my_items; ++k) {
     if (*abort_flag) break;
-    const int st = (int)(k & 1);
-    const long long next = item + n_cc;
-    if (next < n_items) {
-      const int pn = (int)(next / chunks_per_panel);
-      if (pn != waited_panel) { wait_panel(pn); waited_panel = pn; }
-      if (threadIdx.x == 0 && !*abort_flag) issue(next, st ^ 1);   // stage st^1 was drained in the previous iteration
-    }
-    if (!mbar_wait(&bars[st], (uint32_t)((k >> 1) & 1), abort_flag)) break;
+    const int st = (int)(k % NS);
+    // stage (k + NS - 1) % NS held item k - 1, which every thread finished reading before the barrier below
+    if (requested < my_items) request(requested++);
+    if (!mbar_wait(&bars[st], (uint32_t)((k / NS) & 1), abort_flag)) break;
+    const long long item = cc + k * n_cc;
     const int p = (int)(item / chunks_per_panel), c = (int)(item % chunks_per_panel);
     OutT* out = reinterpret_cast<OutT*>(static_cast<char*>(rs.out) + (long long)p * rs.panel_bytes + (long long)c * kRsChunk);
     const uint8_t* sm = stage_mem + (size_t)st * stage_bytes;

@@ -24,8 +24,8 @@ _ids = itertools.count()
 class FusedTensorParallel:
     FLAG_BYTES = 1 << 20
 
-    def __init__(self, max_shard_bytes: int, max_rows: int, group=None, device=None, copier_pairs: int = 8,
-                 max_partial_bytes: int = 0, reducer_pairs: int = 8):
+    def __init__(self, max_shard_bytes: int, max_rows: int, group=None, device=None, copier_pairs: int = 16,
+                 max_partial_bytes: int = 0, reducer_pairs: int = 16):
         import torch_musa_b200 as bw
 
         self.group = group
@@ -48,13 +48,26 @@ class FusedTensorParallel:
         dist.barrier(group)          # every rank's flag table is zero before anyone's kernel can raise a flag in it
         self.calls = self.rs_calls = 0
 
+    def _helper_pairs(self, pull_bytes: float, flops: float, limit: int) -> int:
+        """SM pairs that move data instead of multiplying: the count that minimises max(transfer, GEMM) under a
+        measured model -- p pairs pull about 35 * p^0.75 GB/s from the peers (99 / 166 / 280 GB/s at 4 / 8 / 16
+        pairs) and the GEMM runs on the remaining 74 - p pairs at about 1.3 PFLOP/s in total."""
+        best, best_t = 1, float("inf")
+        for p in range(1, limit + 1):
+            t = max(pull_bytes / (35e9 * p ** 0.75), flops / 1.3e15 * 74.0 / (74 - p))
+            if t < best_t:
+                best, best_t = p, t
+        return best
+
     def ag_matmul(self, x_shard: torch.Tensor, w: torch.Tensor, group):
         rows, K = x_shard.shape
         M = rows * self.world
         if (x_shard.dtype not in (torch.bfloat16, torch.float16) or w.dtype != x_shard.dtype or M % (256 * self.world)
                 or K % 64 or rows * K * x_shard.element_size() > self.max_shard_bytes or M // 256 > self.flags.numel()):
             return None
-        y, x_full = self.sm.gemm_allgather(x_shard.contiguous(), w, 0, self.flags, self.copier_pairs)
+        N = w.shape[0]
+        pairs = self._helper_pairs((self.world - 1) * rows * K * 2.0, 2.0 * M * N * K, self.copier_pairs)
+        y, x_full = self.sm.gemm_allgather(x_shard.contiguous(), w, 0, self.flags, pairs)
         self.calls += 1
         return y, x_full
 
@@ -65,7 +78,8 @@ class FusedTensorParallel:
         if (x.dtype not in (torch.bfloat16, torch.float16) or w.dtype != x.dtype or M % (256 * self.world) or N % 256
                 or K % 8 or self.world > 8 or M * N * 2 > self.max_partial_bytes or flag_words * 4 > self.FLAG_BYTES):
             return None
-        y = self.sm.gemm_reduce_scatter(x.contiguous(), w, self.partial_off, self.flag_off, self.reducer_pairs)
+        pairs = self._helper_pairs((self.world - 1) * (M // self.world) * N * 2.0, 2.0 * M * N * K, self.reducer_pairs)
+        y = self.sm.gemm_reduce_scatter(x.contiguous(), w, self.partial_off, self.flag_off, pairs)
         self.rs_calls += 1
         return y
 
