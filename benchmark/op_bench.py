@@ -125,6 +125,20 @@ def bench_gemm_sweep(dev, iters=10, rounds=3):
     return out
 
 
+def bench_gemm_fp8(dev, m, n, k, iters=20):
+    """Block-scaled fp8 GEMM (1x128 activation scales, 128x128 weight scales); fraction is of the bf16 peak, so a
+    value above 1 means fp8 beats the best bf16 GEMM of this machine."""
+    a = torch.randn(m, k, device=dev, dtype=torch.bfloat16)
+    qa, sa = torch.ops.blackwell.quantize_fp8_1x128(a)
+    qb = (torch.randn(n, k, device=dev) * 0.5).to(torch.float8_e4m3fn)
+    sb = torch.rand((n + 127) // 128, k // 128, device=dev) + 0.5
+    us = timeit(lambda: torch.ops.blackwell.scaled_mm(qa, qb, sa, sb, None, None, None, torch.bfloat16), dev, iters)
+    r = report("gemm_fp8_blockwise", [m, n, k], "float8_e4m3fn", us, flops=2.0 * m * n * k, launches=1)
+    usq = timeit(lambda: torch.ops.blackwell.quantize_fp8_1x128(a), dev, iters)
+    report("quantize_fp8_1x128", [m, k], torch.bfloat16, usq, nbytes=m * k * 3 + m * k // 32)
+    return r
+
+
 def bench_rmsnorm(dev, rows, cols, dt=torch.bfloat16, backward=False):
     x = torch.randn(rows, cols, device=dev, dtype=dt, requires_grad=backward)
     w = torch.ones(cols, device=dev, dtype=dt, requires_grad=backward)
@@ -198,6 +212,8 @@ def main():
     dt = getattr(torch, a.dtype)
     if a.op == "gemm":
         bench_gemm(dev, a.m, a.n, a.k, dt, a.layout, a.iters)
+    elif a.op == "gemm_fp8":
+        bench_gemm_fp8(dev, a.m, a.n, a.k, a.iters)
     elif a.op == "gemm_sweep":
         bench_gemm_sweep(dev, a.iters)
     elif a.op == "rmsnorm":

@@ -1,0 +1,65 @@
+"""The hand-written tcgen05 flash-attention forward (head_dim 128) against an fp32 softmax(QK^T)V reference, and its
+use inside F.scaled_dot_product_attention together with the library backward."""
+import math
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+
+def ref_attention(q, k, v, causal):
+    B, H, Sq, D = q.shape
+    Hkv, Sk = k.shape[1], k.shape[2]
+    kf = k.float().repeat_interleave(H // Hkv, dim=1)
+    vf = v.float().repeat_interleave(H // Hkv, dim=1)
+    s = q.float() @ kf.transpose(-1, -2) / math.sqrt(D)
+    if causal:
+        mask = torch.ones(Sq, Sk, dtype=torch.bool).tril()
+        s = s.masked_fill(~mask, float("-inf"))
+    return torch.softmax(s, -1) @ vf, torch.logsumexp(s, -1)
+
+
+@pytest.fixture
+def native_sdp(bw):
+    prev = bw._C._sdp_impl()
+    bw._C._set_sdp_impl(2)
+    yield
+    bw._C._set_sdp_impl(prev)
+
+
+@pytest.mark.parametrize("B,H,Hkv,Sq,Sk,causal", [(1, 2, 2, 128, 128, False), (2, 4, 4, 256, 256, True),
+                                                   (1, 4, 2, 384, 384, True), (1, 2, 1, 200, 200, True),
+                                                   (2, 2, 2, 128, 320, False), (1, 8, 8, 1024, 1024, True)])
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_native_forward(bw, dev, native_sdp, B, H, Hkv, Sq, Sk, causal, dt):
+    torch.manual_seed(0)
+    # [B, S, H, D] memory viewed as [B, H, S, D]: what a transformer block passes
+    q = torch.randn(B, Sq, H, 128).to(dt).transpose(1, 2)
+    k = torch.randn(B, Sk, Hkv, 128).to(dt).transpose(1, 2)
+    v = torch.randn(B, Sk, Hkv, 128).to(dt).transpose(1, 2)
+    ref, ref_lse = ref_attention(q, k, v, causal)
+    before = bw._C._native_sdp_forward_calls()
+    out = F.scaled_dot_product_attention(q.to(dev), k.to(dev), v.to(dev), is_causal=causal, enable_gqa=(H != Hkv))
+    assert bw._C._native_sdp_forward_calls() == before + 1, "the hand-written forward did not run"
+    tol = 2e-2 if dt == torch.bfloat16 else 4e-3
+    err = (out.float().cpu() - ref).abs().max()
+    assert err < tol, float(err)
+    bw.synchronize()
+    assert bw._C._gemm_status(False) == 0
+
+
+def test_native_forward_with_library_backward(bw, dev, native_sdp):
+    torch.manual_seed(1)
+    B, H, S = 2, 4, 256
+    q, k, v = (torch.randn(B, S, H, 128).to(torch.bfloat16).transpose(1, 2) for _ in range(3))
+    g = torch.randn(B, H, S, 128).to(torch.bfloat16)
+    qr, kr, vr = (t.float().requires_grad_() for t in (q, k, v))
+    ref, _ = ref_attention(qr, kr, vr, True)
+    ref.backward(g.float())
+    qd, kd, vd = (t.to(dev).requires_grad_() for t in (q, k, v))
+    out = F.scaled_dot_product_attention(qd, kd, vd, is_causal=True)
+    out.backward(g.to(dev))
+    for a, b in ((qd.grad, qr.grad), (kd.grad, kr.grad), (vd.grad, vr.grad)):
+        assert (a.float().cpu() - b).abs().max() / b.abs().max() < 3e-2

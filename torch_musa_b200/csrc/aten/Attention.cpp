@@ -19,6 +19,7 @@
 #include <torch/library.h>
 
 #include <atomic>
+#include <cmath>
 
 namespace b200 {
 namespace ops {
@@ -27,8 +28,42 @@ namespace {
 
 constexpr int64_t kMath = 0, kOverrideable = 4;
 std::atomic<bool> g_fused_sdp{true};
-// which kernel family serves the fused path: 0 = flash, 1 = cuDNN.  Fixed between a forward and its backward.
+// which kernel family serves the fused path: 0 = library flash, 1 = library cuDNN, 2 = the hand-written tcgen05
+// forward (head_dim 128) with the library flash backward.  Fixed between a forward and its backward.
 std::atomic<int> g_sdp_impl{1};
+std::atomic<int64_t> g_native_fwd_calls{0};
+
+// The hand-written forward: q [B, H, Sq, 128], k / v [B, Hkv, Sk, 128] with a contiguous last dimension.
+bool native_fwd_eligible(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, double dropout_p) {
+  return q.size(3) == 128 && dropout_p == 0.0 && q.stride(3) == 1 && k.stride(3) == 1 && v.stride(3) == 1 &&
+         q.size(0) == k.size(0) && q.numel() > 0 && k.numel() > 0;
+}
+
+bool native_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, bool is_causal, std::optional<double> scale,
+                at::Tensor* out, at::Tensor* lse) {
+  const int64_t B = q.size(0), H = q.size(1), Sq = q.size(2), D = q.size(3), Hkv = k.size(1), Sk = k.size(2);
+  // output in [B, Sq, H, D] memory viewed as [B, H, Sq, D], the layout the library kernels return
+  at::Tensor o = at::empty({B, Sq, H, D}, q.options()).transpose(1, 2);
+  at::Tensor l = at::empty({B, H, Sq}, q.options().dtype(at::kFloat));
+  b200_attn_t a{};
+  a.B = (int)B; a.H = (int)H; a.Hkv = (int)Hkv; a.Sq = (int)Sq; a.Sk = (int)Sk; a.head_dim = (int)D;
+  a.dtype = kdtype(q.scalar_type());
+  a.causal = is_causal ? 1 : 0;
+  a.scale = (float)scale.value_or(1.0 / std::sqrt((double)D));
+  a.q_sb = q.stride(0); a.q_sh = q.stride(1); a.q_ss = q.stride(2);
+  a.k_sb = k.stride(0); a.k_sh = k.stride(1); a.k_ss = k.stride(2);
+  a.v_sb = v.stride(0); a.v_sh = v.stride(1); a.v_ss = v.stride(2);
+  a.o_sb = o.stride(0); a.o_sh = o.stride(1); a.o_ss = o.stride(2);
+  DeviceSwitch sw(q.device().index());
+  int e = b200_flash_attn_fwd(&a, o.mutable_data_ptr(), l.data_ptr<float>(), q.const_data_ptr(), k.const_data_ptr(),
+                              v.const_data_ptr(), current_raw_stream(q));
+  if (e == (int)cudaErrorNotSupported) return false;
+  B200_KERNEL_CALL(e);
+  g_native_fwd_calls.fetch_add(1, std::memory_order_relaxed);
+  *out = o;
+  *lse = l;
+  return true;
+}
 
 bool fused_eligible(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
                     const std::optional<at::Tensor>& mask, double dropout_p) {
@@ -71,6 +106,15 @@ FwdRet sdpa_fused_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor
                       bool return_debug_mask, std::optional<double> scale) {
   TORCH_CHECK(!(attn_bias.has_value() && attn_bias->defined()),
               "blackwell fused attention: explicit masks take the math path (this is a dispatch bug)");
+  if (g_sdp_impl.load() == 2 && native_fwd_eligible(q, k, v, dropout_p)) {
+    at::Tensor o, l;
+    if (native_fwd(q, k, v, is_causal, scale, &o, &l)) {
+      at::Tensor none = at::empty({0}, q.options().dtype(at::kLong));
+      at::Tensor seed = at::zeros({}, q.options().dtype(at::kLong));
+      return FwdRet(o, l, at::Tensor(), at::Tensor(), c10::SymInt(q.size(2)), c10::SymInt(k.size(2)), seed, seed.clone(),
+                    at::empty({0}, q.options()));
+    }
+  }
   if (g_sdp_impl.load() == 1 && q.size(1) == k.size(1) && q.size(3) <= 128) {
     std::optional<at::Tensor> no_bias;
     auto st = run_fallback(B200_OP_HANDLE("aten::_scaled_dot_product_cudnn_attention", ""), q, k, v, no_bias,
@@ -108,6 +152,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> sdpa_fused_bwd(
 
 }  // namespace
 
+int64_t native_sdp_forward_calls() { return g_native_fwd_calls.load(); }
 void set_fused_sdp(bool on) { g_fused_sdp = on; }
 void set_sdp_impl(int impl) { g_sdp_impl = impl; }
 int sdp_impl() { return g_sdp_impl; }

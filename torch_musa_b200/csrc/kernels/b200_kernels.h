@@ -299,6 +299,40 @@ B200_API int b200_gemm_reduce_scatter(const b200_gemm_desc_t* desc, const b200_s
                                       int64_t flag_off, uint32_t epoch, int reducer_pairs, void* out, const void* a,
                                       const void* b, cudaStream_t stream);
 
+/* ---------------------------------------------------------------- block-scaled fp8 GEMM (tcgen05 kind::f8f6f4)
+ * D[M,N] = sum_kb bsa[m, kb] * bsb[n / 128, kb] * (A[m, kb-th 128 of K] . B[n, same]) * row_scale[m] * col_scale[n] + bias.
+ * A [M,K], B [N,K]: fp8 bytes, K contiguous, lda / ldb in bytes (multiples of 16). Any scale pointer may be NULL (= 1);
+ * a stride of 0 broadcasts (tensor-wise scaling = row_scale with stride 0). Block scales need K % 128 == 0. */
+typedef struct {
+  int m, n, k;
+  int64_t lda, ldb, ldd;
+  int a_e5m2, b_e5m2;
+  int out_dtype;
+  const float* block_scale_a; int64_t bsa_stride_m, bsa_stride_kb;
+  const float* block_scale_b; int64_t bsb_stride_nb, bsb_stride_kb;
+  const float* row_scale; int64_t row_scale_stride;
+  const float* col_scale; int64_t col_scale_stride;
+  const void* bias; int bias_dtype;
+} b200_fp8_gemm_t;
+B200_API int b200_gemm_fp8(const b200_fp8_gemm_t* desc, void* d, const void* a, const void* b, cudaStream_t stream);
+/* q [rows, k] fp8 bytes and scales [rows, k / 128] (amax / 448 per 1 x 128 block) from x [rows, k] (ldx elements) */
+B200_API int b200_quantize_fp8_1x128(int dtype, const void* x, void* q, float* scales, int64_t rows, int k, int64_t ldx,
+                                     int e5m2, cudaStream_t stream);
+
+/* ---------------------------------------------------------------- flash attention forward (tcgen05 + TMEM)
+ * q [B, H, Sq, 128], k / v [B, Hkv, Sk, 128] (H % Hkv == 0), out [B, H, Sq, 128], all with a contiguous last dimension
+ * and element strides (multiples of 8) for batch, head and sequence; lse [B, H, Sq] fp32 natural-log (may be NULL).
+ * causal != 0: key index <= query index. */
+typedef struct {
+  int B, H, Hkv, Sq, Sk, head_dim;
+  int dtype;
+  int causal;
+  float scale;
+  int64_t q_sb, q_sh, q_ss, k_sb, k_sh, k_ss, v_sb, v_sh, v_ss, o_sb, o_sh, o_ss;
+} b200_attn_t;
+B200_API int b200_flash_attn_fwd(const b200_attn_t* desc, void* out, float* lse, const void* q, const void* k,
+                                 const void* v, cudaStream_t stream);
+
 /* ---------------------------------------------------------------- expert-parallel MoE token exchange (bf16 rows)
  * E experts, E / world per rank in rank order; idx / slot / pos are int32 [T*K]; receive buffers hold cap_rows
  * rows of d elements at a byte offset of every rank's arena; counts_off points at world*E int32 of scratch in the

@@ -90,3 +90,14 @@ def _(grad_out, input, out, weight, save_mean, save_invstd, relu, has_residual):
     return (torch.empty_like(input), input.new_empty((c,), dtype=torch.float32),
             input.new_empty((c,), dtype=torch.float32),
             torch.empty_like(input) if has_residual else input.new_empty((0,)))
+
+
+@_reg("scaled_mm")
+def _(a, b, block_scale_a, block_scale_b, row_scale, col_scale, bias, out_dtype):
+    return a.new_empty((a.shape[0], b.shape[0]), dtype=out_dtype)
+
+
+@_reg("quantize_fp8_1x128")
+def _(x, e5m2=False):
+    q = x.new_empty(x.shape, dtype=torch.float8_e5m2 if e5m2 else torch.float8_e4m3fn)
+    return q, x.new_empty((x.shape[0], x.shape[1] // 128), dtype=torch.float32)
