@@ -1,0 +1,69 @@
+#!/usr/bin/env python
+"""Decode throughput of the Llama-7B architecture with a static KV cache: eager step loop against the same step
+replayed from a device graph.
+
+  python benchmark/decode_bench.py [--batch 32] [--kv 2048] [--layers 32] [--tokens 32]
+
+One JSON line: {"op": "decode", "batch", "kv_len", "eager_ms_per_token", "graph_ms_per_token", "graph_tokens_per_s", ...}.
+Random-init bf16 weights, random prompt; CUDA-event times after warm-up.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+import torch_musa_b200 as bw  # noqa: E402
+from torch_musa_b200.models import Llama, LlamaConfig  # noqa: E402
+from torch_musa_b200.models.decode import LlamaDecoder  # noqa: E402
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--batch", type=int, default=32)
+    ap.add_argument("--kv", type=int, default=2048)
+    ap.add_argument("--layers", type=int, default=32)
+    ap.add_argument("--tokens", type=int, default=32)
+    a = ap.parse_args()
+    dev = torch.device("blackwell:0")
+    cfg = LlamaConfig(n_layers=a.layers, max_seq_len=a.kv + a.tokens * 3 + 8)
+    torch.manual_seed(0)
+    with torch.device(dev):
+        model = Llama(cfg).to(torch.bfloat16).eval()
+    model.init_rope_cache(dev)
+    with torch.no_grad():
+        for p in model.parameters():
+            if p.dim() >= 2:
+                p.normal_(0.0, 0.02)
+    prompt = torch.randint(0, cfg.vocab_size, (a.batch, a.kv), device=dev)
+    dec = LlamaDecoder(model, a.batch, cfg.max_seq_len, device=dev)
+    dec.prefill(prompt)
+
+    def timed(n):
+        bw.synchronize()
+        s, e = bw.Event(enable_timing=True), bw.Event(enable_timing=True)
+        s.record()
+        dec.decode(n)
+        e.record()
+        bw.synchronize()
+        return s.elapsed_time(e) / n
+
+    dec.decode(4)
+    eager = timed(a.tokens)
+    dec.capture()
+    dec.decode(4)
+    graph = timed(a.tokens)
+    print(json.dumps({"op": "decode", "model": f"llama-7b dims, {a.layers} layers", "batch": a.batch, "kv_len": a.kv,
+                      "eager_ms_per_token": round(eager, 3), "graph_ms_per_token": round(graph, 3),
+                      "graph_tokens_per_s": round(a.batch / graph * 1e3, 1), "speedup": round(eager / graph, 2)}))
+
+
+if __name__ == "__main__":
+    main()
