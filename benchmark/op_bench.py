@@ -139,6 +139,23 @@ def bench_gemm_fp8(dev, m, n, k, iters=20):
     return r
 
 
+def bench_attention(dev, batch, heads, seq, dt=torch.bfloat16, iters=10):
+    """Causal attention forward, head_dim 128: the hand-written tcgen05 kernel (impl 2) and the library cuDNN kernel."""
+    q, k, v = (torch.randn(batch, seq, heads, 128, device=dev, dtype=dt).transpose(1, 2) for _ in range(3))
+    flops = 4.0 * batch * heads * seq * seq * 128 / 2          # causal: half of QK^T and PV
+    prev = bw._C._sdp_impl()
+    out = {}
+    try:
+        for impl, name in ((2, "attention_fwd_tcgen05"), (1, "attention_fwd_library_cudnn")):
+            bw._C._set_sdp_impl(impl)
+            with torch.no_grad():
+                us = timeit(lambda: F.scaled_dot_product_attention(q, k, v, is_causal=True), dev, iters)
+            out[name] = report(name, [batch, heads, seq, 128], dt, us, flops=flops)
+    finally:
+        bw._C._set_sdp_impl(prev)
+    return out
+
+
 def bench_rmsnorm(dev, rows, cols, dt=torch.bfloat16, backward=False):
     x = torch.randn(rows, cols, device=dev, dtype=dt, requires_grad=backward)
     w = torch.ones(cols, device=dev, dtype=dt, requires_grad=backward)
@@ -214,6 +231,8 @@ def main():
         bench_gemm(dev, a.m, a.n, a.k, dt, a.layout, a.iters)
     elif a.op == "gemm_fp8":
         bench_gemm_fp8(dev, a.m, a.n, a.k, a.iters)
+    elif a.op == "attention":
+        bench_attention(dev, 1, 32, a.rows, dt, a.iters)
     elif a.op == "gemm_sweep":
         bench_gemm_sweep(dev, a.iters)
     elif a.op == "rmsnorm":

@@ -63,3 +63,33 @@ def test_native_forward_with_library_backward(bw, dev, native_sdp):
     out.backward(g.to(dev))
     for a, b in ((qd.grad, qr.grad), (kd.grad, kr.grad), (vd.grad, vr.grad)):
         assert (a.float().cpu() - b).abs().max() / b.abs().max() < 3e-2
+
+
+@pytest.mark.parametrize("H,Hkv,pos", [(4, 4, 0), (8, 2, 37), (4, 4, 255), (4, 1, 100)])
+def test_decode_attention(bw, dev, H, Hkv, pos):
+    torch.manual_seed(0)
+    B, L = 3, 256
+    q = torch.randn(B, H, 128).to(torch.bfloat16)
+    kc, vc = (torch.randn(B, Hkv, L, 128).to(torch.bfloat16) for _ in range(2))
+    ref, _ = ref_attention(q.unsqueeze(2), kc[:, :, :pos + 1], vc[:, :, :pos + 1], False)
+    p = torch.tensor([pos], dtype=torch.long, device=dev)
+    out = torch.ops.blackwell.decode_attention(q.to(dev), kc.to(dev), vc.to(dev), p)
+    assert (out.float().cpu() - ref.squeeze(2)).abs().max() < 2e-2
+
+
+def test_bf16_graph_decode_runs_fused_kernel(bw, dev):
+    from torch_musa_b200.models import Llama, LlamaConfig
+    from torch_musa_b200.models.decode import LlamaDecoder
+
+    cfg = LlamaConfig(vocab_size=512, dim=256, n_layers=2, n_heads=2, ffn_dim=512, max_seq_len=64)   # head_dim 128
+    torch.manual_seed(0)
+    model = Llama(cfg).to(dev).to(torch.bfloat16).eval()
+    prompt = torch.randint(0, 512, (4, 9), device=dev)
+    a = LlamaDecoder(model, 4, 64, device=dev)
+    assert a._fused_decode
+    a.prefill(prompt)
+    eager = a.decode(6).cpu()
+    b = LlamaDecoder(model, 4, 64, device=dev)
+    b.prefill(prompt)
+    b.capture()
+    assert torch.equal(b.decode(6).cpu(), eager)

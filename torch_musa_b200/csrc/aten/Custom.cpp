@@ -12,6 +12,8 @@
 #include "aten/Ops.h"
 
 #include <ATen/Functions.h>
+
+#include <cmath>
 #include <torch/library.h>
 
 namespace b200 {
@@ -208,6 +210,26 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> rms_norm_residual(const at::Tenso
   return {y, res, rstd};
 }
 
+at::Tensor decode_attention(const at::Tensor& q, const at::Tensor& k_cache, const at::Tensor& v_cache,
+                            const at::Tensor& pos, std::optional<double> scale) {
+  check_fast(q, "decode_attention");
+  check_devices("decode_attention", q, k_cache, v_cache, pos);
+  TORCH_CHECK(q.dim() == 3 && k_cache.dim() == 4 && v_cache.sizes() == k_cache.sizes() && q.size(0) == k_cache.size(0) &&
+              q.size(2) == k_cache.size(3) && q.is_contiguous() && k_cache.is_contiguous() && v_cache.is_contiguous() &&
+              k_cache.scalar_type() == q.scalar_type() && v_cache.scalar_type() == q.scalar_type(),
+              "decode_attention: q [B, H, D] and contiguous caches [B, Hkv, max_len, D] of one dtype");
+  TORCH_CHECK(pos.scalar_type() == at::kLong && pos.numel() == 1, "decode_attention: pos must be one int64 element");
+  at::Tensor out = at::empty_like(q);
+  DeviceSwitch sw(q.device().index());
+  int e = b200_decode_attention(kdtype(q.scalar_type()), out.mutable_data_ptr(), q.const_data_ptr(), k_cache.const_data_ptr(),
+                                v_cache.const_data_ptr(), reinterpret_cast<const long long*>(pos.const_data_ptr<int64_t>()),
+                                (int)q.size(0), (int)q.size(1), (int)k_cache.size(1), (int)k_cache.size(2), (int)q.size(2),
+                                (float)scale.value_or(1.0 / std::sqrt((double)q.size(2))), current_raw_stream(q));
+  TORCH_CHECK(e != (int)cudaErrorNotSupported, "decode_attention: head_dim 128, bf16 / fp16 only");
+  B200_KERNEL_CALL(e);
+  return out;
+}
+
 void sleep_cycles(int64_t cycles) {
   B200_KERNEL_CALL(b200_sleep(cycles, get_current_stream().stream()));
 }
@@ -230,10 +252,12 @@ TORCH_LIBRARY(blackwell, m) {
   m.def("multi_tensor_scale_(Tensor(a!)[] tensors, Tensor? inv_scale, float scale, Tensor(b!) found_inf) -> ()");
   m.def("multi_tensor_axpby_(Tensor(a!)[] out, Tensor[] x, Tensor[] y, float a, float b) -> ()");
   m.def("multi_tensor_lamb_(Tensor(a!)[] params, Tensor[] grads, Tensor(b!)[] exp_avg, Tensor(c!)[] exp_avg_sq, float lr, float beta1, float beta2, float eps, float weight_decay, int step, bool bias_correction, bool grad_averaging, bool adam_w_mode, float max_grad_norm, bool use_nvlamb, Tensor? global_grad_norm) -> ()");
+  m.def("decode_attention(Tensor q, Tensor k_cache, Tensor v_cache, Tensor pos, float? scale=None) -> Tensor");
   m.def("_sleep(int cycles) -> ()");
 }
 
 TORCH_LIBRARY_IMPL(blackwell, PrivateUse1, m) {
+  m.impl("decode_attention", TORCH_FN(decode_attention));
   m.impl("rope", TORCH_FN(rope));
   m.impl("swiglu", TORCH_FN(swiglu));
   m.impl("swiglu_backward", TORCH_FN(swiglu_backward));

@@ -333,6 +333,12 @@ typedef struct {
 B200_API int b200_flash_attn_fwd(const b200_attn_t* desc, void* out, float* lse, const void* q, const void* k,
                                  const void* v, cudaStream_t stream);
 
+/* single-query attention over a static KV cache: q / out [B, H, 128], caches [B, Hkv, max_len, 128] contiguous, keys
+ * [0, *pos] visible (pos: device int64, read by the kernel, so the call is graph-capturable) */
+B200_API int b200_decode_attention(int dtype, void* out, const void* q, const void* k_cache, const void* v_cache,
+                                   const long long* pos, int B, int H, int Hkv, int max_len, int head_dim, float scale,
+                                   cudaStream_t stream);
+
 /* ---------------------------------------------------------------- expert-parallel MoE token exchange (bf16 rows)
  * E experts, E / world per rank in rank order; idx / slot / pos are int32 [T*K]; receive buffers hold cap_rows
  * rows of d elements at a byte offset of every rank's arena; counts_off points at world*E int32 of scratch in the

@@ -35,6 +35,7 @@ class LlamaDecoder:
         cos, sin = BF.precompute_rope_cache(max_len, hd, cfg.rope_theta)
         self.cos, self.sin = cos.to(self.device), sin.to(self.device)
         self._graph = None
+        self._fused_decode = (self.device.type == "blackwell" and hd == 128 and dt in (torch.bfloat16, torch.float16))
 
     # ------------------------------------------------------------------ prefill (eager, whole prompt at once)
     @torch.no_grad()
@@ -84,9 +85,14 @@ class LlamaDecoder:
             k = BF.rope(k, self.cos, self.sin, positions)
             self.k_cache[li].index_copy_(2, self.pos, k.transpose(1, 2))
             self.v_cache[li].index_copy_(2, self.pos, v.transpose(1, 2))
-            o = F.scaled_dot_product_attention(q.transpose(1, 2), self.k_cache[li], self.v_cache[li], attn_mask=mask,
-                                               enable_gqa=(kv != h))
-            x = x + a.wo(o.transpose(1, 2).reshape(B, 1, h * hd))
+            if self._fused_decode:
+                # one memory-bound kernel over the cache; the visible length comes from the device counter
+                o = torch.ops.blackwell.decode_attention(q.reshape(B, h, hd), self.k_cache[li], self.v_cache[li], self.pos)
+                o = o.view(B, 1, h * hd)
+            else:
+                o = F.scaled_dot_product_attention(q.transpose(1, 2), self.k_cache[li], self.v_cache[li], attn_mask=mask,
+                                                   enable_gqa=(kv != h)).transpose(1, 2).reshape(B, 1, h * hd)
+            x = x + a.wo(o)
             x = x + layer.ffn(layer.ffn_norm(x))
         logits = m.lm_head(m.norm(x))
         self.next_tokens.copy_(logits.argmax(-1))

@@ -101,3 +101,8 @@ def _(a, b, block_scale_a, block_scale_b, row_scale, col_scale, bias, out_dtype)
 def _(x, e5m2=False):
     q = x.new_empty(x.shape, dtype=torch.float8_e5m2 if e5m2 else torch.float8_e4m3fn)
     return q, x.new_empty((x.shape[0], x.shape[1] // 128), dtype=torch.float32)
+
+
+@_reg("decode_attention")
+def _(q, k_cache, v_cache, pos, scale=None):
+    return torch.empty_like(q)
