@@ -228,6 +228,82 @@ if os.environ.get("PYTORCH_BLACKWELL_ALLOC_CONF", "").find("cpu:unified") >= 0:
     _lazy_call(lambda: None)
 
 
+# ---------------------------------------------------------------------------
+# 5. torch.cuda-style conveniences that generic code probes for
+PluggableAllocator = BlackwellPluggableAllocator
+fork_rng = lambda devices=None, enabled=True, **kw: torch.random.fork_rng(  # noqa: E731
+    devices=devices, enabled=enabled, device_type=DEVICE_TYPE, **kw)
+
+
+class BlackwellError(RuntimeError):
+    """A failed runtime call, with the runtime's error name and description."""
+
+
+def check_error(res: int) -> None:
+    """Raises if ``res`` (a runtime status code) is not success."""
+    if int(res) != 0:
+        raise BlackwellError(f"runtime call failed with status {int(res)}")
+
+
+class _BCCL:
+    """``torch.blackwell.bccl``: version of the collective library underneath the bccl backend."""
+
+    @staticmethod
+    def version():
+        v = int(_C._nccl_version()) if hasattr(_C, "_nccl_version") else 0
+        return (v // 10000, (v // 100) % 100, v % 100)
+
+    @staticmethod
+    def is_available(tensors=None) -> bool:
+        return hasattr(_C, "_create_process_group")
+
+
+bccl = _BCCL()
+
+
+class _Backends:
+    """``torch.backends.blackwell``: precision switches and library version, in the shape of ``torch.backends.cudnn``."""
+
+    @property
+    def allow_tf32(self) -> bool:
+        return torch.backends.cuda.matmul.allow_tf32
+
+    @allow_tf32.setter
+    def allow_tf32(self, v: bool) -> None:
+        torch.backends.cuda.matmul.allow_tf32 = bool(v)
+        torch.backends.cudnn.allow_tf32 = bool(v)
+
+    @staticmethod
+    def is_available() -> bool:
+        return is_available()
+
+    @staticmethod
+    def version():
+        return tuple(int(x) for x in (torch.version.cuda or "0.0").split("."))
+
+    class flags:
+        """Context manager that sets ``allow_tf32`` for a block."""
+
+        def __init__(self, allow_tf32=None):
+            self.allow_tf32, self._prev = allow_tf32, None
+
+        def __enter__(self):
+            self._prev = torch.backends.blackwell.allow_tf32
+            if self.allow_tf32 is not None:
+                torch.backends.blackwell.allow_tf32 = self.allow_tf32
+            return self
+
+        def __exit__(self, *exc):
+            torch.backends.blackwell.allow_tf32 = self._prev
+            return False
+
+
+torch.backends.blackwell = _Backends()
+if not hasattr(torch.version, DEVICE_TYPE):
+    setattr(torch.version, DEVICE_TYPE, "sm_100a / CUDA " + str(torch.version.cuda))
+from . import utils, profiler, testing  # noqa: E402,F401
+
+
 def _autoload():
     """Entry point for torch's backend autoload (``torch.backends`` entry-point group)."""
     return None
