@@ -167,6 +167,35 @@ void init_distributed_bindings(py::module& m) {
         B200_KERNEL_CALL(e);
         return y;
       })
+      // reduce-scatter fused with the fp32 cast and the sharded AdamW step (kernels/comm.cu): grads [world * n]
+      // (bf16 or fp32, one slice per rank) are summed over ranks for this rank's slice, scaled, and applied to the
+      // owner's fp32 master shard / moments; p16 (optional) receives the updated bf16 shard.
+      .def("reduce_scatter_adamw", [](SymmetricMemory& s, const at::Tensor& grads, at::Tensor& p32, at::Tensor& m,
+                                      at::Tensor& v, const std::optional<at::Tensor>& p16, const at::Tensor& step,
+                                      double lr, double beta1, double beta2, double eps, double wd, double scale) {
+        TORCH_CHECK(s.ok(), "symmetric memory is not usable: ", s.why_not());
+        const int64_t n = p32.numel();
+        TORCH_CHECK(ops::on_device(grads) && grads.is_contiguous() && grads.numel() == n * s.world() &&
+                    (grads.scalar_type() == at::kBFloat16 || grads.scalar_type() == at::kFloat),
+                    "reduce_scatter_adamw: grads must be contiguous bf16/fp32 with world * shard elements");
+        for (const at::Tensor* t : {&p32, &m, &v})
+          TORCH_CHECK(ops::on_device(*t) && t->scalar_type() == at::kFloat && t->is_contiguous() && t->numel() == n &&
+                      t->device() == grads.device(), "reduce_scatter_adamw: p32 / m / v must be fp32 shards of equal size");
+        TORCH_CHECK(!p16 || (ops::on_device(*p16) && p16->scalar_type() == at::kBFloat16 && p16->is_contiguous() &&
+                             p16->numel() == n), "reduce_scatter_adamw: p16 must be a bf16 shard");
+        TORCH_CHECK(ops::on_device(step) && step.scalar_type() == at::kFloat && step.numel() == 1, "step: fp32 scalar on the device");
+        TORCH_CHECK(grads.numel() * (int64_t)grads.element_size() <= (int64_t)s.half_bytes(), "reduce_scatter_adamw: bucket exceeds the arena half");
+        DeviceSwitch sw(grads.device().index());
+        int64_t half = 0;
+        const uint32_t epoch = s.next_epoch(&half);
+        int e = b200_comm_reduce_scatter_adamw(s.desc(), ops::kdtype(grads.scalar_type()), grads.const_data_ptr(),
+                                               p32.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(),
+                                               p16 ? p16->mutable_data_ptr() : nullptr, n, (float)scale, epoch, half,
+                                               (float)lr, (float)beta1, (float)beta2, (float)eps, (float)wd,
+                                               step.const_data_ptr<float>(), ops::current_raw_stream(grads));
+        TORCH_CHECK(e != (int)cudaErrorNotSupported, "reduce_scatter_adamw: shard size must be a multiple of 8 and 16-byte aligned");
+        B200_KERNEL_CALL(e);
+      })
       .def("moe_gather_dot", [](SymmetricMemory& s, const at::Tensor& grad, const at::Tensor& idx, const at::Tensor& pos,
                                 int64_t E, int64_t src_off) {
         TORCH_CHECK(s.ok(), "symmetric memory is not usable: ", s.why_not());
