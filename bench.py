@@ -319,8 +319,11 @@ def main_tp(args):
         from torch_musa_b200.parallel.fused_tp import FusedTensorParallel
 
         T = B * S
+        # all-gather -> GEMM runs as one launch; GEMM -> reduce-scatter stays GEMM + the backend's reduce-scatter kernel
+        # unless B200_TP_FUSED_RS=1 (the one-launch version is slower with few ranks, see profiles/)
+        fused_rs = os.environ.get("B200_TP_FUSED_RS", "0") == "1"
         fused = FusedTensorParallel(max_shard_bytes=T // world * cfg.dim * 2, max_rows=T, device=device,
-                                    max_partial_bytes=T * cfg.dim * 2).install()
+                                    max_partial_bytes=T * cfg.dim * 2 if fused_rs else 0).install()
     opt = torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1, fused=True)
     gen = torch.Generator().manual_seed(1000)          # every rank sees the same batch: tensor parallelism
     n_batches = 4
