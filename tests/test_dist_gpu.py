@@ -334,3 +334,27 @@ def _sharded_adamw_body(rank, world):
 
 def test_fused_reduce_scatter_adamw_matches_unfused():
     run_ranks(_sharded_adamw_body, 2, "bccl", env={"NCCL_NVLS_ENABLE": "0"})
+
+
+def _remote_error_body(rank, world):
+    import datetime
+    import time
+    import torch.distributed as dist
+    import torch_musa_b200 as bw
+
+    dev = torch.device("blackwell", rank)
+    t = torch.ones(8, device=dev)
+    dist.all_reduce(t)                      # communicators are up; nothing is in flight afterwards
+    bw.synchronize()
+    pg = dist.group.WORLD._get_backend(dev)
+    if rank == 1:
+        bw._C._pg_make_test_work(pg, datetime.timedelta(milliseconds=200))     # a collective that never completes
+    deadline = time.time() + 8.0
+    while time.time() < deadline and bw._C._pg_error(pg) == 0:
+        time.sleep(0.2)
+    # rank 1 sees its own time-out, rank 0 learns of it through the store (no GPU involved on either side)
+    assert bw._C._pg_error(pg) != 0, f"rank {rank} never learned of the failure"
+
+
+def test_failure_on_one_rank_is_propagated_through_the_store():
+    run_ranks(_remote_error_body, 2, "bccl", env={"NCCL_NVLS_ENABLE": "0"})

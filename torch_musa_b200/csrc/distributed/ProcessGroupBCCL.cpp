@@ -1,5 +1,7 @@
 #include "distributed/ProcessGroupBCCL.h"
 
+#include <cstdio>
+
 #include "aten/Ops.h"
 #include "core/Backend.h"
 #include "core/CachingAllocator.h"
@@ -185,13 +187,20 @@ ProcessGroupBCCL::ProcessGroupBCCL(c10::intrusive_ptr<c10d::Store> store, int ra
   blocking_wait_ = env_flag("BCCL_BLOCKING_WAIT", false);
   if (std::getenv("BCCL_FUSED_COLLECTIVES")) opts_->use_fused_collectives = env_flag("BCCL_FUSED_COLLECTIVES", true);
   if (const char* e = std::getenv("BCCL_SYMM_HALF_MB")) opts_->fused_max_bytes = (int64_t)std::atoll(e) << 20;
+  monitoring_ = env_flag("BCCL_ENABLE_MONITORING", true);
+  propagate_error_ = env_flag("BCCL_PROPAGATE_ERROR", true);
+  dump_on_timeout_ = env_flag("BCCL_DUMP_ON_TIMEOUT", false);
+  if (const char* e = std::getenv("BCCL_HEARTBEAT_TIMEOUT_SEC")) heartbeat_timeout_s_ = std::max(1, std::atoi(e));
   watchdog_ = std::thread([this] { watchdog_loop(); });
+  if (monitoring_) monitor_ = std::thread([this] { monitor_loop(); });
 }
 
 ProcessGroupBCCL::~ProcessGroupBCCL() {
   stop_ = true;
   work_cv_.notify_all();
   if (watchdog_.joinable()) watchdog_.join();
+  monitor_cv_.notify_all();
+  if (monitor_.joinable()) monitor_.join();
   std::lock_guard<std::mutex> g(mu_);
   symm_.clear();
   for (auto& kv : comms_) {
@@ -765,6 +774,22 @@ void ProcessGroupBCCL::watchdog_loop() {
       work_cv_.wait_for(lk, period);
     }
     if (stop_.load()) break;
+    const uint64_t beat = heartbeat_.fetch_add(1, std::memory_order_relaxed) + 1;
+    // another rank reported a failed collective: surface it here without waiting for our own time-out
+    if (propagate_error_ && size_ > 1 && beat % 10 == 0 && error_.load() == c10d::ErrorType::SUCCESS) {
+      try {
+        const std::string key = "bccl/" + std::to_string(instance_id_) + "/remote_error";
+        if (store_->check({key})) {
+          auto v = store_->get(key);
+          const std::string who(v.begin(), v.end());
+          if (who != std::to_string(rank_)) {
+            error_ = c10d::ErrorType::REMOTE_ERROR;
+            LOG(ERROR) << "bccl watchdog: rank " << who << " reported a failed collective (seen on rank " << rank_ << ")";
+          }
+        }
+      } catch (...) {
+      }
+    }
     std::vector<c10::intrusive_ptr<WorkBCCL>> snapshot;
     {
       std::lock_guard<std::mutex> g(work_mu_);
@@ -830,6 +855,43 @@ void ProcessGroupBCCL::watchdog_loop() {
           }
         }
       }
+    }
+  }
+}
+
+// Heartbeat monitor: the watchdog bumps a counter every period; if the counter stands still for the heartbeat
+// time-out (a watchdog stuck inside a driver or library call), the flight recorder is dumped and the error is
+// recorded so that the training loop can react.  The process is never killed from here.
+void ProcessGroupBCCL::monitor_loop() {
+  uint64_t last = heartbeat_.load();
+  auto last_change = std::chrono::steady_clock::now();
+  while (!stop_.load()) {
+    {
+      std::unique_lock<std::mutex> lk(monitor_mu_);
+      monitor_cv_.wait_for(lk, std::chrono::seconds(1));
+    }
+    if (stop_.load()) break;
+    const uint64_t now = heartbeat_.load();
+    const auto t = std::chrono::steady_clock::now();
+    if (now != last) {
+      last = now;
+      last_change = t;
+      continue;
+    }
+    if (std::chrono::duration_cast<std::chrono::seconds>(t - last_change).count() >= heartbeat_timeout_s_) {
+      LOG(ERROR) << "bccl monitor: the watchdog of rank " << rank_ << " made no progress for " << heartbeat_timeout_s_
+                 << " s; flight recorder: " << recorder_.dump_json().substr(0, 4000);
+      if (dump_on_timeout_) {
+        const char* prefix = std::getenv("BCCL_DEBUG_INFO_TEMP_FILE");
+        const std::string path = std::string(prefix ? prefix : "/tmp/bccl_trace_rank_") + std::to_string(rank_);
+        if (FILE* f = std::fopen(path.c_str(), "w")) {
+          const std::string js = recorder_.dump_json();
+          std::fwrite(js.data(), 1, js.size(), f);
+          std::fclose(f);
+        }
+      }
+      error_ = c10d::ErrorType::TIMEOUT;
+      last_change = t;   // report once per time-out period
     }
   }
 }

@@ -185,6 +185,7 @@ class B200_EXPORT ProcessGroupBCCL final : public c10d::Backend {
                                             std::vector<at::Tensor> outputs, Fn fn, bool fused = false);
   void enqueue(c10::intrusive_ptr<WorkBCCL> w);
   void watchdog_loop();
+  void monitor_loop();   // heartbeat monitor: notices a watchdog thread that stopped making progress
   void check_tensor(const at::Tensor& t, const char* what) const;
   bool try_fused_allreduce(at::Tensor& t, const c10d::ReduceOp& op, cudaStream_t s, c10::DeviceIndex dev);
   bool try_fused_allgather(at::Tensor& out, at::Tensor& in, cudaStream_t s, c10::DeviceIndex dev);
@@ -205,6 +206,12 @@ class B200_EXPORT ProcessGroupBCCL final : public c10d::Backend {
   c10::DeviceIndex coalesced_device_ = -1;
 
   std::thread watchdog_;
+  std::thread monitor_;
+  std::atomic<uint64_t> heartbeat_{0};
+  std::mutex monitor_mu_;
+  std::condition_variable monitor_cv_;
+  bool monitoring_ = true, propagate_error_ = true, dump_on_timeout_ = false;
+  int heartbeat_timeout_s_ = 480;
   std::mutex work_mu_;
   std::condition_variable work_cv_;
   std::list<c10::intrusive_ptr<WorkBCCL>> works_;

@@ -242,10 +242,12 @@ __global__ void __launch_bounds__(THREADS) layernorm_bwd_kernel(T* __restrict__ 
 // (threads, vectors per thread) for a row of `nvec` 16-byte vectors; rows beyond 512*8 vectors are not covered
 #define B200K_ROW_LAUNCH(KERNEL, NVEC, GRID, STREAM, ...)                                        \
   do {                                                                                           \
+    /* few threads with several independent 16-byte loads each: more bytes in flight per SM and    \
+       more resident CTAs than one vector per thread */                                            \
     if ((NVEC) <= 128) KERNEL<T, 128, 1><<<(GRID), 128, 0, (STREAM)>>>(__VA_ARGS__);             \
-    else if ((NVEC) <= 256) KERNEL<T, 256, 1><<<(GRID), 256, 0, (STREAM)>>>(__VA_ARGS__);        \
-    else if ((NVEC) <= 512) KERNEL<T, 512, 1><<<(GRID), 512, 0, (STREAM)>>>(__VA_ARGS__);        \
-    else if ((NVEC) <= 1024) KERNEL<T, 512, 2><<<(GRID), 512, 0, (STREAM)>>>(__VA_ARGS__);       \
+    else if ((NVEC) <= 256) KERNEL<T, 128, 2><<<(GRID), 128, 0, (STREAM)>>>(__VA_ARGS__);        \
+    else if ((NVEC) <= 512) KERNEL<T, 128, 4><<<(GRID), 128, 0, (STREAM)>>>(__VA_ARGS__);        \
+    else if ((NVEC) <= 1024) KERNEL<T, 256, 4><<<(GRID), 256, 0, (STREAM)>>>(__VA_ARGS__);       \
     else if ((NVEC) <= 2048) KERNEL<T, 512, 4><<<(GRID), 512, 0, (STREAM)>>>(__VA_ARGS__);       \
     else KERNEL<T, 512, 8><<<(GRID), 512, 0, (STREAM)>>>(__VA_ARGS__);                           \
   } while (0)
