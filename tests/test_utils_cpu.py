@@ -41,3 +41,34 @@ def test_op_harness_on_cpu():
     OpTest(torch.add, {"input": torch.randn(4), "other": torch.randn(4)}, device="cpu").check_out_ops()
     InplaceOpCheck("mul_", torch.mul, device="cpu").check(torch.randn(6), 3.0)
     assert not DefaultComparator()(torch.zeros(2), torch.ones(2))
+
+
+def test_sharded_adamw_single_process_matches_torch():
+    from torch_musa_b200.parallel.zero import ShardedFusedAdamW
+
+    torch.manual_seed(0)
+    base = [torch.randn(64, 32) * 0.1, torch.randn(32) * 0.1]
+    ps = [torch.nn.Parameter(b.to(torch.bfloat16)) for b in base]
+    ref = [torch.nn.Parameter(b.to(torch.bfloat16).float()) for b in base]
+    o = ShardedFusedAdamW(ps, lr=1e-2, weight_decay=0.1, bucket_mb=1)
+    r = torch.optim.AdamW(ref, lr=1e-2, weight_decay=0.1)
+    for _ in range(3):
+        o.zero_grad()
+        for p, q in zip(ps, ref):
+            g = (torch.randn(p.shape) * 0.05).to(torch.bfloat16)
+            p.grad.copy_(g)
+            q.grad = g.float()
+        o.step()
+        r.step()
+    assert max(float((p.float() - q).abs().max()) for p, q in zip(ps, ref)) < 4e-3
+
+
+def test_comm_helpers_on_cpu_tensors():
+    from torch_musa_b200.parallel import data_parallel as dp
+
+    ts = [torch.randn(3, 4), torch.arange(5), torch.randn(7)]
+    out = dp.broadcast_coalesced(ts, ["cpu", "cpu"], buffer_size=64)
+    assert all(torch.equal(a, b) for copy_ in out for a, b in zip(copy_, ts))
+    x = torch.arange(12.0).view(6, 2)
+    parts = dp.scatter(x, ["cpu", "cpu", "cpu"])
+    assert torch.equal(dp.gather(parts), x) and torch.equal(dp.reduce_add(parts), parts[0] + parts[1] + parts[2])
