@@ -71,38 +71,76 @@ __global__ void __launch_bounds__(kThreads) rope_kernel(T* __restrict__ out, con
 // ------------------------------------------------------------------- SwiGLU
 __device__ __forceinline__ float silu_f(float g) { return g / (1.f + __expf(-g)); }
 
+// One CTA per (row, chunk of kSwU * blockDim vectors): no index division, four independent gate / up loads in
+// flight per thread before the first use.
+constexpr int kSwU = 4;
+constexpr int kSwThreads = 128;
+
 template <typename T>
-__global__ void __launch_bounds__(kThreads) swiglu_fwd_kernel(T* __restrict__ out, const T* __restrict__ x,
-                                                              int64_t rows, int64_t h) {
+__global__ void __launch_bounds__(kSwThreads) swiglu_fwd_kernel(T* __restrict__ out, const T* __restrict__ x,
+                                                                int64_t rows, int64_t h) {
   constexpr int V = Vec16<T>::N;
-  const int64_t vh = h / V, total = rows * vh;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    int64_t r = i / vh, c = (i % vh) * V;
-    Vec16<T> g = ld16_stream(x + r * 2 * h + c), u = ld16_stream(x + r * 2 * h + h + c), o;
+  const int vh = (int)(h / V);
+  const int64_t r = blockIdx.x;
+  const T* gp = x + r * 2 * h;
+  const T* up = gp + h;
+  T* op = out + r * h;
+  const int v0 = blockIdx.y * (kSwThreads * kSwU) + threadIdx.x;
+  Vec16<T> g[kSwU], u[kSwU];
 #pragma unroll
-    for (int k = 0; k < V; ++k) o.v[k] = ToF<T>::from(silu_f(ToF<T>::to(g.v[k])) * ToF<T>::to(u.v[k]));
-    st16_stream(out + r * h + c, o);
+  for (int k = 0; k < kSwU; ++k) {
+    const int v = v0 + k * kSwThreads;
+    if (v < vh) { g[k] = ld16_stream(gp + (int64_t)v * V); u[k] = ld16_stream(up + (int64_t)v * V); }
+  }
+#pragma unroll
+  for (int k = 0; k < kSwU; ++k) {
+    const int v = v0 + k * kSwThreads;
+    if (v < vh) {
+      Vec16<T> o;
+#pragma unroll
+      for (int e = 0; e < V; ++e) o.v[e] = ToF<T>::from(silu_f(ToF<T>::to(g[k].v[e])) * ToF<T>::to(u[k].v[e]));
+      st16_stream(op + (int64_t)v * V, o);
+    }
   }
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kThreads) swiglu_bwd_kernel(T* __restrict__ dx, const T* __restrict__ dy,
-                                                              const T* __restrict__ x, int64_t rows, int64_t h) {
+__global__ void __launch_bounds__(kSwThreads) swiglu_bwd_kernel(T* __restrict__ dx, const T* __restrict__ dy,
+                                                                const T* __restrict__ x, int64_t rows, int64_t h) {
   constexpr int V = Vec16<T>::N;
-  const int64_t vh = h / V, total = rows * vh;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    int64_t r = i / vh, c = (i % vh) * V;
-    Vec16<T> g = ld16_stream(x + r * 2 * h + c), u = ld16_stream(x + r * 2 * h + h + c), d = ld16_stream(dy + r * h + c);
-    Vec16<T> dg, du;
+  const int vh = (int)(h / V);
+  const int64_t r = blockIdx.x;
+  const T* gp = x + r * 2 * h;
+  const T* up = gp + h;
+  const T* dp = dy + r * h;
+  T* dgp = dx + r * 2 * h;
+  T* dup = dgp + h;
+  const int v0 = blockIdx.y * (kSwThreads * kSwU) + threadIdx.x;
+  Vec16<T> g[kSwU], u[kSwU], d[kSwU];
 #pragma unroll
-    for (int k = 0; k < V; ++k) {
-      float gf = ToF<T>::to(g.v[k]), uf = ToF<T>::to(u.v[k]), df = ToF<T>::to(d.v[k]);
-      float s = 1.f / (1.f + __expf(-gf));
-      dg.v[k] = ToF<T>::from(df * uf * s * (1.f + gf * (1.f - s)));
-      du.v[k] = ToF<T>::from(df * gf * s);
+  for (int k = 0; k < kSwU; ++k) {
+    const int v = v0 + k * kSwThreads;
+    if (v < vh) {
+      g[k] = ld16_stream(gp + (int64_t)v * V);
+      u[k] = ld16_stream(up + (int64_t)v * V);
+      d[k] = ld16_stream(dp + (int64_t)v * V);
     }
-    st16_stream(dx + r * 2 * h + c, dg);
-    st16_stream(dx + r * 2 * h + h + c, du);
+  }
+#pragma unroll
+  for (int k = 0; k < kSwU; ++k) {
+    const int v = v0 + k * kSwThreads;
+    if (v < vh) {
+      Vec16<T> dg, du;
+#pragma unroll
+      for (int e = 0; e < V; ++e) {
+        const float gf = ToF<T>::to(g[k].v[e]), uf = ToF<T>::to(u[k].v[e]), df = ToF<T>::to(d[k].v[e]);
+        const float sg = 1.f / (1.f + __expf(-gf));
+        dg.v[e] = ToF<T>::from(df * uf * sg * (1.f + gf * (1.f - sg)));
+        du.v[e] = ToF<T>::from(df * gf * sg);
+      }
+      st16_stream(dgp + (int64_t)v * V, dg);
+      st16_stream(dup + (int64_t)v * V, du);
+    }
   }
 }
 
@@ -335,7 +373,9 @@ int b200_swiglu_fwd(int dtype, void* out, const void* x, int64_t rows, int64_t h
   if (rows == 0 || h == 0) return 0;
   B200K_DISPATCH_FLOAT(dtype, T, {
     if (h % Vec16<T>::N != 0 || !aligned16((const T*)x) || !aligned16((T*)out)) return (int)cudaErrorNotSupported;
-    swiglu_fwd_kernel<T><<<grid_cap(rows * h / Vec16<T>::N), kThreads, 0, stream>>>((T*)out, (const T*)x, rows, h);
+    const unsigned chunks = (unsigned)cdiv(h / Vec16<T>::N, (int64_t)kSwThreads * kSwU);
+    if (rows > 2147483647ll || chunks > 65535u) return (int)cudaErrorNotSupported;
+    swiglu_fwd_kernel<T><<<dim3((unsigned)rows, chunks), kSwThreads, 0, stream>>>((T*)out, (const T*)x, rows, h);
     B200K_LAUNCH_RET();
   })
   return (int)cudaErrorNotSupported;
@@ -346,7 +386,9 @@ int b200_swiglu_bwd(int dtype, void* dx, const void* dy, const void* x, int64_t 
   B200K_DISPATCH_FLOAT(dtype, T, {
     if (h % Vec16<T>::N != 0 || !aligned16((const T*)x) || !aligned16((T*)dx) || !aligned16((const T*)dy))
       return (int)cudaErrorNotSupported;
-    swiglu_bwd_kernel<T><<<grid_cap(rows * h / Vec16<T>::N), kThreads, 0, stream>>>((T*)dx, (const T*)dy, (const T*)x, rows, h);
+    const unsigned chunks = (unsigned)cdiv(h / Vec16<T>::N, (int64_t)kSwThreads * kSwU);
+    if (rows > 2147483647ll || chunks > 65535u) return (int)cudaErrorNotSupported;
+    swiglu_bwd_kernel<T><<<dim3((unsigned)rows, chunks), kSwThreads, 0, stream>>>((T*)dx, (const T*)dy, (const T*)x, rows, h);
     B200K_LAUNCH_RET();
   })
   return (int)cudaErrorNotSupported;
