@@ -213,3 +213,14 @@ def test_module_and_autocast(bw, dev):
         assert s.dtype == torch.float32
     ref = torch.nn.functional.linear(x.cpu(), lin.weight.detach().cpu(), lin.bias.detach().cpu())
     assert torch.allclose(y.float().cpu(), ref, atol=5e-2, rtol=5e-2)
+
+
+def test_legacy_autograd_profiler_uses_device_stubs(bw, dev):
+    """torch.autograd.profiler with use_device='blackwell' times operators through the backend's profiler stubs."""
+    x = torch.randn(512, 512, device=dev)
+    with torch.autograd.profiler.profile(use_device="blackwell", use_kineto=False) as prof:
+        for _ in range(3):
+            (x @ x).relu_()
+        bw.synchronize()
+    table = prof.key_averages().table(sort_by="self_cpu_time_total", row_limit=5)
+    assert "aten::mm" in table
