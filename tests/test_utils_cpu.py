@@ -72,3 +72,23 @@ def test_comm_helpers_on_cpu_tensors():
     x = torch.arange(12.0).view(6, 2)
     parts = dp.scatter(x, ["cpu", "cpu", "cpu"])
     assert torch.equal(dp.gather(parts), x) and torch.equal(dp.reduce_add(parts), parts[0] + parts[1] + parts[2])
+
+
+def test_kv_cache_decoder_matches_full_recompute_on_cpu():
+    from torch_musa_b200.models import Llama, llama_tiny_config
+    from torch_musa_b200.models.decode import LlamaDecoder
+
+    cfg = llama_tiny_config(n_kv_heads=2)
+    torch.manual_seed(0)
+    m = Llama(cfg).eval()
+    prompt = torch.randint(0, cfg.vocab_size, (3, 5))
+    d = LlamaDecoder(m, 3, 32)
+    d.prefill(prompt)
+    got = d.decode(6)
+    seq, want = prompt.clone(), []
+    with torch.no_grad():
+        for _ in range(6):
+            nxt = m(seq)[:, -1].argmax(-1, keepdim=True)
+            want.append(nxt)
+            seq = torch.cat([seq, nxt], 1)
+    assert torch.equal(got, torch.cat(want, 1))
