@@ -452,7 +452,7 @@ def main_moe(args):
         dist.init_process_group(backend=backend, rank=rank, world_size=world, device_id=device if not ours else None)
 
     B, S = 2, 4096
-    cfg = MoEConfig(n_layers=args.layers if args.layers != 32 else 8, max_seq_len=S)
+    cfg = MoEConfig(n_layers=args.layers if args.layers != 32 else 8, max_seq_len=S, synthetic_router_logits=True)
     torch.manual_seed(1234)
     with torch.device(device):
         model = MoETransformer(cfg, ep_world=world).to(torch.bfloat16)
@@ -557,7 +557,7 @@ def main_moe(args):
             "config": {"model": f"mixtral-style moe ({cfg.n_layers}L d4096 h32/kv8, 8 experts x ffn14336, top-2)",
                        "global_batch": B * world, "seq_len": S, "tokens_per_gpu": B * S,
                        "parallelism": f"ep{world} ({cfg.n_experts // world} expert(s) per GPU), replicated attention/router",
-                       "expert_gemm": "bf16", "optimizer": "fused AdamW lr 3e-4 on bf16 parameters",
+                       "expert_gemm": "bf16", "router": "top-2 softmax over logits drawn N(0,1) per token", "optimizer": "fused AdamW lr 3e-4 on bf16 parameters",
                        "cache": "weights and activations per step are far larger than the 126 MB L2"},
             "final_loss": final_loss, "gpu_launches": launches, "clocks": clocks,
         }

@@ -34,6 +34,9 @@ class MoEConfig:
     rope_theta: float = 10000.0
     max_seq_len: int = 4096
     capacity_factor: float = 2.0
+    # benchmark mode: router logits are drawn N(0,1) per token instead of computed, so that expert loads are
+    # balanced in expectation whatever the weights are (the router projection stays in the graph with zero weight)
+    synthetic_router_logits: bool = False
 
     def attention_config(self) -> LlamaConfig:
         return LlamaConfig(vocab_size=self.vocab_size, dim=self.dim, n_layers=self.n_layers, n_heads=self.n_heads,
@@ -84,6 +87,8 @@ class MoEFeedForward(nn.Module):
         B, S, D = x.shape
         flat = x.reshape(B * S, D)
         logits = self.router(flat).float()
+        if self.cfg.synthetic_router_logits:
+            logits = logits * 0.0 + torch.randn(logits.shape, device=logits.device, dtype=torch.float32)
         top, idx = torch.topk(logits, self.cfg.top_k, dim=-1)
         gates = torch.softmax(top, dim=-1)                 # softmax over the selected logits (Mixtral)
         ex = self._exchange[0]
