@@ -55,17 +55,27 @@ __device__ __forceinline__ MaxSum row_stats(const T* __restrict__ xr, int64_t co
   constexpr int V = Vec16<T>::N;
   MaxSum acc{-INFINITY, 0.f};
   if constexpr (VEC) {
-    int64_t nvec = cols / V;
-    for (int64_t i = threadIdx.x; i < nvec; i += blockDim.x) {
-      Vec16<T> v = ld16(xr + i * V);
-      float f[V];
-      float lm = -INFINITY;
+    const int64_t nvec = cols / V;
+    constexpr int U = 4;   // independent 16-byte loads in flight per thread; the max / sum update stays sequential
+    for (int64_t i0 = threadIdx.x; i0 < nvec; i0 += (int64_t)blockDim.x * U) {
+      Vec16<T> vv[U];
 #pragma unroll
-      for (int k = 0; k < V; ++k) { f[k] = ToF<T>::to(v.v[k]); lm = fmaxf(lm, f[k]); }
-      if (lm > acc.m) { acc.s *= __expf(acc.m - lm); acc.m = lm; }
-      if (acc.m != -INFINITY) {
+      for (int u = 0; u < U; ++u) {
+        const int64_t i = i0 + (int64_t)u * blockDim.x;
+        if (i < nvec) vv[u] = ld16(xr + i * V);
+      }
 #pragma unroll
-        for (int k = 0; k < V; ++k) acc.s += __expf(f[k] - acc.m);
+      for (int u = 0; u < U; ++u) {
+        if (i0 + (int64_t)u * blockDim.x >= nvec) break;
+        float f[V];
+        float lm = -INFINITY;
+#pragma unroll
+        for (int k = 0; k < V; ++k) { f[k] = ToF<T>::to(vv[u].v[k]); lm = fmaxf(lm, f[k]); }
+        if (lm > acc.m) { acc.s *= __expf(acc.m - lm); acc.m = lm; }
+        if (acc.m != -INFINITY) {
+#pragma unroll
+          for (int k = 0; k < V; ++k) acc.s += __expf(f[k] - acc.m);
+        }
       }
     }
   } else {
@@ -172,16 +182,29 @@ __global__ void __launch_bounds__(kThreads) ce_bwd_kernel(T* __restrict__ dlogit
   T* dr = dlogits + row * cols;
   const float on = 1.f - smoothing, off = smoothing / (float)cols;
   if constexpr (VEC) {
-    int64_t nvec = cols / V;
-    for (int64_t i = threadIdx.x; i < nvec; i += blockDim.x) {
-      Vec16<T> v = ld16(xr + i * V), o;
+    const int64_t nvec = cols / V;
+    constexpr int U = 4;   // independent 16-byte loads in flight per thread
+    for (int64_t i0 = threadIdx.x; i0 < nvec; i0 += (int64_t)blockDim.x * U) {
+      Vec16<T> v[U];
 #pragma unroll
-      for (int k = 0; k < V; ++k) {
-        float p = __expf(ToF<T>::to(v.v[k]) - l);
-        float y = ((i * V + k) == t ? on : 0.f) + off;
-        o.v[k] = ToF<T>::from(g * (p - y));
+      for (int u = 0; u < U; ++u) {
+        const int64_t i = i0 + (int64_t)u * blockDim.x;
+        if (i < nvec) v[u] = ld16(xr + i * V);
       }
-      st16(dr + i * V, o);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int64_t i = i0 + (int64_t)u * blockDim.x;
+        if (i < nvec) {
+          Vec16<T> o;
+#pragma unroll
+          for (int k = 0; k < V; ++k) {
+            const float p = __expf(ToF<T>::to(v[u].v[k]) - l);
+            const float y = ((i * V + k) == t ? on : 0.f) + off;
+            o.v[k] = ToF<T>::from(g * (p - y));
+          }
+          st16(dr + i * V, o);
+        }
+      }
     }
   } else {
     for (int64_t i = threadIdx.x; i < cols; i += blockDim.x) {
