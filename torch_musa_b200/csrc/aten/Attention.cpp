@@ -19,6 +19,7 @@
 #include <torch/library.h>
 
 #include <atomic>
+#include <cstdlib>
 #include <cmath>
 
 namespace b200 {
@@ -34,6 +35,16 @@ std::atomic<int> g_sdp_impl{1};
 std::atomic<int64_t> g_native_fwd_calls{0};
 
 // The hand-written forward: q [B, H, Sq, 128], k / v [B, Hkv, Sk, 128] with a contiguous last dimension.
+// The cuDNN-style library kernels: head_dim <= 128; grouped-query heads only when B200_SDP_CUDNN_GQA=1 (default on).
+bool cudnn_route_ok(const at::Tensor& q, const at::Tensor& k) {
+  static const bool gqa = [] {
+    const char* e = std::getenv("B200_SDP_CUDNN_GQA");
+    return !(e && e[0] == '0');
+  }();
+  if (q.size(3) > 128) return false;
+  return q.size(1) == k.size(1) || (gqa && q.size(1) % k.size(1) == 0);
+}
+
 bool native_fwd_eligible(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, double dropout_p) {
   return q.size(3) == 128 && dropout_p == 0.0 && q.stride(3) == 1 && k.stride(3) == 1 && v.stride(3) == 1 &&
          q.size(0) == k.size(0) && q.numel() > 0 && k.numel() > 0;
@@ -115,7 +126,7 @@ FwdRet sdpa_fused_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor
                     at::empty({0}, q.options()));
     }
   }
-  if (g_sdp_impl.load() == 1 && q.size(1) == k.size(1) && q.size(3) <= 128) {
+  if (g_sdp_impl.load() == 1 && cudnn_route_ok(q, k)) {
     std::optional<at::Tensor> no_bias;
     auto st = run_fallback(B200_OP_HANDLE("aten::_scaled_dot_product_cudnn_attention", ""), q, k, v, no_bias,
                            /*compute_log_sumexp=*/true, dropout_p, is_causal, return_debug_mask, scale);
@@ -136,7 +147,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> sdpa_fused_bwd(
     c10::SymInt max_k, double dropout_p, bool is_causal, const at::Tensor& philox_seed,
     const at::Tensor& philox_offset, std::optional<double> scale) {
   (void)grad_input_mask;
-  if (g_sdp_impl.load() == 1 && q.size(1) == k.size(1) && q.size(3) <= 128) {
+  if (g_sdp_impl.load() == 1 && cudnn_route_ok(q, k)) {
     at::Tensor no_bias;
     auto st = run_fallback(B200_OP_HANDLE("aten::_scaled_dot_product_cudnn_attention_backward", ""), grad_out, q, k, v,
                            out, logsumexp, philox_seed, philox_offset, no_bias, cum_seq_q, cum_seq_k, max_q, max_k,

@@ -99,8 +99,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         const int r = tb - b * tiles_per_batch;
         const int kb0 = split * p.kb_per_split;
         const int kb1 = min(k_blocks, kb0 + p.kb_per_split);
-        const int m0 = (r % p.tiles_m) * BM;
-        const int n0 = (r / p.tiles_m) * BN;
+        int mt, nt;
+        decode_tile(r, p.tiles_m, p.tiles_n, p.group_m, mt, nt);
+        const int m0 = mt * BM;
+        const int n0 = nt * BN;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
           mbar_expect_tx(&full_bar[stage], kStageBytes);
@@ -171,8 +173,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const int tb = tile - split * tiles_all_batches;
       const int b = tb / tiles_per_batch;
       const int r = tb - b * tiles_per_batch;
-      const int m0 = (r % p.tiles_m) * BM;
-      const int n0 = (r / p.tiles_m) * BN;
+      int mt, nt;
+      decode_tile(r, p.tiles_m, p.tiles_n, p.group_m, mt, nt);
+      const int m0 = mt * BM;
+      const int n0 = nt * BN;
       if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) break;
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
@@ -364,6 +368,7 @@ int launch(const b200_gemm_desc_t* g, void* d, const void* a, const void* b, cud
   p.splits = plan.splits;
   p.kb_per_split = plan.kb_per_split;
   p.split_stride = (int64_t)g->m * g->n;
+  p.group_m = gemm_group_m(BM, plan.splits > 1 ? plan.kb_per_split * BK : g->k);
 
   const int total = p.tiles_m * p.tiles_n * p.batch * p.splits;
   int dev = 0, sms = kSMs;

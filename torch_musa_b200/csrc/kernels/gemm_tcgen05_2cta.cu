@@ -451,9 +451,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int r = tb - b * tiles_per_batch;
         const int kb0 = split * p.kb_per_split;
         const int kb1 = min(k_blocks, kb0 + p.kb_per_split);
-        const int mt = ((r % p.tiles_m) + m_rot) % p.tiles_m;
+        int mt_raw, nt;
+        decode_tile(r, p.tiles_m, p.tiles_n, p.group_m, mt_raw, nt);
+        const int mt = (mt_raw + m_rot) % p.tiles_m;
         const int m0 = mt * BM2 + (int)rank * BMH;
-        const int n0 = (r / p.tiles_m) * BN + (int)rank * C::kBHalf;
+        const int n0 = nt * BN + (int)rank * C::kBHalf;
         if (ag.enabled) {
           // the 256-row panel of this tile must have been assembled by a copier CTA of this launch
           if (!wait_word<false>(ag.flags + mt, ag.epoch, abort_flag)) { ok = false; break; }
@@ -554,8 +556,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const int tb = tile - split * tiles_all_batches;
       const int b = tb / tiles_per_batch;
       const int r = tb - b * tiles_per_batch;
-      const int m0 = (((r % p.tiles_m) + m_rot) % p.tiles_m) * BM2 + (int)rank * BMH;
-      const int n0 = (r / p.tiles_m) * BN;
+      int mt_raw, nt;
+      decode_tile(r, p.tiles_m, p.tiles_n, p.group_m, mt_raw, nt);
+      const int mt_e = (mt_raw + m_rot) % p.tiles_m;
+      const int m0 = mt_e * BM2 + (int)rank * BMH;
+      const int n0 = nt * BN;
       if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) break;
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
@@ -600,9 +605,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         __threadfence_system();
         asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps
         if (warp == 2 && lane == 0) {
-          const int mt = ((r % p.tiles_m) + m_rot) % p.tiles_m;
-          const int owner = mt / rs.panels_per_shard, pin = mt - owner * rs.panels_per_shard;
-          uint32_t* f = rs.flag[owner] + (((size_t)rs.rank * rs.panels_per_shard + pin) * p.tiles_n + (r / p.tiles_m)) * 2 + rank;
+          const int owner = mt_e / rs.panels_per_shard, pin = mt_e - owner * rs.panels_per_shard;
+          uint32_t* f = rs.flag[owner] + (((size_t)rs.rank * rs.panels_per_shard + pin) * p.tiles_n + nt) * 2 + rank;
           asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(rs.epoch) : "memory");
         }
       }
@@ -683,6 +687,7 @@ int launch_pair(const b200_gemm_desc_t* g, void* d, const void* a, const void* b
   p.splits = plan.splits;
   p.kb_per_split = plan.kb_per_split;
   p.split_stride = (int64_t)g->m * g->n;
+  p.group_m = gemm_group_m(BM2, plan.splits > 1 ? plan.kb_per_split * BK : g->k);
 
   const int total = p.tiles_m * p.tiles_n * p.batch * p.splits;
   const int pairs = std::max(1, gemm_sm_count() / 2);
