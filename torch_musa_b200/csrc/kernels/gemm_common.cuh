@@ -139,10 +139,12 @@ struct Params {
   int group_m;   // row tiles per L2 group (see decode_tile)
 };
 
-// Row tiles per group such that the A rows of one group (group x tile_rows x K elements of 2 bytes) take about 48 MB,
-// well inside the 126 MB L2 together with the B tiles in flight.
-inline int gemm_group_m(int tile_rows, int k) {
+// Row tiles per L2 group.  While all of A (M x K elements of 2 bytes) fits in about three quarters of the 126 MB L2
+// one group covers every row tile (A stays resident, B streams once); beyond that a group's A rows take about 48 MB.
+inline int gemm_group_m(int tile_rows, int m, int k) {
   const long long per_tile = (long long)tile_rows * k * 2;
+  const int tiles_m = (m + tile_rows - 1) / tile_rows;
+  if ((long long)m * k * 2 <= (96ll << 20)) return tiles_m > 0 ? tiles_m : 1;
   long long g = (48ll << 20) / (per_tile > 0 ? per_tile : 1);
   if (g < 2) g = 2;
   if (g > 32) g = 32;

@@ -368,7 +368,7 @@ int launch(const b200_gemm_desc_t* g, void* d, const void* a, const void* b, cud
   p.splits = plan.splits;
   p.kb_per_split = plan.kb_per_split;
   p.split_stride = (int64_t)g->m * g->n;
-  p.group_m = gemm_group_m(BM, plan.splits > 1 ? plan.kb_per_split * BK : g->k);
+  p.group_m = gemm_group_m(BM, g->m, plan.splits > 1 ? plan.kb_per_split * BK : g->k);
 
   const int total = p.tiles_m * p.tiles_n * p.batch * p.splits;
   int dev = 0, sms = kSMs;
