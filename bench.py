@@ -576,6 +576,11 @@ def main_moe(args):
 
 def main():
     args = parse()
+    if os.environ.get("B200_BENCH_DUMP_AFTER_S"):
+        # debugging aid: if the run is still alive after this many seconds, print every thread's Python stack and exit
+        import faulthandler
+
+        faulthandler.dump_traceback_later(int(os.environ["B200_BENCH_DUMP_AFTER_S"]), exit=True)
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
         return 0
