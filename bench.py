@@ -576,11 +576,13 @@ def main_moe(args):
 
 def main():
     args = parse()
-    if os.environ.get("B200_BENCH_DUMP_AFTER_S"):
-        # debugging aid: if the run is still alive after this many seconds, print every thread's Python stack and exit
+    deadline = int(os.environ.get("B200_BENCH_DUMP_AFTER_S", "900"))
+    if deadline > 0:
+        # a run normally ends within two minutes; one that is still alive after the deadline prints every thread's
+        # Python stack and exits instead of occupying the GPUs until somebody kills it (0 disables)
         import faulthandler
 
-        faulthandler.dump_traceback_later(int(os.environ["B200_BENCH_DUMP_AFTER_S"]), exit=True)
+        faulthandler.dump_traceback_later(deadline, exit=True)
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
         return 0
