@@ -42,6 +42,17 @@ bool try_native_cast_copy(const at::Tensor& src, const at::Tensor& dst, cudaStre
 
 inline cudaStream_t current_raw_stream(const at::Tensor& t) { return get_current_stream(t.device().index()).stream(); }
 
+// Kernels that take an epoch, a sequence number or an arena half as a launch argument must not be recorded into a
+// graph: a replay would repeat the recorded value and skip the cross-rank ordering.
+inline void check_not_capturing(cudaStream_t s, const char* what) {
+  cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(s, &st) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return;
+  }
+  TORCH_CHECK(st == cudaStreamCaptureStatusNone, what, ": peer-memory kernels cannot be captured into a graph");
+}
+
 // Switch the tcgen05 GEMM off/on (off: every matmul goes to the library GEMM through the fallback).
 B200_EXPORT void set_tensor_core_gemm(bool on);
 B200_EXPORT bool tensor_core_gemm_enabled();

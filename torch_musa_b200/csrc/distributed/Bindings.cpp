@@ -18,6 +18,32 @@ void init_distributed_bindings(py::module& m) {
   using dist::ProcessGroupBCCL;
   using dist::SymmetricMemory;
 
+  // Layout of one sharded parameter group (kernels/fsdp_comm.cu): built once, passed to every launch.
+  struct FsdpLayout { b200_fsdp_layout_t L{}; };
+  py::class_<FsdpLayout, std::shared_ptr<FsdpLayout>>(m, "_FsdpLayout")
+      .def(py::init([](std::vector<int64_t> shard_numel, std::vector<int64_t> shard_off, std::vector<int64_t> full_numel,
+                       int64_t total) {
+        TORCH_CHECK(!shard_numel.empty() && shard_numel.size() <= B200_FSDP_MAX_TENSORS, "fsdp layout: 1..",
+                    B200_FSDP_MAX_TENSORS, " tensors per group");
+        TORCH_CHECK(shard_off.size() == shard_numel.size() && full_numel.size() == shard_numel.size(), "fsdp layout: list lengths differ");
+        auto l = std::make_shared<FsdpLayout>();
+        l->L.n = (int)shard_numel.size();
+        for (size_t i = 0; i < shard_numel.size(); ++i) {
+          l->L.shard_numel[i] = shard_numel[i];
+          l->L.shard_off[i] = shard_off[i];
+          l->L.full_numel[i] = full_numel[i];
+        }
+        l->L.total = total;
+        return l;
+      }))
+      .def_property_readonly("n", [](FsdpLayout& l) { return l.L.n; })
+      .def_property_readonly("total", [](FsdpLayout& l) { return l.L.total; });
+  m.attr("_FSDP_MAX_TENSORS") = (int)B200_FSDP_MAX_TENSORS;
+  m.def("_comm_user_word0", [] { return b200_comm_user_word0(); });
+  m.def("_comm_pad_words", [] { return b200_comm_pad_words(); });
+  m.def("_comm_set_wait_ms", [](double ms) { b200_comm_set_wait_ms(ms); });
+  m.def("_comm_get_wait_ms", [] { return b200_comm_get_wait_ms(); });
+
   py::class_<SymmetricMemory, std::shared_ptr<SymmetricMemory>>(m, "_SymmetricMemory")
       .def_property_readonly("ok", &SymmetricMemory::ok)
       .def_property_readonly("why_not", &SymmetricMemory::why_not)
@@ -29,6 +55,107 @@ void init_distributed_bindings(py::module& m) {
         return s.local_tensor(off, sizes, dt);
       })
       .def_property_readonly("size_bytes", [](SymmetricMemory& s) { return (int64_t)(2 * s.half_bytes()); })
+      // ---- sharded-parameter collectives (kernels/fsdp_comm.cu); all on the device's current stream
+      .def("fsdp_pack", [](SymmetricMemory& s, const std::shared_ptr<FsdpLayout>& lay, const std::vector<at::Tensor>& srcs,
+                           int64_t shadow_off, at::ScalarType shadow_dtype, int64_t flag_word, int64_t version,
+                           int64_t counter_word, int64_t n_ctas) {
+        TORCH_CHECK(s.ok(), "symmetric memory is not usable: ", s.why_not());
+        TORCH_CHECK((int)srcs.size() == lay->L.n, "fsdp_pack: expected ", lay->L.n, " tensors");
+        const void* ptrs[B200_FSDP_MAX_TENSORS];
+        for (int i = 0; i < lay->L.n; ++i) {
+          const at::Tensor& t = srcs[i];
+          TORCH_CHECK(ops::on_device(t) && t.is_contiguous() && t.numel() >= lay->L.shard_numel[i] &&
+                      t.scalar_type() == srcs[0].scalar_type() && t.device() == srcs[0].device(),
+                      "fsdp_pack: tensor ", i, " must be a contiguous device shard of the group's dtype");
+          ptrs[i] = t.const_data_ptr();
+        }
+        TORCH_CHECK(shadow_off >= 0 && shadow_off + lay->L.total * (int64_t)c10::elementSize(shadow_dtype) <=
+                    (int64_t)(2 * s.half_bytes()), "fsdp_pack: the flat shard does not fit the arena");
+        DeviceSwitch sw(srcs[0].device().index());
+        cudaStream_t stream = ops::current_raw_stream(srcs[0]);
+        ops::check_not_capturing(stream, "fsdp_pack");
+        int e = b200_fsdp_pack(s.desc(), &lay->L, ptrs, ops::kdtype(srcs[0].scalar_type()), shadow_off,
+                               ops::kdtype(shadow_dtype), (int)flag_word, (uint32_t)version, (int)counter_word,
+                               (int)n_ctas, stream);
+        TORCH_CHECK(e != (int)cudaErrorNotSupported, "fsdp_pack: dtype pair not covered");
+        B200_KERNEL_CALL(e);
+      })
+      .def("fsdp_gather", [](SymmetricMemory& s, const std::shared_ptr<FsdpLayout>& lay, const std::vector<at::Tensor>& outs,
+                             int64_t shadow_off, int64_t flag_word, int64_t version, int64_t n_ctas) {
+        TORCH_CHECK(s.ok(), "symmetric memory is not usable: ", s.why_not());
+        TORCH_CHECK((int)outs.size() == lay->L.n, "fsdp_gather: expected ", lay->L.n, " tensors");
+        void* ptrs[B200_FSDP_MAX_TENSORS];
+        for (int i = 0; i < lay->L.n; ++i) {
+          const at::Tensor& t = outs[i];
+          TORCH_CHECK(ops::on_device(t) && t.is_contiguous() && t.numel() >= lay->L.shard_numel[i] * s.world() &&
+                      t.scalar_type() == outs[0].scalar_type() && t.device() == outs[0].device(),
+                      "fsdp_gather: output ", i, " must hold world * shard elements of the group's dtype");
+          ptrs[i] = t.mutable_data_ptr();
+        }
+        DeviceSwitch sw(outs[0].device().index());
+        cudaStream_t stream = ops::current_raw_stream(outs[0]);
+        ops::check_not_capturing(stream, "fsdp_gather");
+        B200_KERNEL_CALL(b200_fsdp_gather(s.desc(), &lay->L, ptrs, ops::kdtype(outs[0].scalar_type()), shadow_off,
+                                          (int)flag_word, (uint32_t)version, (int)n_ctas, stream));
+      })
+      .def("fsdp_reduce", [](SymmetricMemory& s, const std::shared_ptr<FsdpLayout>& lay, const std::vector<at::Tensor>& grads,
+                             int64_t stage_off, double scale, const std::optional<at::Tensor>& out32,
+                             const std::vector<at::Tensor>& p32, const std::vector<at::Tensor>& m1,
+                             const std::vector<at::Tensor>& m2, std::vector<double> hyper, int64_t shadow_off,
+                             at::ScalarType shadow_dtype, int64_t shadow_word, int64_t shadow_version,
+                             int64_t ready_word, int64_t ack_word, int64_t seq, int64_t ack_need, int64_t counter_word,
+                             int64_t n_ctas) {
+        TORCH_CHECK(s.ok(), "symmetric memory is not usable: ", s.why_not());
+        const int n = lay->L.n;
+        TORCH_CHECK((int)grads.size() == n, "fsdp_reduce: expected ", n, " gradients");
+        const void* gp[B200_FSDP_MAX_TENSORS];
+        for (int i = 0; i < n; ++i) {
+          const at::Tensor& t = grads[i];
+          TORCH_CHECK(ops::on_device(t) && t.is_contiguous() && t.numel() == lay->L.full_numel[i] &&
+                      t.scalar_type() == grads[0].scalar_type() && t.device() == grads[0].device(),
+                      "fsdp_reduce: gradient ", i, " must be contiguous with the unsharded element count");
+          gp[i] = t.const_data_ptr();
+        }
+        const int64_t esz = (int64_t)grads[0].element_size();
+        TORCH_CHECK(stage_off >= 0 && (s.world() == 1 || stage_off + (int64_t)s.world() * lay->L.total * esz <=
+                    (int64_t)(2 * s.half_bytes())), "fsdp_reduce: staging slots exceed the arena");
+        b200_fsdp_adamw_t opt{};
+        const bool fused_opt = !p32.empty();
+        if (fused_opt) {
+          TORCH_CHECK((int)p32.size() == n && (int)m1.size() == n && (int)m2.size() == n && hyper.size() == 6,
+                      "fsdp_reduce: optimizer state lists must match the group");
+          for (int i = 0; i < n; ++i) {
+            for (const at::Tensor* t : {&p32[i], &m1[i], &m2[i]})
+              TORCH_CHECK(ops::on_device(*t) && t->scalar_type() == at::kFloat && t->is_contiguous() &&
+                          t->numel() >= lay->L.shard_numel[i] && t->device() == grads[0].device(),
+                          "fsdp_reduce: master shards and moments must be fp32 with shard_numel elements");
+            opt.p[i] = p32[i].data_ptr<float>();
+            opt.m[i] = m1[i].data_ptr<float>();
+            opt.v[i] = m2[i].data_ptr<float>();
+          }
+          opt.lr = (float)hyper[0]; opt.beta1 = (float)hyper[1]; opt.beta2 = (float)hyper[2]; opt.eps = (float)hyper[3];
+          opt.weight_decay = (float)hyper[4]; opt.step = (float)hyper[5];
+          opt.shadow_off = shadow_off;
+          opt.shadow_dtype = ops::kdtype(shadow_dtype);
+          opt.shadow_flag_word = (int)shadow_word;
+          opt.shadow_version = (uint32_t)shadow_version;
+          if (shadow_off >= 0)
+            TORCH_CHECK(shadow_off + lay->L.total * (int64_t)c10::elementSize(shadow_dtype) <= (int64_t)(2 * s.half_bytes()),
+                        "fsdp_reduce: the flat shard does not fit the arena");
+        } else {
+          TORCH_CHECK(out32 && ops::on_device(*out32) && out32->scalar_type() == at::kFloat && out32->is_contiguous() &&
+                      out32->numel() >= lay->L.total, "fsdp_reduce: out32 must be an fp32 flat shard");
+        }
+        DeviceSwitch sw(grads[0].device().index());
+        cudaStream_t stream = ops::current_raw_stream(grads[0]);
+        ops::check_not_capturing(stream, "fsdp_reduce");
+        int e = b200_fsdp_reduce(s.desc(), &lay->L, gp, ops::kdtype(grads[0].scalar_type()), stage_off, (float)scale,
+                                 fused_opt ? nullptr : out32->data_ptr<float>(), fused_opt ? &opt : nullptr,
+                                 (int)ready_word, (int)ack_word, (uint32_t)seq, (uint32_t)ack_need, (int)counter_word,
+                                 (int)n_ctas, stream);
+        TORCH_CHECK(e != (int)cudaErrorNotSupported, "fsdp_reduce: dtype combination not covered");
+        B200_KERNEL_CALL(e);
+      })
       // ---- expert-parallel token exchange (kernels/moe.cu); all on the device's current stream
       .def("moe_count", [](SymmetricMemory& s, const at::Tensor& idx, int64_t E) {
         TORCH_CHECK(ops::on_device(idx) && idx.scalar_type() == at::kInt && idx.is_contiguous(), "idx: int32 device tensor");
@@ -54,6 +181,7 @@ void init_distributed_bindings(py::module& m) {
         DeviceSwitch sw(x.device().index());
         at::Tensor pos = at::empty_like(idx);
         at::Tensor recv_counts = at::empty({E / s.world()}, idx.options());
+        ops::check_not_capturing(ops::current_raw_stream(x), "moe_dispatch");
         const uint32_t epoch = s.next_epoch(nullptr);
         B200_KERNEL_CALL(b200_moe_dispatch(s.desc(), x.const_data_ptr(), idx.const_data_ptr<int>(),
                                            slot.const_data_ptr<int>(), counts.const_data_ptr<int>(), pos.data_ptr<int>(),
@@ -70,6 +198,7 @@ void init_distributed_bindings(py::module& m) {
                     "moe_gather: weights must be fp32 [tokens, k]");
         DeviceSwitch sw(idx.device().index());
         at::Tensor out = at::empty({idx.size(0), d}, idx.options().dtype(at::kBFloat16));
+        ops::check_not_capturing(ops::current_raw_stream(idx), "moe_gather");
         const uint32_t epoch = s.next_epoch(nullptr);
         B200_KERNEL_CALL(b200_moe_gather(s.desc(), out.mutable_data_ptr(), idx.const_data_ptr<int>(),
                                          pos.const_data_ptr<int>(), w ? w->const_data_ptr<float>() : nullptr,
@@ -86,6 +215,7 @@ void init_distributed_bindings(py::module& m) {
         TORCH_CHECK(!w || (w->scalar_type() == at::kFloat && w->sizes() == idx.sizes() && w->is_contiguous()),
                     "moe_scatter: weights must be fp32 [tokens, k]");
         DeviceSwitch sw(x.device().index());
+        ops::check_not_capturing(ops::current_raw_stream(x), "moe_scatter");
         const uint32_t epoch = s.next_epoch(nullptr);
         B200_KERNEL_CALL(b200_moe_scatter(s.desc(), x.const_data_ptr(), idx.const_data_ptr<int>(),
                                           pos.const_data_ptr<int>(), w ? w->const_data_ptr<float>() : nullptr,
@@ -123,6 +253,7 @@ void init_distributed_bindings(py::module& m) {
         g.out_dtype = g.in_dtype;
         g.batch = 1;
         g.alpha = 1.f;
+        ops::check_not_capturing(ops::current_raw_stream(x_shard), "gemm_allgather");
         const uint32_t epoch = s.next_epoch(nullptr);
         int e = b200_gemm_allgather(&g, s.desc(), shard_off, x_full.mutable_data_ptr(),
                                     reinterpret_cast<uint32_t*>(flags.data_ptr<int>()), epoch, (int)copier_pairs,
@@ -158,6 +289,7 @@ void init_distributed_bindings(py::module& m) {
         g.out_dtype = g.in_dtype;
         g.batch = 1;
         g.alpha = 1.f;
+        ops::check_not_capturing(ops::current_raw_stream(x), "gemm_reduce_scatter");
         const uint32_t epoch = s.next_epoch(nullptr);
         int e = b200_gemm_reduce_scatter(&g, s.desc(), partial_off, flag_off, epoch, (int)reducer_pairs,
                                          y.mutable_data_ptr(), x.const_data_ptr(), w.const_data_ptr(),
@@ -186,6 +318,7 @@ void init_distributed_bindings(py::module& m) {
         TORCH_CHECK(ops::on_device(step) && step.scalar_type() == at::kFloat && step.numel() == 1, "step: fp32 scalar on the device");
         TORCH_CHECK(grads.numel() * (int64_t)grads.element_size() <= (int64_t)s.half_bytes(), "reduce_scatter_adamw: bucket exceeds the arena half");
         DeviceSwitch sw(grads.device().index());
+        ops::check_not_capturing(ops::current_raw_stream(grads), "reduce_scatter_adamw");
         int64_t half = 0;
         const uint32_t epoch = s.next_epoch(&half);
         int e = b200_comm_reduce_scatter_adamw(s.desc(), ops::kdtype(grads.scalar_type()), grads.const_data_ptr(),

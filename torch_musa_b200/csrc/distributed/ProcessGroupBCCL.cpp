@@ -16,7 +16,6 @@
 namespace b200 {
 namespace dist {
 
-std::atomic<int> ProcessGroupBCCL::g_instances{0};
 
 namespace {
 
@@ -165,6 +164,12 @@ bool WorkBCCL::wait(std::chrono::milliseconds timeout) {
       }
       std::this_thread::sleep_for(std::chrono::microseconds(200));
     }
+    if (symm_) {
+      if (const int st = symm_->peek_status())
+        set_exception(std::make_exception_ptr(c10::DistBackendError(
+            {__func__, __FILE__, static_cast<uint32_t>(__LINE__)},
+            c10::str("bccl: the peer-memory kernel of work seq ", seq_, " gave up waiting for rank ", st - 1))));
+    }
     std::lock_guard<std::mutex> g(mutex_);
     if (exception_) std::rethrow_exception(exception_);
   }
@@ -181,8 +186,7 @@ float WorkBCCL::getDuration() const {
 ProcessGroupBCCL::ProcessGroupBCCL(c10::intrusive_ptr<c10d::Store> store, int rank, int size,
                                    c10::intrusive_ptr<Options> opts)
     : c10d::Backend(rank, size), store_(std::move(store)), opts_(std::move(opts)),
-      recorder_((size_t)(std::getenv("BCCL_TRACE_BUFFER_SIZE") ? std::atoi(std::getenv("BCCL_TRACE_BUFFER_SIZE")) : 2048)),
-      instance_id_(g_instances.fetch_add(1)) {
+      recorder_((size_t)(std::getenv("BCCL_TRACE_BUFFER_SIZE") ? std::atoi(std::getenv("BCCL_TRACE_BUFFER_SIZE")) : 2048)) {
   timing_ = env_flag("BCCL_ENABLE_TIMING", false);
   blocking_wait_ = env_flag("BCCL_BLOCKING_WAIT", false);
   if (std::getenv("BCCL_FUSED_COLLECTIVES")) opts_->use_fused_collectives = env_flag("BCCL_FUSED_COLLECTIVES", true);
@@ -191,6 +195,9 @@ ProcessGroupBCCL::ProcessGroupBCCL(c10::intrusive_ptr<c10d::Store> store, int ra
   propagate_error_ = env_flag("BCCL_PROPAGATE_ERROR", true);
   dump_on_timeout_ = env_flag("BCCL_DUMP_ON_TIMEOUT", false);
   if (const char* e = std::getenv("BCCL_HEARTBEAT_TIMEOUT_SEC")) heartbeat_timeout_s_ = std::max(1, std::atoi(e));
+  // device-side waits on other ranks give up after the group's time-out (BCCL_DEVICE_WAIT_MS overrides)
+  if (const char* e = std::getenv("BCCL_DEVICE_WAIT_MS")) b200_comm_set_wait_ms(std::atof(e));
+  else if (opts_->timeout.count() > 0) b200_comm_set_wait_ms((double)opts_->timeout.count());
   watchdog_ = std::thread([this] { watchdog_loop(); });
   if (monitoring_) monitor_ = std::thread([this] { monitor_loop(); });
 }
@@ -223,9 +230,11 @@ ProcessGroupBCCL::Comm& ProcessGroupBCCL::get_comm(c10::DeviceIndex device) {
   if (it != comms_.end()) return *it->second;
   DeviceSwitch sw(device);
   auto c = std::make_unique<Comm>(get_stream_from_pool(opts_->is_high_priority_stream, device));
-  // rendezvous: rank 0 creates the id and publishes it under a key unique to (this group instance, device slot)
+  // rendezvous: rank 0 creates the id and publishes it under a key unique to the device slot.  The store handed to a
+  // backend is already prefixed per group, and a process-local counter in the key would differ between members
+  // that created their groups in different orders.
   ncclUniqueId id;
-  const std::string key = "bccl/" + std::to_string(instance_id_) + "/uid/" + std::to_string(comms_.size());
+  const std::string key = "bccl/uid/" + std::to_string(comms_.size());
   if (rank_ == 0) {
     BCCL_NCCL_CHECK(ncclGetUniqueId(&id));
     store_->set(key, std::vector<uint8_t>(reinterpret_cast<uint8_t*>(&id), reinterpret_cast<uint8_t*>(&id) + sizeof(id)));
@@ -248,7 +257,7 @@ std::shared_ptr<SymmetricMemory> ProcessGroupBCCL::symmetric_memory(c10::DeviceI
   std::lock_guard<std::mutex> g(mu_);
   auto it = symm_.find(device);
   if (it != symm_.end()) return it->second;
-  const std::string key = "bccl/" + std::to_string(instance_id_) + "/symm/" + std::to_string(symm_.size());
+  const std::string key = "bccl/symm/" + std::to_string(symm_.size());
   auto s = std::make_shared<SymmetricMemory>(store_, key, rank_, size_, device, (size_t)opts_->fused_max_bytes);
   if (!s->ok() && rank_ == 0)
     TORCH_WARN("bccl: peer-memory collectives are off for this group (", s->why_not(), "); using NCCL");
@@ -309,6 +318,7 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupBCCL::collective(c10d::OpType type, c
   for (auto& t : inputs) a->record_stream(t.storage().data_ptr(), dev, c.stream.stream());
   for (auto& t : outputs) a->record_stream(t.storage().data_ptr(), dev, c.stream.stream());
 
+  const uint64_t fused_before = fused_count_.load();
   try {
     fn(c.comm, c.stream.stream());
   } catch (...) {
@@ -320,6 +330,11 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupBCCL::collective(c10d::OpType type, c
     for (auto& t : outputs) coalesced_tensors_.push_back(t);
     coalesced_device_ = dev;
     return work;  // the group's single Work is produced by endCoalescing()
+  }
+  if (fused_count_.load() != fused_before) {
+    std::lock_guard<std::mutex> g(mu_);
+    auto it = symm_.find(dev);
+    if (it != symm_.end()) work->symm_ = it->second;
   }
   work->end_.record(c.stream);
   {
@@ -370,12 +385,23 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupBCCL::endCoalescing() {
 // ------------------------------------------------------------------ fused (peer-memory) paths
 namespace {
 bool fused_dtype(at::ScalarType t) { return t == at::kFloat || t == at::kBFloat16 || t == at::kHalf; }
+// The peer-memory kernels take their epoch and arena half as launch arguments, so a replayed graph would reuse
+// stale values: while the stream is being captured every rank takes the NCCL path instead (capture state is
+// rank-invariant: all ranks capture the same program).
+bool capturing(cudaStream_t s) {
+  cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(s, &st) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return false;
+  }
+  return st != cudaStreamCaptureStatusNone;
+}
 }
 
 bool ProcessGroupBCCL::try_fused_allreduce(at::Tensor& t, const c10d::ReduceOp& op, cudaStream_t s,
                                            c10::DeviceIndex dev) {
   // rank-invariant eligibility only: every rank must take the same branch
-  if (!opts_->use_fused_collectives || size_ < 2 || coalescing_ > 0) return false;
+  if (!opts_->use_fused_collectives || size_ < 2 || coalescing_ > 0 || capturing(s)) return false;
   if (!(op == c10d::ReduceOp::SUM || op == c10d::ReduceOp::AVG) || !fused_dtype(t.scalar_type())) return false;
   const int64_t n = t.numel();
   const int64_t bytes = n * (int64_t)t.element_size();
@@ -395,7 +421,7 @@ bool ProcessGroupBCCL::try_fused_allreduce(at::Tensor& t, const c10d::ReduceOp& 
 }
 
 bool ProcessGroupBCCL::try_fused_allgather(at::Tensor& out, at::Tensor& in, cudaStream_t s, c10::DeviceIndex dev) {
-  if (!opts_->use_fused_collectives || size_ < 2 || coalescing_ > 0) return false;
+  if (!opts_->use_fused_collectives || size_ < 2 || coalescing_ > 0 || capturing(s)) return false;
   const int64_t bytes = in.numel() * (int64_t)in.element_size();
   if (bytes % 16 != 0 || bytes > opts_->fused_max_bytes || bytes < 1024) return false;
   auto sm = symmetric_memory(dev);
@@ -411,7 +437,7 @@ bool ProcessGroupBCCL::try_fused_allgather(at::Tensor& out, at::Tensor& in, cuda
 
 bool ProcessGroupBCCL::try_fused_reduce_scatter(at::Tensor& out, at::Tensor& in, const c10d::ReduceOp& op,
                                                 cudaStream_t s, c10::DeviceIndex dev) {
-  if (!opts_->use_fused_collectives || size_ < 2 || coalescing_ > 0) return false;
+  if (!opts_->use_fused_collectives || size_ < 2 || coalescing_ > 0 || capturing(s)) return false;
   if (!(op == c10d::ReduceOp::SUM || op == c10d::ReduceOp::AVG) || !fused_dtype(in.scalar_type()) ||
       !fused_dtype(out.scalar_type()))
     return false;
@@ -436,7 +462,7 @@ bool ProcessGroupBCCL::try_fused_reduce_scatter(at::Tensor& out, at::Tensor& in,
 
 // Equal splits only: every rank can then compute every offset without an exchange of split tables.
 bool ProcessGroupBCCL::try_fused_alltoall_equal(at::Tensor& out, at::Tensor& in, cudaStream_t s, c10::DeviceIndex dev) {
-  if (!opts_->use_fused_collectives || size_ < 2 || coalescing_ > 0) return false;
+  if (!opts_->use_fused_collectives || size_ < 2 || coalescing_ > 0 || capturing(s)) return false;
   const int64_t bytes = in.numel() * (int64_t)in.element_size();
   if (bytes % (16 * size_) != 0 || bytes > opts_->fused_max_bytes || bytes < 1024 || out.numel() != in.numel()) return false;
   auto sm = symmetric_memory(dev);
@@ -778,7 +804,7 @@ void ProcessGroupBCCL::watchdog_loop() {
     // another rank reported a failed collective: surface it here without waiting for our own time-out
     if (propagate_error_ && size_ > 1 && beat % 10 == 0 && error_.load() == c10d::ErrorType::SUCCESS) {
       try {
-        const std::string key = "bccl/" + std::to_string(instance_id_) + "/remote_error";
+        const std::string key = std::string("bccl/remote_error");
         if (store_->check({key})) {
           auto v = store_->get(key);
           const std::string who(v.begin(), v.end());
@@ -799,7 +825,17 @@ void ProcessGroupBCCL::watchdog_loop() {
       bool retire = false;
       try {
         bool done = !w->test_only_ && w->end_.is_created() && w->end_.query();
-        if (done) {
+        const int kst = done && w->symm_ ? w->symm_->peek_status() : 0;
+        if (done && kst) {
+          // the kernel ran to its end, but only because one of its waits on a peer ran out: its output is not valid
+          w->set_exception(std::make_exception_ptr(c10::DistBackendError(
+              {__func__, __FILE__, static_cast<uint32_t>(__LINE__)},
+              c10::str("bccl: the peer-memory kernel of collective seq ", w->seq_, " on rank ", rank_,
+                       " gave up waiting for rank ", kst - 1))));
+          recorder_.complete(w->record_id_, "failed", -1.f);
+          error_ = c10d::ErrorType::TIMEOUT;
+          retire = true;
+        } else if (done) {
           float ms = -1.f;
           if (w->timing_) ms = w->start_.elapsed_ms(w->end_);
           recorder_.complete(w->record_id_, "completed", ms);
@@ -818,7 +854,7 @@ void ProcessGroupBCCL::watchdog_loop() {
           LOG(ERROR) << "bccl watchdog: collective seq " << w->seq_ << " timed out on rank " << rank_
                      << "; flight recorder: " << recorder_.dump_json().substr(0, 2000);
           try {
-            store_->set("bccl/" + std::to_string(instance_id_) + "/remote_error", std::to_string(rank_));
+            store_->set(std::string("bccl/remote_error"), std::to_string(rank_));
           } catch (...) {
           }
           retire = true;

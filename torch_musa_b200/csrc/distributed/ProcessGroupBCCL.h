@@ -99,6 +99,8 @@ class WorkBCCL final : public c10d::Work {
   uint64_t record_id_ = 0;
   std::atomic<bool> aborted_{false};
   bool test_only_ = false;
+  // set when the collective ran on a peer-memory kernel: its bounded waits report through this arena's status word
+  std::shared_ptr<SymmetricMemory> symm_;
 };
 
 class B200_EXPORT ProcessGroupBCCL final : public c10d::Backend {
@@ -219,8 +221,6 @@ class B200_EXPORT ProcessGroupBCCL final : public c10d::Backend {
   std::atomic<c10d::ErrorType> error_{c10d::ErrorType::SUCCESS};
   FlightRecorder recorder_;
   std::atomic<int64_t> fused_count_{0};
-  static std::atomic<int> g_instances;
-  int instance_id_;
 };
 
 }  // namespace dist

@@ -41,6 +41,8 @@ class B200_EXPORT SymmetricMemory {
   uint32_t next_epoch(int64_t* half_offset);
   // Non-zero if any kernel on this arena gave up on a bounded wait (cleared by the read).
   int take_status();
+  // Same word without clearing it.
+  int peek_status() const { return status_host_ ? *(volatile int*)status_host_ : 0; }
   // A tensor view over the local arena (byte offset from the arena base).
   at::Tensor local_tensor(int64_t byte_offset, at::IntArrayRef sizes, at::ScalarType dtype);
   void* peer_base(int r) const { return desc_.bufs[r]; }

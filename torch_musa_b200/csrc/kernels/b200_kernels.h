@@ -258,7 +258,14 @@ typedef struct {
   int* status;
 } b200_symm_t;
 B200_API int b200_comm_max_world(void);
+/* Limit of every device-side wait on another rank (default 2 s); a kernel whose wait runs out sets `status`
+ * and returns.  Process-wide, read at launch time. */
+B200_API void b200_comm_set_wait_ms(double ms);
+B200_API double b200_comm_get_wait_ms(void);
 B200_API size_t b200_comm_signal_bytes(void);
+/* words [user_word0, pad_words) of a signal pad belong to the arena's owner (kernel-wide flags, counters) */
+B200_API int b200_comm_user_word0(void);
+B200_API int b200_comm_pad_words(void);
 /* out = scale * sum_ranks(in), n elements (n % 8 == 0); arena use: n*sizeof(in) at in_off, n*sizeof(out) at out_off */
 B200_API int b200_comm_allreduce(const b200_symm_t* s, int in_dtype, int out_dtype, const void* in, void* out,
                                  int64_t n, float scale, uint32_t epoch, int64_t in_off, int64_t out_off,
@@ -280,6 +287,46 @@ B200_API int b200_comm_reduce_scatter_adamw(const b200_symm_t* s, int in_dtype, 
 B200_API int b200_comm_alltoall(const b200_symm_t* s, const void* in, void* out, int64_t in_bytes,
                                 const int64_t* send_off, const int64_t* recv_off, const int64_t* recv_len,
                                 const int64_t* peer_send_off, uint32_t epoch, int64_t in_off, cudaStream_t stream);
+
+/* ---- sharded-parameter collectives (kernels/fsdp_comm.cu).  A parameter group is a list of tensors, each cut
+ * into `world` equal (padded) shards along its first dimension; rank r's shards are laid out in one flat buffer
+ * ("flat shard": tensor i at element offset shard_off[i], a multiple of 8, `total` elements, a multiple of 8).
+ * Flag and counter arguments are word indices into the signal pad (b200_comm_user_word0 and up); a flag occupies
+ * 16 consecutive words (one per source rank), a counter block 2 words that are zero between launches. */
+#define B200_FSDP_MAX_TENSORS 40
+typedef struct {
+  int n;
+  int64_t shard_numel[B200_FSDP_MAX_TENSORS];
+  int64_t shard_off[B200_FSDP_MAX_TENSORS];
+  int64_t full_numel[B200_FSDP_MAX_TENSORS]; /* elements of the unsharded tensor, <= world * shard_numel */
+  int64_t total;
+} b200_fsdp_layout_t;
+typedef struct {
+  float* p[B200_FSDP_MAX_TENSORS];           /* fp32 master shards, moments: shard_numel[i] elements each */
+  float* m[B200_FSDP_MAX_TENSORS];
+  float* v[B200_FSDP_MAX_TENSORS];
+  float lr, beta1, beta2, eps, weight_decay, step;
+  int64_t shadow_off;                        /* byte offset of the low-precision flat shard in the arena, -1: none */
+  int shadow_dtype;
+  int shadow_flag_word;
+  uint32_t shadow_version;
+} b200_fsdp_adamw_t;
+/* shadow (flat shard at shadow_off of the local arena, dst_dtype) = cast(srcs[i]); then flag_word[rank] = version
+ * in every peer's pad. */
+B200_API int b200_fsdp_pack(const b200_symm_t* s, const b200_fsdp_layout_t* L, const void* const* srcs, int src_dtype,
+                            int64_t shadow_off, int dst_dtype, int flag_word, uint32_t version, int counter_word,
+                            int n_ctas, cudaStream_t stream);
+/* outs[i][p * shard_numel[i] + e] = rank p's flat shard [shard_off[i] + e], after flag_word[p] >= version */
+B200_API int b200_fsdp_gather(const b200_symm_t* s, const b200_fsdp_layout_t* L, void* const* outs, int dtype,
+                              int64_t shadow_off, int flag_word, uint32_t version, int n_ctas, cudaStream_t stream);
+/* Gradient reduce-scatter: grads[i] (grad_dtype, full_numel[i] elements) -> this rank's shard of the sum over
+ * ranks, times scale, in fp32: written to out32 (flat shard) or consumed by the AdamW epilogue (`opt`).  Staging:
+ * world slots of `total` elements (grad_dtype) at stage_off of every arena.  seq: number of this call (same on all
+ * ranks, growing); ack_need: the call number whose completion on every peer frees this staging buffer (0: none). */
+B200_API int b200_fsdp_reduce(const b200_symm_t* s, const b200_fsdp_layout_t* L, const void* const* grads,
+                              int grad_dtype, int64_t stage_off, float scale, float* out32,
+                              const b200_fsdp_adamw_t* opt, int ready_word, int ack_word, uint32_t seq,
+                              uint32_t ack_need, int counter_word, int n_ctas, cudaStream_t stream);
 
 /* all-gather -> GEMM in ONE launch: D[M, N] = rows gathered from every rank's shard [M / world, K] (at shard_off of
  * its arena) times B[N, K]^T.  A few copier CTAs stream the peers' shards into a_full [M, K] (local) with bulk

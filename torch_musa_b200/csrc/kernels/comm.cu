@@ -43,31 +43,6 @@ __device__ __forceinline__ void copy_packets(T* __restrict__ dst, const T* __res
   for (; v < npk; v += stride) st16(dst + v * V, ld16(src + v * V));
 }
 
-// 8-element packet load converted to fp32 and added into acc
-template <typename TI>
-__device__ __forceinline__ void load_packet(const TI* __restrict__ p, TI (&tmp)[8]) {
-#pragma unroll
-  for (int q = 0; q < 8 * (int)sizeof(TI) / 16; ++q)
-    *reinterpret_cast<uint4*>(tmp + q * (16 / sizeof(TI))) = *reinterpret_cast<const uint4*>(p + q * (16 / sizeof(TI)));
-}
-
-template <typename TO, int V>
-__device__ __forceinline__ void store_acc(TO* dst, const float (&acc)[V]) {
-  if constexpr (sizeof(TO) == 4) {
-#pragma unroll
-    for (int k = 0; k < V; k += 4)
-      *reinterpret_cast<float4*>(reinterpret_cast<float*>(dst) + k) = make_float4(acc[k], acc[k + 1], acc[k + 2], acc[k + 3]);
-  } else {
-#pragma unroll
-    for (int k = 0; k < V; k += 8) {
-      Vec16<TO> o;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) o.v[j] = ToF<TO>::from(acc[k + j]);
-      st16(dst + k, o);
-    }
-  }
-}
-
 // ------------------------------------------------------------------ all-reduce (two-shot)
 // arena layout for this call: [in region: n elements of TI][out region: n elements of TO]
 template <typename TI, typename TO>
@@ -310,6 +285,7 @@ __global__ void __launch_bounds__(kThreads) reduce_scatter_adamw_kernel(
 // in_splits / out_splits / in_offsets / out_offsets in elements, all multiples of the 16-byte packet.
 struct A2ASplits {
   int64_t send_off[kMaxWorld];  // where the slice for peer p starts in MY input
+  int64_t send_len[kMaxWorld];  // elements sent to peer p
   int64_t recv_off[kMaxWorld];  // where the slice from peer p lands in MY output
   int64_t recv_len[kMaxWorld];  // elements received from peer p
   int64_t peer_send_off[kMaxWorld];  // where MY slice starts in peer p's input (computed by the host from all splits)
@@ -321,7 +297,12 @@ __global__ void __launch_bounds__(kThreads) alltoall_kernel(Peers P, const T* __
   __shared__ int sh_ok;
   const int W = P.world, r = P.rank;
   T* my_in = reinterpret_cast<T*>(static_cast<char*>(P.buf[r]) + in_off);
-  copy_packets(my_in, in, n_in / V);
+  // Copy in slice by slice with slice-relative packet numbers: packet v of a slice is then written by the same
+  // CTA (v modulo the grid) that pulls packet v of it on the receiving rank, which is the only pairing that
+  // cta_exchange orders.  Every rank launches the same grid (equal splits).
+  (void)n_in;
+  for (int p = 0; p < W; ++p)
+    if (p != r) copy_packets(my_in + S.send_off[p], in + S.send_off[p], S.send_len[p] / V);
   if (!cta_exchange(P, epoch, &sh_ok)) return;
   for (int p = 0; p < W; ++p) {
     const int src = (r + p) % W;
@@ -332,6 +313,11 @@ __global__ void __launch_bounds__(kThreads) alltoall_kernel(Peers P, const T* __
 }
 
 }  // namespace
+
+namespace commdev {
+static std::atomic<long long> g_peer_wait_cycles{4000000000ll};
+long long peer_wait_cycles() { return g_peer_wait_cycles.load(std::memory_order_relaxed); }
+}  // namespace commdev
 
 static int grid_for(int64_t packets) {
   int64_t b = cdiv(packets, kThreads);
@@ -349,7 +335,16 @@ using namespace b200k;
 extern "C" {
 
 int b200_comm_max_world(void) { return kMaxWorld; }
-size_t b200_comm_signal_bytes(void) { return (size_t)kMaxChannels * kMaxWorld * sizeof(uint32_t); }
+/* SM clock ticks run at up to ~2 GHz: the conversion assumes that rate, so the limit is never shorter than asked */
+void b200_comm_set_wait_ms(double ms) {
+  long long c = (long long)(ms * 2.0e6);
+  if (c < 1000) c = 1000;
+  commdev::g_peer_wait_cycles.store(c, std::memory_order_relaxed);
+}
+double b200_comm_get_wait_ms(void) { return (double)commdev::peer_wait_cycles() / 2.0e6; }
+size_t b200_comm_signal_bytes(void) { return (size_t)kPadWords * sizeof(uint32_t); }
+int b200_comm_user_word0(void) { return kUserWords; }
+int b200_comm_pad_words(void) { return kPadWords; }
 
 #define COMM_DISPATCH2(IN, OUT, TI, TO, ...)                                                       \
   if (IN == B200_F32 && OUT == B200_F32) { using TI = float; using TO = float; __VA_ARGS__; }      \
@@ -427,10 +422,14 @@ int b200_comm_alltoall(const b200_symm_t* s, const void* in, void* out, int64_t 
     // byte offsets -> fp32 elements
     S.send_off[i] = send_off[i] / 4; S.recv_off[i] = recv_off[i] / 4; S.recv_len[i] = recv_len[i] / 4;
     S.peer_send_off[i] = peer_send_off[i] / 4;
+    const int64_t send_end = i + 1 < s->world ? send_off[i + 1] : in_bytes;
+    if (send_end < send_off[i] || (send_end - send_off[i]) % 16) return (int)cudaErrorNotSupported;
+    S.send_len[i] = (send_end - send_off[i]) / 4;
     maxlen = std::max(maxlen, recv_len[i]);
   }
   Peers P = make_peers(s);
-  alltoall_kernel<float><<<grid_for(std::max<int64_t>(maxlen, in_bytes) / 16), kThreads, 0, stream>>>(
+  // the grid depends on the largest slice only, which equal splits make the same on every rank
+  alltoall_kernel<float><<<grid_for(maxlen / 16), kThreads, 0, stream>>>(
       P, (const float*)in, (float*)out, in_bytes / 4, S, epoch, in_off);
   B200K_LAUNCH_RET();
 }

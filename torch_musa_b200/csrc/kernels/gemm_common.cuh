@@ -9,7 +9,10 @@
 namespace b200k {
 namespace gemmdev {
 
-constexpr long long kWaitCycles = 4000000000ll;  // ~2 s: far beyond any legitimate wait
+constexpr long long kWaitCycles = 4000000000ll;  // ~2 s: far beyond any legitimate wait inside one GPU
+// Limit that the pipeline waits of this translation unit use.  Kernels that also wait for other ranks raise it
+// to the process group's limit before they launch (one copy per translation unit and device).
+static __constant__ long long c_wait_cycles = kWaitCycles;
 
 // ------------------------------------------------------------------ PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -42,7 +45,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   while (!mbar_try(bar, parity)) {
     if ((++spins & 0x3ff) == 0) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitCycles) {
+      if (clock64() - t0 > c_wait_cycles) {
         *abort_flag = 1;
         return false;
       }
@@ -216,6 +219,7 @@ struct AgParams {
   uint32_t* flags;           // local, one word per panel: epoch of the last call that completed it
   uint32_t* sig[16];         // signal pads (peer-mapped), slot [copier CTA][source rank]
   uint32_t epoch;            // this call: epoch = shards ready, epoch + 1 = peer finished pulling
+  long long wait_cycles;     // limit of the waits on other ranks
 };
 
 // GEMM -> reduce-scatter: every rank multiplies into a partial [M, N] buffer of its arena, visiting the row panels
@@ -233,6 +237,7 @@ struct RsParams {
   uint32_t* sig[16];         // signal pads for the trailing barrier
   void* out;                 // local [M / world, N]
   uint32_t epoch;
+  long long wait_cycles;     // limit of the waits on other ranks
 };
 
 // What the host decided for one problem: how many K-splits and which kernel family.

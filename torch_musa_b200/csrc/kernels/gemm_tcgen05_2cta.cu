@@ -24,6 +24,7 @@
 // Parity: the reference sends mm/addmm/bmm to a closed vendor library
 // (reference torch_musa/csrc/aten/ops/Matmul.cpp:293-335,373-380).
 #include "gemm_common.cuh"
+#include "comm_common.cuh"
 
 #include <algorithm>
 #include <atomic>
@@ -191,13 +192,14 @@ __device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
 }
 // spins until (int)(*p - want) >= 0; false when the wait limit expired or another thread of the CTA gave up
 template <bool SYS>
-__device__ __forceinline__ bool wait_word(const uint32_t* p, uint32_t want, volatile int* abort_flag) {
+__device__ __forceinline__ bool wait_word(const uint32_t* p, uint32_t want, volatile int* abort_flag,
+                                          long long limit = c_wait_cycles) {
   const long long t0 = clock64();
   uint32_t spins = 0;
   while ((int32_t)((SYS ? ld_acquire_sys_u32(p) : ld_acquire_gpu_u32(p)) - want) < 0) {
     if ((++spins & 0xff) == 0) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitCycles) { *abort_flag = 1; return false; }
+      if (clock64() - t0 > limit) { *abort_flag = 1; return false; }
     }
   }
   return true;
@@ -214,7 +216,7 @@ __device__ void ag_copier(const AgParams& ag, uint8_t* ring, uint64_t* bars, vol
   for (int peer = 0; peer < W; ++peer)
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(ag.sig[peer] + cc * 16 + r), "r"(ag.epoch) : "memory");
   bool ok = true;
-  for (int peer = 0; peer < W && ok; ++peer) ok = wait_word<true>(ag.sig[r] + cc * 16 + peer, ag.epoch, abort_flag);
+  for (int peer = 0; peer < W && ok; ++peer) ok = wait_word<true>(ag.sig[r] + cc * 16 + peer, ag.epoch, abort_flag, ag.wait_cycles);
   // 2. my panels, own shard first (the GEMM clusters consume panels in the same rotated order)
   const int n_panels = ag.panels_per_shard * W;
   const int chunks_per_panel = (int)(ag.panel_bytes / kAgChunk);
@@ -261,7 +263,7 @@ __device__ void ag_copier(const AgParams& ag, uint8_t* ring, uint64_t* bars, vol
   // 3. nobody's shard may be overwritten before every peer has finished pulling from it
   for (int peer = 0; peer < W; ++peer)
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(ag.sig[peer] + cc * 16 + r), "r"(ag.epoch + 1) : "memory");
-  for (int peer = 0; peer < W && ok; ++peer) ok = wait_word<true>(ag.sig[r] + cc * 16 + peer, ag.epoch + 1, abort_flag);
+  for (int peer = 0; peer < W && ok; ++peer) ok = wait_word<true>(ag.sig[r] + cc * 16 + peer, ag.epoch + 1, abort_flag, ag.wait_cycles);
 }
 
 // ---- reduce-scatter reducer: all threads of the CTA.  Work items are 8 KB chunks of this rank's own panels;
@@ -283,7 +285,7 @@ __device__ void rs_reducer(const RsParams& rs, int tiles_n, uint8_t* stage_mem, 
     const int per_src = rs.panels_per_shard * tiles_n * 2;
     for (int i = threadIdx.x; i < W * tiles_n * 2; i += blockDim.x) {
       const int src = i / (tiles_n * 2), j = i - src * (tiles_n * 2);
-      wait_word<true>(base + src * per_src + p * tiles_n * 2 + j, rs.epoch, abort_flag);
+      wait_word<true>(base + src * per_src + p * tiles_n * 2 + j, rs.epoch, abort_flag, rs.wait_cycles);
     }
     __syncthreads();
   };
@@ -345,7 +347,7 @@ __device__ void rs_reducer(const RsParams& rs, int tiles_n, uint8_t* stage_mem, 
     for (int peer = 0; peer < W; ++peer)
       asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(rs.sig[peer] + cc * 16 + r), "r"(rs.epoch + 1) : "memory");
     bool ok = !*abort_flag;
-    for (int peer = 0; peer < W && ok; ++peer) ok = wait_word<true>(rs.sig[r] + cc * 16 + peer, rs.epoch + 1, abort_flag);
+    for (int peer = 0; peer < W && ok; ++peer) ok = wait_word<true>(rs.sig[r] + cc * 16 + peer, rs.epoch + 1, abort_flag, rs.wait_cycles);
   }
   __syncthreads();
 }
@@ -458,7 +460,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int n0 = nt * BN + (int)rank * C::kBHalf;
         if (ag.enabled) {
           // the 256-row panel of this tile must have been assembled by a copier CTA of this launch
-          if (!wait_word<false>(ag.flags + mt, ag.epoch, abort_flag)) { ok = false; break; }
+          if (!wait_word<false>(ag.flags + mt, ag.epoch, abort_flag, ag.wait_cycles)) { ok = false; break; }
           asm volatile("fence.proxy.async;" ::: "memory");
         }
         for (int kb = kb0; kb < kb1; ++kb) {
@@ -844,6 +846,19 @@ extern "C" int b200_gemm_force_config(int config) {
   return b200k::gemm_forced_config_exchange(config);
 }
 
+// The pipeline waits of a launch that also waits for other ranks must not give up before the cross-rank waits do:
+// raise this translation unit's limit to the collective limit on the current device (once per change).
+static int sync_wait_limit(long long want, cudaStream_t stream) {
+  static std::atomic<long long> applied[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
+  if (want < b200k::kWaitCycles) want = b200k::kWaitCycles;
+  if (applied[dev].load(std::memory_order_relaxed) == want) return 0;
+  cudaError_t e = cudaMemcpyToSymbolAsync(b200k::c_wait_cycles, &want, sizeof(want), 0, cudaMemcpyHostToDevice, stream);
+  if (e == cudaSuccess) applied[dev].store(want, std::memory_order_relaxed);
+  return (int)e;
+}
+
 // all-gather -> GEMM in one launch.  D[M, N] = gather_rows(A shards)[M, K] x B[N, K]^T with M = world * shard
 // rows; every rank's shard lives at `shard_off` of its arena; a_full [M, K] and flags [M / 256] are local
 // (flags persistent, zero-initialised once).  Consumes epochs `epoch` and `epoch + 1` of the arena's pad.
@@ -859,6 +874,7 @@ extern "C" int b200_gemm_allgather(const b200_gemm_desc_t* g, const b200_symm_t*
   if (copier_pairs * 2 >= gemm_sm_count() / 2) return (int)cudaErrorNotSupported;
   AgParams ag{};
   ag.enabled = 1;
+  ag.wait_cycles = commdev::peer_wait_cycles();
   ag.world = s->world;
   ag.rank = s->rank;
   ag.copier_pairs = copier_pairs;
@@ -871,6 +887,7 @@ extern "C" int b200_gemm_allgather(const b200_gemm_desc_t* g, const b200_symm_t*
   ag.dst = a_full;
   ag.flags = flags;
   ag.epoch = epoch;
+  if (int e = sync_wait_limit(ag.wait_cycles, stream)) return e;
   GemmPlan plan;
   plan.pair = 1;
   plan.dynamic = 0;
@@ -894,6 +911,7 @@ extern "C" int b200_gemm_reduce_scatter(const b200_gemm_desc_t* g, const b200_sy
   if (reducer_pairs * 2 >= gemm_sm_count() / 2) return (int)cudaErrorNotSupported;
   RsParams rs{};
   rs.enabled = 1;
+  rs.wait_cycles = commdev::peer_wait_cycles();
   rs.world = s->world;
   rs.rank = s->rank;
   rs.reducer_pairs = reducer_pairs;
@@ -906,6 +924,7 @@ extern "C" int b200_gemm_reduce_scatter(const b200_gemm_desc_t* g, const b200_sy
   }
   rs.out = out;
   rs.epoch = epoch;
+  if (int e = sync_wait_limit(rs.wait_cycles, stream)) return e;
   GemmPlan plan;
   plan.pair = 1;
   plan.dynamic = 0;

@@ -135,6 +135,20 @@ def _rope_reference(x, cos, sin, positions, interleaved, conj):
     return out.to(x.dtype)
 
 
+def _rope_rotate_half(x, cos, sin, positions):
+    """The usual library formulation (four elementwise kernels, in the input dtype): ``x * cos + rotate_half(x) * sin``
+    with full-width tables.  What a stock CUDA run of this model uses."""
+    B, S, H, D = x.shape
+    if positions is not None:
+        c, s = cos[positions.reshape(B, S)].unsqueeze(2), sin[positions.reshape(B, S)].unsqueeze(2)
+    else:
+        c, s = cos[:S].view(1, S, 1, D // 2), sin[:S].view(1, S, 1, D // 2)
+    c = torch.cat((c, c), dim=-1).to(x.dtype)
+    s = torch.cat((s, s), dim=-1).to(x.dtype)
+    x0, x1 = x[..., : D // 2], x[..., D // 2:]
+    return x * c + torch.cat((-x1, x0), dim=-1) * s
+
+
 class _Rope(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, cos, sin, positions, interleaved):
@@ -158,6 +172,8 @@ def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, positions: Optio
     ``True`` rotates adjacent pairs (GPT-J layout). Backward is the conjugate rotation."""
     if _on_device(x):
         return _Rope.apply(x, cos, sin, positions, interleaved)
+    if x.is_cuda and not interleaved and x.dtype in (torch.bfloat16, torch.float16):
+        return _rope_rotate_half(x, cos, sin, positions)
     return _rope_reference(x, cos, sin, positions, interleaved, False)
 
 

@@ -11,14 +11,11 @@ calls (reference torch_musa/csrc/distributed/ProcessGroupMCCL.cpp:4678-4735).
 """
 from __future__ import annotations
 
-import itertools
-
 import torch
 import torch.distributed as dist
 
 from . import tensor_parallel as TP
-
-_ids = itertools.count()
+from ._symm import group_store_and_key
 
 
 class FusedTensorParallel:
@@ -37,8 +34,8 @@ class FusedTensorParallel:
         self.partial_off = (self.max_shard_bytes + 1023) // 1024 * 1024
         self.flag_off = self.partial_off + self.max_partial_bytes
         total = self.flag_off + self.FLAG_BYTES
-        store = dist.distributed_c10d._get_default_store()
-        self.sm = bw._C._create_symmetric_memory(store, f"tp_arena/{next(_ids)}", self.rank, self.world,
+        store, key = group_store_and_key(group, "tp_arena")
+        self.sm = bw._C._create_symmetric_memory(store, key, self.rank, self.world,
                                                  self.device.index or 0, total)
         if not self.sm.ok:
             raise RuntimeError(f"tensor-parallel arena unavailable: {self.sm.why_not}")

@@ -22,13 +22,11 @@ Parity: the reference has no expert parallelism; its all_to_all is a loop of sen
 """
 from __future__ import annotations
 
-import itertools
 from typing import List, Optional, Tuple
 
 import torch
 import torch.distributed as dist
 
-_arena_ids = itertools.count()
 
 
 def _group_info(group) -> Tuple[int, int]:
@@ -163,11 +161,9 @@ class FusedExpertExchange:
         self._region = (self.cap_rows * d_model * 2 + 255) // 256 * 256
         self._table = (self.world * num_experts * 4 + 255) // 256 * 256
         total = self._table + (2 * slots + 2) * self._region
-        if self.world > 1:
-            store = dist.distributed_c10d._get_default_store() if group is None else dist.distributed_c10d._world.pg_map[group][1]
-        else:
-            store = dist.HashStore()
-        key = f"moe_arena/{next(_arena_ids)}"
+        from torch_musa_b200.parallel._symm import group_store_and_key  # this file also loads stand-alone (no package)
+
+        store, key = group_store_and_key(group, "moe_arena")
         self.sm = bw._C._create_symmetric_memory(store, key, self.rank, self.world, self.device.index or 0, total)
         if not self.sm.ok:
             raise RuntimeError(f"expert-parallel arena unavailable: {self.sm.why_not}")

@@ -16,13 +16,12 @@ fused path.
 """
 from __future__ import annotations
 
-import itertools
 from typing import Iterable, List
 
 import torch
 import torch.distributed as dist
 
-_ids = itertools.count()
+from ._symm import group_store_and_key
 
 
 class ShardedFusedAdamW:
@@ -65,8 +64,8 @@ class ShardedFusedAdamW:
         self.fused = fused and dev.type == "blackwell" and self.world > 1
         self.sm = None
         if self.fused:
-            store = dist.distributed_c10d._get_default_store()
-            self.sm = bw._C._create_symmetric_memory(store, f"zero_arena/{next(_ids)}", self.rank, self.world,
+            store, key = group_store_and_key(group, "zero_arena")
+            self.sm = bw._C._create_symmetric_memory(store, key, self.rank, self.world,
                                                      dev.index or 0, 2 * chunk * 2)
             if not self.sm.ok:
                 self.fused, self.sm = False, None
