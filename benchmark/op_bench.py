@@ -140,17 +140,22 @@ def bench_gemm_fp8(dev, m, n, k, iters=20):
 
 
 def bench_attention(dev, batch, heads, seq, dt=torch.bfloat16, iters=10):
-    """Causal attention forward, head_dim 128: the hand-written tcgen05 kernel (impl 2) and the library cuDNN kernel."""
-    q, k, v = (torch.randn(batch, seq, heads, 128, device=dev, dtype=dt).transpose(1, 2) for _ in range(3))
+    """Causal attention forward and backward, head_dim 128: the hand-written tcgen05 kernels (impl 2) and the library
+    cuDNN kernels (impl 1).  Backward FLOPs: five GEMMs against the forward's two."""
+    q, k, v = (torch.randn(batch, seq, heads, 128, device=dev, dtype=dt).transpose(1, 2).requires_grad_() for _ in range(3))
+    g = torch.randn(batch, seq, heads, 128, device=dev, dtype=dt).transpose(1, 2)
     flops = 4.0 * batch * heads * seq * seq * 128 / 2          # causal: half of QK^T and PV
     prev = bw._C._sdp_impl()
     out = {}
     try:
-        for impl, name in ((2, "attention_fwd_tcgen05"), (1, "attention_fwd_library_cudnn")):
+        for impl, name in ((2, "tcgen05"), (1, "library_cudnn")):
             bw._C._set_sdp_impl(impl)
             with torch.no_grad():
                 us = timeit(lambda: F.scaled_dot_product_attention(q, k, v, is_causal=True), dev, iters)
-            out[name] = report(name, [batch, heads, seq, 128], dt, us, flops=flops)
+            out["fwd_" + name] = report("attention_fwd_" + name, [batch, heads, seq, 128], dt, us, flops=flops)
+            o = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+            us = timeit(lambda: torch.autograd.grad(o, (q, k, v), g, retain_graph=True), dev, iters)
+            out["bwd_" + name] = report("attention_bwd_" + name, [batch, heads, seq, 128], dt, us, flops=2.5 * flops)
     finally:
         bw._C._set_sdp_impl(prev)
     return out

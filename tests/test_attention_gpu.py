@@ -1,5 +1,5 @@
-"""The hand-written tcgen05 flash-attention forward (head_dim 128) against an fp32 softmax(QK^T)V reference, and its
-use inside F.scaled_dot_product_attention together with the library backward."""
+"""The hand-written tcgen05 flash-attention forward and backward (head_dim 128) against an fp32 softmax(QK^T)V
+reference and its autograd gradients, through F.scaled_dot_product_attention (the default route on the device)."""
 import math
 
 import pytest
@@ -50,19 +50,51 @@ def test_native_forward(bw, dev, native_sdp, B, H, Hkv, Sq, Sk, causal, dt):
     assert bw._C._gemm_status(False) == 0
 
 
-def test_native_forward_with_library_backward(bw, dev, native_sdp):
+def test_native_is_the_default_route(bw):
+    assert bw._C._sdp_impl() == 2
+
+
+@pytest.mark.parametrize("B,H,Hkv,Sq,Sk,causal", [(2, 4, 4, 256, 256, True), (1, 2, 2, 128, 128, False),
+                                                   (1, 4, 2, 384, 384, True), (1, 2, 1, 200, 200, True),
+                                                   (2, 2, 2, 128, 320, False), (1, 4, 4, 1024, 1024, True),
+                                                   (1, 2, 2, 330, 200, False)])
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_native_backward(bw, dev, native_sdp, B, H, Hkv, Sq, Sk, causal, dt):
     torch.manual_seed(1)
-    B, H, S = 2, 4, 256
-    q, k, v = (torch.randn(B, S, H, 128).to(torch.bfloat16).transpose(1, 2) for _ in range(3))
-    g = torch.randn(B, H, S, 128).to(torch.bfloat16)
+    q = torch.randn(B, Sq, H, 128).to(dt).transpose(1, 2)
+    k = torch.randn(B, Sk, Hkv, 128).to(dt).transpose(1, 2)
+    v = torch.randn(B, Sk, Hkv, 128).to(dt).transpose(1, 2)
+    g = torch.randn(B, Sq, H, 128).to(dt).transpose(1, 2)
     qr, kr, vr = (t.float().requires_grad_() for t in (q, k, v))
-    ref, _ = ref_attention(qr, kr, vr, True)
+    ref, _ = ref_attention(qr, kr, vr, causal)
     ref.backward(g.float())
     qd, kd, vd = (t.to(dev).requires_grad_() for t in (q, k, v))
-    out = F.scaled_dot_product_attention(qd, kd, vd, is_causal=True)
+    before = bw._C._native_sdp_backward_calls()
+    out = F.scaled_dot_product_attention(qd, kd, vd, is_causal=causal, enable_gqa=(H != Hkv))
     out.backward(g.to(dev))
-    for a, b in ((qd.grad, qr.grad), (kd.grad, kr.grad), (vd.grad, vr.grad)):
-        assert (a.float().cpu() - b).abs().max() / b.abs().max() < 3e-2
+    assert bw._C._native_sdp_backward_calls() == before + 1, "the hand-written backward did not run"
+    tol = 3e-2 if dt == torch.bfloat16 else 8e-3
+    for name, a, b in (("dq", qd.grad, qr.grad), ("dk", kd.grad, kr.grad), ("dv", vd.grad, vr.grad)):
+        assert a.shape == b.shape
+        rel = (a.float().cpu() - b).abs().max() / b.abs().max()
+        assert rel < tol, (name, float(rel))
+    bw.synchronize()
+    assert bw._C._gemm_status(False) == 0
+
+
+def test_library_routes_still_work(bw, dev):
+    """impl 0 / 1 (library flash / cuDNN kernels over the same memory) stay selectable."""
+    torch.manual_seed(2)
+    q, k, v = (torch.randn(1, 128, 2, 64).to(torch.bfloat16).transpose(1, 2) for _ in range(3))
+    ref, _ = ref_attention(q, k, v, True)
+    prev = bw._C._sdp_impl()
+    try:
+        for impl in (0, 1, 2):     # head_dim 64 is not covered by the hand-written kernels: impl 2 falls to flash
+            bw._C._set_sdp_impl(impl)
+            out = F.scaled_dot_product_attention(q.to(dev), k.to(dev), v.to(dev), is_causal=True)
+            assert (out.float().cpu() - ref).abs().max() < 2e-2, impl
+    finally:
+        bw._C._set_sdp_impl(prev)
 
 
 @pytest.mark.parametrize("H,Hkv,pos", [(4, 4, 0), (8, 2, 37), (4, 4, 255), (4, 1, 100)])

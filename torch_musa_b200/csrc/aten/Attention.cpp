@@ -30,9 +30,11 @@ namespace {
 constexpr int64_t kMath = 0, kOverrideable = 4;
 std::atomic<bool> g_fused_sdp{true};
 // which kernel family serves the fused path: 0 = library flash, 1 = library cuDNN, 2 = the hand-written tcgen05
-// forward (head_dim 128) with the library flash backward.  Fixed between a forward and its backward.
-std::atomic<int> g_sdp_impl{1};
+// forward and backward (head_dim 128; other head sizes fall to the library flash kernels).  Fixed between a forward
+// and its backward.
+std::atomic<int> g_sdp_impl{2};
 std::atomic<int64_t> g_native_fwd_calls{0};
+std::atomic<int64_t> g_native_bwd_calls{0};
 
 // The hand-written forward: q [B, H, Sq, 128], k / v [B, Hkv, Sk, 128] with a contiguous last dimension.
 // The cuDNN-style library kernels: head_dim <= 128; grouped-query heads only when B200_SDP_CUDNN_GQA=1 (default on).
@@ -73,6 +75,54 @@ bool native_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, b
   g_native_fwd_calls.fetch_add(1, std::memory_order_relaxed);
   *out = o;
   *lse = l;
+  return true;
+}
+
+bool stride_ok(const at::Tensor& t) {
+  return t.stride(3) == 1 && t.stride(0) % 8 == 0 && t.stride(1) % 8 == 0 && t.stride(2) % 8 == 0 && t.stride(2) != 0 &&
+         (t.size(0) == 1 || t.stride(0) != 0) && (t.size(1) == 1 || t.stride(1) != 0) &&
+         (reinterpret_cast<uintptr_t>(t.const_data_ptr()) & 15) == 0;
+}
+
+// The hand-written backward: dq / dk / dv for the tensors of native_fwd.  Returns false when the shape is not covered.
+bool native_bwd(const at::Tensor& grad_out_, const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+                const at::Tensor& out_, const at::Tensor& lse, bool is_causal, std::optional<double> scale,
+                at::Tensor* dq, at::Tensor* dk, at::Tensor* dv) {
+  const int64_t B = q.size(0), H = q.size(1), Sq = q.size(2), D = q.size(3), Hkv = k.size(1), Sk = k.size(2);
+  if (D != 128 || !stride_ok(q) || !stride_ok(k) || !stride_ok(v)) return false;
+  if (!lse.defined() || lse.scalar_type() != at::kFloat || lse.numel() != B * H * Sq) return false;
+  at::Tensor go = stride_ok(grad_out_) ? grad_out_ : grad_out_.contiguous();
+  at::Tensor o = stride_ok(out_) ? out_ : out_.contiguous();
+  at::Tensor l = lse.is_contiguous() ? lse : lse.contiguous();
+  at::Tensor dq32 = at::empty({B, H, Sq, D}, q.options().dtype(at::kFloat));
+  at::Tensor delta = at::empty({B, H, Sq}, q.options().dtype(at::kFloat));
+  at::Tensor gk = at::empty({B, Sk, Hkv, D}, k.options()).transpose(1, 2);
+  at::Tensor gv = at::empty({B, Sk, Hkv, D}, v.options()).transpose(1, 2);
+  b200_attn_t a{};
+  a.B = (int)B; a.H = (int)H; a.Hkv = (int)Hkv; a.Sq = (int)Sq; a.Sk = (int)Sk; a.head_dim = (int)D;
+  a.dtype = kdtype(q.scalar_type());
+  a.causal = is_causal ? 1 : 0;
+  a.scale = (float)scale.value_or(1.0 / std::sqrt((double)D));
+  a.q_sb = q.stride(0); a.q_sh = q.stride(1); a.q_ss = q.stride(2);
+  a.k_sb = k.stride(0); a.k_sh = k.stride(1); a.k_ss = k.stride(2);
+  a.v_sb = v.stride(0); a.v_sh = v.stride(1); a.v_ss = v.stride(2);
+  a.o_sb = o.stride(0); a.o_sh = o.stride(1); a.o_ss = o.stride(2);
+  const int64_t extra[9] = {go.stride(0), go.stride(1), go.stride(2), gk.stride(0), gk.stride(1), gk.stride(2),
+                            gv.stride(0), gv.stride(1), gv.stride(2)};
+  DeviceSwitch sw(q.device().index());
+  int e = b200_flash_attn_bwd(&a, dq32.data_ptr<float>(), gk.mutable_data_ptr(), gv.mutable_data_ptr(),
+                              delta.data_ptr<float>(), q.const_data_ptr(), k.const_data_ptr(), v.const_data_ptr(),
+                              o.const_data_ptr(), go.const_data_ptr(), l.const_data_ptr<float>(), extra,
+                              current_raw_stream(q));
+  if (e == (int)cudaErrorNotSupported) return false;
+  B200_KERNEL_CALL(e);
+  g_native_bwd_calls.fetch_add(1, std::memory_order_relaxed);
+  // the fp32 accumulator becomes the gradient in [B, Sq, H, D] memory, the layout of the projections' output
+  at::Tensor gq = at::empty({B, Sq, H, D}, q.options()).transpose(1, 2);
+  gq.copy_(dq32);
+  *dq = gq;
+  *dk = gk;
+  *dv = gv;
   return true;
 }
 
@@ -147,6 +197,12 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> sdpa_fused_bwd(
     c10::SymInt max_k, double dropout_p, bool is_causal, const at::Tensor& philox_seed,
     const at::Tensor& philox_offset, std::optional<double> scale) {
   (void)grad_input_mask;
+  // a forward that ran on the hand-written kernel left no rng state and an empty cum_seq: its backward is ours too
+  if (g_sdp_impl.load() == 2 && dropout_p == 0.0 && native_fwd_eligible(q, k, v, dropout_p)) {
+    at::Tensor dq, dk, dv;
+    if (native_bwd(grad_out, q, k, v, out, logsumexp, is_causal, scale, &dq, &dk, &dv))
+      return {dq, dk, dv, at::Tensor()};
+  }
   if (g_sdp_impl.load() == 1 && cudnn_route_ok(q, k)) {
     at::Tensor no_bias;
     auto st = run_fallback(B200_OP_HANDLE("aten::_scaled_dot_product_cudnn_attention_backward", ""), grad_out, q, k, v,
@@ -164,6 +220,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> sdpa_fused_bwd(
 }  // namespace
 
 int64_t native_sdp_forward_calls() { return g_native_fwd_calls.load(); }
+int64_t native_sdp_backward_calls() { return g_native_bwd_calls.load(); }
 void set_fused_sdp(bool on) { g_fused_sdp = on; }
 void set_sdp_impl(int impl) { g_sdp_impl = impl; }
 int sdp_impl() { return g_sdp_impl; }

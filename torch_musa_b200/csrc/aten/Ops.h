@@ -60,9 +60,10 @@ B200_EXPORT bool tensor_core_gemm_enabled();
 // Fused scaled-dot-product attention on/off (off: the math decomposition is always chosen).
 B200_EXPORT void set_fused_sdp(bool on);
 B200_EXPORT bool fused_sdp_enabled();
-B200_EXPORT void set_sdp_impl(int impl);  // 0 library flash, 1 library cuDNN, 2 hand-written tcgen05 forward + library flash backward
+B200_EXPORT void set_sdp_impl(int impl);  // 0 library flash, 1 library cuDNN, 2 hand-written tcgen05 forward and backward (default)
 B200_EXPORT int sdp_impl();
 B200_EXPORT int64_t native_sdp_forward_calls();  // launches of the hand-written attention forward
+B200_EXPORT int64_t native_sdp_backward_calls();
 
 // 1x1 convolutions as GEMMs over the channels-last matrix view (off: every convolution uses the library route).
 B200_EXPORT void set_pointwise_conv_gemm(bool on);

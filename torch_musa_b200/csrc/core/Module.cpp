@@ -214,6 +214,7 @@ PYBIND11_MODULE(_C, m) {
   m.def("_set_sdp_impl", [](int impl) { ops::set_sdp_impl(impl); });
   m.def("_sdp_impl", [] { return ops::sdp_impl(); });
   m.def("_native_sdp_forward_calls", [] { return ops::native_sdp_forward_calls(); });
+  m.def("_native_sdp_backward_calls", [] { return ops::native_sdp_backward_calls(); });
   m.def("_fused_sdp_enabled", [] { return ops::fused_sdp_enabled(); });
   m.def("_tensor_core_gemm_enabled", [] { return ops::tensor_core_gemm_enabled(); });
   m.def("_runtime_version", [] {

@@ -1,0 +1,462 @@
+// Flash-attention backward on the 5th-generation tensor cores (head_dim 128, bf16 / fp16, optional causal mask,
+// grouped-query heads).
+//
+// One CTA owns one block of 128 keys of one (batch, kv head); K and V stay resident in shared memory, dK and dV
+// accumulate in TMEM over every query block (and every query head of the group) that sees the keys.  Everything is
+// computed transposed, keys along the 128 TMEM lanes, so that one thread owns one key row:
+//   S^T  = K Q^T          tcgen05.mma, both operands K-major                         -> TMEM columns [0, 128)
+//   dP^T = V dO^T         the same shape                                             -> TMEM columns [128, 256)
+//   P^T  = exp2(S^T * scale - lse[q]),  dS^T = P^T * (dP^T - delta[q]) * scale       two warpgroups, half of the
+//                         query columns each; both written as bf16 into shared memory in the layout of an A operand
+//   dV  += P^T dO         A = P^T (K-major over queries), B = dO read MN-major       -> TMEM columns [256, 384)
+//   dK  += dS^T Q         A = dS^T, B = Q read MN-major                              -> TMEM columns [384, 512)
+//   dQ   = dS K           A = dS^T read MN-major, B = K read MN-major, fresh         -> TMEM columns [128, 256) again
+// dQ of this (query block, key block) pair is added to an fp32 buffer in global memory with vector reductions
+// (red.global.add.v4.f32); the caller zeroes that buffer and converts it afterwards.  delta = rowsum(dO * O) comes
+// from a small preprocessing kernel.  Q and dO stream through a three-slot TMA ring; every wait is bounded.
+//
+// Parity: the reference calls a closed vendor flash backward (reference torch_musa/csrc/aten/ops/attention/mudnn/SDP.cpp:678-845).
+#include "attention_common.cuh"
+
+#include <algorithm>
+
+namespace b200k {
+namespace {
+using namespace gemmdev;
+using namespace attndev;
+
+constexpr int BQ = 128, BK = 128, BD = 128;
+constexpr int kTile = 128 * 128 * 2;
+constexpr int kRing = 3;
+constexpr int kBwdSmem = 2 * kTile /*K, V*/ + kRing * kTile /*Q, dO ring*/ + 2 * kTile /*P^T, dS^T*/ + 1024 +
+                         2 * 128 * 4 /*lse, delta*/ + 128;
+static_assert(kBwdSmem <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
+constexpr int kBwdThreads = 320;
+constexpr uint32_t kBwdTmemCols = 512;
+
+struct BwdParams {
+  int B, H, Hkv, Sq, Sk;
+  int causal;
+  float scale, scale_log2;
+  const float* lse;       // [B, H, Sq] natural log
+  const float* delta;     // [B, H, Sq]
+  float* dq;              // [B, H, Sq, 128] fp32, zeroed
+  int64_t dk_sb, dk_sh, dk_ss, dv_sb, dv_sh, dv_ss;
+  int kv_blocks, q_blocks;
+  int* status;
+};
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+__device__ __forceinline__ void named_bar_sync(int id, int count) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
+                T* __restrict__ dk, T* __restrict__ dv, const BwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* sK = smem;
+  uint8_t* sV = smem + kTile;
+  uint8_t* sR = smem + 2 * kTile;                    // [kRing][kTile]: Q_i, dO_i, Q_{i+1}, ...
+  uint8_t* sP = smem + (2 + kRing) * kTile;          // P^T  [keys x queries]
+  uint8_t* sS = smem + (3 + kRing) * kTile;          // dS^T [keys x queries]
+  float* s_lse = reinterpret_cast<float*>(smem + (4 + kRing) * kTile);   // [128]
+  float* s_dlt = s_lse + 128;                                              // [128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_dlt + 128);
+  uint64_t* kv_full = bars;                  // 1
+  uint64_t* r_full = bars + 1;               // [kRing]
+  uint64_t* r_empty = r_full + kRing;        // [kRing]  tcgen05.commit
+  uint64_t* s_full = r_empty + kRing;        // tcgen05.commit: S^T ready
+  uint64_t* dp_full = s_full + 1;            // tcgen05.commit: dP^T ready
+  uint64_t* s_free = dp_full + 1;            // 8 warps: S^T read
+  uint64_t* p_ready = s_free + 1;            // 8 warps: P^T in shared memory
+  uint64_t* ds_ready = p_ready + 1;          // 8 warps: dS^T in shared memory, dP^T read
+  uint64_t* mma2_done = ds_ready + 1;        // tcgen05.commit: dV, dK, dQ of this pair complete
+  uint64_t* dq_drained = mma2_done + 1;      // 8 warps: dQ read out of TMEM
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dq_drained + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kb = (int)(blockIdx.x % p.kv_blocks);   // early key blocks (most query blocks under a causal mask) first
+  const int bh = blockIdx.x / p.kv_blocks;
+  const int b = bh / p.Hkv, hk = bh - b * p.Hkv;
+  const int G = p.H / p.Hkv;
+  const int k0 = kb * BK;
+  const int i0 = p.causal ? min(p.q_blocks, k0 / BQ) : 0;   // first query block that sees these keys
+  const int n_i = p.q_blocks - i0;
+  const int n_it = n_i * G;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < kRing; ++s) {
+      mbar_init(&r_full[s], 1);
+      mbar_init(&r_empty[s], 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(dp_full, 1);
+    mbar_init(s_free, 8);
+    mbar_init(p_ready, 8);
+    mbar_init(ds_ready, 8);
+    mbar_init(mma2_done, 1);
+    mbar_init(dq_drained, 8);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    prefetch_tmap(&tmap_q);
+    prefetch_tmap(&tmap_k);
+    prefetch_tmap(&tmap_v);
+    prefetch_tmap(&tmap_do);
+  }
+  if (warp == 9) {
+    tmem_alloc(tmem_slot, kBwdTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  constexpr uint32_t kColS = 0, kColDP = 128, kColDV = 256, kColDK = 384;
+
+  if (warp == 8) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0 && n_it > 0) {
+      mbar_expect_tx(kv_full, 2 * kTile);
+      tma_load_4d(sK, &tmap_k, kv_full, 0, k0, hk, b);
+      tma_load_4d(sK + kTile / 2, &tmap_k, kv_full, 64, k0, hk, b);
+      tma_load_4d(sV, &tmap_v, kv_full, 0, k0, hk, b);
+      tma_load_4d(sV + kTile / 2, &tmap_v, kv_full, 64, k0, hk, b);
+      for (int n = 0; n < 2 * n_it; ++n) {
+        const int st = n % kRing;
+        if (!mbar_wait(&r_empty[st], (uint32_t)(((n / kRing) & 1) ^ 1), abort_flag)) break;
+        mbar_expect_tx(&r_full[st], kTile);
+        const int it = n >> 1;
+        const int h = hk * G + it / n_i;
+        const int q0 = (i0 + it % n_i) * BQ;
+        const CUtensorMap* map = (n & 1) ? &tmap_do : &tmap_q;
+        tma_load_4d(sR + st * kTile, map, &r_full[st], 0, q0, h, b);
+        tma_load_4d(sR + st * kTile + kTile / 2, map, &r_full[st], 64, q0, h, b);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 9) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0 && n_it > 0) {
+      const uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+      const uint32_t idesc_kk = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+      const uint32_t idesc_kmn = idesc_kk | (1u << 16);                 // B read MN-major
+      const uint32_t idesc_mnmn = idesc_kk | (1u << 15) | (1u << 16);   // A and B read MN-major
+      auto ring_wait = [&](int n) { return mbar_wait(&r_full[n % kRing], (uint32_t)((n / kRing) & 1), abort_flag); };
+      // D = A B^T with both tiles K-major (two 64-column atoms, 32 bytes per k16 step)
+      auto mma_kk = [&](uint32_t dcol, const uint8_t* a, const uint8_t* bt) {
+        const uint32_t aa = smem_u32(a), ba = smem_u32(bt);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (uint32_t)(kk >> 2) * (kTile / 2) + (uint32_t)(kk & 3) * 32;
+          umma_f16(tmem_base + dcol, make_desc(aa + off, 16, 1024), make_desc(ba + off, 16, 1024), idesc_kk, kk != 0 ? 1u : 0u);
+        }
+      };
+      // D (+)= A B with A K-major and B a [k rows x n columns] tile read MN-major (16 k rows = 2048 bytes per step)
+      auto mma_kmn = [&](uint32_t dcol, const uint8_t* a, const uint8_t* bt, bool fresh) {
+        const uint32_t aa = smem_u32(a), ba = smem_u32(bt);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t aoff = (uint32_t)(kk >> 2) * (kTile / 2) + (uint32_t)(kk & 3) * 32;
+          umma_f16(tmem_base + dcol, make_desc(aa + aoff, 16, 1024), make_desc(ba + (uint32_t)kk * 2048, kTile / 2, 1024),
+                   idesc_kmn, (fresh && kk == 0) ? 0u : 1u);
+        }
+      };
+      // D = A^T B with A a [k rows x m columns] tile and B a [k rows x n columns] tile, both read MN-major
+      auto mma_mnmn = [&](uint32_t dcol, const uint8_t* a, const uint8_t* bt) {
+        const uint32_t aa = smem_u32(a), ba = smem_u32(bt);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_f16(tmem_base + dcol, make_desc(aa + (uint32_t)kk * 2048, kTile / 2, 1024),
+                   make_desc(ba + (uint32_t)kk * 2048, kTile / 2, 1024), idesc_mnmn, kk != 0 ? 1u : 0u);
+      };
+      bool ok = mbar_wait(kv_full, 0, abort_flag);
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int nq = 2 * it, ndo = 2 * it + 1;
+        const uint32_t par = (uint32_t)(it & 1), prev = par ^ 1u;
+        const uint8_t* tQ = sR + (nq % kRing) * kTile;
+        const uint8_t* tdO = sR + (ndo % kRing) * kTile;
+        if (!ring_wait(nq)) { ok = false; break; }
+        if (it > 0 && !mbar_wait(s_free, prev, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        mma_kk(kColS, sK, tQ);                       // S^T = K Q^T
+        umma_commit(s_full);
+        if (!ring_wait(ndo)) { ok = false; break; }
+        if (it > 0 && !mbar_wait(dq_drained, prev, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        mma_kk(kColDP, sV, tdO);                     // dP^T = V dO^T
+        umma_commit(dp_full);
+        if (!mbar_wait(p_ready, par, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        mma_kmn(kColDV, sP, tdO, it == 0);           // dV += P^T dO
+        if (!mbar_wait(ds_ready, par, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        mma_kmn(kColDK, sS, tQ, it == 0);            // dK += dS^T Q
+        mma_mnmn(kColDP, sS, sK);                    // dQ = dS K (over the consumed dP^T)
+        umma_commit(mma2_done);
+        umma_commit(&r_empty[nq % kRing]);
+        umma_commit(&r_empty[ndo % kRing]);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ two compute warpgroups (warps 0-3, 4-7)
+    const int wg = warp >> 2;
+    const int qw = warp & 3;
+    const int r = qw * 32 + lane;                 // key row inside the block = TMEM lane
+    const int kj = k0 + r;
+    const uint32_t lane_base = ((uint32_t)(qw * 32) << 16);
+    const int tid = threadIdx.x;                  // 0..255 here
+    uint8_t* prow = sP + (size_t)wg * (kTile / 2) + (size_t)r * 128;   // this warpgroup's 64 query columns = atom `wg`
+    uint8_t* srow = sS + (size_t)wg * (kTile / 2) + (size_t)r * 128;
+    bool ok = true;
+    auto wait_all = [&](uint64_t* bar, uint32_t parity) {
+      const bool w = mbar_wait(bar, parity, abort_flag);
+      return __all_sync(0xffffffffu, w);
+    };
+    for (int it = 0; it < n_it; ++it) {
+      const uint32_t par = (uint32_t)(it & 1);
+      const int h = hk * G + it / n_i;
+      const int q0 = (i0 + it % n_i) * BQ;
+      // lse (log2 domain) and delta of the 128 query rows of this block; +inf switches a row off.  Single buffers:
+      // a thread gets here only after mma2_done of the previous pair, which needs every warp's ds_ready, i.e. all
+      // reads of the previous values.
+      {
+        const int which = tid >> 7, q = tid & 127, qi = q0 + q;
+        const int64_t idx = ((int64_t)b * p.H + h) * p.Sq + qi;
+        if (which == 0) {
+          float l = qi < p.Sq ? p.lse[idx] : -INFINITY;
+          s_lse[q] = l > -INFINITY ? l * 1.4426950408889634f : INFINITY;
+        } else {
+          s_dlt[q] = qi < p.Sq ? p.delta[idx] : 0.f;
+        }
+      }
+      named_bar_sync(1, 256);
+      const float* lse2 = s_lse + wg * 64;
+      const float* dlt = s_dlt + wg * 64;
+      const bool diag = p.causal && q0 < k0 + BK;       // only then can a query be older than a key of this block
+      if (!wait_all(s_full, par)) { ok = false; break; }
+      tc_fence_after();
+      float pf[64];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t raw[32];
+        tmem_ld32(tmem_base + lane_base + kColS + (uint32_t)(wg * 64 + c * 32), raw);
+        tmem_ld_wait();
+#pragma unroll
+        for (int g8 = 0; g8 < 4; ++g8) {
+          Vec16<T> pk;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int cc = c * 32 + g8 * 8 + e;                 // query column inside this warpgroup's half
+            const int qi = q0 + wg * 64 + cc;
+            float pv = exp2f(fmaf(__uint_as_float(raw[g8 * 8 + e]), p.scale_log2, -lse2[cc]));
+            if (kj >= p.Sk || (diag && qi < kj)) pv = 0.f;
+            pf[cc] = pv;
+            pk.v[e] = ToF<T>::from(pv);
+          }
+          const int ch = c * 4 + g8;
+          *reinterpret_cast<Vec16<T>*>(prow + (size_t)((ch ^ (r & 7)) * 16)) = pk;
+        }
+      }
+      tc_fence_before();
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(s_free);
+        mbar_arrive(p_ready);
+      }
+      if (!wait_all(dp_full, par)) { ok = false; break; }
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t raw[32];
+        tmem_ld32(tmem_base + lane_base + kColDP + (uint32_t)(wg * 64 + c * 32), raw);
+        tmem_ld_wait();
+#pragma unroll
+        for (int g8 = 0; g8 < 4; ++g8) {
+          Vec16<T> pk;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int cc = c * 32 + g8 * 8 + e;
+            const float ds = pf[cc] * (__uint_as_float(raw[g8 * 8 + e]) - dlt[cc]) * p.scale;
+            pk.v[e] = ToF<T>::from(ds);
+          }
+          const int ch = c * 4 + g8;
+          *reinterpret_cast<Vec16<T>*>(srow + (size_t)((ch ^ (r & 7)) * 16)) = pk;
+        }
+      }
+      tc_fence_before();
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(ds_ready);
+      // dQ of this pair: lane = query row, this warpgroup's 64 head-dim columns
+      if (!wait_all(mma2_done, par)) { ok = false; break; }
+      tc_fence_after();
+      {
+        const int qi = q0 + r;
+        float* dq_row = p.dq + (((int64_t)b * p.H + h) * p.Sq + qi) * BD + wg * 64;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t raw[32];
+          tmem_ld32(tmem_base + lane_base + kColDP + (uint32_t)(wg * 64 + c * 32), raw);
+          tmem_ld_wait();
+          if (qi < p.Sq) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 4)
+              red_add_v4(dq_row + c * 32 + e, __uint_as_float(raw[e]), __uint_as_float(raw[e + 1]),
+                         __uint_as_float(raw[e + 2]), __uint_as_float(raw[e + 3]));
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dq_drained);
+    }
+    // ---- dK, dV of this key block (all pairs have completed: the last mma2_done was waited for above)
+    if (ok) {
+      tc_fence_after();
+      const bool row_ok = kj < p.Sk;
+      T* dk_row = dk + (int64_t)b * p.dk_sb + (int64_t)hk * p.dk_sh + (int64_t)kj * p.dk_ss + wg * 64;
+      T* dv_row = dv + (int64_t)b * p.dv_sb + (int64_t)hk * p.dv_sh + (int64_t)kj * p.dv_ss + wg * 64;
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t raw[32];
+          if (n_it > 0) {
+            tmem_ld32(tmem_base + lane_base + (which ? kColDK : kColDV) + (uint32_t)(wg * 64 + c * 32), raw);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) raw[e] = 0u;
+          }
+          if (row_ok) {
+            T* dst = (which ? dk_row : dv_row) + c * 32;
+#pragma unroll
+            for (int g8 = 0; g8 < 4; ++g8) {
+              Vec16<T> v;
+#pragma unroll
+              for (int e = 0; e < 8; ++e) v.v[e] = ToF<T>::from(__uint_as_float(raw[g8 * 8 + e]));
+              st16(dst + g8 * 8, v);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kBwdTmemCols);
+  }
+  if (threadIdx.x == 0 && *abort_flag && p.status) atomicExch(p.status, 1);
+}
+
+// delta[b, h, q] = sum_d O[b, h, q, d] * dO[b, h, q, d]; one warp per row
+template <typename T>
+__global__ void attn_delta_kernel(const T* __restrict__ o, const T* __restrict__ d_o, float* __restrict__ delta, int B,
+                                  int H, int Sq, int64_t o_sb, int64_t o_sh, int64_t o_ss, int64_t g_sb, int64_t g_sh,
+                                  int64_t g_ss) {
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= (int64_t)B * H * Sq) return;
+  const int q = (int)(row % Sq);
+  const int h = (int)((row / Sq) % H);
+  const int b = (int)(row / ((int64_t)Sq * H));
+  const T* po = o + b * o_sb + h * o_sh + q * o_ss + lane * 4;
+  const T* pg = d_o + b * g_sb + h * g_sh + q * g_ss + lane * 4;
+  const uint2 a = *reinterpret_cast<const uint2*>(po), g = *reinterpret_cast<const uint2*>(pg);
+  const T* av = reinterpret_cast<const T*>(&a);
+  const T* gv = reinterpret_cast<const T*>(&g);
+  float s = 0.f;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) s += ToF<T>::to(av[e]) * ToF<T>::to(gv[e]);
+  s = warp_sum(s);
+  if (lane == 0) delta[row] = s;
+}
+
+}  // namespace
+}  // namespace b200k
+
+using namespace b200k;
+
+extern "C" int b200_flash_attn_bwd(const b200_attn_t* a, float* dq_accum, void* dk, void* dv, float* delta, const void* q,
+                                   const void* k, const void* v, const void* o, const void* d_o, const float* lse,
+                                   const int64_t* extra_strides, cudaStream_t stream) {
+  // extra_strides: do_sb, do_sh, do_ss, dk_sb, dk_sh, dk_ss, dv_sb, dv_sh, dv_ss (elements)
+  if (a->head_dim != BD || (a->dtype != B200_BF16 && a->dtype != B200_F16) || a->B <= 0 || a->H <= 0 || a->Hkv <= 0 ||
+      a->H % a->Hkv != 0 || a->Sq <= 0 || a->Sk <= 0)
+    return (int)cudaErrorNotSupported;
+  auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  const int64_t* x = extra_strides;
+  const int64_t strides[] = {a->q_sb, a->q_sh, a->q_ss, a->k_sb, a->k_sh, a->k_ss, a->v_sb, a->v_sh, a->v_ss,
+                             a->o_sb, a->o_sh, a->o_ss, x[0], x[1], x[2], x[3], x[4], x[5], x[6], x[7], x[8]};
+  for (int64_t s : strides)
+    if (s % 8 != 0) return (int)cudaErrorNotSupported;
+  if (!al(q) || !al(k) || !al(v) || !al(o) || !al(d_o) || !al(dk) || !al(dv) || !al(dq_accum)) return (int)cudaErrorNotSupported;
+  if ((a->B > 1 && (a->q_sb == 0 || a->k_sb == 0 || a->v_sb == 0 || x[0] == 0)) ||
+      (a->H > 1 && (a->q_sh == 0 || x[1] == 0)) || (a->Hkv > 1 && (a->k_sh == 0 || a->v_sh == 0)) || a->q_ss == 0 ||
+      a->k_ss == 0 || a->v_ss == 0 || x[2] == 0)
+    return (int)cudaErrorNotSupported;
+  const int bf16 = a->dtype == B200_BF16;
+  CUtensorMap mq, mk, mv, mdo;
+  auto nz = [](int64_t s, int64_t fallback) { return s ? s : fallback; };
+  if (!make_attn_map(&mq, q, bf16, a->B, a->H, a->Sq, nz(a->q_sb, 8), nz(a->q_sh, 8), a->q_ss) ||
+      !make_attn_map(&mk, k, bf16, a->B, a->Hkv, a->Sk, nz(a->k_sb, 8), nz(a->k_sh, 8), a->k_ss) ||
+      !make_attn_map(&mv, v, bf16, a->B, a->Hkv, a->Sk, nz(a->v_sb, 8), nz(a->v_sh, 8), a->v_ss) ||
+      !make_attn_map(&mdo, d_o, bf16, a->B, a->H, a->Sq, nz(x[0], 8), nz(x[1], 8), x[2]))
+    return (int)cudaErrorNotSupported;
+  BwdParams p{};
+  p.B = a->B; p.H = a->H; p.Hkv = a->Hkv; p.Sq = a->Sq; p.Sk = a->Sk;
+  p.causal = a->causal;
+  p.scale = a->scale;
+  p.scale_log2 = a->scale * 1.4426950408889634f;
+  p.lse = lse;
+  p.delta = delta;
+  p.dq = dq_accum;
+  p.dk_sb = x[3]; p.dk_sh = x[4]; p.dk_ss = x[5];
+  p.dv_sb = x[6]; p.dv_sh = x[7]; p.dv_ss = x[8];
+  p.kv_blocks = (a->Sk + BK - 1) / BK;
+  p.q_blocks = (a->Sq + BQ - 1) / BQ;
+  p.status = gemm_status_word_device();
+  const long long rows = (long long)a->B * a->H * a->Sq;
+  const long long grid = (long long)a->B * a->Hkv * p.kv_blocks;
+  if (grid > 2147483647ll || rows / 8 + 1 > 2147483647ll) return (int)cudaErrorNotSupported;
+  cudaError_t e = cudaMemsetAsync(dq_accum, 0, (size_t)rows * BD * sizeof(float), stream);
+  if (e != cudaSuccess) return (int)e;
+  if (bf16) {
+    attn_delta_kernel<__nv_bfloat16><<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>(
+        (const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, delta, a->B, a->H, a->Sq, a->o_sb, a->o_sh, a->o_ss, x[0], x[1], x[2]);
+    static bool set = false;
+    auto kern = attn_bwd_kernel<__nv_bfloat16>;
+    if (!set) {
+      e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem);
+      if (e != cudaSuccess) return (int)e;
+      set = true;
+    }
+    kern<<<(unsigned)grid, kBwdThreads, kBwdSmem, stream>>>(mq, mk, mv, mdo, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, p);
+  } else {
+    attn_delta_kernel<__half><<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>(
+        (const __half*)o, (const __half*)d_o, delta, a->B, a->H, a->Sq, a->o_sb, a->o_sh, a->o_ss, x[0], x[1], x[2]);
+    static bool set = false;
+    auto kern = attn_bwd_kernel<__half>;
+    if (!set) {
+      e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem);
+      if (e != cudaSuccess) return (int)e;
+      set = true;
+    }
+    kern<<<(unsigned)grid, kBwdThreads, kBwdSmem, stream>>>(mq, mk, mv, mdo, (__half*)dk, (__half*)dv, p);
+  }
+  note_launch(2);
+  return (int)cudaGetLastError();
+}

@@ -379,6 +379,13 @@ typedef struct {
 } b200_attn_t;
 B200_API int b200_flash_attn_fwd(const b200_attn_t* desc, void* out, float* lse, const void* q, const void* k,
                                  const void* v, cudaStream_t stream);
+/* Backward of the same attention.  dq_accum [B, H, Sq, 128] fp32 (the call zeroes it; the caller converts it),
+ * dk / dv [B, Hkv, Sk, 128] and d_o [B, H, Sq, 128] with the element strides in extra_strides = {do_sb, do_sh, do_ss,
+ * dk_sb, dk_sh, dk_ss, dv_sb, dv_sh, dv_ss}; o uses desc->o_*; delta [B, H, Sq] fp32 is scratch the call fills;
+ * lse [B, H, Sq] is the forward's natural-log row sum. */
+B200_API int b200_flash_attn_bwd(const b200_attn_t* desc, float* dq_accum, void* dk, void* dv, float* delta,
+                                 const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                                 const float* lse, const int64_t* extra_strides, cudaStream_t stream);
 
 /* single-query attention over a static KV cache: q / out [B, H, 128], caches [B, Hkv, max_len, 128] contiguous, keys
  * [0, *pos] visible (pos: device int64, read by the kernel, so the call is graph-capturable) */
