@@ -11,8 +11,9 @@
 //   dV  += P^T dO         A = P^T (K-major over queries), B = dO read MN-major       -> TMEM columns [256, 384)
 //   dK  += dS^T Q         A = dS^T, B = Q read MN-major                              -> TMEM columns [384, 512)
 //   dQ   = dS K           A = dS^T read MN-major, B = K read MN-major, fresh         -> TMEM columns [128, 256) again
-// dQ of this (query block, key block) pair is added to an fp32 buffer in global memory with vector reductions
-// (red.global.add.v4.f32); the caller zeroes that buffer and converts it afterwards.  delta = rowsum(dO * O) comes
+// dQ of this (query block, key block) pair is staged as fp32 in the shared memory that P^T / dS^T occupied and added
+// to an fp32 buffer in global memory by TMA reductions (cp.reduce.async.bulk.tensor ... add); the caller zeroes that
+// buffer and converts it afterwards.  delta = rowsum(dO * O) comes
 // from a small preprocessing kernel.  Q and dO stream through a three-slot TMA ring; every wait is bounded.
 //
 // Parity: the reference calls a closed vendor flash backward (reference torch_musa/csrc/aten/ops/attention/mudnn/SDP.cpp:678-845).
@@ -46,8 +47,11 @@ struct BwdParams {
   int* status;
 };
 
-__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+// adds a [128 rows x 32 floats] box of shared memory (128B-swizzled) into global memory at (x, y) of the tensor map
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+               : "memory");
 }
 __device__ __forceinline__ void named_bar_sync(int id, int count) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
@@ -57,7 +61,7 @@ template <typename T>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
-                T* __restrict__ dk, T* __restrict__ dv, const BwdParams p) {
+                const __grid_constant__ CUtensorMap tmap_dq, T* __restrict__ dk, T* __restrict__ dv, const BwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sK = smem;
@@ -78,12 +82,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   uint64_t* ds_ready = p_ready + 1;          // 8 warps: dS^T in shared memory, dP^T read
   uint64_t* mma2_done = ds_ready + 1;        // tcgen05.commit: dV, dK, dQ of this pair complete
   uint64_t* dq_drained = mma2_done + 1;      // 8 warps: dQ read out of TMEM
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dq_drained + 1);
+  uint64_t* stage_free = dq_drained + 1;     // one thread: the TMA reduction has read the staged dQ
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(stage_free + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kb = (int)(blockIdx.x % p.kv_blocks);   // early key blocks (most query blocks under a causal mask) first
-  const int bh = blockIdx.x / p.kv_blocks;
+  // all (batch, head) instances of the earliest key block first: under a causal mask it meets the most query blocks
+  const int n_bh = p.B * p.Hkv;
+  const int kb = (int)(blockIdx.x / n_bh);
+  const int bh = (int)(blockIdx.x % n_bh);
   const int b = bh / p.Hkv, hk = bh - b * p.Hkv;
   const int G = p.H / p.Hkv;
   const int k0 = kb * BK;
@@ -105,11 +112,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     mbar_init(ds_ready, 8);
     mbar_init(mma2_done, 1);
     mbar_init(dq_drained, 8);
+    mbar_init(stage_free, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     prefetch_tmap(&tmap_q);
     prefetch_tmap(&tmap_k);
     prefetch_tmap(&tmap_v);
     prefetch_tmap(&tmap_do);
+    prefetch_tmap(&tmap_dq);
   }
   if (warp == 9) {
     tmem_alloc(tmem_slot, kBwdTmemCols);
@@ -177,17 +186,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           umma_f16(tmem_base + dcol, make_desc(aa + (uint32_t)kk * 2048, kTile / 2, 1024),
                    make_desc(ba + (uint32_t)kk * 2048, kTile / 2, 1024), idesc_mnmn, kk != 0 ? 1u : 0u);
       };
-      bool ok = mbar_wait(kv_full, 0, abort_flag);
+      // Issue order per pair: dP^T, dV, then S^T of the NEXT pair (its TMEM columns are free once P^T has been formed, so
+      // the tensor core computes it while the warpgroups still work on dS^T), then dK and dQ.
+      bool ok = mbar_wait(kv_full, 0, abort_flag) && ring_wait(0);
+      if (ok) {
+        tc_fence_after();
+        mma_kk(kColS, sK, sR);                         // S^T of the first pair (ring item 0)
+        umma_commit(s_full);
+      }
       for (int it = 0; it < n_it && ok; ++it) {
         const int nq = 2 * it, ndo = 2 * it + 1;
         const uint32_t par = (uint32_t)(it & 1), prev = par ^ 1u;
         const uint8_t* tQ = sR + (nq % kRing) * kTile;
         const uint8_t* tdO = sR + (ndo % kRing) * kTile;
-        if (!ring_wait(nq)) { ok = false; break; }
-        if (it > 0 && !mbar_wait(s_free, prev, abort_flag)) { ok = false; break; }
-        tc_fence_after();
-        mma_kk(kColS, sK, tQ);                       // S^T = K Q^T
-        umma_commit(s_full);
         if (!ring_wait(ndo)) { ok = false; break; }
         if (it > 0 && !mbar_wait(dq_drained, prev, abort_flag)) { ok = false; break; }
         tc_fence_after();
@@ -196,6 +207,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         if (!mbar_wait(p_ready, par, abort_flag)) { ok = false; break; }
         tc_fence_after();
         mma_kmn(kColDV, sP, tdO, it == 0);           // dV += P^T dO
+        if (it + 1 < n_it) {
+          if (!ring_wait(nq + 2)) { ok = false; break; }
+          if (!mbar_wait(s_free, par, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          mma_kk(kColS, sK, sR + ((nq + 2) % kRing) * kTile);   // S^T of the next pair
+          umma_commit(s_full);
+        }
         if (!mbar_wait(ds_ready, par, abort_flag)) { ok = false; break; }
         tc_fence_after();
         mma_kmn(kColDK, sS, tQ, it == 0);            // dK += dS^T Q
@@ -225,46 +243,67 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       const uint32_t par = (uint32_t)(it & 1);
       const int h = hk * G + it / n_i;
       const int q0 = (i0 + it % n_i) * BQ;
-      // lse (log2 domain) and delta of the 128 query rows of this block; +inf switches a row off.  Single buffers:
-      // a thread gets here only after mma2_done of the previous pair, which needs every warp's ds_ready, i.e. all
-      // reads of the previous values.
+      // lse (log2 domain) and delta (times the softmax scale) of the 128 query rows of this block; +inf switches a row
+      // off.  Single buffers: a thread gets here only after mma2_done of the previous pair, which needs every warp's
+      // ds_ready, i.e. all reads of the previous values.
       {
         const int which = tid >> 7, q = tid & 127, qi = q0 + q;
         const int64_t idx = ((int64_t)b * p.H + h) * p.Sq + qi;
         if (which == 0) {
           float l = qi < p.Sq ? p.lse[idx] : -INFINITY;
-          s_lse[q] = l > -INFINITY ? l * 1.4426950408889634f : INFINITY;
+          s_lse[q] = l > -INFINITY ? -l * 1.4426950408889634f : -INFINITY;   // negated: an addend of the exponent
         } else {
-          s_dlt[q] = qi < p.Sq ? p.delta[idx] : 0.f;
+          s_dlt[q] = qi < p.Sq ? -p.delta[idx] * p.scale : 0.f;              // negated and scaled likewise
         }
       }
       named_bar_sync(1, 256);
-      const float* lse2 = s_lse + wg * 64;
-      const float* dlt = s_dlt + wg * 64;
+      const float4* nlse4 = reinterpret_cast<const float4*>(s_lse + wg * 64);
+      const float4* ndlt4 = reinterpret_cast<const float4*>(s_dlt + wg * 64);
       const bool diag = p.causal && q0 < k0 + BK;       // only then can a query be older than a key of this block
+      const bool key_off = kj >= p.Sk;
       if (!wait_all(s_full, par)) { ok = false; break; }
+      // the staged dQ of the previous pair must have left the shared memory that P^T is written to
+      if (it > 0 && !wait_all(stage_free, par ^ 1u)) { ok = false; break; }
       tc_fence_after();
       float pf[64];
+      {
+        uint32_t ra[32], rb[32];
+        auto chunk_p = [&](const uint32_t (&raw)[32], int c) {
+          uint32_t pk[16];
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t raw[32];
-        tmem_ld32(tmem_base + lane_base + kColS + (uint32_t)(wg * 64 + c * 32), raw);
-        tmem_ld_wait();
+          for (int e4 = 0; e4 < 8; ++e4) {
+            const float4 nl = nlse4[c * 8 + e4];
+            const float nls[4] = {nl.x, nl.y, nl.z, nl.w};
 #pragma unroll
-        for (int g8 = 0; g8 < 4; ++g8) {
-          Vec16<T> pk;
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const int cc = c * 32 + g8 * 8 + e;                 // query column inside this warpgroup's half
-            const int qi = q0 + wg * 64 + cc;
-            float pv = exp2f(fmaf(__uint_as_float(raw[g8 * 8 + e]), p.scale_log2, -lse2[cc]));
-            if (kj >= p.Sk || (diag && qi < kj)) pv = 0.f;
-            pf[cc] = pv;
-            pk.v[e] = ToF<T>::from(pv);
+            for (int e2 = 0; e2 < 4; e2 += 2) {
+              const int e = e4 * 4 + e2, cc = c * 32 + e;
+              float x0, x1;
+              fma2v(x0, x1, __uint_as_float(raw[e]), __uint_as_float(raw[e + 1]), p.scale_log2, nls[e2], nls[e2 + 1]);
+              float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+              if (key_off || diag) {
+                const int qi = q0 + wg * 64 + cc;
+                if (key_off || qi < kj) p0 = 0.f;
+                if (key_off || qi + 1 < kj) p1 = 0.f;
+              }
+              pf[cc] = p0;
+              pf[cc + 1] = p1;
+              pk[e >> 1] = pack2<T>(p0, p1);
+            }
           }
-          const int ch = c * 4 + g8;
-          *reinterpret_cast<Vec16<T>*>(prow + (size_t)((ch ^ (r & 7)) * 16)) = pk;
-        }
+#pragma unroll
+          for (int g8 = 0; g8 < 4; ++g8) {
+            const int ch = c * 4 + g8;
+            *reinterpret_cast<uint4*>(prow + (size_t)((ch ^ (r & 7)) * 16)) =
+                make_uint4(pk[g8 * 4], pk[g8 * 4 + 1], pk[g8 * 4 + 2], pk[g8 * 4 + 3]);
+          }
+        };
+        const uint32_t addr = tmem_base + lane_base + kColS + (uint32_t)(wg * 64);
+        tmem_ld32(addr, ra);
+        tmem_ld_wait();
+        tmem_ld32(addr + 32u, rb);
+        chunk_p(ra, 0);
+        tmem_ld_wait();
+        chunk_p(rb, 1);
       }
       tc_fence_before();
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -275,51 +314,81 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       }
       if (!wait_all(dp_full, par)) { ok = false; break; }
       tc_fence_after();
+      {
+        uint32_t ra[32], rb[32];
+        auto chunk_ds = [&](const uint32_t (&raw)[32], int c) {
+          uint32_t pk[16];
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t raw[32];
-        tmem_ld32(tmem_base + lane_base + kColDP + (uint32_t)(wg * 64 + c * 32), raw);
-        tmem_ld_wait();
+          for (int e4 = 0; e4 < 8; ++e4) {
+            const float4 nd = ndlt4[c * 8 + e4];
+            const float nds[4] = {nd.x, nd.y, nd.z, nd.w};
 #pragma unroll
-        for (int g8 = 0; g8 < 4; ++g8) {
-          Vec16<T> pk;
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const int cc = c * 32 + g8 * 8 + e;
-            const float ds = pf[cc] * (__uint_as_float(raw[g8 * 8 + e]) - dlt[cc]) * p.scale;
-            pk.v[e] = ToF<T>::from(ds);
+            for (int e2 = 0; e2 < 4; e2 += 2) {
+              const int e = e4 * 4 + e2, cc = c * 32 + e;
+              float t0, t1, d0, d1;
+              fma2v(t0, t1, __uint_as_float(raw[e]), __uint_as_float(raw[e + 1]), p.scale, nds[e2], nds[e2 + 1]);
+              mul2(d0, d1, pf[cc], pf[cc + 1], t0, t1);
+              pk[e >> 1] = pack2<T>(d0, d1);
+            }
           }
-          const int ch = c * 4 + g8;
-          *reinterpret_cast<Vec16<T>*>(srow + (size_t)((ch ^ (r & 7)) * 16)) = pk;
-        }
+#pragma unroll
+          for (int g8 = 0; g8 < 4; ++g8) {
+            const int ch = c * 4 + g8;
+            *reinterpret_cast<uint4*>(srow + (size_t)((ch ^ (r & 7)) * 16)) =
+                make_uint4(pk[g8 * 4], pk[g8 * 4 + 1], pk[g8 * 4 + 2], pk[g8 * 4 + 3]);
+          }
+        };
+        const uint32_t addr = tmem_base + lane_base + kColDP + (uint32_t)(wg * 64);
+        tmem_ld32(addr, ra);
+        tmem_ld_wait();
+        tmem_ld32(addr + 32u, rb);
+        chunk_ds(ra, 0);
+        tmem_ld_wait();
+        chunk_ds(rb, 1);
       }
       tc_fence_before();
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(ds_ready);
-      // dQ of this pair: lane = query row, this warpgroup's 64 head-dim columns
+      // dQ of this pair: lane = query row, this warpgroup's 64 head-dim columns.  Staged as fp32 in the 64 KB that
+      // P^T and dS^T occupied (the MMAs that read them have completed): four [128 rows x 128 bytes] boxes, 128B-swizzled.
       if (!wait_all(mma2_done, par)) { ok = false; break; }
       tc_fence_after();
       {
-        const int qi = q0 + r;
-        float* dq_row = p.dq + (((int64_t)b * p.H + h) * p.Sq + qi) * BD + wg * 64;
+        uint32_t ra[32], rb[32];
+        auto stage = [&](const uint32_t (&raw)[32], int c) {
+          uint8_t* box = sP + (size_t)(wg * 2 + c) * (kTile / 2) + (size_t)r * 128;
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t raw[32];
-          tmem_ld32(tmem_base + lane_base + kColDP + (uint32_t)(wg * 64 + c * 32), raw);
-          tmem_ld_wait();
-          if (qi < p.Sq) {
-#pragma unroll
-            for (int e = 0; e < 32; e += 4)
-              red_add_v4(dq_row + c * 32 + e, __uint_as_float(raw[e]), __uint_as_float(raw[e + 1]),
-                         __uint_as_float(raw[e + 2]), __uint_as_float(raw[e + 3]));
-          }
-        }
+          for (int ch = 0; ch < 8; ++ch)
+            *reinterpret_cast<uint4*>(box + (size_t)((ch ^ (r & 7)) * 16)) =
+                make_uint4(raw[ch * 4], raw[ch * 4 + 1], raw[ch * 4 + 2], raw[ch * 4 + 3]);
+        };
+        const uint32_t addr = tmem_base + lane_base + kColDP + (uint32_t)(wg * 64);
+        tmem_ld32(addr, ra);
+        tmem_ld_wait();
+        tmem_ld32(addr + 32u, rb);
+        stage(ra, 0);
+        tmem_ld_wait();
+        stage(rb, 1);
       }
       tc_fence_before();
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(dq_drained);
+      named_bar_sync(2, 256);
+      if (tid == 0) {
+        const int row0 = (int)(((int64_t)b * p.H + h) * p.Sq + q0);
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          tma_reduce_add_2d(&tmap_dq, sP + (size_t)c * (kTile / 2), c * 32, row0);
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        mbar_arrive(stage_free);
+      }
+      __syncwarp();
     }
+    // every reduction must have completed before the CTA exits
+    if (tid == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     // ---- dK, dV of this key block (all pairs have completed: the last mma2_done was waited for above)
     if (ok) {
       tc_fence_after();
@@ -360,6 +429,26 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     tmem_dealloc(tmem_base, kBwdTmemCols);
   }
   if (threadIdx.x == 0 && *abort_flag && p.status) atomicExch(p.status, 1);
+}
+
+bool make_dq_map(CUtensorMap* out, float* ptr, int64_t rows) {
+  static EncodeTiledFn enc = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess) {
+      (void)cudaGetLastError();
+      return (EncodeTiledFn) nullptr;
+    }
+    return (EncodeTiledFn)p;
+  }();
+  if (!enc || rows <= 0) return false;
+  cuuint64_t dims[2] = {128, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {128 * sizeof(float)};
+  cuuint32_t box[2] = {32, 128};
+  cuuint32_t estr[2] = {1, 1};
+  return enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 // delta[b, h, q] = sum_d O[b, h, q, d] * dO[b, h, q, d]; one warp per row
@@ -416,6 +505,9 @@ extern "C" int b200_flash_attn_bwd(const b200_attn_t* a, float* dq_accum, void* 
       !make_attn_map(&mv, v, bf16, a->B, a->Hkv, a->Sk, nz(a->v_sb, 8), nz(a->v_sh, 8), a->v_ss) ||
       !make_attn_map(&mdo, d_o, bf16, a->B, a->H, a->Sq, nz(x[0], 8), nz(x[1], 8), x[2]))
     return (int)cudaErrorNotSupported;
+  // dq_accum as a [B * H * Sq, 128] fp32 matrix; one box = 32 columns (128 bytes) of 128 rows
+  CUtensorMap mdq;
+  if (!make_dq_map(&mdq, dq_accum, (int64_t)a->B * a->H * a->Sq)) return (int)cudaErrorNotSupported;
   BwdParams p{};
   p.B = a->B; p.H = a->H; p.Hkv = a->Hkv; p.Sq = a->Sq; p.Sk = a->Sk;
   p.causal = a->causal;
@@ -444,7 +536,7 @@ extern "C" int b200_flash_attn_bwd(const b200_attn_t* a, float* dq_accum, void* 
       if (e != cudaSuccess) return (int)e;
       set = true;
     }
-    kern<<<(unsigned)grid, kBwdThreads, kBwdSmem, stream>>>(mq, mk, mv, mdo, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, p);
+    kern<<<(unsigned)grid, kBwdThreads, kBwdSmem, stream>>>(mq, mk, mv, mdo, mdq, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, p);
   } else {
     attn_delta_kernel<__half><<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>(
         (const __half*)o, (const __half*)d_o, delta, a->B, a->H, a->Sq, a->o_sb, a->o_sh, a->o_ss, x[0], x[1], x[2]);
@@ -455,7 +547,7 @@ extern "C" int b200_flash_attn_bwd(const b200_attn_t* a, float* dq_accum, void* 
       if (e != cudaSuccess) return (int)e;
       set = true;
     }
-    kern<<<(unsigned)grid, kBwdThreads, kBwdSmem, stream>>>(mq, mk, mv, mdo, (__half*)dk, (__half*)dv, p);
+    kern<<<(unsigned)grid, kBwdThreads, kBwdSmem, stream>>>(mq, mk, mv, mdo, mdq, (__half*)dk, (__half*)dv, p);
   }
   note_launch(2);
   return (int)cudaGetLastError();

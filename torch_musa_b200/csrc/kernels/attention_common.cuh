@@ -27,6 +27,59 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
+// 2^x on the special-function unit, one instruction (flush-to-zero: the arguments here are <= 8 and any
+// subnormal result rounds to zero in bf16 anyway)
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// two fp32 operations per instruction (sm_100 packed fp32): (d0, d1) = (x0, x1) * s + c
+__device__ __forceinline__ void fma2(float& d0, float& d1, float x0, float x1, float s, float c) {
+  asm("{\n\t.reg .b64 rx, rs, rc, rd;\n\t"
+      "mov.b64 rx, {%2, %3};\n\tmov.b64 rs, {%4, %4};\n\tmov.b64 rc, {%5, %5};\n\t"
+      "fma.rn.f32x2 rd, rx, rs, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d0), "=f"(d1)
+      : "f"(x0), "f"(x1), "f"(s), "f"(c));
+}
+// (d0, d1) = (x0, x1) * s + (c0, c1)
+__device__ __forceinline__ void fma2v(float& d0, float& d1, float x0, float x1, float s, float c0, float c1) {
+  asm("{\n\t.reg .b64 rx, rs, rc, rd;\n\t"
+      "mov.b64 rx, {%2, %3};\n\tmov.b64 rs, {%4, %4};\n\tmov.b64 rc, {%5, %6};\n\t"
+      "fma.rn.f32x2 rd, rx, rs, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d0), "=f"(d1)
+      : "f"(x0), "f"(x1), "f"(s), "f"(c0), "f"(c1));
+}
+// (a0, a1) += (b0, b1)
+__device__ __forceinline__ void add2(float& a0, float& a1, float b0, float b1) {
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
+      "mov.b64 ra, {%0, %1};\n\tmov.b64 rb, {%2, %3};\n\t"
+      "add.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "+f"(a0), "+f"(a1)
+      : "f"(b0), "f"(b1));
+}
+// (d0, d1) = (x0, x1) * (y0, y1)
+__device__ __forceinline__ void mul2(float& d0, float& d1, float x0, float x1, float y0, float y1) {
+  asm("{\n\t.reg .b64 rx, ry, rd;\n\t"
+      "mov.b64 rx, {%2, %3};\n\tmov.b64 ry, {%4, %5};\n\t"
+      "mul.rn.f32x2 rd, rx, ry;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d0), "=f"(d1)
+      : "f"(x0), "f"(x1), "f"(y0), "f"(y1));
+}
+// two floats to one packed pair of 16-bit values (one conversion instruction)
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float a, float b);
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  const __half2 v = __floats2half2_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 

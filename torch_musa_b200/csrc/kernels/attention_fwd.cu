@@ -61,9 +61,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // heavy (late) query tiles first
-  const int qp = p.q_pairs - 1 - (int)(blockIdx.x % p.q_pairs);
-  const int bh = blockIdx.x / p.q_pairs;
+  // heavy (late) query tiles first, across all (batch, head) instances
+  const int n_bh = p.B * p.H;
+  const int qp = p.q_pairs - 1 - (int)(blockIdx.x / n_bh);
+  const int bh = (int)(blockIdx.x % n_bh);
   const int b = bh / p.H, h = bh - b * p.H;
   const int hk = h / (p.H / p.Hkv);
   int nb[2];
@@ -217,21 +218,32 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       if (p.causal) lim = min(lim, qi - k0 + 1);
       lim = max(0, min(lim, AK));
       const bool full = __all_sync(0xffffffffu, lim == AK);
-      // pass 1: block maximum of the raw scores
+      // pass 1: block maximum of the raw scores (the TMEM load of one 32-column chunk overlaps the work on the other)
       float m_blk = -INFINITY;
+      {
+        uint32_t ra[32], rb[32];
+        auto chunk_max = [&](const uint32_t (&raw)[32], int c) {
+          if (full) {
 #pragma unroll
-      for (int c = 0; c < AK / 32; ++c) {
-        uint32_t raw[32];
-        tmem_ld32(s_addr + (uint32_t)(c * 32), raw);
+            for (int e = 0; e < 32; ++e) m_blk = fmaxf(m_blk, __uint_as_float(raw[e]));
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+              if (c * 32 + e < lim) m_blk = fmaxf(m_blk, __uint_as_float(raw[e]));
+          }
+        };
+        tmem_ld32(s_addr, ra);
         tmem_ld_wait();
-        if (full) {
-#pragma unroll
-          for (int e = 0; e < 32; ++e) m_blk = fmaxf(m_blk, __uint_as_float(raw[e]));
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; ++e)
-            if (c * 32 + e < lim) m_blk = fmaxf(m_blk, __uint_as_float(raw[e]));
-        }
+        tmem_ld32(s_addr + 32u, rb);
+        chunk_max(ra, 0);
+        tmem_ld_wait();
+        tmem_ld32(s_addr + 64u, ra);
+        chunk_max(rb, 1);
+        tmem_ld_wait();
+        tmem_ld32(s_addr + 96u, rb);
+        chunk_max(ra, 2);
+        tmem_ld_wait();
+        chunk_max(rb, 3);
       }
       const float m_new = fmaxf(m_ref, m_blk * p.scale_log2);
       // P of the previous block must have been consumed (and O updated) before P is rewritten or O rescaled
@@ -258,29 +270,48 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         }
       }
       const float m_use = m_ref == -INFINITY ? 0.f : m_ref;       // row without any visible key so far
-      // pass 2: P = exp2(S * scale - m) as bf16/fp16 into the swizzled K-major tile
-      float l_blk = 0.f;
+      // pass 2: P = exp2(S * scale - m) as bf16/fp16 into the swizzled K-major tile; packed fp32 arithmetic, one
+      // special-function instruction per exponential, one conversion per pair
+      float l0 = 0.f, l1 = 0.f;
+      {
+        uint32_t ra[32], rb[32];
+        const float neg_m = -m_use;
+        auto chunk_p = [&](const uint32_t (&raw)[32], int c) {
+          uint32_t pk[16];
 #pragma unroll
-      for (int c = 0; c < AK / 32; ++c) {
-        uint32_t raw[32];
-        tmem_ld32(s_addr + (uint32_t)(c * 32), raw);
-        tmem_ld_wait();
-#pragma unroll
-        for (int g8 = 0; g8 < 4; ++g8) {
-          Vec16<T> pk;
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const int col = c * 32 + g8 * 8 + e;
-            float pv = exp2f(fmaf(__uint_as_float(raw[g8 * 8 + e]), p.scale_log2, -m_use));
-            if (!full && col >= lim) pv = 0.f;
-            l_blk += pv;
-            pk.v[e] = ToF<T>::from(pv);
+          for (int e = 0; e < 32; e += 2) {
+            float x0, x1;
+            fma2(x0, x1, __uint_as_float(raw[e]), __uint_as_float(raw[e + 1]), p.scale_log2, neg_m);
+            float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+            if (!full) {
+              if (c * 32 + e >= lim) p0 = 0.f;
+              if (c * 32 + e + 1 >= lim) p1 = 0.f;
+            }
+            add2(l0, l1, p0, p1);
+            pk[e >> 1] = pack2<T>(p0, p1);
           }
-          const int c8 = c * 4 + g8;
-          const int atom = c8 >> 3, ch = c8 & 7;
-          *reinterpret_cast<Vec16<T>*>(prow + (size_t)atom * (kTile / 2) + (size_t)((ch ^ (r & 7)) * 16)) = pk;
-        }
+#pragma unroll
+          for (int g8 = 0; g8 < 4; ++g8) {
+            const int c8 = c * 4 + g8;
+            const int atom = c8 >> 3, ch = c8 & 7;
+            *reinterpret_cast<uint4*>(prow + (size_t)atom * (kTile / 2) + (size_t)((ch ^ (r & 7)) * 16)) =
+                make_uint4(pk[g8 * 4], pk[g8 * 4 + 1], pk[g8 * 4 + 2], pk[g8 * 4 + 3]);
+          }
+        };
+        tmem_ld32(s_addr, ra);
+        tmem_ld_wait();
+        tmem_ld32(s_addr + 32u, rb);
+        chunk_p(ra, 0);
+        tmem_ld_wait();
+        tmem_ld32(s_addr + 64u, ra);
+        chunk_p(rb, 1);
+        tmem_ld_wait();
+        tmem_ld32(s_addr + 96u, rb);
+        chunk_p(ra, 2);
+        tmem_ld_wait();
+        chunk_p(rb, 3);
       }
+      const float l_blk = l0 + l1;
       l_run += l_blk;
       tc_fence_before();
       // make the generic-proxy writes of P visible to the tensor core (async proxy), then signal
