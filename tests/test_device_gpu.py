@@ -228,3 +228,25 @@ def test_legacy_autograd_profiler_uses_device_stubs(bw, dev):
     except (RuntimeError, AssertionError, TypeError, ValueError) as e:
         pytest.skip(f"legacy autograd profiler unavailable here: {e}")
     assert "aten::mm" in table
+
+
+def test_legacy_typed_tensor_classes_on_device(bw, dev):
+    t = bw.FloatTensor(2, 3)
+    assert t.shape == (2, 3) and t.dtype == torch.float32 and t.device.type == "blackwell"
+    assert isinstance(t, bw.FloatTensor) and not isinstance(t, bw.HalfTensor)
+    h = bw.HalfTensor([1.0, 2.0, 3.0])
+    assert isinstance(h, bw.HalfTensor) and h.cpu().tolist() == [1.0, 2.0, 3.0]
+    assert isinstance(bw.LongTensor(torch.arange(4)), bw.LongTensor)
+    assert bw.BFloat16Tensor().numel() == 0
+
+
+def test_cpp_example_runs(bw):
+    import os
+    import subprocess
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run(["make", "-C", os.path.join(root, "examples", "cpp")], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    r = subprocess.run([os.path.join(root, "examples", "cpp", "rmsnorm_example")], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "max abs error" in r.stdout

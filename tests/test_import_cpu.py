@@ -82,3 +82,12 @@ def test_fake_tensor_rules(bw):
     assert y.shape == (4, 32)
     l, lse = torch.ops.blackwell.cross_entropy_fwd(torch.empty(8, 100, device="meta"), torch.empty(8, dtype=torch.long, device="meta"))
     assert l.shape == (8,) and l.dtype == torch.float32
+
+
+def test_legacy_typed_tensor_classes(bw):
+    for name, dt in [("FloatTensor", torch.float32), ("HalfTensor", torch.float16), ("BFloat16Tensor", torch.bfloat16),
+                     ("LongTensor", torch.int64), ("BoolTensor", torch.bool), ("DoubleTensor", torch.float64)]:
+        cls = getattr(torch.blackwell, name)
+        assert cls.dtype == dt and cls.is_blackwell
+        assert not isinstance(torch.zeros(1, dtype=dt), cls)        # a CPU tensor is not a device tensor
+    assert repr(bw.FloatTensor) == "<class 'torch.blackwell.FloatTensor'>"

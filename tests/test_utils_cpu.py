@@ -92,3 +92,17 @@ def test_kv_cache_decoder_matches_full_recompute_on_cpu():
             want.append(nxt)
             seq = torch.cat([seq, nxt], 1)
     assert torch.equal(got, torch.cat(want, 1))
+
+
+def test_cpp_example_builds():
+    """The stand-alone C++ example compiles and links against the in-tree kernel library (running it needs a GPU)."""
+    import os
+    import subprocess
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    if not os.path.exists(os.path.join(root, "torch_musa_b200", "libb200_kernels.so")):
+        import pytest
+
+        pytest.skip("kernel library not built")
+    r = subprocess.run(["make", "-C", os.path.join(root, "examples", "cpp"), "-B"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr

@@ -175,6 +175,10 @@ from .core import attrs as _attrs  # noqa: E402
 
 CUDAGraph = BlackwellGraph  # torch.cuda-style alias used by generic code
 
+from .core.tensor_types import make_types as _make_tensor_types  # noqa: E402
+
+globals().update(_make_tensor_types())  # FloatTensor, HalfTensor, BFloat16Tensor, ... (legacy typed classes)
+
 
 def ipc_collect():
     """Release device memory held for tensors received from other processes (no-op: IPC mappings

@@ -247,7 +247,9 @@ class FusedFSDP:
         self.group = mesh_pg
         self.rank, self.world = mesh_pg.rank(), mesh_pg.size()
         self.gather_ctas = int(gather_ctas or os.environ.get("B200_FSDP_GATHER_CTAS", 32))
-        self.reduce_ctas = int(reduce_ctas or os.environ.get("B200_FSDP_REDUCE_CTAS", 48))
+        # With one rank the reduce kernel is the optimizer pass over the whole model, bound by HBM bandwidth: two CTAs
+        # per SM.  With several ranks it shares the SMs with the backward GEMMs while it waits for its peers: fewer.
+        self.reduce_ctas = int(reduce_ctas or os.environ.get("B200_FSDP_REDUCE_CTAS", 296 if self.world == 1 else 64))
         self.calls: Dict[str, int] = {"pack": 0, "gather": 0, "reduce": 0, "reduce_adamw": 0}
         self.skipped: Dict[str, str] = {}
         self.seq = 0                      # reduce calls issued so far (same on every rank)
