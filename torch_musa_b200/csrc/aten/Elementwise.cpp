@@ -5,6 +5,7 @@
 // Parity: reference torch_musa/csrc/aten/ops/{Binary,Unary,Activation,Fill}.cpp and
 // musa/{Add,Mul,Div,Fill}.mu.
 #include "aten/FallbackCall.h"
+#include "aten/Loops.h"
 #include "aten/Ops.h"
 
 #include <ATen/Functions.h>
@@ -14,6 +15,13 @@
 
 namespace b200 {
 namespace ops {
+
+// the general loops behind the fast paths (aten/Pointwise.cpp)
+bool generic_binary(int op, at::Tensor& out, const at::Tensor& a, const at::Tensor& b, double alpha, bool float_result,
+                    bool resize_out);
+bool generic_binary_scalar(int op, at::Tensor& out, const at::Tensor& a, const at::Scalar& s, double alpha);
+bool generic_unary(int op, at::Tensor& out, const at::Tensor& a, bool float_result, bool resize_out);
+bool generic_binary_same(int op, at::Tensor& out, const at::Tensor& a, const at::Tensor& b, double p0, double p1);
 
 namespace {
 std::atomic<int64_t> g_unused{0};
@@ -66,16 +74,21 @@ bool unary_fast(int op, const at::Tensor& out, const at::Tensor& a) {
 inline at::Tensor like(const at::Tensor& a) { return at::empty_strided(a.sizes(), a.strides(), a.options()); }
 
 // ----------------------------------------------------------------- binary (Tensor, Tensor[, alpha])
-#define B200_BINARY_ALPHA(NAME, OPC)                                                                       \
+#define B200_BINARY_ALPHA(NAME, OPC, OPG)                                                                  \
   at::Tensor NAME##_tensor(const at::Tensor& a, const at::Tensor& b, const at::Scalar& alpha) {            \
     if (a.dim() > 0 && b.dim() > 0 && fast_dtype(a) && a.is_non_overlapping_and_dense()) {                 \
       at::Tensor out = like(a);                                                                            \
       if (binary_fast(OPC, out, a, b, alpha.toDouble())) return out;                                       \
     }                                                                                                      \
+    if (!alpha.isComplex()) {                                                                              \
+      at::Tensor out;                                                                                      \
+      if (generic_binary(OPG, out, a, b, alpha.toDouble(), false, false)) return out;                      \
+    }                                                                                                      \
     return fallback_tensor(B200_OP_HANDLE("aten::" #NAME, "Tensor"), a, b, alpha);                         \
   }                                                                                                        \
   at::Tensor& NAME##_tensor_(at::Tensor& a, const at::Tensor& b, const at::Scalar& alpha) {                \
     if (a.dim() > 0 && b.dim() > 0 && binary_fast(OPC, a, a, b, alpha.toDouble())) return a;               \
+    if (!alpha.isComplex() && generic_binary(OPG, a, a, b, alpha.toDouble(), false, false)) return a;      \
     run_fallback(B200_OP_HANDLE("aten::" #NAME "_", "Tensor"), a, b, alpha);                               \
     return a;                                                                                              \
   }                                                                                                        \
@@ -83,14 +96,15 @@ inline at::Tensor like(const at::Tensor& a) { return at::empty_strided(a.sizes()
                                 at::Tensor& out) {                                                         \
     if (a.dim() > 0 && b.dim() > 0 && out.sizes() == a.sizes() && binary_fast(OPC, out, a, b, alpha.toDouble())) \
       return out;                                                                                          \
+    if (!alpha.isComplex() && generic_binary(OPG, out, a, b, alpha.toDouble(), false, true)) return out;   \
     run_fallback(B200_OP_HANDLE("aten::" #NAME, "out"), a, b, alpha, out);                                 \
     return out;                                                                                            \
   }
 
-B200_BINARY_ALPHA(add, B200_OP_ADD)
-B200_BINARY_ALPHA(sub, B200_OP_SUB)
+B200_BINARY_ALPHA(add, B200_OP_ADD, B200_EW_ADD)
+B200_BINARY_ALPHA(sub, B200_OP_SUB, B200_EW_SUB)
 
-#define B200_BINARY(NAME, OPC)                                                                             \
+#define B200_BINARY(NAME, OPC, OPG, FLOATRES)                                                              \
   at::Tensor NAME##_tensor(const at::Tensor& a, const at::Tensor& b) {                                     \
     if (a.dim() > 0 && b.dim() > 0 && fast_dtype(a) && a.is_non_overlapping_and_dense()) {                 \
       at::Tensor out = like(a);                                                                            \
@@ -101,50 +115,70 @@ B200_BINARY_ALPHA(sub, B200_OP_SUB)
       at::Tensor out = like(a);                                                                            \
       if (binary_scalar_fast(OPC, out, a, b.item<double>(), 1.0)) return out;                              \
     }                                                                                                      \
+    {                                                                                                      \
+      at::Tensor out;                                                                                      \
+      if (generic_binary(OPG, out, a, b, 1.0, FLOATRES, false)) return out;                                \
+    }                                                                                                      \
     return fallback_tensor(B200_OP_HANDLE("aten::" #NAME, "Tensor"), a, b);                                \
+  }                                                                                                        \
+  at::Tensor& NAME##_tensor_out(const at::Tensor& a, const at::Tensor& b, at::Tensor& out) {               \
+    if (a.dim() > 0 && b.dim() > 0 && out.sizes() == a.sizes() && binary_fast(OPC, out, a, b, 1.0)) return out; \
+    if (generic_binary(OPG, out, a, b, 1.0, FLOATRES, true)) return out;                                   \
+    run_fallback(B200_OP_HANDLE("aten::" #NAME, "out"), a, b, out);                                        \
+    return out;                                                                                            \
   }                                                                                                        \
   at::Tensor& NAME##_tensor_(at::Tensor& a, const at::Tensor& b) {                                         \
     if (a.dim() > 0 && b.dim() > 0 && binary_fast(OPC, a, a, b, 1.0)) return a;                            \
     if (a.dim() > 0 && b.dim() == 0 && b.device().is_cpu() && b.is_floating_point() &&                     \
         binary_scalar_fast(OPC, a, a, b.item<double>(), 1.0))                                              \
       return a;                                                                                            \
+    if (generic_binary(OPG, a, a, b, 1.0, FLOATRES, false)) return a;                                      \
     run_fallback(B200_OP_HANDLE("aten::" #NAME "_", "Tensor"), a, b);                                      \
     return a;                                                                                              \
   }
 
-B200_BINARY(mul, B200_OP_MUL)
-B200_BINARY(div, B200_OP_DIV)
+B200_BINARY(mul, B200_OP_MUL, B200_EW_MUL, false)
+B200_BINARY(div, B200_OP_DIV, B200_EW_DIV, true)
 
 // ----------------------------------------------------------------- unary
-#define B200_UNARY(NAME, OPC)                                                                              \
+#define B200_UNARY(NAME, OPC, OPG, FLOATRES)                                                               \
   at::Tensor NAME(const at::Tensor& a) {                                                                   \
     if (fast_dtype(a) && a.is_non_overlapping_and_dense()) {                                               \
       at::Tensor out = like(a);                                                                            \
       if (unary_fast(OPC, out, a)) return out;                                                             \
     }                                                                                                      \
+    {                                                                                                      \
+      at::Tensor out;                                                                                      \
+      if (generic_unary(OPG, out, a, FLOATRES, false)) return out;                                         \
+    }                                                                                                      \
     return fallback_tensor(B200_OP_HANDLE("aten::" #NAME, ""), a);                                         \
   }                                                                                                        \
   at::Tensor& NAME##_(at::Tensor& a) {                                                                     \
     if (unary_fast(OPC, a, a)) return a;                                                                   \
+    if (generic_unary(OPG, a, a, FLOATRES, false)) return a;                                               \
     run_fallback(B200_OP_HANDLE("aten::" #NAME "_", ""), a);                                               \
     return a;                                                                                              \
   }
 
-B200_UNARY(relu, B200_OP_RELU)
-B200_UNARY(silu, B200_OP_SILU)
-B200_UNARY(sigmoid, B200_OP_SIGMOID)
-B200_UNARY(tanh, B200_OP_TANH)
-B200_UNARY(exp, B200_OP_EXP)
-B200_UNARY(neg, B200_OP_NEG)
-B200_UNARY(abs, B200_OP_ABS)
-B200_UNARY(sqrt, B200_OP_SQRT)
-B200_UNARY(rsqrt, B200_OP_RSQRT)
-B200_UNARY(reciprocal, B200_OP_RECIPROCAL)
+B200_UNARY(relu, B200_OP_RELU, B200_EW_RELU, false)
+B200_UNARY(silu, B200_OP_SILU, B200_EW_SILU, true)
+B200_UNARY(sigmoid, B200_OP_SIGMOID, B200_EW_SIGMOID, true)
+B200_UNARY(tanh, B200_OP_TANH, B200_EW_TANH, true)
+B200_UNARY(exp, B200_OP_EXP, B200_EW_EXP, true)
+B200_UNARY(neg, B200_OP_NEG, B200_EW_NEG, false)
+B200_UNARY(abs, B200_OP_ABS, B200_EW_ABS, false)
+B200_UNARY(sqrt, B200_OP_SQRT, B200_EW_SQRT, true)
+B200_UNARY(rsqrt, B200_OP_RSQRT, B200_EW_RSQRT, true)
+B200_UNARY(reciprocal, B200_OP_RECIPROCAL, B200_EW_RECIPROCAL, true)
 
 at::Tensor gelu(const at::Tensor& a, c10::string_view approximate) {
   if (fast_dtype(a) && a.is_non_overlapping_and_dense()) {
     at::Tensor out = like(a);
     if (unary_fast(approximate == "tanh" ? B200_OP_GELU_TANH : B200_OP_GELU_ERF, out, a)) return out;
+  }
+  {
+    at::Tensor out;
+    if (generic_unary(approximate == "tanh" ? B200_EW_GELU_TANH : B200_EW_GELU_ERF, out, a, true, false)) return out;
   }
   return fallback_tensor(B200_OP_HANDLE("aten::gelu", ""), a, approximate);
 }
@@ -166,6 +200,10 @@ at::Tensor threshold_backward(const at::Tensor& grad, const at::Tensor& a, const
   if (threshold.toDouble() == 0.0 && fast_dtype(a) && a.is_non_overlapping_and_dense()) {
     at::Tensor out = like(a);
     if (binary_fast(B200_OP_RELU_BWD, out, grad, a, 1.0)) return out;
+  }
+  {
+    at::Tensor out;
+    if (generic_binary_same(B200_EW_THRESHOLD_BWD, out, grad, a, threshold.toDouble(), 0.0)) return out;
   }
   return fallback_tensor(B200_OP_HANDLE("aten::threshold_backward", ""), grad, a, threshold);
 }
@@ -190,10 +228,15 @@ at::Tensor mul_scalar(const at::Tensor& a, const at::Scalar& s) {
     at::Tensor out = like(a);
     if (binary_scalar_fast(B200_OP_MUL, out, a, s.toDouble(), 1.0)) return out;
   }
+  if (!s.isComplex()) {
+    at::Tensor out;
+    if (generic_binary_scalar(B200_EW_MUL, out, a, s, 1.0)) return out;
+  }
   return fallback_tensor(B200_OP_HANDLE("aten::mul", "Scalar"), a, s);
 }
 at::Tensor& mul_scalar_(at::Tensor& a, const at::Scalar& s) {
   if (!s.isComplex() && binary_scalar_fast(B200_OP_MUL, a, a, s.toDouble(), 1.0)) return a;
+  if (!s.isComplex() && generic_binary_scalar(B200_EW_MUL, a, a, s, 1.0)) return a;
   run_fallback(B200_OP_HANDLE("aten::mul_", "Scalar"), a, s);
   return a;
 }
@@ -201,6 +244,10 @@ at::Tensor add_scalar(const at::Tensor& a, const at::Scalar& s, const at::Scalar
   if (fast_dtype(a) && a.is_non_overlapping_and_dense() && !s.isComplex()) {
     at::Tensor out = like(a);
     if (binary_scalar_fast(B200_OP_ADD, out, a, s.toDouble(), alpha.toDouble())) return out;
+  }
+  if (!s.isComplex() && !alpha.isComplex()) {
+    at::Tensor out;
+    if (generic_binary_scalar(B200_EW_ADD, out, a, s, alpha.toDouble())) return out;
   }
   return fallback_tensor(B200_OP_HANDLE("aten::add", "Scalar"), a, s, alpha);
 }
@@ -220,6 +267,9 @@ at::Tensor& fill_scalar_(at::Tensor& self, const at::Scalar& v) {
     if (e == 0) return self;
     if (e != (int)cudaErrorNotSupported) B200_KERNEL_CALL(e);
   }
+  if (on_device(self) && !v.isComplex() && !self.is_complex() &&
+      loops::run(B200_EW_FILL, self, loops::In(), loops::In(), loops::In(), v.toDouble()))
+    return self;
   run_fallback(B200_OP_HANDLE("aten::fill_", "Scalar"), self, v);
   return self;
 }
@@ -263,8 +313,10 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
   m.impl("sub.out", TORCH_FN(sub_tensor_out));
   m.impl("mul.Tensor", TORCH_FN(mul_tensor));
   m.impl("mul_.Tensor", TORCH_FN(mul_tensor_));
+  m.impl("mul.out", TORCH_FN(mul_tensor_out));
   m.impl("div.Tensor", TORCH_FN(div_tensor));
   m.impl("div_.Tensor", TORCH_FN(div_tensor_));
+  m.impl("div.out", TORCH_FN(div_tensor_out));
   m.impl("relu", TORCH_FN(relu));
   m.impl("relu_", TORCH_FN(relu_));
   m.impl("silu", TORCH_FN(silu));

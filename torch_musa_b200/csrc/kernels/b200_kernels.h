@@ -50,6 +50,38 @@ B200_API int b200_addcmul(int dtype, void* out, const void* a, const void* t1, c
 /* busy-wait for `cycles` SM clock ticks, never longer than max_cycles (bounded) */
 B200_API int b200_sleep(int64_t cycles, cudaStream_t stream);
 
+/* ---- general pointwise loops (kernels/ew_generic.cu): broadcast / strided / mixed-dtype operands.
+ * out = op(in1[, in2[, in3]]); p0 / p1 are operator parameters (alpha for ADD / SUB / ADDCMUL / ADDCDIV / LERP,
+ * the bounds of CLAMP / HARDTANH_BWD, the slope of LEAKY_RELU, the value of FILL / MASKED_FILL, ...). */
+enum {
+  B200_EW_ADD = 100, B200_EW_SUB, B200_EW_RSUB, B200_EW_MUL, B200_EW_DIV, B200_EW_DIV_FLOOR, B200_EW_DIV_TRUNC,
+  B200_EW_REMAINDER, B200_EW_FMOD, B200_EW_POW, B200_EW_ATAN2, B200_EW_MAXIMUM, B200_EW_MINIMUM,
+  B200_EW_EQ, B200_EW_NE, B200_EW_LT, B200_EW_LE, B200_EW_GT, B200_EW_GE,
+  B200_EW_LOGICAL_AND, B200_EW_LOGICAL_OR, B200_EW_LOGICAL_XOR, B200_EW_BITWISE_AND, B200_EW_BITWISE_OR,
+  B200_EW_BITWISE_XOR, B200_EW_LSHIFT, B200_EW_RSHIFT,
+  B200_EW_WHERE, B200_EW_MASKED_FILL, B200_EW_CLAMP, B200_EW_CLAMP_TENSOR, B200_EW_ADDCMUL, B200_EW_ADDCDIV,
+  B200_EW_LERP, B200_EW_LERP_TENSOR, B200_EW_THRESHOLD_BWD, B200_EW_LEAKY_RELU, B200_EW_LEAKY_RELU_BWD, B200_EW_ELU,
+  B200_EW_HARDTANH_BWD, B200_EW_SOFTPLUS,
+  B200_EW_NEG = 200, B200_EW_ABS, B200_EW_SIGN, B200_EW_FLOOR, B200_EW_CEIL, B200_EW_ROUND, B200_EW_TRUNC,
+  B200_EW_FRAC, B200_EW_EXP, B200_EW_EXP2, B200_EW_EXPM1, B200_EW_LOG, B200_EW_LOG2, B200_EW_LOG10, B200_EW_LOG1P,
+  B200_EW_SQRT, B200_EW_RSQRT, B200_EW_RECIPROCAL, B200_EW_SQUARE, B200_EW_SIN, B200_EW_COS, B200_EW_TAN,
+  B200_EW_TANH, B200_EW_SIGMOID, B200_EW_ERF, B200_EW_RELU, B200_EW_SILU, B200_EW_GELU_ERF, B200_EW_GELU_TANH,
+  B200_EW_ISNAN, B200_EW_ISINF, B200_EW_ISFINITE, B200_EW_LOGICAL_NOT, B200_EW_BITWISE_NOT, B200_EW_COPY, B200_EW_FILL
+};
+typedef struct {
+  int ndim;                 /* 1..8 coalesced dimensions, innermost first */
+  int64_t sizes[8];
+  int64_t strides[4][8];    /* elements; [0] output, [1..3] inputs; 0 = broadcast */
+  int dtype[4];
+  void* ptr[4];
+  int n_in;                 /* 0..3 */
+  double scalar[3];         /* value of input k when bit k of scalar_mask is set */
+  int scalar_mask;
+  double p0, p1;
+  int float_compute;        /* force floating compute although every input is integral (true division, ...) */
+} b200_ew_t;
+B200_API int b200_ew(int op, const b200_ew_t* desc, cudaStream_t stream);
+
 /* ---------------------------------------------------------------- reductions */
 enum { B200_RED_SUM = 0, B200_RED_MEAN, B200_RED_MAX, B200_RED_MIN, B200_RED_SUMSQ, B200_RED_ABSMAX };
 /* reduce the last dimension: in [rows, cols] contiguous -> out [rows]; out dtype = in dtype (accumulation fp32) */
