@@ -94,6 +94,25 @@ B200_API int b200_reduce_all(int op, int dtype, void* out, int out_f32, const vo
 B200_API int b200_reduce_cols_sum(int dtype, void* out, int out_dtype, const void* in, int64_t rows, int64_t cols,
                                   cudaStream_t stream);
 
+/* ---- general reductions (kernels/reduce_generic.cu): `in` contiguous, viewed as [outer, reduce, inner]; out (and
+ * out_index for the arg operators; either may be NULL there) has outer * inner elements.  p0: the factor of MEAN, the
+ * correction of VAR / STD.  scratch: device memory for the partial states of split reductions (scratch_bytes; at least
+ * b200_reduce_state_bytes() * 65536 keeps every split available; NULL / 0 disables splitting). */
+enum { B200_RD_SUM = 0, B200_RD_MEAN, B200_RD_PROD, B200_RD_AMAX, B200_RD_AMIN, B200_RD_ANY, B200_RD_ALL, B200_RD_SUMSQ,
+       B200_RD_NORM2, B200_RD_SUMABS, B200_RD_ABSMAX, B200_RD_ARGMAX, B200_RD_ARGMIN, B200_RD_VAR, B200_RD_STD };
+typedef struct {
+  int op, in_dtype, out_dtype;
+  int64_t outer, reduce, inner;
+  double p0, p1;
+  const void* in;
+  void* out;
+  int64_t* out_index;
+  void* scratch;
+  size_t scratch_bytes;
+} b200_reduce_t;
+B200_API size_t b200_reduce_state_bytes(void);
+B200_API int b200_reduce(const b200_reduce_t* desc, cudaStream_t stream);
+
 /* ---------------------------------------------------------------- normalisation */
 /* y = x * rstd * w ; rstd[rows] fp32.  residual (optional): x_in = x + residual, written to res_out. */
 B200_API int b200_rmsnorm_fwd(int dtype, void* y, float* rstd, const void* x, const void* w, const void* residual,
