@@ -1,4 +1,5 @@
 #include "core/Device.h"
+#include "core/DeviceAssert.h"
 
 #include <c10/util/CallOnce.h>
 #include <c10/util/Logging.h>
@@ -114,6 +115,9 @@ c10::DeviceIndex maybe_exchange_device(c10::DeviceIndex d) {
 void device_synchronize() {
   note_implicit_sync("device_synchronize");
   B200_CUDA_CHECK(cudaDeviceSynchronize());
+  // kernels that met an out-of-range index (or another recorded condition) report here, as an exception
+  int cur = -1;
+  if (cudaGetDevice(&cur) == cudaSuccess) check_device_asserts((c10::DeviceIndex)cur);
 }
 
 const cudaDeviceProp& device_properties(c10::DeviceIndex d) {

@@ -7,6 +7,7 @@
 #include "core/Backend.h"
 #include "core/CachingAllocator.h"
 #include "core/Device.h"
+#include "core/DeviceAssert.h"
 #include "core/Generator.h"
 #include "core/Graph.h"
 #include "core/HostAllocator.h"
@@ -213,6 +214,7 @@ PYBIND11_MODULE(_C, m) {
   m.def("_set_fused_sdp", [](bool on) { ops::set_fused_sdp(on); });
   m.def("_set_sdp_impl", [](int impl) { ops::set_sdp_impl(impl); });
   m.def("_sdp_impl", [] { return ops::sdp_impl(); });
+  m.def("_take_device_assert", [](int dev) { return take_device_assert((c10::DeviceIndex)dev); });
   m.def("_native_sdp_forward_calls", [] { return ops::native_sdp_forward_calls(); });
   m.def("_native_sdp_backward_calls", [] { return ops::native_sdp_backward_calls(); });
   m.def("_fused_sdp_enabled", [] { return ops::fused_sdp_enabled(); });

@@ -113,6 +113,31 @@ typedef struct {
 B200_API size_t b200_reduce_state_bytes(void);
 B200_API int b200_reduce(const b200_reduce_t* desc, cudaStream_t stream);
 
+/* ---- indexing, scan and selection (kernels/index_ops.cu).  Tensors are contiguous views [outer, D, inner];
+ * idx_dtype is B200_I64 or B200_I32; `status` (may be NULL) is set to 1 when an index was out of range (the access
+ * is clamped, never wild). */
+B200_API int b200_index_select(void* out, const void* in, const void* idx, int idx_dtype, int elem_bytes, int64_t outer,
+                               int64_t D, int64_t inner, int64_t J, int* status, cudaStream_t stream);
+B200_API int b200_gather(void* out, const void* in, const void* idx, int idx_dtype, int elem_bytes, int64_t outer, int64_t D,
+                         int64_t inner, int64_t J, int* status, cudaStream_t stream);
+/* self[o, idx[j], i] (+)= val[o * val_stride_o + j * val_stride_j + i] */
+B200_API int b200_index_put(void* self, const void* val, const void* idx, int idx_dtype, int dtype, int accumulate,
+                            int64_t outer, int64_t D, int64_t inner, int64_t J, int64_t val_stride_j, int64_t val_stride_o,
+                            int* status, cudaStream_t stream);
+/* mode 0: self[o, idx[o,j,i], i] = src[o,j,i]; 1: += ; 2: = value */
+B200_API int b200_scatter(void* self, const void* src, double value, const void* idx, int idx_dtype, int dtype, int mode,
+                          int64_t outer, int64_t D, int64_t inner, int64_t J, int* status, cudaStream_t stream);
+B200_API int b200_tri(void* out, const void* in, int elem_bytes, int64_t batch, int64_t rows, int64_t cols, int64_t diagonal,
+                      int upper, cudaStream_t stream);
+B200_API int b200_arange(void* out, int dtype, double start, double step, int64_t n, cudaStream_t stream);
+B200_API int b200_cumsum_rows(void* out, const void* in, int dtype, int64_t rows, int64_t cols, cudaStream_t stream);
+/* k <= 16 best of every row of cols <= 1024 elements, sorted; one thread per row */
+B200_API int b200_topk_small(void* vals, int64_t* idxs, const void* in, int dtype, int64_t rows, int cols, int k, int largest,
+                             cudaStream_t stream);
+/* stable sort of every row; vals_out = original columns.  temp == NULL: only *temp_bytes is written. */
+B200_API int b200_sort_rows(void* temp, size_t* temp_bytes, const void* keys_in, void* keys_out, int64_t* vals_out, int dtype,
+                            int64_t rows, int64_t cols, int descending, cudaStream_t stream);
+
 /* ---------------------------------------------------------------- normalisation */
 /* y = x * rstd * w ; rstd[rows] fp32.  residual (optional): x_in = x + residual, written to res_out. */
 B200_API int b200_rmsnorm_fwd(int dtype, void* y, float* rstd, const void* x, const void* w, const void* residual,
