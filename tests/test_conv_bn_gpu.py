@@ -138,3 +138,37 @@ def test_resnet18_step_matches_cpu(bw, dev):
     assert abs(float(loss) - float(loss_ref)) < 0.08, (float(loss), float(loss_ref))
     g, gr = m.fc.weight.grad, ref.fc.weight.grad
     assert rel_err(g, gr) < 0.15
+
+
+@pytest.mark.parametrize("cl", [True, False])
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_pooling_forward_backward(bw, dev, cl, dt):
+    """max / average pooling on the pooling kernels against CPU autograd (ResNet's 3x3 stride-2 max pool included)."""
+    import torch.nn.functional as F
+
+    bw.reset_fallback_counts()
+    torch.manual_seed(0)
+    x = torch.randn(3, 16, 23, 19).to(dt)
+    if cl:
+        x = x.contiguous(memory_format=torch.channels_last)
+    tol = 1e-5 if dt == torch.float32 else 2e-2
+    cases = [
+        lambda t: F.max_pool2d(t, 3, 2, 1),
+        lambda t: F.max_pool2d(t, 2, 2),
+        lambda t: F.max_pool2d(t, (3, 2), (1, 2), (1, 0), dilation=(2, 1)),
+        lambda t: F.avg_pool2d(t, 3, 2, 1),
+        lambda t: F.avg_pool2d(t, 2, 2, count_include_pad=False),
+        lambda t: F.avg_pool2d(t, 3, 1, 1, count_include_pad=False),
+        lambda t: F.adaptive_avg_pool2d(t, 1),
+    ]
+    for fn in cases:
+        xr = x.float().clone().requires_grad_()
+        xd = x.to(dev).requires_grad_()
+        r, o = fn(xr), fn(xd)
+        assert o.shape == r.shape
+        assert torch.allclose(o.float().cpu(), r, atol=tol, rtol=tol)
+        g = torch.randn_like(r)
+        r.backward(g)
+        o.backward(g.to(dt).to(dev))
+        assert torch.allclose(xd.grad.float().cpu(), xr.grad, atol=tol * 4, rtol=tol * 4)
+    assert not any("pool" in k for k in bw.fallback_counts()), bw.fallback_counts()

@@ -184,9 +184,18 @@ def test_fallback_ops_share_memory(bw, dev):
     d.clamp_(min=-0.5, max=0.5)  # in-place through the fallback writes the original memory
     assert torch.equal(d.cpu(), x.clamp(-0.5, 0.5))
     out = torch.empty(0, device=dev)
-    torch.mul(d, d, out=out)      # out= resize through the fallback
+    torch.mul(d, d, out=out)      # out= resize
     assert out.shape == d.shape
-    assert any("sort" in k for k in bw.fallback_counts())
+    # operators without a hand-written kernel (here: a matrix inverse, a complex product) take the fallback: the
+    # library kernel runs on the same memory, in place / out= semantics included
+    a = (torch.eye(6) * 2 + torch.randn(6, 6) * 0.1)
+    inv = torch.linalg.inv(a.to(dev))
+    assert inv.device.type == "blackwell" and torch.allclose(inv.cpu(), torch.linalg.inv(a), atol=1e-4)
+    z = torch.randn(5, dtype=torch.complex64)
+    zd = z.to(dev)
+    zd.mul_(zd)
+    assert torch.allclose(zd.cpu(), z * z)
+    assert any("linalg_inv" in k for k in bw.fallback_counts()), bw.fallback_counts()
 
 
 def test_serialization_roundtrip(bw, dev, tmp_path):

@@ -129,6 +129,18 @@ B200_PW_BINARY_SCALAR(pow_ts, "pow", "Tensor_Scalar", "Scalar", "Tensor_Scalar_o
 B200_PW_BINARY(remainder_t, "remainder", "Tensor", "Tensor", "Tensor_out", B200_EW_REMAINDER, kSame)
 B200_PW_BINARY(fmod_t, "fmod", "Tensor", "Tensor", "Tensor_out", B200_EW_FMOD, kSame)
 B200_PW_BINARY(atan2, "atan2", "", "", "out", B200_EW_ATAN2, kFloat)
+B200_PW_BINARY(xlogy_t, "xlogy", "Tensor", "Tensor", "OutTensor", B200_EW_XLOGY, kFloat)
+
+at::Tensor rsub_scalar(const at::Tensor& a, const at::Scalar& other, const at::Scalar& alpha) {
+  at::Tensor out;
+  if (!alpha.isComplex() && pointwise_into(B200_EW_RSUB, kSame, out, In(a), In(other), In(), alpha.toDouble())) return out;
+  return fallback_tensor(B200_OP_HANDLE("aten::rsub", "Scalar"), a, other, alpha);
+}
+at::Tensor rsub_tensor(const at::Tensor& a, const at::Tensor& other, const at::Scalar& alpha) {
+  at::Tensor out;
+  if (!alpha.isComplex() && pointwise_into(B200_EW_RSUB, kSame, out, In(a), In(other), In(), alpha.toDouble())) return out;
+  return fallback_tensor(B200_OP_HANDLE("aten::rsub", "Tensor"), a, other, alpha);
+}
 
 at::Tensor pow_scalar_base(const at::Scalar& base, const at::Tensor& e) {
   at::Tensor out;
@@ -194,6 +206,7 @@ B200_PW_UNARY(round, "round", B200_EW_ROUND, kSame)
 B200_PW_UNARY(trunc, "trunc", B200_EW_TRUNC, kSame)
 B200_PW_UNARY(frac, "frac", B200_EW_FRAC, kSame)
 B200_PW_UNARY(sign, "sign", B200_EW_SIGN, kSame)
+B200_PW_UNARY(sgn, "sgn", B200_EW_SIGN, kSame)
 B200_PW_UNARY(exp2, "exp2", B200_EW_EXP2, kFloat)
 B200_PW_UNARY(expm1, "expm1", B200_EW_EXPM1, kFloat)
 B200_PW_UNARY(log, "log", B200_EW_LOG, kFloat)
@@ -370,6 +383,17 @@ at::Tensor elu(const at::Tensor& a, const at::Scalar& alpha, const at::Scalar& s
     return out;
   return fallback_tensor(B200_OP_HANDLE("aten::elu", ""), a, alpha, scale, input_scale);
 }
+std::tuple<at::Tensor, at::Tensor> log_sigmoid_forward(const at::Tensor& a) {
+  at::Tensor out;
+  if (pointwise_into(B200_EW_LOG_SIGMOID, kSame, out, In(a))) return {out, at::empty({0}, a.options())};
+  auto st = run_fallback(B200_OP_HANDLE("aten::log_sigmoid_forward", ""), a);
+  return {st[0].toTensor(), st[1].toTensor()};
+}
+at::Tensor log_sigmoid_backward(const at::Tensor& g, const at::Tensor& x, const at::Tensor& buffer) {
+  at::Tensor out;
+  if (pointwise_into(B200_EW_LOG_SIGMOID_BWD, kSame, out, In(g), In(x))) return out;
+  return fallback_tensor(B200_OP_HANDLE("aten::log_sigmoid_backward", ""), g, x, buffer);
+}
 at::Tensor softplus(const at::Tensor& a, const at::Scalar& beta, const at::Scalar& threshold) {
   at::Tensor out;
   if (pointwise_into(B200_EW_SOFTPLUS, kSame, out, In(a), In(), In(), beta.toDouble(), threshold.toDouble())) return out;
@@ -406,7 +430,12 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
   REG3(remainder_t, "remainder", ".Tensor", ".Tensor", ".Tensor_out")
   REG3(fmod_t, "fmod", ".Tensor", ".Tensor", ".Tensor_out")
   REG3(atan2, "atan2", "", "", ".out")
+  REG3(xlogy_t, "xlogy", ".Tensor", ".Tensor", ".OutTensor")
+  m.impl("log_sigmoid_forward", TORCH_FN(log_sigmoid_forward));
+  m.impl("log_sigmoid_backward", TORCH_FN(log_sigmoid_backward));
   m.impl("pow.Scalar", TORCH_FN(pow_scalar_base));
+  m.impl("rsub.Scalar", TORCH_FN(rsub_scalar));
+  m.impl("rsub.Tensor", TORCH_FN(rsub_tensor));
   m.impl("div.Tensor_mode", TORCH_FN(div_mode));
   m.impl("div_.Tensor_mode", TORCH_FN(div_mode_));
   m.impl("div.out_mode", TORCH_FN(div_mode_out));
@@ -417,6 +446,7 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
   REG3(trunc, "trunc", "", "", ".out")
   REG3(frac, "frac", "", "", ".out")
   REG3(sign, "sign", "", "", ".out")
+  REG3(sgn, "sgn", "", "", ".out")
   REG3(exp2, "exp2", "", "", ".out")
   REG3(expm1, "expm1", "", "", ".out")
   REG3(log, "log", "", "", ".out")

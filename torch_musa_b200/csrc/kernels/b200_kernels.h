@@ -61,12 +61,13 @@ enum {
   B200_EW_BITWISE_XOR, B200_EW_LSHIFT, B200_EW_RSHIFT,
   B200_EW_WHERE, B200_EW_MASKED_FILL, B200_EW_CLAMP, B200_EW_CLAMP_TENSOR, B200_EW_ADDCMUL, B200_EW_ADDCDIV,
   B200_EW_LERP, B200_EW_LERP_TENSOR, B200_EW_THRESHOLD_BWD, B200_EW_LEAKY_RELU, B200_EW_LEAKY_RELU_BWD, B200_EW_ELU,
-  B200_EW_HARDTANH_BWD, B200_EW_SOFTPLUS,
+  B200_EW_HARDTANH_BWD, B200_EW_SOFTPLUS, B200_EW_XLOGY, B200_EW_LOG_SIGMOID_BWD,
   B200_EW_NEG = 200, B200_EW_ABS, B200_EW_SIGN, B200_EW_FLOOR, B200_EW_CEIL, B200_EW_ROUND, B200_EW_TRUNC,
   B200_EW_FRAC, B200_EW_EXP, B200_EW_EXP2, B200_EW_EXPM1, B200_EW_LOG, B200_EW_LOG2, B200_EW_LOG10, B200_EW_LOG1P,
   B200_EW_SQRT, B200_EW_RSQRT, B200_EW_RECIPROCAL, B200_EW_SQUARE, B200_EW_SIN, B200_EW_COS, B200_EW_TAN,
   B200_EW_TANH, B200_EW_SIGMOID, B200_EW_ERF, B200_EW_RELU, B200_EW_SILU, B200_EW_GELU_ERF, B200_EW_GELU_TANH,
-  B200_EW_ISNAN, B200_EW_ISINF, B200_EW_ISFINITE, B200_EW_LOGICAL_NOT, B200_EW_BITWISE_NOT, B200_EW_COPY, B200_EW_FILL
+  B200_EW_ISNAN, B200_EW_ISINF, B200_EW_ISFINITE, B200_EW_LOGICAL_NOT, B200_EW_BITWISE_NOT, B200_EW_COPY, B200_EW_FILL,
+  B200_EW_LOG_SIGMOID
 };
 typedef struct {
   int ndim;                 /* 1..8 coalesced dimensions, innermost first */
@@ -137,6 +138,18 @@ B200_API int b200_topk_small(void* vals, int64_t* idxs, const void* in, int dtyp
 /* stable sort of every row; vals_out = original columns.  temp == NULL: only *temp_bytes is written. */
 B200_API int b200_sort_rows(void* temp, size_t* temp_bytes, const void* keys_in, void* keys_out, int64_t* vals_out, int dtype,
                             int64_t rows, int64_t cols, int descending, cudaStream_t stream);
+
+/* ---- 2-D pooling over [N, H, W, C] (kernels/pool.cu); idx = h * W + w of the maximum inside its image plane */
+typedef struct {
+  int64_t N, H, W, C, Ho, Wo;
+  int kh, kw, sh, sw, ph, pw, dh, dw;
+} b200_pool_t;
+B200_API int b200_maxpool2d_fwd(const b200_pool_t* p, int dtype, void* out, int64_t* idx, const void* in, cudaStream_t stream);
+B200_API int b200_maxpool2d_bwd(const b200_pool_t* p, int dtype, void* gin, const void* gout, const int64_t* idx,
+                                cudaStream_t stream);
+/* divisor: 0 = window size clipped to the padded extent (count_include_pad), -1 = valid elements only, > 0 = override */
+B200_API int b200_avgpool2d_fwd(const b200_pool_t* p, int dtype, void* out, const void* in, int divisor, cudaStream_t stream);
+B200_API int b200_avgpool2d_bwd(const b200_pool_t* p, int dtype, void* gin, const void* gout, int divisor, cudaStream_t stream);
 
 /* ---------------------------------------------------------------- normalisation */
 /* y = x * rstd * w ; rstd[rows] fp32.  residual (optional): x_in = x + residual, written to res_out. */
@@ -254,6 +267,13 @@ B200_API int b200_multi_tensor_scale(int n_tensors, int dtype, void* const* tens
                                      const float* inv_scale_ptr, float host_scale, float* found_inf,
                                      cudaStream_t stream);
 /* generic foreach binary with scalar: t = op(t, s) or t = t + alpha * u */
+/* out[i] = f(a[i][, b[i][, c[i]]]) over whole tensor lists in a couple of launches (the _foreach_* family); b / c may
+ * be NULL; all tensors of one floating dtype, dense, same numel per position */
+enum { B200_FE_ADD_SCALAR = 0, B200_FE_MUL_SCALAR, B200_FE_DIV_SCALAR, B200_FE_ADD, B200_FE_MUL, B200_FE_DIV,
+       B200_FE_ADDCMUL, B200_FE_ADDCDIV, B200_FE_LERP, B200_FE_SQRT, B200_FE_NEG, B200_FE_RECIPROCAL, B200_FE_ABS,
+       B200_FE_MAXIMUM, B200_FE_MINIMUM, B200_FE_CLAMP, B200_FE_ZERO, B200_FE_COPY };
+B200_API int b200_multi_tensor_pointwise(int op, int n, int dtype, void* const* out, void* const* a, void* const* b,
+                                         void* const* c, const int64_t* numels, float s0, float s1, cudaStream_t stream);
 B200_API int b200_multi_tensor_axpby(int n_tensors, int dtype, void* const* out, void* const* x, void* const* y,
                                      const int64_t* numels, float a, float b, cudaStream_t stream);
 /* LAMB: stage 1 computes update in `update` list; stage 2 applies trust ratio per tensor */

@@ -158,6 +158,8 @@ __device__ __forceinline__ C apply_float(int op, C a, C b, C c, double s0, doubl
     case B200_EW_LEAKY_RELU_BWD: return b > (C)0 ? a : a * (C)s0;    // a = grad, b = input
     case B200_EW_ELU: return a > (C)0 ? a * (C)s1 : (C)s0 * (C)s1 * M::em1(a);   // s0 alpha, s1 scale
     case B200_EW_HARDTANH_BWD: return (b <= (C)s0 || b >= (C)s1) ? (C)0 : a;
+    case B200_EW_XLOGY: return (b != b) ? b : (a == (C)0 ? (C)0 : a * M::lg(b));
+    case B200_EW_LOG_SIGMOID_BWD: { C z = M::ex(-M::ab(b)); C s = b < (C)0 ? (C)1 / ((C)1 + z) : z / ((C)1 + z); return a * s; }   // a = grad, b = x: grad * sigmoid(-x)
     case B200_EW_SOFTPLUS: { C z = a * (C)s0; return z > (C)s1 ? a : M::l1p(M::ex(z)) / (C)s0; }
     // unary
     case B200_EW_NEG: return -a;
@@ -189,6 +191,7 @@ __device__ __forceinline__ C apply_float(int op, C a, C b, C c, double s0, doubl
     case B200_EW_SILU: return a / ((C)1 + M::ex(-a));
     case B200_EW_GELU_ERF: return (C)0.5 * a * ((C)1 + M::er(a * (C)0.70710678118654752));
     case B200_EW_GELU_TANH: { C in = (C)0.7978845608028654 * (a + (C)0.044715 * a * a * a); return (C)0.5 * a * ((C)1 + M::th(in)); }
+    case B200_EW_LOG_SIGMOID: return (a < (C)0 ? a : (C)0) - M::l1p(M::ex(-M::ab(a)));
     case B200_EW_ISNAN: return (C)(a != a);
     case B200_EW_ISINF: return (C)(a == (C)INFINITY || a == -(C)INFINITY);
     case B200_EW_ISFINITE: return (C)(a == a && a != (C)INFINITY && a != -(C)INFINITY);

@@ -322,6 +322,54 @@ struct AxpbyFunctor {
   }
 };
 
+// ---------------------------------------------------------------- generic pointwise over tensor lists (_foreach_*)
+// out = f(a[, b[, c]]); packets of four elements when every pointer of the chunk is suitably aligned
+template <typename T>
+struct ForeachFunctor {
+  __device__ __forceinline__ static float apply(int op, float a, float b, float c, float s0, float s1) {
+    switch (op) {
+      case B200_FE_ADD_SCALAR: return a + s0;
+      case B200_FE_MUL_SCALAR: return a * s0;
+      case B200_FE_DIV_SCALAR: return a / s0;
+      case B200_FE_ADD: return a + s0 * b;
+      case B200_FE_MUL: return a * b;
+      case B200_FE_DIV: return a / b;
+      case B200_FE_ADDCMUL: return a + s0 * b * c;
+      case B200_FE_ADDCDIV: return a + s0 * b / c;
+      case B200_FE_LERP: return a + s0 * (b - a);
+      case B200_FE_SQRT: return sqrtf(a);
+      case B200_FE_NEG: return -a;
+      case B200_FE_RECIPROCAL: return 1.f / a;
+      case B200_FE_ABS: return fabsf(a);
+      case B200_FE_MAXIMUM: return (a != a || b != b) ? NAN : fmaxf(a, b);
+      case B200_FE_MINIMUM: return (a != a || b != b) ? NAN : fminf(a, b);
+      case B200_FE_CLAMP: return a != a ? a : fminf(fmaxf(a, s0), s1);
+      case B200_FE_ZERO: return 0.f;
+      default: return a;   // COPY
+    }
+  }
+  __device__ void operator()(const Meta<4>& m, int t, int64_t begin, int64_t n, int op, float s0, float s1) const {
+    T* o = (T*)m.addr[0][t] + begin;
+    const T* a = (const T*)m.addr[1][t] + begin;
+    const T* b = m.addr[2][t] ? (const T*)m.addr[2][t] + begin : nullptr;
+    const T* c = m.addr[3][t] ? (const T*)m.addr[3][t] + begin : nullptr;
+    constexpr uintptr_t kMask = sizeof(T) * 4 - 1;
+    const bool vec = (((uintptr_t)o | (uintptr_t)a | (uintptr_t)(b ? b : a) | (uintptr_t)(c ? c : a)) & kMask) == 0;
+    const int64_t n4 = vec ? n / 4 : 0;
+    for (int64_t i = threadIdx.x; i < n4; i += kThreads) {
+      float va[4], vb[4] = {0.f, 0.f, 0.f, 0.f}, vc[4] = {0.f, 0.f, 0.f, 0.f}, r[4];
+      load4(a + i * 4, va);
+      if (b) load4(b + i * 4, vb);
+      if (c) load4(c + i * 4, vc);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) r[k] = apply(op, va[k], vb[k], vc[k], s0, s1);
+      store4(o + i * 4, r);
+    }
+    for (int64_t i = n4 * 4 + threadIdx.x; i < n; i += kThreads)
+      o[i] = ToF<T>::from(apply(op, ToF<T>::to(a[i]), b ? ToF<T>::to(b[i]) : 0.f, c ? ToF<T>::to(c[i]) : 0.f, s0, s1));
+  }
+};
+
 // ---------------------------------------------------------------- LAMB
 // stage 1: moments + raw update u (written over the gradient copy in `upd`), stage 2: trust-ratio apply
 template <typename T>
@@ -486,6 +534,15 @@ int b200_multi_tensor_axpby(int n, int dtype, void* const* out, void* const* x, 
   void* const* lists[3] = {out, x, y};
   int64_t chunk = pick_chunk(n, numels);
   B200K_DISPATCH_FLOAT(dtype, T, return mta_launch<3>(n, lists, numels, chunk, stream, AxpbyFunctor<T>(), a, b));
+  return (int)cudaErrorNotSupported;
+}
+
+int b200_multi_tensor_pointwise(int op, int n, int dtype, void* const* out, void* const* a, void* const* b, void* const* c,
+                                const int64_t* numels, float s0, float s1, cudaStream_t stream) {
+  if (n == 0) return 0;
+  void* const* lists[4] = {out, a, b, c};
+  int64_t chunk = pick_chunk(n, numels);
+  B200K_DISPATCH_FLOAT(dtype, T, return mta_launch<4>(n, lists, numels, chunk, stream, ForeachFunctor<T>(), op, s0, s1));
   return (int)cudaErrorNotSupported;
 }
 
