@@ -116,3 +116,110 @@ def test_stats_peaks(h):
     h.free(a); h.free(b)
     s = h.stats()["allocated_bytes"]["all"]
     assert s["peak"] == 16 * MiB and s["current"] == 0 and s["allocated"] == 16 * MiB and s["freed"] == 16 * MiB
+
+
+# ---------------------------------------------------------------- expandable segments
+@pytest.fixture
+def xh(bw):
+    """Harness with expandable segments on (host backend: mmap/mprotect stand in for the driver's VMM)."""
+    bw._C._set_allocator_settings("expandable_segments:True")
+    try:
+        yield bw._C._HostCacheHarness()
+    finally:
+        bw._C._set_allocator_settings("expandable_segments:False")
+
+
+def test_expandable_segment_grows_in_place(xh):
+    a = xh.alloc(30 * MiB)            # two 20 MiB units mapped at the start of the reserved range
+    s = xh.stats()
+    assert s["reserved_bytes"]["large_pool"]["current"] == 40 * MiB
+    assert s["segment"]["all"]["current"] == 1
+    b = xh.alloc(50 * MiB)            # 10 MiB free tail + 40 MiB newly mapped, contiguous with `a`
+    assert b == a + 30 * MiB
+    s = xh.stats()
+    assert s["reserved_bytes"]["large_pool"]["current"] == 80 * MiB
+    assert s["segment"]["all"]["current"] == 1   # still one segment: no second, differently sized one
+    snap = xh.snapshot()
+    assert len(snap) == 1 and snap[0]["is_expandable"] and snap[0]["total_size"] == 80 * MiB
+    assert xh.write_read(b, 50 * MiB, 7) == 7    # the mapped range is real memory
+    xh.free(a); xh.free(b)
+    assert xh.stats()["reserved_bytes"]["all"]["current"] == 80 * MiB  # cached
+    xh.empty_cache()
+    s = xh.stats()
+    assert s["reserved_bytes"]["all"]["current"] == 0 and s["segment"]["all"]["current"] == 0
+    assert xh.snapshot() == []
+
+
+def test_expandable_unmaps_only_whole_units_and_refills_holes(xh):
+    a = xh.alloc(20 * MiB)
+    b = xh.alloc(60 * MiB)
+    c = xh.alloc(20 * MiB)
+    assert b == a + 20 * MiB and c == b + 60 * MiB
+    xh.free(b)
+    xh.empty_cache()                  # the three units under `b` go back; `a` and `c` stay mapped
+    s = xh.stats()
+    assert s["reserved_bytes"]["all"]["current"] == 40 * MiB
+    snap = xh.snapshot()
+    assert [x["total_size"] for x in snap] == [20 * MiB, 20 * MiB]   # two mapped runs around the hole
+    d = xh.alloc(40 * MiB)            # fits the hole: mapped again at the old address
+    assert d == b
+    assert xh.stats()["reserved_bytes"]["all"]["current"] == 80 * MiB
+    e = xh.alloc(30 * MiB)            # hole has 20 MiB left: too small, grows past `c` instead
+    assert e == c + 20 * MiB
+    for p in (a, c, d, e):
+        xh.free(p)
+    xh.empty_cache()
+    assert xh.stats()["reserved_bytes"]["all"]["current"] == 0
+
+
+def test_expandable_small_pool_and_streams(xh):
+    p = xh.alloc(1000)
+    q = xh.alloc(1000, stream=0x20)   # another stream gets its own address range
+    s = xh.stats()
+    assert s["reserved_bytes"]["small_pool"]["current"] == 4 * MiB
+    assert s["segment"]["small_pool"]["current"] == 2
+    assert abs(p - q) >= 2 * MiB
+    many = [xh.alloc(512 * 1024) for _ in range(7)]   # 3.5 MiB more on the default stream: grows by one unit
+    assert xh.stats()["reserved_bytes"]["small_pool"]["current"] == 6 * MiB
+    assert xh.stats()["segment"]["small_pool"]["current"] == 2
+    for x in many + [p, q]:
+        xh.free(x)
+    xh.empty_cache()
+    assert xh.stats()["reserved_bytes"]["all"]["current"] == 0
+
+
+def test_expandable_respects_memory_fraction(xh):
+    xh.set_memory_fraction(0.004)     # 16 GiB * 0.004 = ~65 MiB
+    a = xh.alloc(30 * MiB)            # 40 MiB mapped
+    with pytest.raises(RuntimeError, match="out of memory"):
+        xh.alloc(60 * MiB)
+    xh.free(a)
+    b = xh.alloc(50 * MiB)            # 40 MiB cached + one more unit = 60 MiB: within the limit
+    assert b == a
+    xh.free(b)
+    xh.empty_cache()
+
+
+# ---------------------------------------------------------------- pool checkpoints
+def test_pool_checkpoint_restore(h):
+    pid = (0, 901)
+    h.begin_pool(pid, 0x30)
+    a = h.alloc(4 * MiB, stream=0x30)
+    b = h.alloc(6 * MiB, stream=0x30)
+    ck = h.checkpoint(pid)
+    assert sorted(ck.live_pointers) == sorted([a, b])
+    c = h.alloc(2 * MiB, stream=0x30)           # allocated after the checkpoint
+    h.free(a)                                   # freed after the checkpoint
+    h.end_pool(pid)
+    freed, created = h.restore(ck)
+    assert freed == [c]
+    assert sorted(created) == sorted([a, b])
+    snap = [s for s in h.snapshot() if tuple(s["pool_id"]) == pid]
+    assert len(snap) == 1
+    assert snap[0]["blocks"] == [(4 * MiB, True), (6 * MiB, True), (10 * MiB, False)]
+    # the re-created blocks are ordinary live allocations again
+    h.free(a); h.free(b)
+    snap = [s for s in h.snapshot() if tuple(s["pool_id"]) == pid]
+    assert snap[0]["blocks"] == [(20 * MiB, False)]
+    h.release_pool(pid)
+    assert h.stats()["reserved_bytes"]["all"]["current"] == 0

@@ -142,6 +142,9 @@ from .core.memory import (  # noqa: E402
     BlackwellPluggableAllocator,
     change_current_allocator,
     MemPool,
+    get_pool_checkpoint,
+    set_pool_checkpoint,
+    adopt_allocation,
     MemPoolContext,
     use_mem_pool,
     use_unified_cpu_allocator,
@@ -180,10 +183,15 @@ from .core.tensor_types import make_types as _make_tensor_types  # noqa: E402
 globals().update(_make_tensor_types())  # FloatTensor, HalfTensor, BFloat16Tensor, ... (legacy typed classes)
 
 
+from .core import reductions as _reductions  # noqa: E402
+
+_reductions.init_reductions()
+
+
 def ipc_collect():
-    """Release device memory held for tensors received from other processes (no-op: IPC mappings
-    here are reference counted and close with their last tensor)."""
-    return None
+    """Drop the references this process holds on tensors it sent to other processes and that every
+    receiver has released since (received mappings close with their last tensor on their own)."""
+    return _reductions.ipc_collect()
 
 
 def fallback_counts():

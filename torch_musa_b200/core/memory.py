@@ -233,6 +233,26 @@ class MemPool:
         return [s for s in memory_snapshot() if tuple(s["segment_pool_id"]) == self._id]
 
 
+def get_pool_checkpoint(device: Any, pool_id: Tuple[int, int]):
+    """Block layout of a private pool right now (``.live_pointers`` lists its live allocations)."""
+    _lazy_init()
+    return _C()._checkpoint_pool(_get_device_index(device, optional=True), tuple(pool_id))
+
+
+def set_pool_checkpoint(device: Any, state, stale=()):
+    """Put a private pool back into the layout of ``state``.  Everything allocated in the pool since is
+    taken back (pass the tensors that still point there as ``stale`` so that they give up ownership) and
+    what was live at the checkpoint is live again at the same addresses.  Returns ``(freed, created)``
+    pointer lists; ``adopt_allocation`` turns a created pointer that no tensor owns into a byte tensor."""
+    _lazy_init()
+    return _C()._restore_pool(_get_device_index(device, optional=True), state, list(stale))
+
+
+def adopt_allocation(device: Any, ptr: int, nbytes: int):
+    _lazy_init()
+    return _C()._adopt_allocation(_get_device_index(device, optional=True), ptr, nbytes)
+
+
 class MemPoolContext:
     """Stack of active pools, thread local (introspection only)."""
 

@@ -3,6 +3,10 @@
 #include <c10/util/Exception.h>
 #include <c10/util/irange.h>
 
+#include <cuda.h>
+#include <sys/mman.h>
+#include <unistd.h>
+
 #include <algorithm>
 #include <chrono>
 #include <cstdlib>
@@ -52,14 +56,11 @@ int unified_alloc(void** p, size_t n, int device, cudaStream_t) {
 }
 int async_alloc(void** p, size_t n, int, cudaStream_t s) { return (int)cudaMallocAsync(p, n, s); }
 int async_free(void* p, size_t, int, cudaStream_t s) { return (int)cudaFreeAsync(p, s); }
+size_t host_cap();
 int host_alloc(void** p, size_t n, int, cudaStream_t) {
   *p = nullptr;
   // An artificial ceiling lets the tests exercise the OOM/retry path without a GPU.
-  static const size_t cap = [] {
-    const char* e = std::getenv("B200_HOST_BACKEND_CAP_MB");
-    return e ? (size_t)std::atoll(e) << 20 : (size_t)1 << 40;
-  }();
-  if (g_host_in_use + n > cap) return (int)cudaErrorMemoryAllocation;
+  if (g_host_in_use + n > host_cap()) return (int)cudaErrorMemoryAllocation;
   if (posix_memalign(p, 512, n) != 0) return (int)cudaErrorMemoryAllocation;
   g_host_in_use += n;
   return 0;
@@ -75,11 +76,181 @@ int host_mem_info(int, size_t* f, size_t* t) {
   return 0;
 }
 
-const RawBackend kNative{"native", native_alloc, native_free, cuda_mem_info, true};
-const RawBackend kUnified{"unified", unified_alloc, native_free, cuda_mem_info, true};
-const RawBackend kAsync{"cudaMallocAsync", async_alloc, async_free, cuda_mem_info, true};
-const RawBackend kHost{"host", host_alloc, host_free, host_mem_info, false};
-RawBackend g_plug{"pluggable", nullptr, nullptr, cuda_mem_info, true};
+size_t host_cap() {
+  static const size_t cap = [] {
+    const char* e = std::getenv("B200_HOST_BACKEND_CAP_MB");
+    return e ? (size_t)std::atoll(e) << 20 : (size_t)1 << 40;
+  }();
+  return cap;
+}
+
+// ---- host VMM: address space from mmap(PROT_NONE), "physical" chunks by mprotect.
+size_t host_vmm_granularity(int) { return 2u << 20; }
+int host_vmm_reserve(void** va, size_t n, int) {
+  void* p = mmap(nullptr, n, PROT_NONE, MAP_PRIVATE | MAP_ANONYMOUS | MAP_NORESERVE, -1, 0);
+  if (p == MAP_FAILED) return (int)cudaErrorMemoryAllocation;
+  *va = p;
+  return 0;
+}
+int host_vmm_release(void* va, size_t n, int) { return munmap(va, n) == 0 ? 0 : (int)cudaErrorInvalidValue; }
+int host_vmm_map(void* va, size_t n, int, uint64_t* handle) {
+  if (g_host_in_use + n > host_cap()) return (int)cudaErrorMemoryAllocation;
+  if (mprotect(va, n, PROT_READ | PROT_WRITE) != 0) return (int)cudaErrorMemoryAllocation;
+  g_host_in_use += n;
+  *handle = (uint64_t)(uintptr_t)va | 1u;  // non-zero token
+  return 0;
+}
+int host_vmm_unmap(void* va, size_t n, int, uint64_t) {
+  madvise(va, n, MADV_DONTNEED);
+  if (mprotect(va, n, PROT_NONE) != 0) return (int)cudaErrorInvalidValue;
+  g_host_in_use -= n;
+  return 0;
+}
+const VmmOps kHostVmm{host_vmm_granularity, host_vmm_reserve, host_vmm_release, host_vmm_map, host_vmm_unmap,
+                      nullptr, nullptr};
+
+// ---- CUDA VMM: the driver's cuMem* calls, looked up through the runtime so that
+// nothing links against libcuda (the package must import on machines without a driver).
+struct DriverVmm {
+  decltype(&cuMemAddressReserve) address_reserve = nullptr;
+  decltype(&cuMemAddressFree) address_free = nullptr;
+  decltype(&cuMemCreate) create = nullptr;
+  decltype(&cuMemRelease) release = nullptr;
+  decltype(&cuMemMap) map = nullptr;
+  decltype(&cuMemUnmap) unmap = nullptr;
+  decltype(&cuMemSetAccess) set_access = nullptr;
+  decltype(&cuMemGetAllocationGranularity) granularity = nullptr;
+  decltype(&cuMemExportToShareableHandle) export_handle = nullptr;
+  decltype(&cuMemImportFromShareableHandle) import_handle = nullptr;
+  bool ok = false;
+  bool fd_handles = true;  // cleared when the driver refuses shareable allocations
+};
+const DriverVmm& driver_vmm() {
+  static DriverVmm d = [] {
+    DriverVmm v;
+    auto get = [](const char* name, void** fn) {
+      cudaDriverEntryPointQueryResult q;
+      cudaError_t e = cudaGetDriverEntryPoint(name, fn, cudaEnableDefault, &q);
+      if (e != cudaSuccess) (void)cudaGetLastError();
+      return e == cudaSuccess && q == cudaDriverEntryPointSuccess && *fn != nullptr;
+    };
+    v.ok = get("cuMemAddressReserve", (void**)&v.address_reserve) && get("cuMemAddressFree", (void**)&v.address_free) &&
+           get("cuMemCreate", (void**)&v.create) && get("cuMemRelease", (void**)&v.release) &&
+           get("cuMemMap", (void**)&v.map) && get("cuMemUnmap", (void**)&v.unmap) &&
+           get("cuMemSetAccess", (void**)&v.set_access) &&
+           get("cuMemGetAllocationGranularity", (void**)&v.granularity) &&
+           get("cuMemExportToShareableHandle", (void**)&v.export_handle) &&
+           get("cuMemImportFromShareableHandle", (void**)&v.import_handle);
+    return v;
+  }();
+  return d;
+}
+bool g_vmm_fd_handles = true;
+CUmemAllocationProp vmm_prop(int device, bool fd) {
+  CUmemAllocationProp prop{};
+  prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
+  prop.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+  prop.location.id = device;
+  prop.requestedHandleTypes = fd ? CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR : CU_MEM_HANDLE_TYPE_NONE;
+  return prop;
+}
+int vmm_err(CUresult r) {
+  if (r == CUDA_SUCCESS) return 0;
+  if (r == CUDA_ERROR_OUT_OF_MEMORY) return (int)cudaErrorMemoryAllocation;
+  return (int)cudaErrorUnknown;
+}
+size_t cuda_vmm_granularity(int device) {
+  const DriverVmm& d = driver_vmm();
+  if (!d.ok) return 0;
+  CUmemAllocationProp prop = vmm_prop(device, false);
+  size_t g = 0;
+  if (d.granularity(&g, &prop, CU_MEM_ALLOC_GRANULARITY_RECOMMENDED) != CUDA_SUCCESS) return 0;
+  return g;
+}
+int cuda_vmm_reserve(void** va, size_t n, int) {
+  CUdeviceptr p = 0;
+  CUresult r = driver_vmm().address_reserve(&p, n, 0, 0, 0);
+  *va = reinterpret_cast<void*>(p);
+  return vmm_err(r);
+}
+int cuda_vmm_release(void* va, size_t n, int) { return vmm_err(driver_vmm().address_free((CUdeviceptr)va, n)); }
+int cuda_vmm_access(void* va, size_t n, int device) {
+  // Read/write for the owning GPU and for every GPU that has peer access to it switched on.
+  std::vector<CUmemAccessDesc> descs;
+  int ndev = device_count();
+  for (int d = 0; d < ndev; ++d) {
+    if (d != device && !peer_access_enabled((c10::DeviceIndex)d, (c10::DeviceIndex)device)) continue;
+    CUmemAccessDesc a{};
+    a.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+    a.location.id = d;
+    a.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+    descs.push_back(a);
+  }
+  return vmm_err(driver_vmm().set_access((CUdeviceptr)va, n, descs.data(), descs.size()));
+}
+int cuda_vmm_map(void* va, size_t n, int device, uint64_t* handle) {
+  const DriverVmm& d = driver_vmm();
+  CUmemGenericAllocationHandle h = 0;
+  CUmemAllocationProp prop = vmm_prop(device, g_vmm_fd_handles);
+  CUresult r = d.create(&h, n, &prop, 0);
+  if (g_vmm_fd_handles && (r == CUDA_ERROR_NOT_PERMITTED || r == CUDA_ERROR_NOT_SUPPORTED)) {
+    g_vmm_fd_handles = false;  // containers without the capability: chunks stay process-private
+    prop = vmm_prop(device, false);
+    r = d.create(&h, n, &prop, 0);
+  }
+  if (r != CUDA_SUCCESS) return vmm_err(r);
+  r = d.map((CUdeviceptr)va, n, 0, h, 0);
+  if (r != CUDA_SUCCESS) {
+    d.release(h);
+    return vmm_err(r);
+  }
+  int e = cuda_vmm_access(va, n, device);
+  if (e != 0) {
+    d.unmap((CUdeviceptr)va, n);
+    d.release(h);
+    return e;
+  }
+  *handle = (uint64_t)h;
+  return 0;
+}
+int cuda_vmm_unmap(void* va, size_t n, int, uint64_t handle) {
+  const DriverVmm& d = driver_vmm();
+  CUresult r = d.unmap((CUdeviceptr)va, n);
+  if (r != CUDA_SUCCESS) return vmm_err(r);
+  return vmm_err(d.release((CUmemGenericAllocationHandle)handle));
+}
+int cuda_vmm_export(uint64_t handle, int* fd) {
+  if (!g_vmm_fd_handles) return (int)cudaErrorNotSupported;
+  return vmm_err(driver_vmm().export_handle(fd, (CUmemGenericAllocationHandle)handle,
+                                            CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0));
+}
+int cuda_vmm_import(int fd, void* va, size_t n, int device, uint64_t* handle) {
+  const DriverVmm& d = driver_vmm();
+  CUmemGenericAllocationHandle h = 0;
+  CUresult r = d.import_handle(&h, (void*)(uintptr_t)fd, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR);
+  if (r != CUDA_SUCCESS) return vmm_err(r);
+  r = d.map((CUdeviceptr)va, n, 0, h, 0);
+  if (r != CUDA_SUCCESS) {
+    d.release(h);
+    return vmm_err(r);
+  }
+  int e = cuda_vmm_access(va, n, device);
+  if (e != 0) {
+    d.unmap((CUdeviceptr)va, n);
+    d.release(h);
+    return e;
+  }
+  *handle = (uint64_t)h;
+  return 0;
+}
+const VmmOps kCudaVmm{cuda_vmm_granularity, cuda_vmm_reserve, cuda_vmm_release, cuda_vmm_map, cuda_vmm_unmap,
+                      cuda_vmm_export, cuda_vmm_import};
+
+const RawBackend kNative{"native", native_alloc, native_free, cuda_mem_info, true, &kCudaVmm};
+const RawBackend kUnified{"unified", unified_alloc, native_free, cuda_mem_info, true, nullptr};
+const RawBackend kAsync{"cudaMallocAsync", async_alloc, async_free, cuda_mem_info, true, nullptr};
+const RawBackend kHost{"host", host_alloc, host_free, host_mem_info, false, &kHostVmm};
+RawBackend g_plug{"pluggable", nullptr, nullptr, cuda_mem_info, true, nullptr};
 
 }  // namespace
 
@@ -170,6 +341,7 @@ void set_config_string(const std::string& s) {
 
 // ------------------------------------------------------------------ blocks
 struct Pool;
+struct XSegment;
 struct Block {
   int device = 0;
   cudaStream_t stream = nullptr;  // allocation stream
@@ -181,7 +353,26 @@ struct Block {
   Block *prev = nullptr, *next = nullptr;
   int event_count = 0;
   int gc_count = 0;
+  XSegment* xseg = nullptr;  // expandable segment this block lies in
+  bool mapped = true;        // false: address space only (never in Pool::blocks)
   bool is_split() const { return prev || next; }
+};
+
+// Address-ordered set of the unmapped ranges of a pool's expandable segments.
+struct UnmappedLess {
+  bool operator()(const Block* a, const Block* b) const {
+    if (a->stream != b->stream) return (uintptr_t)a->stream < (uintptr_t)b->stream;
+    return (uintptr_t)a->ptr < (uintptr_t)b->ptr;
+  }
+};
+
+// One reserved address range that grows and shrinks in `unit`-sized physical chunks.
+struct XSegment {
+  char* base = nullptr;
+  size_t reserved = 0, unit = 0, mapped_bytes = 0;
+  cudaStream_t stream = nullptr;
+  Pool* pool = nullptr;
+  std::vector<uint64_t> handles;  // one per unit; 0 = not mapped
 };
 
 struct BlockLess {
@@ -195,6 +386,7 @@ struct BlockLess {
 struct PrivatePool;
 struct Pool {
   std::set<Block*, BlockLess> blocks;
+  std::set<Block*, UnmappedLess> unmapped;
   bool is_small;
   PrivatePool* owner = nullptr;
   explicit Pool(bool s, PrivatePool* o = nullptr) : is_small(s), owner(o) {}
@@ -261,6 +453,7 @@ class DeviceAllocatorImpl {
       rem->device = device_;
       rem->stream = b->stream;
       rem->pool = &pool;
+      rem->xseg = b->xseg;
       rem->ptr = static_cast<char*>(b->ptr) + size;
       rem->size = b->size - size;
       rem->prev = b;
@@ -271,8 +464,14 @@ class DeviceAllocatorImpl {
       pool.blocks.insert(rem);
       bump([&](int t) { stats_.inactive_split[t].inc(1); stats_.inactive_split_bytes[t].inc(rem->size); }, pool);
     }
+    mark_allocated(b, orig);
+    return b;
+  }
+
+  void mark_allocated(Block* b, size_t requested) {
+    Pool& pool = *b->pool;
     b->allocated = true;
-    b->requested = orig;
+    b->requested = requested;
     live_[b->ptr] = b;
     if (pool.owner) ++pool.owner->live_allocs;
     bump([&](int t) {
@@ -283,12 +482,16 @@ class DeviceAllocatorImpl {
       stats_.requested_bytes[t].inc(b->requested);
     }, pool);
     if (b->size >= config().max_split_size) stats_.oversize_allocations.inc(1);
-    trace(TraceEntry::ALLOC, b->ptr, b->size, stream);
-    return b;
+    trace(TraceEntry::ALLOC, b->ptr, b->size, b->stream);
   }
 
   void free(Block* b) {
     std::lock_guard<std::mutex> lk(mu_);
+    free_locked(b, /*ignore_stream_uses=*/false);
+  }
+
+  void free_locked(Block* b, bool ignore_stream_uses) {
+    if (ignore_stream_uses) b->stream_uses.clear();
     b->allocated = false;
     live_.erase(b->ptr);
     Pool& pool = *b->pool;
@@ -397,30 +600,150 @@ class DeviceAllocatorImpl {
         for (auto& kv : private_) if (kv.second.get() == h->pool->owner) id = kv.first;
       }
       if ((filter.first || filter.second) && id != filter) continue;
-      SegmentInfo s;
-      s.device = device_;
-      s.address = (uintptr_t)h->ptr;
-      s.stream = h->stream;
-      s.is_large = !h->pool->is_small;
-      s.is_expandable = false;
-      s.pool_id_first = id.first;
-      s.pool_id_second = id.second;
-      for (Block* b = h; b; b = b->next) {
-        s.total_size += b->size;
-        BlockInfo bi;
-        bi.size = b->size;
-        bi.requested = b->requested;
-        bi.allocated = b->allocated;
-        bi.active = b->allocated || b->event_count > 0 || !b->stream_uses.empty();
-        if (bi.allocated) { s.allocated_size += b->size; s.requested_size += b->requested; }
-        if (bi.active) s.active_size += b->size;
-        s.blocks.push_back(bi);
+      // An expandable segment reports each run of mapped blocks as a segment of its own.
+      Block* b = h;
+      while (b) {
+        while (b && !b->mapped) b = b->next;
+        if (!b) break;
+        SegmentInfo s;
+        s.device = device_;
+        s.address = (uintptr_t)b->ptr;
+        s.stream = b->stream;
+        s.is_large = !b->pool->is_small;
+        s.is_expandable = b->xseg != nullptr;
+        s.pool_id_first = id.first;
+        s.pool_id_second = id.second;
+        for (; b && b->mapped; b = b->next) {
+          s.total_size += b->size;
+          BlockInfo bi;
+          bi.address = (uintptr_t)b->ptr;
+          bi.size = b->size;
+          bi.requested = b->requested;
+          bi.allocated = b->allocated;
+          bi.active = b->allocated || b->event_count > 0 || !b->stream_uses.empty();
+          if (bi.allocated) { s.allocated_size += b->size; s.requested_size += b->requested; }
+          if (bi.active) s.active_size += b->size;
+          s.blocks.push_back(bi);
+        }
+        out.push_back(std::move(s));
       }
-      out.push_back(std::move(s));
     }
     std::sort(out.begin(), out.end(), [](const SegmentInfo& a, const SegmentInfo& b) { return a.address < b.address; });
     trace(TraceEntry::SNAPSHOT, nullptr, 0, nullptr);
     return out;
+  }
+
+  // Puts the private pool `state.pool` back into the block layout of the checkpoint: everything live in it is
+  // freed, then each checkpointed segment is carved into the recorded blocks and the ones that were allocated
+  // become live again at their old addresses.
+  RestoreResult restore(const PoolCheckpoint& state) {
+    std::lock_guard<std::mutex> lk(mu_);
+    auto pit = private_.find(state.pool);
+    TORCH_CHECK(pit != private_.end(), "restore_pool: the pool of this checkpoint no longer exists");
+    PrivatePool* pp = pit->second.get();
+    TORCH_CHECK(capturing_depth_ == 0, "restore_pool cannot run while a capture is under way");
+    sync_and_drain();
+    std::vector<Block*> mine;
+    for (auto& kv : live_) if (kv.second->pool->owner == pp) mine.push_back(kv.second);
+    std::set<void*> was_live;
+    ++pp->use_count;  // a pool nobody captures into any more must not hand its segments back half-way through
+    for (Block* b : mine) {
+      was_live.insert(b->ptr);
+      free_locked(b, /*ignore_stream_uses=*/true);
+    }
+    --pp->use_count;
+    RestoreResult res;
+    for (const SegmentInfo& seg : state.segments) {
+      Pool& pool = seg.is_large ? pp->large : pp->small;
+      char* lo = reinterpret_cast<char*>(seg.address);
+      Block* f = nullptr;
+      for (Block* b : pool.blocks) {
+        if (static_cast<char*>(b->ptr) <= lo && static_cast<char*>(b->ptr) + b->size >= lo + seg.total_size) {
+          f = b;
+          break;
+        }
+      }
+      TORCH_CHECK(f, "restore_pool: the segment at ", (void*)lo, " (", seg.total_size,
+                  " bytes) is no longer a free range of the pool");
+      pool.blocks.erase(f);
+      if (f->is_split()) bump([&](int t) { stats_.inactive_split[t].dec(1); stats_.inactive_split_bytes[t].dec(f->size); }, pool);
+      auto put_free = [&](Block* b) {
+        pool.blocks.insert(b);
+        if (b->is_split()) bump([&](int t) { stats_.inactive_split[t].inc(1); stats_.inactive_split_bytes[t].inc(b->size); }, pool);
+      };
+      // cuts the first `n` bytes off `b`; returns the rest (linked, in no set) or null when nothing is left
+      auto cut = [&](Block* b, size_t n) -> Block* {
+        if (b->size == n) return nullptr;
+        Block* rem = new Block();
+        rem->device = device_;
+        rem->stream = b->stream;
+        rem->pool = &pool;
+        rem->xseg = b->xseg;
+        rem->ptr = static_cast<char*>(b->ptr) + n;
+        rem->size = b->size - n;
+        rem->prev = b;
+        rem->next = b->next;
+        if (rem->next) rem->next->prev = rem;
+        b->next = rem;
+        b->size = n;
+        return rem;
+      };
+      if (static_cast<char*>(f->ptr) < lo) {  // an expandable range that has grown downwards since
+        Block* rest = cut(f, (size_t)(lo - static_cast<char*>(f->ptr)));
+        put_free(f);
+        f = rest;
+      }
+      for (const BlockInfo& bi : seg.blocks) {
+        TORCH_INTERNAL_ASSERT(f && (uintptr_t)f->ptr == bi.address && f->size >= bi.size);
+        Block* rest = cut(f, bi.size);
+        if (bi.allocated) {
+          mark_allocated(f, bi.requested);
+          res.allocated.push_back(f->ptr);
+        } else {
+          put_free(f);
+        }
+        f = rest;
+      }
+      if (f) put_free(f);
+    }
+    std::set<void*> now(res.allocated.begin(), res.allocated.end());
+    for (void* p : was_live) if (!now.count(p)) res.freed.push_back(p);
+    return res;
+  }
+
+  bool share(void* p, CachingAllocator::ShareInfo* out) {
+    std::lock_guard<std::mutex> lk(mu_);
+    auto it = live_.upper_bound(p);
+    if (it == live_.begin()) return false;
+    --it;
+    Block* b = it->second;
+    if (static_cast<char*>(p) >= static_cast<char*>(b->ptr) + b->size) return false;
+    if (!b->xseg || !be_->vmm->export_fd) return false;
+    XSegment* xs = b->xseg;
+    size_t off = (size_t)(static_cast<char*>(p) - xs->base);
+    size_t len = b->size - (size_t)(static_cast<char*>(p) - static_cast<char*>(b->ptr));
+    size_t first = off / xs->unit, last = (off + len - 1) / xs->unit;
+    out->fds.clear();
+    for (size_t i = first; i <= last; ++i) {
+      int fd = -1;
+      if (be_->vmm->export_fd(xs->handles[i], &fd) != 0) {
+        if (be_->device_events) (void)cudaGetLastError();
+        for (int f : out->fds) ::close(f);
+        out->fds.clear();
+        return false;
+      }
+      out->fds.push_back(fd);
+    }
+    out->chunk_bytes = xs->unit;
+    out->offset = off - first * xs->unit;
+    out->size = len;
+    return true;
+  }
+
+  void refresh_peer_access() {
+    std::lock_guard<std::mutex> lk(mu_);
+    DeviceSwitch sw(be_->device_events ? device_ : -1);
+    refresh_peer_access_locked();
   }
 
   // ------------------------------------------------------- private pools
@@ -549,7 +872,257 @@ class DeviceAllocatorImpl {
     return rem > kSmallSize;
   }
 
+  // ------------------------------------------------- expandable segments
+  bool use_expandable() const { return config().expandable_segments && be_->vmm != nullptr; }
+
+  bool is_free_mapped(const Block* b) const {
+    return b && b->mapped && !b->allocated && b->event_count == 0 && b->stream_uses.empty() &&
+           b->pool->blocks.count(const_cast<Block*>(b));
+  }
+
+  XSegment* new_xsegment(Pool& pool, cudaStream_t stream) {
+    size_t gran = be_->vmm->granularity(device_);
+    if (gran == 0) return nullptr;
+    size_t unit = pool.is_small ? kSmallBuffer : std::max(config().large_segment_bytes, (size_t)(20u << 20));
+    unit = (unit + gran - 1) / gran * gran;
+    size_t fr = 0, tot = 0;
+    if (be_->mem_info(device_, &fr, &tot) != 0 || tot == 0) return nullptr;
+    // Room for the whole device plus slack: a segment never has to move.
+    size_t reserve = (tot + tot / 8 + unit - 1) / unit * unit;
+    void* va = nullptr;
+    if (be_->vmm->reserve(&va, reserve, device_) != 0) {
+      if (be_->device_events) (void)cudaGetLastError();
+      return nullptr;
+    }
+    auto xs = std::make_unique<XSegment>();
+    xs->base = static_cast<char*>(va);
+    xs->reserved = reserve;
+    xs->unit = unit;
+    xs->stream = stream;
+    xs->pool = &pool;
+    xs->handles.assign(reserve / unit, 0);
+    Block* u = new Block();
+    u->device = device_;
+    u->stream = stream;
+    u->pool = &pool;
+    u->ptr = va;
+    u->size = reserve;
+    u->xseg = xs.get();
+    u->mapped = false;
+    pool.unmapped.insert(u);
+    xsegs_.push_back(std::move(xs));
+    return xsegs_.back().get();
+  }
+
+  // Maps the first `bytes` (rounded up to whole units) of the unmapped block `u`; returns the new
+  // free mapped block (merged with a free mapped predecessor), not inserted in the pool.
+  Block* map_front(Block* u, size_t bytes) {
+    XSegment* xs = u->xseg;
+    Pool& pool = *u->pool;
+    bytes = (bytes + xs->unit - 1) / xs->unit * xs->unit;
+    if (bytes > u->size) return nullptr;
+    if (limited_ && (size_t)stats_.reserved_bytes[kAll].current + bytes > allowed_) return nullptr;
+    size_t first = (size_t)(static_cast<char*>(u->ptr) - xs->base) / xs->unit, n = bytes / xs->unit, done = 0;
+    int e = 0;
+    for (; done < n; ++done) {
+      e = be_->vmm->map(xs->base + (first + done) * xs->unit, xs->unit, device_, &xs->handles[first + done]);
+      if (e != 0) break;
+    }
+    if (e != 0) {
+      if (be_->device_events) (void)cudaGetLastError();
+      for (size_t i = 0; i < done; ++i) {
+        be_->vmm->unmap(xs->base + (first + i) * xs->unit, xs->unit, device_, xs->handles[first + i]);
+        xs->handles[first + i] = 0;
+      }
+      if (e != (int)cudaErrorMemoryAllocation) check_cuda((cudaError_t)e, "expandable segment map", __FILE__, __LINE__);
+      return nullptr;
+    }
+    ++stats_.num_device_alloc;
+    if (xs->mapped_bytes == 0) bump([&](int t) { stats_.segment[t].inc(1); }, pool);
+    xs->mapped_bytes += bytes;
+    bump([&](int t) { stats_.reserved_bytes[t].inc(bytes); }, pool);
+    trace(TraceEntry::SEGMENT_ALLOC, u->ptr, bytes, u->stream);
+    // carve [u->ptr, u->ptr + bytes) off the front of u
+    Block* m = new Block();
+    m->device = device_;
+    m->stream = u->stream;
+    m->pool = &pool;
+    m->xseg = xs;
+    m->ptr = u->ptr;
+    m->size = bytes;
+    m->prev = u->prev;
+    if (m->prev) m->prev->next = m;
+    pool.unmapped.erase(u);
+    if (u->size == bytes) {
+      m->next = u->next;
+      if (m->next) m->next->prev = m;
+      delete u;
+    } else {
+      u->ptr = static_cast<char*>(u->ptr) + bytes;
+      u->size -= bytes;
+      u->prev = m;
+      m->next = u;
+      pool.unmapped.insert(u);
+    }
+    // join free mapped neighbours (the successor can be one when a hole was re-mapped)
+    for (Block* nb : {m->prev, m->next}) {
+      if (!is_free_mapped(nb)) continue;
+      pool.blocks.erase(nb);
+      bump([&](int t) { stats_.inactive_split[t].dec(1); stats_.inactive_split_bytes[t].dec(nb->size); }, pool);
+      if (nb == m->prev) {
+        m->ptr = nb->ptr;
+        m->prev = nb->prev;
+        if (m->prev) m->prev->next = m;
+      } else {
+        m->next = nb->next;
+        if (m->next) m->next->prev = m;
+      }
+      m->size += nb->size;
+      delete nb;
+    }
+    return m;
+  }
+
+  Block* alloc_expandable(Pool& pool, size_t size, cudaStream_t stream) {
+    Block key;
+    key.stream = stream;
+    key.ptr = nullptr;
+    for (auto it = pool.unmapped.lower_bound(&key); it != pool.unmapped.end() && (*it)->stream == stream; ++it) {
+      Block* u = *it;
+      size_t have = is_free_mapped(u->prev) ? u->prev->size : 0;
+      size_t need = size > have ? size - have : u->xseg->unit;
+      size_t rounded = (need + u->xseg->unit - 1) / u->xseg->unit * u->xseg->unit;
+      if (rounded > u->size) continue;
+      // A hole between mapped ranges has to be filled whole or the result would not be contiguous enough.
+      return map_front(u, need);
+    }
+    XSegment* xs = new_xsegment(pool, stream);
+    if (!xs) return nullptr;
+    Block k2;
+    k2.stream = stream;
+    k2.ptr = xs->base;
+    auto it = pool.unmapped.find(&k2);
+    if (it == pool.unmapped.end()) return nullptr;
+    Block* m = map_front(*it, size);
+    if (!m) drop_if_empty(xs);
+    return m;
+  }
+
+  // Releases the address range of a segment with nothing mapped.
+  void drop_if_empty(XSegment* xs) {
+    if (xs->mapped_bytes != 0) return;
+    Pool& pool = *xs->pool;
+    Block k;
+    k.stream = xs->stream;
+    k.ptr = xs->base;
+    auto it = pool.unmapped.find(&k);
+    if (it == pool.unmapped.end() || (*it)->size != xs->reserved) return;
+    Block* u = *it;
+    pool.unmapped.erase(it);
+    delete u;
+    be_->vmm->release(xs->base, xs->reserved, device_);
+    for (auto i = xsegs_.begin(); i != xsegs_.end(); ++i) {
+      if (i->get() == xs) {
+        xsegs_.erase(i);
+        break;
+      }
+    }
+  }
+
+  // Unmaps the whole units inside the free mapped block `b` (which sits in its pool).  Returns the bytes given back.
+  size_t unmap_block(Block* b) {
+    XSegment* xs = b->xseg;
+    Pool& pool = *b->pool;
+    size_t off = (size_t)(static_cast<char*>(b->ptr) - xs->base);
+    size_t lo = (off + xs->unit - 1) / xs->unit * xs->unit;
+    size_t hi = (off + b->size) / xs->unit * xs->unit;
+    if (hi <= lo) return 0;
+    if (be_->device_events) {
+      // Work queued on the block's stream may still touch it: unmapping, unlike cudaFree, does not wait.
+      DeviceSwitch sw(device_);
+      B200_CUDA_CHECK(cudaStreamSynchronize(b->stream));
+    }
+    pool.blocks.erase(b);
+    if (b->is_split()) bump([&](int t) { stats_.inactive_split[t].dec(1); stats_.inactive_split_bytes[t].dec(b->size); }, pool);
+    for (size_t i = lo / xs->unit; i < hi / xs->unit; ++i) {
+      B200_KERNEL_CALL(be_->vmm->unmap(xs->base + i * xs->unit, xs->unit, device_, xs->handles[i]));
+      xs->handles[i] = 0;
+    }
+    size_t bytes = hi - lo;
+    ++stats_.num_device_free;
+    xs->mapped_bytes -= bytes;
+    bump([&](int t) { stats_.reserved_bytes[t].dec(bytes); }, pool);
+    if (xs->mapped_bytes == 0) bump([&](int t) { stats_.segment[t].dec(1); }, pool);
+    trace(TraceEntry::SEGMENT_FREE, xs->base + lo, bytes, b->stream);
+    // b becomes [head mapped][middle unmapped][tail mapped]
+    size_t head = lo - off, tail = off + b->size - hi;
+    Block* mid = b;
+    if (head) {
+      Block* hb = new Block();
+      hb->device = device_;
+      hb->stream = b->stream;
+      hb->pool = &pool;
+      hb->xseg = xs;
+      hb->ptr = b->ptr;
+      hb->size = head;
+      hb->prev = b->prev;
+      if (hb->prev) hb->prev->next = hb;
+      hb->next = mid;
+      mid->prev = hb;
+      pool.blocks.insert(hb);
+      bump([&](int t) { stats_.inactive_split[t].inc(1); stats_.inactive_split_bytes[t].inc(head); }, pool);
+    }
+    if (tail) {
+      Block* tb = new Block();
+      tb->device = device_;
+      tb->stream = b->stream;
+      tb->pool = &pool;
+      tb->xseg = xs;
+      tb->ptr = xs->base + hi;
+      tb->size = tail;
+      tb->next = b->next;
+      if (tb->next) tb->next->prev = tb;
+      tb->prev = mid;
+      mid->next = tb;
+      pool.blocks.insert(tb);
+      bump([&](int t) { stats_.inactive_split[t].inc(1); stats_.inactive_split_bytes[t].inc(tail); }, pool);
+    }
+    mid->ptr = xs->base + lo;
+    mid->size = bytes;
+    mid->mapped = false;
+    mid->gc_count = 0;
+    // join neighbouring unmapped ranges
+    for (Block* nb : {mid->prev, mid->next}) {
+      if (!nb || nb->mapped) continue;
+      pool.unmapped.erase(nb);
+      if (nb == mid->prev) {
+        mid->ptr = nb->ptr;
+        mid->prev = nb->prev;
+        if (mid->prev) mid->prev->next = mid;
+      } else {
+        mid->next = nb->next;
+        if (mid->next) mid->next->prev = mid;
+      }
+      mid->size += nb->size;
+      delete nb;
+    }
+    pool.unmapped.insert(mid);
+    drop_if_empty(xs);
+    return bytes;
+  }
+
+  void refresh_peer_access_locked() {
+    if (!be_->vmm || !be_->device_events) return;
+    for (auto& xs : xsegs_)
+      for (size_t i = 0; i < xs->handles.size(); ++i)
+        if (xs->handles[i]) B200_CUDA_WARN((cudaError_t)cuda_vmm_access(xs->base + i * xs->unit, xs->unit, device_));
+  }
+
   Block* alloc_segment(Pool& pool, size_t size, cudaStream_t stream) {
+    if (use_expandable()) {
+      DeviceSwitch sw(be_->device_events ? device_ : -1);
+      return alloc_expandable(pool, size, stream);
+    }
     size_t seg = segment_size(size);
     if (limited_ && (size_t)stats_.reserved_bytes[kAll].current + seg > allowed_) return nullptr;
     void* p = nullptr;
@@ -603,7 +1176,7 @@ class DeviceAllocatorImpl {
     // Only worth it for oversize requests: free the smallest whole cached segment >= size.
     if (config().max_split_size == SIZE_MAX || size < config().max_split_size) return false;
     for (Block* b : pool.blocks) {
-      if (!b->is_split() && b->size >= size) {
+      if (!b->is_split() && !b->xseg && b->size >= size) {
         sync_and_drain();
         release_block(b);
         return true;
@@ -613,9 +1186,13 @@ class DeviceAllocatorImpl {
   }
 
   void release_pool_blocks(Pool& pool) {
-    std::vector<Block*> whole;
-    for (Block* b : pool.blocks) if (!b->is_split()) whole.push_back(b);
+    std::vector<Block*> whole, growable;
+    for (Block* b : pool.blocks) {
+      if (b->xseg) growable.push_back(b);
+      else if (!b->is_split()) whole.push_back(b);
+    }
     for (Block* b : whole) release_block(b);
+    if (capturing_depth_ == 0) for (Block* b : growable) unmap_block(b);
   }
 
   void sync_and_drain() {
@@ -670,7 +1247,7 @@ class DeviceAllocatorImpl {
     size_t excess = (size_t)stats_.reserved_bytes[kAll].current - target;
     // age the cached whole large segments; free the oldest until under target
     std::vector<Block*> cands;
-    for (Block* b : large_.blocks) if (!b->is_split()) { ++b->gc_count; cands.push_back(b); }
+    for (Block* b : large_.blocks) if (!b->is_split() && !b->xseg) { ++b->gc_count; cands.push_back(b); }
     std::sort(cands.begin(), cands.end(), [](Block* a, Block* b) { return a->gc_count > b->gc_count; });
     size_t freed = 0;
     for (Block* b : cands) {
@@ -803,6 +1380,7 @@ class DeviceAllocatorImpl {
   std::mutex mu_;
   Pool small_{true}, large_{false};
   std::map<void*, Block*> live_;
+  std::vector<std::unique_ptr<XSegment>> xsegs_;
   std::unordered_map<MempoolId, std::unique_ptr<PrivatePool>, PoolIdHash> private_;
   std::vector<std::pair<MempoolId, std::function<bool(cudaStream_t)>>> captures_;
   int capturing_depth_ = 0;
@@ -843,27 +1421,26 @@ void CachingAllocator::init(int n) {
 }
 
 namespace {
-struct Ctx {
-  CachingAllocator* owner;
-  Block* block;     // null in no-caching mode
-  void* ptr;
-};
-// ctx pointers are Block* tagged through a side table to keep DataPtr contexts one word.
+// A DataPtr's context is its data pointer; this table finds the allocator that owns it.
 std::mutex g_ctx_mu;
-std::unordered_map<void*, CachingAllocator*> g_block_owner;  // Block* -> owner
+std::unordered_map<void*, CachingAllocator*> g_ptr_owner;
+bool g_pool_restored = false;  // a restore may leave DataPtrs behind whose memory it already took back
 
 void deleter(void* ctx) {
-  Block* b = static_cast<Block*>(ctx);
   CachingAllocator* owner;
   {
     std::lock_guard<std::mutex> g(g_ctx_mu);
-    auto it = g_block_owner.find(ctx);
-    TORCH_INTERNAL_ASSERT(it != g_block_owner.end(), "blackwell allocator: freeing an unknown block");
+    auto it = g_ptr_owner.find(ctx);
+    if (it == g_ptr_owner.end()) {
+      TORCH_INTERNAL_ASSERT(g_pool_restored, "blackwell allocator: freeing an unknown pointer");
+      return;
+    }
     owner = it->second;
-    g_block_owner.erase(it);
+    g_ptr_owner.erase(it);
   }
-  owner->raw_delete(b->ptr);
+  owner->raw_delete(ctx);
 }
+void noop(void*) {}
 
 void nocache_deleter(void* p) {
   NoCacheEntry e;
@@ -902,9 +1479,77 @@ c10::DataPtr CachingAllocator::allocate(size_t n) {
   Block* b = devs_[device]->malloc(n, stream);
   {
     std::lock_guard<std::mutex> g(g_ctx_mu);
-    g_block_owner[b] = this;
+    g_ptr_owner[b->ptr] = this;
   }
-  return c10::DataPtr(b->ptr, b, &deleter, make_device(device));
+  return c10::DataPtr(b->ptr, b->ptr, &deleter, make_device(device));
+}
+
+c10::DeleterFnPtr CachingAllocator::noop_deleter() { return &noop; }
+
+c10::DataPtr CachingAllocator::adopt(void* p, int device) {
+  TORCH_CHECK(device < (int)devs_.size() && devs_[device]->find_live(p), "blackwell allocator: ", p,
+              " is not a live allocation on device ", device);
+  {
+    std::lock_guard<std::mutex> g(g_ctx_mu);
+    TORCH_CHECK(!g_ptr_owner.count(p), "blackwell allocator: ", p, " already has an owner");
+    g_ptr_owner[p] = this;
+  }
+  return c10::DataPtr(p, p, &deleter, make_device(device));
+}
+
+PoolCheckpoint CachingAllocator::checkpoint_pool(int device, MempoolId pool) {
+  TORCH_CHECK(pool.first || pool.second, "checkpoint_pool needs a private pool id");
+  PoolCheckpoint c;
+  c.device = device;
+  c.pool = pool;
+  if (device < (int)devs_.size()) c.segments = devs_[device]->snapshot(pool);
+  return c;
+}
+
+RestoreResult CachingAllocator::restore_pool(int device, const PoolCheckpoint& state) {
+  TORCH_CHECK(device < (int)devs_.size() && state.device == device, "restore_pool: checkpoint of another device");
+  RestoreResult r = devs_[device]->restore(state);
+  std::lock_guard<std::mutex> g(g_ctx_mu);
+  g_pool_restored = true;
+  for (void* p : r.freed) g_ptr_owner.erase(p);
+  return r;
+}
+
+bool CachingAllocator::share_expandable(void* p, ShareInfo* out) {
+  for (auto& d : devs_)
+    if (d->share(p, out)) return true;
+  return false;
+}
+
+void* CachingAllocator::map_imported(const std::vector<int>& fds, size_t chunk, int device,
+                                     std::vector<uint64_t>* handles) {
+  const VmmOps* v = backend_->vmm;
+  TORCH_CHECK(v && v->import_fd, "this allocator backend cannot import shared memory chunks");
+  DeviceSwitch sw(backend_->device_events ? device : -1);
+  void* va = nullptr;
+  B200_KERNEL_CALL(v->reserve(&va, chunk * fds.size(), device));
+  handles->assign(fds.size(), 0);
+  for (size_t i = 0; i < fds.size(); ++i) {
+    int e = v->import_fd(fds[i], static_cast<char*>(va) + i * chunk, chunk, device, &(*handles)[i]);
+    if (e != 0) {
+      for (size_t j = 0; j < i; ++j) v->unmap(static_cast<char*>(va) + j * chunk, chunk, device, (*handles)[j]);
+      v->release(va, chunk * fds.size(), device);
+      check_cuda((cudaError_t)e, "import of a shared memory chunk", __FILE__, __LINE__);
+    }
+  }
+  return va;
+}
+
+void CachingAllocator::unmap_imported(void* va, size_t chunk, int device, const std::vector<uint64_t>& handles) {
+  const VmmOps* v = backend_->vmm;
+  DeviceSwitch sw(backend_->device_events ? device : -1);
+  for (size_t i = 0; i < handles.size(); ++i)
+    B200_CUDA_WARN((cudaError_t)v->unmap(static_cast<char*>(va) + i * chunk, chunk, device, handles[i]));
+  B200_CUDA_WARN((cudaError_t)v->release(va, chunk * handles.size(), device));
+}
+
+void CachingAllocator::refresh_peer_access(int device) {
+  if (device < (int)devs_.size()) devs_[device]->refresh_peer_access();
 }
 
 c10::DeleterFnPtr CachingAllocator::raw_deleter() const { return &deleter; }
@@ -937,8 +1582,12 @@ void CachingAllocator::raw_delete(void* p) {
 void CachingAllocator::record_stream(const c10::DataPtr& p, int device, cudaStream_t stream) {
   if (!p.get()) return;
   if (p.get_deleter() != &deleter) return;  // foreign / no-cache memory: nothing to track
-  Block* b = static_cast<Block*>(p.get_context());
-  devs_[b->device]->record_stream(b, stream);
+  for (auto& d : devs_) {
+    if (Block* b = d->find_live(p.get())) {
+      d->record_stream(b, stream);
+      return;
+    }
+  }
 }
 
 void CachingAllocator::record_stream_ptr(void* p, int device, cudaStream_t stream) {
@@ -986,9 +1635,9 @@ void* CachingAllocator::base_allocation(void* p, size_t* size) {
   for (auto& d : devs_) {
     if (Block* b = d->find_containing(p)) {
       Block* h = b;
-      while (h->prev) h = h->prev;
+      while (h->prev && h->prev->mapped) h = h->prev;
       size_t tot = 0;
-      for (Block* x = h; x; x = x->next) tot += x->size;
+      for (Block* x = h; x && x->mapped; x = x->next) tot += x->size;
       if (size) *size = tot;
       return h->ptr;
     }
@@ -1060,6 +1709,8 @@ CachingAllocator* get() {
                            : b == "host" ? host_backend()
                                          : native_backend();
     g_current = new CachingAllocator(be);  // leaked on purpose: tensors may outlive static destruction
+    if (be->vmm && be->device_events)
+      set_peer_access_hook([](int, int owner) { if (g_current) g_current->refresh_peer_access(owner); });
   }
   return g_current;
 }

@@ -37,6 +37,26 @@
 namespace b200 {
 namespace alloc {
 
+using MempoolId = std::pair<uint64_t, uint64_t>;
+
+// Virtual-memory operations behind expandable segments: address space is
+// reserved once per (pool, stream) and physical chunks are mapped into it as the
+// pool grows, so one segment grows in place instead of the cache collecting
+// differently sized cudaMalloc segments that fragment.  The CUDA table uses the
+// driver's cuMem* calls; the host table uses mmap/mprotect so the block logic
+// is exercised by the CPU tests.
+struct VmmOps {
+  size_t (*granularity)(int device);
+  int (*reserve)(void** va, size_t n, int device);
+  int (*release)(void* va, size_t n, int device);
+  // Creates `n` bytes of physical memory on `device`, maps them at `va` read/write and returns a handle.
+  int (*map)(void* va, size_t n, int device, uint64_t* handle);
+  int (*unmap)(void* va, size_t n, int device, uint64_t handle);
+  // POSIX file descriptor that another process can import (storage sharing); -1 table entries mean unsupported.
+  int (*export_fd)(uint64_t handle, int* fd);
+  int (*import_fd)(int fd, void* va, size_t n, int device, uint64_t* handle);
+};
+
 struct RawBackend {
   const char* name;
   // All functions are called with `device` current.
@@ -45,6 +65,8 @@ struct RawBackend {
   int (*mem_info)(int device, size_t* free_b, size_t* total_b);
   // Event hooks; null table entries mean "events complete immediately".
   bool device_events;
+  // Null when the memory source cannot grow a segment in place.
+  const VmmOps* vmm = nullptr;
 };
 
 B200_EXPORT const RawBackend* native_backend();
@@ -57,7 +79,7 @@ struct Config {
   double gc_threshold = 0.0;                 // fraction of the allowed memory that triggers cache GC
   size_t roundup_power2_divisions = 0;       // 0 = off
   size_t large_segment_bytes = 20u << 20;    // segment size for mid-sized requests
-  bool expandable_segments = false;          // parsed and reported; growth is by whole segments
+  bool expandable_segments = false;          // grow segments in place through the backend's VmmOps
   bool release_lock_on_malloc = false;
   bool pinned_use_host_register = false;
   int pinned_num_register_threads = 1;
@@ -92,6 +114,7 @@ struct DeviceStats {
 };
 
 struct BlockInfo {
+  uintptr_t address = 0;
   size_t size = 0, requested = 0;
   bool allocated = false, active = false;
 };
@@ -105,6 +128,19 @@ struct SegmentInfo {
   std::vector<BlockInfo> blocks;
 };
 
+// Block layout of one private pool at a point in time.  Restoring it frees what
+// was allocated since and re-creates the blocks that were live then at the
+// same addresses (graph trees replay an earlier graph's outputs this way).
+struct PoolCheckpoint {
+  int device = 0;
+  MempoolId pool{0, 0};
+  std::vector<SegmentInfo> segments;
+};
+struct RestoreResult {
+  std::vector<void*> freed;      // live before the restore, not live in the checkpoint
+  std::vector<void*> allocated;  // live in the checkpoint (whether or not they were live before)
+};
+
 struct TraceEntry {
   enum Action { ALLOC, FREE_REQUESTED, FREE_COMPLETED, SEGMENT_ALLOC, SEGMENT_FREE, OOM, SNAPSHOT } action;
   int device;
@@ -114,7 +150,6 @@ struct TraceEntry {
   uint64_t time_ns;
 };
 
-using MempoolId = std::pair<uint64_t, uint64_t>;
 using OomObserver = std::function<void(int device, size_t requested, size_t total, size_t free_b)>;
 
 class DeviceAllocatorImpl;
@@ -157,6 +192,24 @@ class B200_EXPORT CachingAllocator final : public c10::Allocator {
   void release_pool(int device, MempoolId pool);
   void create_or_incref_pool(int device, MempoolId pool);
   int pool_use_count(int device, MempoolId pool);
+
+  // Private-pool checkpointing (reference MUSACachingAllocator.cpp:1207-1319 keeps the same pair).
+  PoolCheckpoint checkpoint_pool(int device, MempoolId pool);
+  RestoreResult restore_pool(int device, const PoolCheckpoint& state);
+  // Swaps the deleter of a DataPtr that a restore freed for a no-op, or back for one it re-created.
+  static c10::DeleterFnPtr noop_deleter();
+  // DataPtr for a pointer that restore_pool() reported as allocated.
+  c10::DataPtr adopt(void* p, int device);
+
+  // Expandable segments: file descriptors of the physical chunks behind the allocation holding `p`
+  // plus its offset in the first chunk, for another process to map (storage sharing without cudaIpc).
+  struct ShareInfo { std::vector<int> fds; size_t chunk_bytes = 0, offset = 0, size = 0; };
+  bool share_expandable(void* p, ShareInfo* out);
+  // The receiving side: maps imported chunks into fresh address space; `unmap_imported` undoes it.
+  void* map_imported(const std::vector<int>& fds, size_t chunk_bytes, int device, std::vector<uint64_t>* handles);
+  void unmap_imported(void* va, size_t chunk_bytes, int device, const std::vector<uint64_t>& handles);
+  // Re-grants read/write on `device`'s mapped chunks to the GPUs that now have peer access to it.
+  void refresh_peer_access(int device);
 
   void attach_oom_observer(OomObserver o);
   void record_history(bool enabled, size_t max_entries);

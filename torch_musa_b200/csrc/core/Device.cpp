@@ -143,6 +143,10 @@ bool g_peer_init = [] {
 }();
 }  // namespace
 
+namespace {
+void (*g_peer_hook)(int, int) = nullptr;
+}
+
 bool can_access_peer(c10::DeviceIndex a, c10::DeviceIndex b) {
   auto n = device_count();
   TORCH_CHECK(a >= 0 && a < n && b >= 0 && b < n, "invalid peer pair ", (int)a, "->", (int)b);
@@ -167,8 +171,17 @@ bool enable_peer_access(c10::DeviceIndex a, c10::DeviceIndex b) {
     }
   }
   g_peer[a][b] = ok ? 1 : 0;
+  if (ok && g_peer_hook) g_peer_hook((int)a, (int)b);
   return ok;
 }
+
+bool peer_access_enabled(c10::DeviceIndex a, c10::DeviceIndex b) {
+  if (a == b) return true;
+  if (a < 0 || b < 0 || a >= kMaxDevices || b >= kMaxDevices) return false;
+  return g_peer[a][b] == 1;
+}
+
+void set_peer_access_hook(void (*hook)(int, int)) { g_peer_hook = hook; }
 
 namespace {
 std::atomic<int> g_sync_debug{0};

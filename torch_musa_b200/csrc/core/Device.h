@@ -75,6 +75,10 @@ B200_EXPORT const cudaDeviceProp& device_properties(c10::DeviceIndex d);
 B200_EXPORT bool can_access_peer(c10::DeviceIndex a, c10::DeviceIndex b);
 // Lazily enables peer access a->b once; returns whether access is possible.
 B200_EXPORT bool enable_peer_access(c10::DeviceIndex a, c10::DeviceIndex b);
+// True once enable_peer_access(a, b) has succeeded (a reads/writes b's memory); never calls the driver.
+B200_EXPORT bool peer_access_enabled(c10::DeviceIndex a, c10::DeviceIndex b);
+// Called as hook(a, b) after a gains access to b: memory mapped outside cudaMalloc needs an explicit grant.
+B200_EXPORT void set_peer_access_hook(void (*hook)(int a, int b));
 
 // Sync-debug mode: 0 off, 1 warn, 2 error on implicit host synchronisation.
 B200_EXPORT void set_sync_debug_mode(int m);

@@ -27,6 +27,7 @@ using namespace b200;
 
 namespace b200 {
 void init_distributed_bindings(py::module& m);
+void init_storage_sharing_bindings(py::module& m);
 }
 
 namespace {
@@ -98,6 +99,7 @@ py::list snapshot(int device) {
     py::list blocks;
     for (auto& b : seg.blocks) {
       py::dict bd;
+      bd["address"] = b.address;
       bd["size"] = b.size;
       bd["requested_size"] = b.requested;
       bd["state"] = b.allocated ? "active_allocated" : (b.active ? "active_pending_free" : "inactive");
@@ -428,6 +430,41 @@ PYBIND11_MODULE(_C, m) {
     return alloc::get()->pool_use_count(device, id);
   });
 
+  // Private-pool checkpoints.  `stale` tensors lose their claim on memory the restore took back (their deleter
+  // becomes a no-op); `adopt` tensors, whose data pointers the restore re-created, get a deleter that frees them.
+  py::class_<alloc::PoolCheckpoint>(m, "_PoolCheckpoint")
+      .def_property_readonly("device", [](const alloc::PoolCheckpoint& c) { return c.device; })
+      .def_property_readonly("pool", [](const alloc::PoolCheckpoint& c) { return c.pool; })
+      .def_property_readonly("live_pointers", [](const alloc::PoolCheckpoint& c) {
+        std::vector<uintptr_t> v;
+        for (auto& s : c.segments)
+          for (auto& b : s.blocks)
+            if (b.allocated) v.push_back(b.address);
+        return v;
+      });
+  m.def("_checkpoint_pool", [](int device, std::pair<uint64_t, uint64_t> id) {
+    return alloc::get()->checkpoint_pool(device, id);
+  });
+  m.def("_restore_pool", [](int device, const alloc::PoolCheckpoint& state, std::vector<at::Tensor> stale) {
+    auto* a = alloc::get();
+    auto res = a->restore_pool(device, state);
+    c10::DeleterFnPtr real = a->raw_deleter(), noop = alloc::CachingAllocator::noop_deleter();
+    for (auto& t : stale) t.storage().mutable_data_ptr().compare_exchange_deleter(real, noop);
+    std::vector<uintptr_t> fr, al;
+    for (void* p : res.freed) fr.push_back((uintptr_t)p);
+    for (void* p : res.allocated) al.push_back((uintptr_t)p);
+    return py::make_tuple(fr, al);
+  }, py::arg("device"), py::arg("state"), py::arg("stale") = std::vector<at::Tensor>());
+  m.def("_adopt_allocation", [](int device, uintptr_t ptr, size_t nbytes) {
+    // A byte tensor that owns a live allocation nobody owns yet (one that a pool restore re-created).
+    c10::DataPtr dp = alloc::get()->adopt(reinterpret_cast<void*>(ptr), device);
+    c10::Storage st(c10::Storage::use_byte_size_t(), nbytes, std::move(dp), nullptr, false);
+    auto out = at::detail::make_tensor<c10::TensorImpl>(std::move(st), c10::DispatchKeySet(c10::DispatchKey::PrivateUse1),
+                                                        caffe2::TypeMeta::Make<uint8_t>());
+    out.unsafeGetTensorImpl()->set_sizes_contiguous({(int64_t)nbytes});
+    return out;
+  });
+
   // A caching allocator over plain host memory (events complete immediately): lets the cache logic
   // (rounding, pools, split/merge, stream affinity, private pools, fraction, OOM retry) be unit-tested
   // on machines without a GPU.
@@ -473,6 +510,7 @@ PYBIND11_MODULE(_C, m) {
           d["allocated_size"] = seg.allocated_size;
           d["is_large"] = seg.is_large;
           d["pool_id"] = py::make_tuple(seg.pool_id_first, seg.pool_id_second);
+          d["is_expandable"] = seg.is_expandable;
           py::list blocks;
           for (auto& b : seg.blocks) blocks.append(py::make_tuple(b.size, b.allocated));
           d["blocks"] = blocks;
@@ -487,6 +525,19 @@ PYBIND11_MODULE(_C, m) {
       })
       .def("end_pool", [](HostCacheHarness& h, std::pair<uint64_t, uint64_t> id) { h.a->end_allocate_to_pool(0, id); })
       .def("release_pool", [](HostCacheHarness& h, std::pair<uint64_t, uint64_t> id) { h.a->release_pool(0, id); })
+      .def("checkpoint", [](HostCacheHarness& h, std::pair<uint64_t, uint64_t> id) { return h.a->checkpoint_pool(0, id); })
+      .def("restore", [](HostCacheHarness& h, const alloc::PoolCheckpoint& c) {
+        auto res = h.a->restore_pool(0, c);
+        std::vector<uintptr_t> fr, al;
+        for (void* p : res.freed) fr.push_back((uintptr_t)p);
+        for (void* p : res.allocated) al.push_back((uintptr_t)p);
+        return py::make_tuple(fr, al);
+      })
+      .def("write_read", [](HostCacheHarness&, uintptr_t p, size_t n, int value) {
+        // touches host-backend memory: proves a mapped range is really usable
+        std::memset(reinterpret_cast<void*>(p), value, n);
+        return (int)reinterpret_cast<unsigned char*>(p)[n - 1];
+      })
       .def("record_history", [](HostCacheHarness& h, bool on, size_t n) { h.a->record_history(on, n); })
       .def("trace", [](HostCacheHarness& h) {
         py::list out;
@@ -543,4 +594,5 @@ PYBIND11_MODULE(_C, m) {
   });
 
   b200::init_distributed_bindings(m);
+  b200::init_storage_sharing_bindings(m);
 }
