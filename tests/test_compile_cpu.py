@@ -1,0 +1,120 @@
+"""Compile stack without a GPU: code generation and run-time compilation of fused groups (fake tensors
+on the device), the partitioner's validity rules, the native graph runner and ahead-of-time packages on
+CPU tensors.  Mirrors what reference tests/unittest/inductor/*.py and export tests check per layer."""
+import os
+
+import pytest
+import torch
+from torch._subclasses.fake_tensor import FakeTensorMode
+from torch.fx.experimental.proxy_tensor import make_fx
+
+
+def _trace_fake(fn, *shapes_dtypes):
+    with FakeTensorMode(allow_non_fake_inputs=True):
+        args = [torch.empty(s, dtype=d, device="blackwell") for s, d in shapes_dtypes]
+        return make_fx(fn)(*args)
+
+
+def test_pointwise_group_becomes_one_kernel(bw):
+    from torch_musa_b200.compile import lower
+
+    def f(x, y, w):
+        h = torch.nn.functional.silu(x) * y + w
+        z = torch.tanh(h) * 0.5 + (h > 0).to(h.dtype)
+        return z, z.sum(-1)
+
+    gm = _trace_fake(f, ((64, 256), torch.bfloat16), ((64, 256), torch.bfloat16), ((256,), torch.float32))
+    kernels = lower.partition_pointwise(gm)
+    assert len(kernels) == 1
+    info = next(iter(kernels.values()))
+    assert info["shape"] == (64, 256) and info["n_ops"] == 8 and info["vec"] == 8
+    assert "sigmoidf(x0)" in info["source"] and "tanhf" in info["source"]
+    targets = [n.target for n in gm.graph.nodes if n.op == "call_function"]
+    assert targets == [torch.ops.aten.sum.dim_IntList]          # everything element-wise left the outer graph
+    ok, why = bw._C._jit_available()
+    if not ok:
+        pytest.skip(why)
+    k = lower.get_kernel(info)                                  # compiled for sm_100a right here, without a GPU
+    assert len(k.cubin) > 1000 and k.entry == info["entry"]
+    desc = lower.describe_program(gm, kernels)
+    assert [i["kind"] for i in desc["instrs"]] == ["fused", "op"]
+    assert len(lower.instantiate(desc)) == 2
+
+
+def test_partitioner_rejects_groups_with_outputs_of_different_shapes(bw):
+    from torch_musa_b200.compile import lower
+
+    def f(x, s):
+        a = torch.exp(s) * 2.0           # [64, 1]
+        b = x * a + 1.0                  # [64, 256]
+        return a, b
+
+    gm = _trace_fake(f, ((64, 256), torch.float32), ((64, 1), torch.float32))
+    kernels = lower.partition_pointwise(gm)
+    for info in kernels.values():        # whatever was grouped has one output shape
+        assert len({tuple(info["shape"])}) == 1
+    out = [n for n in gm.graph.nodes if n.op == "output"][0]
+    assert len(out.args[0]) == 2
+
+
+def test_addmm_activation_pass(bw):
+    from torch_musa_b200.compile import lower
+
+    def f(b, x, w):
+        return torch.relu(torch.addmm(b, x, w))
+
+    gm = _trace_fake(f, ((32,), torch.bfloat16), ((8, 16), torch.bfloat16), ((16, 32), torch.bfloat16))
+    assert lower.fuse_addmm_activation(gm) == 1
+    targets = [n.target for n in gm.graph.nodes if n.op == "call_function"]
+    assert targets == [torch.ops.aten._addmm_activation.default]
+
+
+def test_native_runner_executes_cpu_graph(bw):
+    from torch_musa_b200.compile import lower
+
+    def f(x, w, b):
+        h = torch.addmm(b, x, w)
+        a, i = torch.topk(h, 3, dim=-1)
+        parts = torch.split(h, [2, 6], dim=1)
+        return torch.cat([parts[1], parts[0]], dim=1).relu(), a, i
+
+    x, w, b = torch.randn(4, 5), torch.randn(5, 8), torch.randn(8)
+    gm = make_fx(f)(x, w, b)
+    runner, desc = lower.lower(gm, fuse=False)
+    out = runner.run([x, w, b])
+    ref = f(x, w, b)
+    assert len(out) == 3
+    for o, r in zip(out, ref):
+        assert torch.equal(o, r)
+    assert runner.runs == 1 and runner.op_calls >= 5
+    # slots are released as soon as their last reader has run
+    assert any(i["free"] for i in desc["instrs"])
+
+
+def test_aot_package_roundtrip_on_cpu(bw, tmp_path):
+    from torch_musa_b200 import export
+
+    class M(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.l1 = torch.nn.Linear(16, 32)
+            self.l2 = torch.nn.Linear(32, 4)
+            self.register_buffer("calls", torch.zeros((), dtype=torch.long))
+
+        def forward(self, x, scale):
+            self.calls.add_(1)
+            return {"y": self.l2(torch.tanh(self.l1(x))) * scale, "n": self.calls + 0}
+
+    m = M().eval()
+    x = torch.randn(3, 16)
+    path = export.aot_compile(m, (x, 2.0), os.path.join(tmp_path, "m.b200pkg"))
+    ref = M().eval()
+    ref.load_state_dict(m.state_dict())
+    loaded = export.aot_load(path)
+    out = loaded(x, 2.0)
+    exp = ref(x, 2.0)
+    assert torch.allclose(out["y"], exp["y"], atol=1e-6) and int(out["n"]) == int(exp["n"])
+    out = loaded(x, 2.0)                 # the buffer update persisted inside the loaded model
+    assert int(out["n"]) == int(exp["n"]) + 1
+    with pytest.raises(TypeError):
+        loaded(x)

@@ -175,3 +175,51 @@ def _moe_ep_body(rank, world):
 def test_expert_parallel_moe_matches_single_process():
     """EP=2 MoE decoder with the sort + all_to_all exchange over gloo against the same model with all experts local."""
     run_ranks(_moe_ep_body, 2, "gloo")
+
+
+def _dtensor_tp_body(rank, world):
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch_musa_b200.models import Llama, llama_tiny_config
+    from torch_musa_b200.parallel.dtensor_tp import parallelize_llama
+
+    cfg = llama_tiny_config(fused_qkv=False, fused_gate_up=False, fused_loss=False)
+    torch.manual_seed(0)
+    full = Llama(cfg)
+    full.reset_parameters(seed=3)
+    tp = Llama(cfg)
+    tp.load_state_dict(full.state_dict())
+    mesh = init_device_mesh("cpu", (world,))
+    parallelize_llama(tp, mesh, loss_parallel=True)
+    torch.manual_seed(11)
+    toks = torch.randint(0, cfg.vocab_size, (2, 17))
+    loss_ref = full(toks[:, :-1], toks[:, 1:])
+    loss_ref.backward()
+    loss = tp(toks[:, :-1], toks[:, 1:])
+    loss.backward()
+    assert abs(float(loss) - float(loss_ref)) < 1e-4, (float(loss), float(loss_ref))
+    # column-parallel weight: this rank's rows of the full gradient; sequence-parallel norm: partial sums to reduce
+    g = tp.layers[0].attn.wq.weight.grad.to_local()
+    rows = g.shape[0]
+    assert torch.allclose(g, full.layers[0].attn.wq.weight.grad[rank * rows:(rank + 1) * rows], atol=1e-5)
+    g = tp.layers[0].ffn.w2.weight.grad.to_local()
+    cols = g.shape[1]
+    assert torch.allclose(g, full.layers[0].ffn.w2.weight.grad[:, rank * cols:(rank + 1) * cols], atol=1e-5)
+    gn = tp.layers[1].attn_norm.weight.grad.full_tensor()
+    assert torch.allclose(gn, full.layers[1].attn_norm.weight.grad, atol=1e-5)
+    ge = tp.tok_emb.weight.grad.full_tensor()
+    assert torch.allclose(ge, full.tok_emb.weight.grad, atol=1e-5)
+
+
+def test_dtensor_tensor_parallel_llama_matches_single_process():
+    """The DTensor plan (Colwise/Rowwise/SequenceParallel + vocabulary-parallel loss) at TP=2 over gloo."""
+    run_ranks(_dtensor_tp_body, 2, "gloo")
+
+
+def test_custom_op_sharding_rules_are_registered():
+    from torch_musa_b200.distributed import tensor_ops
+    from torch.distributed.tensor import DTensor
+
+    tensor_ops.register()
+    table = DTensor._op_dispatcher.sharding_propagator.op_strategy_funcs
+    for name in ("silu_mul", "swiglu", "rope", "rms_norm_residual", "cross_entropy_fwd"):
+        assert getattr(torch.ops.blackwell, name).default in table, name

@@ -1,4 +1,4 @@
-"""Collectives of the bccl backend on real GPUs (2 ranks): closed-form expected values for every
+"""Collectives of the bccl backend on real GPUs (2, 4 and 8 ranks, as many as the box has): closed-form expected values for every
 collective (reference tests/unittest/distributed/test_dist.py:29-300), the peer-memory kernels
 against NCCL, DDP and FSDP2 training parity, the watchdog."""
 import pytest
@@ -7,6 +7,15 @@ import torch
 from _dist_utils import run_ranks
 
 pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+WORLDS = [2, 4, 8]
+
+
+def _need(world):
+    import torch_musa_b200 as bw
+
+    if bw.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
 
 
 def _collectives_body(rank, world):
@@ -68,8 +77,10 @@ def _collectives_body(rank, world):
     assert "all_gather_into_tensor" in bw._C._pg_dump_flight_recorder(pg)
 
 
-def test_collectives_closed_form():
-    run_ranks(_collectives_body, 2, "bccl")
+@pytest.mark.parametrize("world", WORLDS)
+def test_collectives_closed_form(world):
+    _need(world)
+    run_ranks(_collectives_body, world, "bccl")
 
 
 def _fused_vs_nccl_body(rank, world):
@@ -115,8 +126,10 @@ def _fused_vs_nccl_body(rank, world):
     bw.synchronize()
 
 
-def test_peer_memory_kernels_match_nccl():
-    run_ranks(_fused_vs_nccl_body, 2, "bccl", env={"NCCL_NVLS_ENABLE": "0"})
+@pytest.mark.parametrize("world", WORLDS)
+def test_peer_memory_kernels_match_nccl(world):
+    _need(world)
+    run_ranks(_fused_vs_nccl_body, world, "bccl", env={"NCCL_NVLS_ENABLE": "0"})
 
 
 def _ddp_body(rank, world):
@@ -141,8 +154,10 @@ def _ddp_body(rank, world):
     bw.synchronize()
 
 
-def test_ddp_matches_single_process():
-    run_ranks(_ddp_body, 2, "bccl")
+@pytest.mark.parametrize("world", WORLDS)
+def test_ddp_matches_single_process(world):
+    _need(world)
+    run_ranks(_ddp_body, world, "bccl")
 
 
 def _fsdp_body(rank, world):
@@ -190,8 +205,10 @@ def _fsdp_body(rank, world):
     bw.synchronize()
 
 
-def test_fsdp2_tracks_single_process_reference():
-    run_ranks(_fsdp_body, 2, "bccl")
+@pytest.mark.parametrize("world", WORLDS)
+def test_fsdp2_tracks_single_process_reference(world):
+    _need(world)
+    run_ranks(_fsdp_body, world, "bccl")
 
 
 def _watchdog_body(rank, world):
@@ -211,8 +228,10 @@ def _watchdog_body(rank, world):
     assert bw._C._pg_error(pg) != 0
 
 
-def test_watchdog_reports_timeout():
-    run_ranks(_watchdog_body, 2, "bccl")
+@pytest.mark.parametrize("world", WORLDS)
+def test_watchdog_reports_timeout(world):
+    _need(world)
+    run_ranks(_watchdog_body, world, "bccl")
 
 
 def _fused_ag_matmul_body(rank, world):
@@ -258,8 +277,10 @@ def _fused_ag_matmul_body(rank, world):
     ctx.check()
 
 
-def test_fused_allgather_gemm_matches_unfused():
-    run_ranks(_fused_ag_matmul_body, 2, "bccl", env={"NCCL_NVLS_ENABLE": "0"})
+@pytest.mark.parametrize("world", WORLDS)
+def test_fused_allgather_gemm_matches_unfused(world):
+    _need(world)
+    run_ranks(_fused_ag_matmul_body, world, "bccl", env={"NCCL_NVLS_ENABLE": "0"})
 
 
 def _fused_matmul_rs_body(rank, world):
@@ -300,8 +321,10 @@ def _fused_matmul_rs_body(rank, world):
     ctx.check()
 
 
-def test_fused_gemm_reduce_scatter_matches_unfused():
-    run_ranks(_fused_matmul_rs_body, 2, "bccl", env={"NCCL_NVLS_ENABLE": "0"})
+@pytest.mark.parametrize("world", WORLDS)
+def test_fused_gemm_reduce_scatter_matches_unfused(world):
+    _need(world)
+    run_ranks(_fused_matmul_rs_body, world, "bccl", env={"NCCL_NVLS_ENABLE": "0"})
 
 
 def _sharded_adamw_body(rank, world):
@@ -332,8 +355,10 @@ def _sharded_adamw_body(rank, world):
     assert all(torch.isfinite(a).all() for a in results[0])
 
 
-def test_fused_reduce_scatter_adamw_matches_unfused():
-    run_ranks(_sharded_adamw_body, 2, "bccl", env={"NCCL_NVLS_ENABLE": "0"})
+@pytest.mark.parametrize("world", WORLDS)
+def test_fused_reduce_scatter_adamw_matches_unfused(world):
+    _need(world)
+    run_ranks(_sharded_adamw_body, world, "bccl", env={"NCCL_NVLS_ENABLE": "0"})
 
 
 def _remote_error_body(rank, world):
@@ -356,5 +381,53 @@ def _remote_error_body(rank, world):
     assert bw._C._pg_error(pg) != 0, f"rank {rank} never learned of the failure"
 
 
-def test_failure_on_one_rank_is_propagated_through_the_store():
-    run_ranks(_remote_error_body, 2, "bccl", env={"NCCL_NVLS_ENABLE": "0"})
+@pytest.mark.parametrize("world", WORLDS)
+def test_failure_on_one_rank_is_propagated_through_the_store(world):
+    _need(world)
+    run_ranks(_remote_error_body, world, "bccl", env={"NCCL_NVLS_ENABLE": "0"})
+
+
+def _dtensor_tp_body(rank, world):
+    import torch.distributed as dist
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor import DTensor, Shard, distribute_tensor
+    import torch_musa_b200 as bw
+    from torch_musa_b200.models import Llama, llama_tiny_config
+    from torch_musa_b200.ops import functional as BF
+    from torch_musa_b200.parallel.dtensor_tp import parallelize_llama
+
+    dev = torch.device("blackwell", rank)
+    mesh = init_device_mesh("blackwell", (world,))
+    cfg = llama_tiny_config(fused_qkv=False, fused_gate_up=False, n_heads=8, n_kv_heads=8, vocab_size=512)
+    torch.manual_seed(0)
+    full = Llama(cfg)
+    full.reset_parameters(seed=3)
+    tp = Llama(cfg)
+    tp.load_state_dict(full.state_dict())
+    tp = tp.to(dev).to(torch.bfloat16)
+    full = full.to(torch.bfloat16)
+    parallelize_llama(tp, mesh, loss_parallel=True)
+    torch.manual_seed(11)
+    toks = torch.randint(0, cfg.vocab_size, (2, 33))
+    loss_ref = full(toks[:, :-1], toks[:, 1:])
+    loss_ref.backward()
+    loss = tp(toks[:, :-1].to(dev), toks[:, 1:].to(dev))
+    loss.backward()
+    assert abs(float(loss) - float(loss_ref)) < 5e-2, (float(loss), float(loss_ref))
+    g = tp.layers[0].attn.wq.weight.grad.to_local().float().cpu()
+    rows = g.shape[0]
+    ref = full.layers[0].attn.wq.weight.grad[rank * rows:(rank + 1) * rows].float()
+    assert (g - ref).abs().max() <= 0.05 * ref.abs().max() + 1e-3
+    # a custom kernel called on DTensors: the registered rule keeps the shards where they are
+    a = distribute_tensor(torch.randn(4, 16, 64).to(torch.bfloat16).to(dev), mesh, [Shard(1)])
+    b = distribute_tensor(torch.randn(4, 16, 64).to(torch.bfloat16).to(dev), mesh, [Shard(1)])
+    out = torch.ops.blackwell.silu_mul(a, b)
+    assert isinstance(out, DTensor) and out.placements == (Shard(1),)
+    ref = torch.nn.functional.silu(a.full_tensor().float()) * b.full_tensor().float()
+    assert (out.full_tensor().float() - ref).abs().max() < 0.1
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_dtensor_tensor_parallel_on_device(world):
+    _need(world)
+    run_ranks(_dtensor_tp_body, world, "bccl")

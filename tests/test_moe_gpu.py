@@ -67,19 +67,23 @@ def test_moe_model_step_matches_reference(bw, dev):
     assert abs(l1 - l2) < 2e-2 and abs(a1 - a2) / max(a2, 1e-6) < 5e-2 and abs(b1 - b2) / max(b2, 1e-6) < 0.1
 
 
-def _two_rank_body(rank, world):
+def _multi_rank_body(rank, world):
     import torch_musa_b200 as bw
     from torch_musa_b200.parallel.moe import FusedExpertExchange, ReferenceExpertExchange
 
     dev = torch.device("blackwell", rank)
-    fused = FusedExpertExchange(4, 64, cap_rows=4 * 96, slots=1, device=dev)
-    _roundtrip(dev, fused, ReferenceExpertExchange(4), seed=rank)
-    _roundtrip(dev, fused, ReferenceExpertExchange(4), T=64 + 32 * rank, seed=10 + rank)   # uneven token counts
+    E = 8                                       # divisible by every world size tested
+    fused = FusedExpertExchange(E, 64, cap_rows=world * 2 * 96, slots=1, device=dev)
+    _roundtrip(dev, fused, ReferenceExpertExchange(E), E=E, seed=rank)
+    _roundtrip(dev, fused, ReferenceExpertExchange(E), E=E, T=64 + 8 * rank, seed=10 + rank)   # uneven token counts
     bw.synchronize()
     fused.check()
 
 
 @pytest.mark.multigpu
-def test_fused_exchange_two_gpus():
-    # plain peer loads/stores only (no NVLS) so that a failing rank cannot disturb its peer's GPU
-    run_ranks(_two_rank_body, 2, "bccl", env={"NCCL_NVLS_ENABLE": "0"})
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_fused_exchange_multi_gpu(bw, world):
+    if bw.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    # plain peer loads/stores only (no NVLS) so that a failing rank cannot disturb its peers' GPUs
+    run_ranks(_multi_rank_body, world, "bccl", env={"NCCL_NVLS_ENABLE": "0"})

@@ -87,3 +87,7 @@ def install() -> None:
     from .compile_backend import register as _register_backend
 
     _register_backend()
+
+    from .compile.backend import register as _register_compiler
+
+    _register_compiler()

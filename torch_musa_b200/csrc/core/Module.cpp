@@ -28,6 +28,7 @@ using namespace b200;
 namespace b200 {
 void init_distributed_bindings(py::module& m);
 void init_storage_sharing_bindings(py::module& m);
+void init_compile_bindings(py::module& m);
 }
 
 namespace {
@@ -595,4 +596,5 @@ PYBIND11_MODULE(_C, m) {
 
   b200::init_distributed_bindings(m);
   b200::init_storage_sharing_bindings(m);
+  b200::init_compile_bindings(m);
 }

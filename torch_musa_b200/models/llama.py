@@ -2,7 +2,8 @@
 
 The module uses only public torch APIs plus ``torch_musa_b200.ops``; on the blackwell device every
 hot operator resolves to a hand-written sm_100a kernel (tcgen05 GEMMs with the bias/activation
-epilogue, fused RMSNorm / RoPE / SwiGLU / cross-entropy), on any other device to plain PyTorch.
+epilogue, tcgen05 flash attention forward and backward, fused RMSNorm / RoPE / SwiGLU /
+cross-entropy), on any other device to plain PyTorch.
 """
 from __future__ import annotations
 
@@ -83,14 +84,15 @@ class Attention(nn.Module):
             # split (not slicing): its backward is one concatenation instead of three zero-fill + add passes
             q, k, v = self.wqkv(x).view(B, S, h + 2 * kv, hd).split([h, kv, kv], dim=2)
         else:
-            q = self.wq(x).view(B, S, h, hd)
-            k = self.wk(x).view(B, S, kv, hd)
-            v = self.wv(x).view(B, S, kv, hd)
+            # -1: under tensor parallelism each rank holds a slice of the heads
+            q = self.wq(x).view(B, S, -1, hd)
+            k = self.wk(x).view(B, S, -1, hd)
+            v = self.wv(x).view(B, S, -1, hd)
         q = BF.rope(q, cos, sin, positions)
         k = BF.rope(k, cos, sin, positions)
         o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True,
                                            enable_gqa=(kv != h))
-        return self.wo(o.transpose(1, 2).reshape(B, S, h * hd))
+        return self.wo(o.transpose(1, 2).reshape(B, S, -1))
 
 
 class FeedForward(nn.Module):
@@ -177,6 +179,8 @@ class Llama(nn.Module):
         logits = self.lm_head(x)
         if targets is None:
             return logits
+        if getattr(self, "loss_fn", None) is not None:  # e.g. the vocabulary-parallel loss of a tensor-parallel plan
+            return self.loss_fn(logits.view(B * S, -1), targets.reshape(-1))
         if self.cfg.fused_loss:
             return BF.fused_cross_entropy(logits.view(B * S, -1), targets.reshape(-1), inplace_backward=True)
         return F.cross_entropy(logits.view(B * S, -1).float(), targets.reshape(-1))
