@@ -46,7 +46,8 @@ class GraphNode:
 
     @staticmethod
     def _use_counts(outputs) -> List[int]:
-        return [t.untyped_storage()._use_count() if isinstance(t, torch.Tensor) else 0 for t in outputs]
+        count = _bw()._C._storage_use_count
+        return [count(t) if isinstance(t, torch.Tensor) else 0 for t in outputs]
 
     def path_outputs_alive(self) -> bool:
         """Does anything outside the tree still reference memory that this path handed out?  (Reference counts of the
@@ -70,7 +71,7 @@ class GraphNode:
 
 
 class GraphTreeManager:
-    """One per device and thread.  ``run(fn_id, fn, args, clone_outputs)`` is the only entry point."""
+    """One per device.  ``run(fn_id, fn, args, clone_outputs)`` is the only entry point; calls are serialised."""
 
     def __init__(self, device_index: int, warmup: int = 1, max_recordings: int = 16):
         self.device_index = device_index
@@ -82,6 +83,7 @@ class GraphTreeManager:
         self.seen: Dict[tuple, int] = {}
         self.recordings: Dict[int, int] = {}
         self.stats = {"warmup_runs": 0, "recorded": 0, "replayed": 0, "eager_runs": 0}
+        self._lock = threading.RLock()
 
     # ------------------------------------------------------------- keys
     @staticmethod
@@ -106,6 +108,10 @@ class GraphTreeManager:
     # -------------------------------------------------------------- run
     def run(self, fn_id: int, fn: Callable[[List[object]], List[object]], args: List[object],
             clone_outputs: bool = False) -> List[object]:
+        with self._lock:
+            return self._run(fn_id, fn, args, clone_outputs)
+
+    def _run(self, fn_id, fn, args, clone_outputs):
         bw = _bw()
         if bw.is_current_stream_capturing() or not any(
                 isinstance(a, torch.Tensor) and a.device.type == "blackwell" for a in args):
@@ -192,22 +198,24 @@ class GraphTreeManager:
         return sum(count(r) for r in self.roots.values())
 
 
-_tls = threading.local()
+# One manager per device for the whole process: the backward of a compiled function runs on the autograd
+# engine's device thread, and it has to find the tree its forward recorded from the caller's thread.
+_managers: Dict[int, GraphTreeManager] = {}
+_managers_lock = threading.Lock()
 
 
 def get_manager(device_index: int) -> GraphTreeManager:
-    table = getattr(_tls, "managers", None)
-    if table is None:
-        table = _tls.managers = {}
-    m = table.get(device_index)
-    if m is None:
-        m = table[device_index] = GraphTreeManager(device_index)
-    return m
+    with _managers_lock:
+        m = _managers.get(device_index)
+        if m is None:
+            m = _managers[device_index] = GraphTreeManager(device_index)
+        return m
 
 
 def reset() -> None:
-    """Forget every recorded graph of this thread (their pool memory returns to the allocator)."""
-    _tls.managers = {}
+    """Forget every recorded graph (their pool memory returns to the allocator)."""
+    with _managers_lock:
+        _managers.clear()
 
 
 def new_function_id() -> int:

@@ -285,6 +285,10 @@ class GraphRunner {
 }  // namespace
 
 void init_compile_bindings(py::module& m) {
+  m.def("_storage_use_count", [](const at::Tensor& t) {
+    // how many tensors / storages objects reference this memory (graph trees decide liveness from it)
+    return (int64_t)t.storage().use_count();
+  });
   m.def("_jit_available", [] {
     std::string why;
     bool ok = jit::compiler_available(&why);
