@@ -1,5 +1,5 @@
-"""Convolution routing (1x1 on the tcgen05 GEMM, the rest on library kernels) and the hand-written
-channels-last batch-norm kernels, against fp32 CPU references."""
+"""Convolution (1x1 on the tcgen05 GEMM, other filters on the implicit-GEMM tcgen05 kernels, the rest on library
+kernels) and the hand-written channels-last batch-norm / pooling kernels, against fp32 CPU references."""
 import pytest
 import torch
 import torch.nn.functional as F
@@ -49,6 +49,63 @@ def test_general_conv(bw, dev, k, stride, pad, groups):
     y.sum().backward()
     assert rel_err(y, yr) < 3e-2 and rel_err(xd.grad, xr.grad) < 3e-2
     assert rel_err(wd.grad, wr.grad) < 3e-2 and rel_err(bd.grad, br.grad) < 3e-2
+
+
+# (N, Cin, H, W, Cout, R, S, stride, pad): ResNet-50's filter shapes on small images, plus ragged edge cases
+IMPLICIT_CASES = [
+    (4, 64, 14, 14, 64, 3, 3, 1, 1),
+    (2, 128, 28, 28, 128, 3, 3, 2, 1),
+    (3, 256, 14, 14, 512, 1, 1, 2, 0),
+    (2, 3, 32, 32, 64, 7, 7, 2, 3),       # RGB stem: channels padded to 8
+    (5, 72, 9, 11, 40, 3, 3, 1, 1),       # nothing a multiple of the tile sizes
+    (2, 64, 13, 13, 136, 3, 3, 2, 1),     # odd extent with stride 2, ragged output channels
+    (1, 16, 8, 8, 16, 5, 3, 1, 2),        # asymmetric filter, padding wider than the filter needs
+    (2, 192, 7, 7, 192, 3, 3, 1, 1),
+]
+
+
+@pytest.mark.parametrize("case", IMPLICIT_CASES)
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_implicit_gemm_conv(bw, dev, case, dt):
+    N, C, H, W, K, R, S, stride, pad = case
+    torch.manual_seed(0)
+    x = torch.randn(N, C, H, W).to(dt)
+    w = (torch.randn(K, C, R, S) * (1.0 / (C * R * S) ** 0.5)).to(dt)
+    b = torch.randn(K).to(dt)
+    xr, wr, br = x.float().requires_grad_(), w.float().requires_grad_(), b.float().requires_grad_()
+    yr = F.conv2d(xr, wr, br, stride, pad)
+    g = torch.randn_like(yr).to(dt)
+    yr.backward(g.float())
+    xd = x.to(dev).contiguous(memory_format=torch.channels_last).requires_grad_()
+    wd = w.to(dev).contiguous(memory_format=torch.channels_last).requires_grad_()
+    bd = b.to(dev).requires_grad_()
+    hits = bw._C._implicit_conv_hits()
+    bw.reset_fallback_counts()
+    y = F.conv2d(xd, wd, bd, stride, pad)
+    y.backward(g.to(dev).contiguous(memory_format=torch.channels_last))
+    bw.synchronize()
+    assert bw._C._implicit_conv_hits() == hits + 2 and bw._C._conv_status(True) == 0
+    assert not any("conv" in k for k in bw.fallback_counts()), bw.fallback_counts()
+    assert y.shape == yr.shape and y.is_contiguous(memory_format=torch.channels_last)
+    tol = 2e-2 if dt == torch.bfloat16 else 4e-3
+    assert rel_err(y, yr) < tol
+    assert rel_err(xd.grad, xr.grad) < tol
+    assert rel_err(wd.grad, wr.grad) < tol
+    assert rel_err(bd.grad, br.grad) < tol
+
+
+def test_implicit_gemm_conv_standard_layout_inputs(bw, dev):
+    """NCHW-contiguous activations and filters are converted on the way in; gradients come back in the callers' layouts."""
+    x = torch.randn(2, 32, 10, 10).to(torch.bfloat16)
+    w = (torch.randn(48, 32, 3, 3) * 0.06).to(torch.bfloat16)
+    xr, wr = x.float().requires_grad_(), w.float().requires_grad_()
+    yr = F.conv2d(xr, wr, None, 1, 1)
+    yr.square().sum().backward()
+    xd, wd = x.to(dev).requires_grad_(), w.to(dev).requires_grad_()
+    y = F.conv2d(xd, wd, None, 1, 1)
+    y.float().square().sum().backward()
+    assert wd.grad.is_contiguous() and wd.grad.shape == w.shape
+    assert rel_err(y, yr) < 2e-2 and rel_err(xd.grad, xr.grad) < 3e-2 and rel_err(wd.grad, wr.grad) < 3e-2
 
 
 @pytest.mark.parametrize("shape", [(8, 64, 14, 14), (4, 256, 7, 7), (3, 8, 5, 5), (64, 128)])

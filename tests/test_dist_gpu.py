@@ -240,7 +240,7 @@ def _fused_ag_matmul_body(rank, world):
     from torch_musa_b200.parallel.fused_tp import FusedTensorParallel
 
     dev = torch.device("blackwell", rank)
-    ctx = FusedTensorParallel(max_shard_bytes=1024 * 1024 * 2, max_rows=4096, device=dev, copier_pairs=4)
+    ctx = FusedTensorParallel(max_shard_bytes=1024 * 1024 * 2, max_rows=2048 * world, device=dev, copier_pairs=4)
     for rows, K, N in [(256, 512, 384), (512, 1024, 512), (1024, 256, 136)]:
         torch.manual_seed(100 + rank)
         x = (torch.randn(rows, K) * 0.5).to(torch.bfloat16).to(dev)
@@ -289,9 +289,10 @@ def _fused_matmul_rs_body(rank, world):
     from torch_musa_b200.parallel.fused_tp import FusedTensorParallel
 
     dev = torch.device("blackwell", rank)
-    ctx = FusedTensorParallel(max_shard_bytes=1 << 21, max_rows=4096, device=dev, copier_pairs=4,
-                              max_partial_bytes=2048 * 1024 * 2, reducer_pairs=4)
-    for M, K, N in [(512, 256, 256), (1024, 520, 512), (2048, 136, 1024), (512, 256, 256)]:
+    sc = world // 2                       # row counts must divide by 256 x world
+    ctx = FusedTensorParallel(max_shard_bytes=1 << 21, max_rows=4096 * sc, device=dev, copier_pairs=4,
+                              max_partial_bytes=2048 * 1024 * 2 * sc, reducer_pairs=4)
+    for M, K, N in [(512 * sc, 256, 256), (1024 * sc, 520, 512), (2048 * sc, 136, 1024), (512 * sc, 256, 256)]:
         torch.manual_seed(200 + rank)
         x = (torch.randn(M, K) * 0.5).to(torch.bfloat16).to(dev)
         w = (torch.randn(N, K) * 0.1).to(torch.bfloat16).to(dev)
@@ -303,7 +304,7 @@ def _fused_matmul_rs_body(rank, world):
             assert err < 3e-2, (M, K, N, float(err))
     ctx.install()
     try:
-        x = (torch.randn(512, 256) * 0.5).to(torch.bfloat16).to(dev).requires_grad_()
+        x = (torch.randn(512 * sc, 256) * 0.5).to(torch.bfloat16).to(dev).requires_grad_()
         w = (torch.randn(256, 256) * 0.1).to(torch.bfloat16).to(dev).requires_grad_()
         y = TP.matmul_rs(x, w)
         y.float().pow(2).sum().backward()

@@ -6,7 +6,12 @@
 //     plain matrix products over the [N*H*W, C] view of the activation: forward, data-gradient and
 //     weight-gradient each run as ONE launch of the tcgen05 GEMM with no copy or transpose (the GEMM takes
 //     K-major and MN-major operands straight from the strides).  That is 36 of ResNet-50's 53 convolutions.
-//   * everything else runs the library convolution on the same memory through the CUDA-alias bridge.
+//   * every other 2-D convolution of 16-bit tensors with stride 1 or 2, no dilation and groups 1 (3x3, 7x7, strided
+//     1x1 ...) runs the implicit-GEMM tcgen05 kernels of kernels/conv_tcgen05.cu: forward, data gradient and weight
+//     gradient read the channels-last activation through shifted TMA boxes, no im2col buffer is built.  A filter
+//     with fewer than 8 input channels (the RGB stem) is zero-padded to 8 channels first.
+//   * what is left (dilation, groups, 1-D/3-D, fp32) runs the library convolution on the same memory through the
+//     CUDA-alias bridge.
 // Parity: reference torch_musa/csrc/aten/ops/Convolution.cpp (vendor-library convolution fwd/dgrad/wgrad).
 #include "aten/FallbackCall.h"
 #include "aten/Ops.h"
@@ -23,6 +28,8 @@ namespace {
 
 std::atomic<bool> g_pointwise_gemm{true};
 std::atomic<int64_t> g_pointwise_hits{0};
+std::atomic<bool> g_implicit_gemm{true};
+std::atomic<int64_t> g_implicit_hits{0};
 
 bool all_eq(at::IntArrayRef v, int64_t x) {
   for (auto e : v)
@@ -63,6 +70,87 @@ at::Tensor nhwc_from_matrix(const at::Tensor& m, int64_t N, int64_t H, int64_t W
   return m.as_strided({N, C, H, W}, {H * W * C, 1, W * C, C});
 }
 
+// ---------------------------------------------------------------- implicit GEMM route
+bool implicit_eligible(const at::Tensor& input, const at::Tensor& weight, at::IntArrayRef stride,
+                       at::IntArrayRef padding, at::IntArrayRef dilation, bool transposed, int64_t groups) {
+  if (!g_implicit_gemm.load(std::memory_order_relaxed)) return false;
+  if (transposed || groups != 1 || input.dim() != 4 || weight.dim() != 4) return false;
+  if (stride.size() != 2 || padding.size() != 2 || !all_eq(dilation, 1)) return false;
+  const auto dt = input.scalar_type();
+  if ((dt != at::kBFloat16 && dt != at::kHalf) || weight.scalar_type() != dt) return false;
+  if (stride[0] < 1 || stride[0] > 2 || stride[1] < 1 || stride[1] > 2) return false;
+  if (weight.size(2) * weight.size(3) > 49 || weight.size(0) % 8 != 0 || input.numel() == 0) return false;
+  if (input.size(1) != weight.size(1)) return false;
+  if (input.size(1) % 8 != 0 && input.size(1) > 8) return false;
+  return true;
+}
+
+b200_conv_t conv_desc(const at::Tensor& x, const at::Tensor& w, at::IntArrayRef stride, at::IntArrayRef padding) {
+  b200_conv_t d{};
+  d.N = x.size(0), d.C = x.size(1), d.H = x.size(2), d.W = x.size(3);
+  d.K = w.size(0), d.R = (int)w.size(2), d.S = (int)w.size(3);
+  d.sh = (int)stride[0], d.sw = (int)stride[1], d.ph = (int)padding[0], d.pw = (int)padding[1];
+  d.Ho = (d.H + 2 * d.ph - d.R) / d.sh + 1;
+  d.Wo = (d.W + 2 * d.pw - d.S) / d.sw + 1;
+  d.dtype = kdtype(x.scalar_type());
+  return d;
+}
+
+// Channels-last dense tensor with the channel dimension zero-padded up to a multiple of 8.
+at::Tensor nhwc_padded(const at::Tensor& t) {
+  const int64_t C = t.size(1), Cp = (C + 7) / 8 * 8;
+  if (Cp == C) return t.contiguous(at::MemoryFormat::ChannelsLast);
+  // (at::zeros drops the memory format of its options)
+  at::Tensor out = at::empty({t.size(0), Cp, t.size(2), t.size(3)}, t.options().memory_format(at::MemoryFormat::ChannelsLast));
+  out.zero_();
+  out.narrow(1, 0, C).copy_(t);
+  return out;
+}
+
+at::Tensor implicit_forward(const at::Tensor& input, const at::Tensor& weight, const std::optional<at::Tensor>& bias,
+                            at::IntArrayRef stride, at::IntArrayRef padding) {
+  const at::Tensor x = nhwc_padded(input);
+  const at::Tensor w = nhwc_padded(weight);
+  b200_conv_t d = conv_desc(x, w, stride, padding);
+  TORCH_CHECK(d.Ho > 0 && d.Wo > 0, "convolution: the filter does not fit the padded input");
+  at::Tensor y = at::empty({d.N, d.K, d.Ho, d.Wo}, x.options().memory_format(at::MemoryFormat::ChannelsLast));
+  at::Tensor b;
+  if (bias.has_value() && bias->defined()) b = bias->to(x.scalar_type()).contiguous();
+  auto stream = current_raw_stream(x);
+  B200_KERNEL_CALL(b200_conv_fwd(&d, y.data_ptr(), x.const_data_ptr(), w.const_data_ptr(),
+                                 b.defined() ? b.const_data_ptr() : nullptr, 0, stream));
+  g_implicit_hits.fetch_add(1, std::memory_order_relaxed);
+  return y;
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor> implicit_backward(const at::Tensor& grad_output, const at::Tensor& input,
+                                                                 const at::Tensor& weight, at::IntArrayRef stride,
+                                                                 at::IntArrayRef padding, std::array<bool, 3> mask) {
+  const at::Tensor x = nhwc_padded(input);
+  const at::Tensor w = nhwc_padded(weight);
+  const at::Tensor gy = grad_output.contiguous(at::MemoryFormat::ChannelsLast);
+  b200_conv_t d = conv_desc(x, w, stride, padding);
+  auto stream = current_raw_stream(x);
+  const int64_t C = input.size(1);
+  at::Tensor gx, gw, gb;
+  if (mask[0]) {
+    gx = at::empty(x.sizes(), x.options().memory_format(at::MemoryFormat::ChannelsLast));
+    B200_KERNEL_CALL(b200_conv_dgrad(&d, gx.data_ptr(), gy.const_data_ptr(), w.const_data_ptr(), stream));
+    if (x.size(1) != C) gx = gx.narrow(1, 0, C).contiguous(at::MemoryFormat::ChannelsLast);
+  }
+  if (mask[1]) {
+    at::Tensor acc = at::zeros({d.K, d.R, d.S, d.C}, x.options().dtype(at::kFloat));
+    B200_KERNEL_CALL(b200_conv_wgrad(&d, acc.data_ptr<float>(), gy.const_data_ptr(), x.const_data_ptr(), stream));
+    gw = acc.to(weight.scalar_type()).permute({0, 3, 1, 2});  // [K, C, R, S] with channels-last strides
+    if (x.size(1) != C) gw = gw.narrow(1, 0, C);
+    const bool cl = weight.is_contiguous(at::MemoryFormat::ChannelsLast) && !weight.is_contiguous();
+    gw = gw.contiguous(cl ? at::MemoryFormat::ChannelsLast : at::MemoryFormat::Contiguous);
+  }
+  if (mask[2]) gb = gy.sum({0, 2, 3});
+  g_implicit_hits.fetch_add(1, std::memory_order_relaxed);
+  return {gx, gw, gb};
+}
+
 at::Tensor convolution_overrideable(const at::Tensor& input, const at::Tensor& weight,
                                     const std::optional<at::Tensor>& bias, at::IntArrayRef stride,
                                     at::IntArrayRef padding, at::IntArrayRef dilation, bool transposed,
@@ -74,6 +162,8 @@ at::Tensor convolution_overrideable(const at::Tensor& input, const at::Tensor& w
     at::Tensor y = (bias.has_value() && bias->defined()) ? at::addmm(*bias, x, w.t()) : at::mm(x, w.t());
     return nhwc_from_matrix(y, input.size(0), input.size(2), input.size(3));
   }
+  if (implicit_eligible(input, weight, stride, padding, dilation, transposed, groups))
+    return implicit_forward(input, weight, bias, stride, padding);
   return fallback_tensor(B200_OP_HANDLE("aten::convolution", ""), input, weight, bias, stride, padding, dilation,
                          transposed, output_padding, groups);
 }
@@ -99,6 +189,9 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> convolution_backward_overrideable
     g_pointwise_hits.fetch_add(1, std::memory_order_relaxed);
     return {gx, gw, gb};
   }
+  if (implicit_eligible(input, weight, stride, padding, dilation, transposed, groups) &&
+      grad_output.scalar_type() == input.scalar_type())
+    return implicit_backward(grad_output, input, weight, stride, padding, output_mask);
   std::optional<std::vector<int64_t>> bias_sizes;
   if (output_mask[2]) bias_sizes = std::vector<int64_t>{weight.size(transposed ? 1 : 0) * (transposed ? groups : 1)};
   c10::List<bool> mask;
@@ -116,6 +209,8 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> convolution_backward_overrideable
 
 void set_pointwise_conv_gemm(bool on) { g_pointwise_gemm.store(on); }
 int64_t pointwise_conv_hits() { return g_pointwise_hits.load(); }
+void set_implicit_conv_gemm(bool on) { g_implicit_gemm.store(on); }
+int64_t implicit_conv_hits() { return g_implicit_hits.load(); }
 
 TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
   m.impl("convolution_overrideable", TORCH_FN(convolution_overrideable));

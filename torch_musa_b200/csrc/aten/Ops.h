@@ -68,6 +68,8 @@ B200_EXPORT int64_t native_sdp_backward_calls();
 // 1x1 convolutions as GEMMs over the channels-last matrix view (off: every convolution uses the library route).
 B200_EXPORT void set_pointwise_conv_gemm(bool on);
 B200_EXPORT int64_t pointwise_conv_hits();
+B200_EXPORT void set_implicit_conv_gemm(bool on);
+B200_EXPORT int64_t implicit_conv_hits();
 
 // Counter of hand-written kernel launches (reported by the benchmark as its own-kernel launch count).
 B200_EXPORT void count_launch(int n = 1);

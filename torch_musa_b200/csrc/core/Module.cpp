@@ -212,6 +212,9 @@ PYBIND11_MODULE(_C, m) {
   m.def("_gemm_status", [](bool clear) { return b200_gemm_status(clear ? 1 : 0); }, py::arg("clear") = false);
   m.def("_set_pointwise_conv_gemm", [](bool on) { ops::set_pointwise_conv_gemm(on); });
   m.def("_pointwise_conv_hits", [] { return ops::pointwise_conv_hits(); });
+  m.def("_set_implicit_conv_gemm", [](bool on) { ops::set_implicit_conv_gemm(on); });
+  m.def("_implicit_conv_hits", [] { return ops::implicit_conv_hits(); });
+  m.def("_conv_status", [](bool clear) { return b200_conv_status(clear ? 1 : 0); });
   m.def("_gemm_force_config", [](int c) { return b200_gemm_force_config(c); });
   m.def("_set_tensor_core_gemm", [](bool on) { ops::set_tensor_core_gemm(on); });
   m.def("_set_fused_sdp", [](bool on) { ops::set_fused_sdp(on); });

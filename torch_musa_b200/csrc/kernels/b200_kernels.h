@@ -151,6 +151,22 @@ B200_API int b200_maxpool2d_bwd(const b200_pool_t* p, int dtype, void* gin, cons
 B200_API int b200_avgpool2d_fwd(const b200_pool_t* p, int dtype, void* out, const void* in, int divisor, cudaStream_t stream);
 B200_API int b200_avgpool2d_bwd(const b200_pool_t* p, int dtype, void* gin, const void* gout, int divisor, cudaStream_t stream);
 
+/* ---- implicit-GEMM convolution on the tensor cores (kernels/conv_tcgen05.cu): NHWC activations x[N,H,W,C],
+ * y[N,Ho,Wo,K], filters w[K,R,S,C] (a channels-last [K,C,R,S] tensor), 16-bit dtypes, stride 1 or 2, zero padding,
+ * no dilation, groups 1, C and K multiples of 8.  wgrad adds into dw_f32[K,R,S,C] (fp32, zeroed by the caller). */
+typedef struct {
+  int64_t N, H, W, C, K, Ho, Wo;
+  int R, S, sh, sw, ph, pw;
+  int dtype;
+} b200_conv_t;
+B200_API int b200_conv_supported(const b200_conv_t* d);
+B200_API int b200_conv_fwd(const b200_conv_t* d, void* y, const void* x, const void* w, const void* bias /*or NULL*/,
+                           int relu, cudaStream_t stream);
+B200_API int b200_conv_dgrad(const b200_conv_t* d, void* dx, const void* dy, const void* w, cudaStream_t stream);
+B200_API int b200_conv_wgrad(const b200_conv_t* d, float* dw_f32, const void* dy, const void* x, cudaStream_t stream);
+/* 1 if a conv kernel gave up a bounded wait since the last clear */
+B200_API int b200_conv_status(int clear);
+
 /* ---------------------------------------------------------------- normalisation */
 /* y = x * rstd * w ; rstd[rows] fp32.  residual (optional): x_in = x + residual, written to res_out. */
 B200_API int b200_rmsnorm_fwd(int dtype, void* y, float* rstd, const void* x, const void* w, const void* residual,
