@@ -107,8 +107,48 @@ at::Tensor nhwc_padded(const at::Tensor& t) {
   return out;
 }
 
+// ---- few-channel first layer: the image is written out with its zero border and 8 channels, filters row-packed
+bool stem_eligible(const at::Tensor& input, const at::Tensor& weight, at::IntArrayRef stride, at::IntArrayRef padding,
+                   b200_conv_t* d) {
+  if (input.size(1) > 8 || weight.size(3) * 8 > 64) return false;
+  *d = b200_conv_t{};
+  d->N = input.size(0), d->C = 8, d->H = input.size(2), d->W = input.size(3);
+  d->K = weight.size(0), d->R = (int)weight.size(2), d->S = (int)weight.size(3);
+  d->sh = (int)stride[0], d->sw = (int)stride[1], d->ph = (int)padding[0], d->pw = (int)padding[1];
+  d->Ho = (d->H + 2 * d->ph - d->R) / d->sh + 1;
+  d->Wo = (d->W + 2 * d->pw - d->S) / d->sw + 1;
+  d->dtype = kdtype(input.scalar_type());
+  return d->Ho > 0 && d->Wo > 0 && b200_conv_stem_supported(d) != 0;
+}
+
+at::Tensor stem_padded_image(const at::Tensor& input, const b200_conv_t& d) {
+  at::Tensor xp = at::empty({d.N, d.H + 2 * d.ph, d.W + 2 * d.pw, 8}, input.options());
+  xp.zero_();
+  xp.narrow(1, d.ph, d.H).narrow(2, d.pw, d.W).narrow(3, 0, input.size(1)).copy_(input.permute({0, 2, 3, 1}));
+  return xp;
+}
+
+at::Tensor stem_packed_filter(const at::Tensor& weight, const b200_conv_t& d) {
+  at::Tensor wp = at::empty({d.K, d.R, 8, 8}, weight.options());
+  wp.zero_();
+  wp.narrow(2, 0, d.S).narrow(3, 0, weight.size(1)).copy_(weight.permute({0, 2, 3, 1}));
+  return wp;
+}
+
 at::Tensor implicit_forward(const at::Tensor& input, const at::Tensor& weight, const std::optional<at::Tensor>& bias,
                             at::IntArrayRef stride, at::IntArrayRef padding) {
+  b200_conv_t sd;
+  if (stem_eligible(input, weight, stride, padding, &sd)) {
+    const at::Tensor xp = stem_padded_image(input, sd);
+    const at::Tensor wp = stem_packed_filter(weight, sd);
+    at::Tensor y = at::empty({sd.N, sd.K, sd.Ho, sd.Wo}, input.options().memory_format(at::MemoryFormat::ChannelsLast));
+    at::Tensor b;
+    if (bias.has_value() && bias->defined()) b = bias->to(input.scalar_type()).contiguous();
+    B200_KERNEL_CALL(b200_conv_stem_fwd(&sd, y.data_ptr(), xp.const_data_ptr(), wp.const_data_ptr(),
+                                        b.defined() ? b.const_data_ptr() : nullptr, 0, current_raw_stream(input)));
+    g_implicit_hits.fetch_add(1, std::memory_order_relaxed);
+    return y;
+  }
   const at::Tensor x = nhwc_padded(input);
   const at::Tensor w = nhwc_padded(weight);
   b200_conv_t d = conv_desc(x, w, stride, padding);
@@ -138,7 +178,15 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> implicit_backward(const at::Tenso
     B200_KERNEL_CALL(b200_conv_dgrad(&d, gx.data_ptr(), gy.const_data_ptr(), w.const_data_ptr(), stream));
     if (x.size(1) != C) gx = gx.narrow(1, 0, C).contiguous(at::MemoryFormat::ChannelsLast);
   }
-  if (mask[1]) {
+  b200_conv_t sd;
+  if (mask[1] && stem_eligible(input, weight, stride, padding, &sd)) {
+    const at::Tensor xp = stem_padded_image(input, sd);
+    at::Tensor acc = at::zeros({sd.K, sd.R, 8, 8}, input.options().dtype(at::kFloat));
+    B200_KERNEL_CALL(b200_conv_stem_wgrad(&sd, acc.data_ptr<float>(), gy.const_data_ptr(), xp.const_data_ptr(), stream));
+    gw = acc.narrow(2, 0, sd.S).narrow(3, 0, C).permute({0, 3, 1, 2}).to(weight.scalar_type());  // [K, C, R, S]
+    const bool cl = weight.is_contiguous(at::MemoryFormat::ChannelsLast) && !weight.is_contiguous();
+    gw = gw.contiguous(cl ? at::MemoryFormat::ChannelsLast : at::MemoryFormat::Contiguous);
+  } else if (mask[1]) {
     at::Tensor acc = at::zeros({d.K, d.R, d.S, d.C}, x.options().dtype(at::kFloat));
     B200_KERNEL_CALL(b200_conv_wgrad(&d, acc.data_ptr<float>(), gy.const_data_ptr(), x.const_data_ptr(), stream));
     gw = acc.to(weight.scalar_type()).permute({0, 3, 1, 2});  // [K, C, R, S] with channels-last strides

@@ -164,6 +164,14 @@ B200_API int b200_conv_fwd(const b200_conv_t* d, void* y, const void* x, const v
                            int relu, cudaStream_t stream);
 B200_API int b200_conv_dgrad(const b200_conv_t* d, void* dx, const void* dy, const void* w, cudaStream_t stream);
 B200_API int b200_conv_wgrad(const b200_conv_t* d, float* dw_f32, const void* dy, const void* x, cudaStream_t stream);
+/* Few-channel first layers (C == 8 after padding, S * 8 <= 64): xpad[N, H + 2 ph, W + 2 pw, 8] is the image with its
+ * zero border written out, wpack[K][R][64] holds filter row r as element s * 8 + c (zero tail); one K step covers a
+ * whole filter row.  wgrad adds into dwpack_f32[K][R][64]. */
+B200_API int b200_conv_stem_supported(const b200_conv_t* d);
+B200_API int b200_conv_stem_fwd(const b200_conv_t* d, void* y, const void* xpad, const void* wpack, const void* bias,
+                                int relu, cudaStream_t stream);
+B200_API int b200_conv_stem_wgrad(const b200_conv_t* d, float* dwpack_f32, const void* dy, const void* xpad,
+                                  cudaStream_t stream);
 /* 1 if a conv kernel gave up a bounded wait since the last clear */
 B200_API int b200_conv_status(int clear);
 

@@ -84,7 +84,23 @@ bn_stats_kernel(const T* __restrict__ x, float* __restrict__ sums, int64_t P, in
   float acc[16];
 #pragma unroll
   for (int i = 0; i < 16; ++i) acc[i] = 0.f;
-  for (int64_t p = (int64_t)blockIdx.y * ty_n + ty; p < P; p += (int64_t)gridDim.y * ty_n) {
+  // four independent 16-byte loads in flight per thread: the loop is latency-bound otherwise
+  const int64_t step = (int64_t)gridDim.y * ty_n;
+  int64_t p = (int64_t)blockIdx.y * ty_n + ty;
+  for (; p + 3 * step < P; p += 4 * step) {
+    Vec16<T> r[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) r[u] = ld16(x + (p + u * step) * C + c0);
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float f = ToF<T>::to(r[u].v[i]);
+        acc[i] += f;
+        acc[8 + i] = fmaf(f, f, acc[8 + i]);
+      }
+  }
+  for (; p < P; p += step) {
     float v[8];
     load8(x + p * C + c0, v);
 #pragma unroll
@@ -165,21 +181,33 @@ bn_bwd_reduce_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T*
     is[i] = invstd[c0 + i];
     acc[i] = acc[8 + i] = 0.f;
   }
-  for (int64_t p = (int64_t)blockIdx.y * ty_n + ty; p < P; p += (int64_t)gridDim.y * ty_n) {
-    float g[8], v[8];
-    load8(dy + p * C + c0, g);
-    load8(x + p * C + c0, v);
-    if constexpr (RELU) {
-      float o[8];
-      load8(y + p * C + c0, o);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) g[i] = o[i] > 0.f ? g[i] : 0.f;
-    }
+  const int64_t step = (int64_t)gridDim.y * ty_n;
+  int64_t p = (int64_t)blockIdx.y * ty_n + ty;
+  auto consume = [&](const Vec16<T>& rg, const Vec16<T>& rx, const Vec16<T>& ro) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      acc[i] += g[i];
-      acc[8 + i] = fmaf(g[i], (v[i] - mu[i]) * is[i], acc[8 + i]);
+      float g = ToF<T>::to(rg.v[i]);
+      if constexpr (RELU) g = ToF<T>::to(ro.v[i]) > 0.f ? g : 0.f;
+      acc[i] += g;
+      acc[8 + i] = fmaf(g, (ToF<T>::to(rx.v[i]) - mu[i]) * is[i], acc[8 + i]);
     }
+  };
+  // two rows per iteration: four to six independent 16-byte loads in flight per thread
+  for (; p + step < P; p += 2 * step) {
+    Vec16<T> g0 = ld16(dy + p * C + c0), g1 = ld16(dy + (p + step) * C + c0);
+    Vec16<T> x0 = ld16(x + p * C + c0), x1 = ld16(x + (p + step) * C + c0);
+    Vec16<T> o0 = g0, o1 = g1;
+    if constexpr (RELU) {
+      o0 = ld16(y + p * C + c0);
+      o1 = ld16(y + (p + step) * C + c0);
+    }
+    consume(g0, x0, o0);
+    consume(g1, x1, o1);
+  }
+  for (; p < P; p += step) {
+    Vec16<T> g0 = ld16(dy + p * C + c0), x0 = ld16(x + p * C + c0), o0 = g0;
+    if constexpr (RELU) o0 = ld16(y + p * C + c0);
+    consume(g0, x0, o0);
   }
   reduce_over_y_and_add<16>(acc, sh, tx_n, ty_n, sums, sums + C, c0);
 }

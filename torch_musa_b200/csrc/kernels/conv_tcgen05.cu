@@ -686,3 +686,150 @@ extern "C" int b200_conv_wgrad(const b200_conv_t* d, float* dw_f32, const void* 
   conv_wgrad_kernel<<<grid, kThreads, kSmemBytes, stream>>>(maps, p, dw_f32);
   return (int)cudaGetLastError();
 }
+
+// ------------------------------------------------------------------ few-channel ("stem") convolutions
+// With C <= 8 input channels a tap holds 16 bytes per pixel and the generic path would spend a whole 128-byte
+// K step on it.  Here the caller provides the image physically zero-padded to [N, Hp, Wp, 8] (Hp = H + 2 ph,
+// Wp = W + 2 pw) and one K step covers a whole filter ROW: the S taps x 8 channels of one output pixel are
+// S * 8 <= 64 consecutive elements of that layout.  Consecutive output pixels start sw * 8 elements apart,
+// which is less than the 64 elements a row of the box spans, so output columns are processed in `cls_n`
+// interleaved classes (wo = cls_n * j + cls) whose starts are >= 64 elements apart: within a class the rows of
+// a box do not overlap and an ordinary tiled tensor map describes them.  Filters are packed as [K][R][64].
+namespace b200k {
+namespace convdev {
+
+struct StemGeom {
+  int cls_n;        // number of output-column classes
+  int64_t Hp, Wp;   // padded image extent
+};
+
+bool stem_geom(const b200_conv_t* d, StemGeom* g) {
+  if (d->dtype != B200_BF16 && d->dtype != B200_F16) return false;
+  if (d->C != 8 || d->S * 8 > 64 || d->R > kMaxTaps || d->K % 8 != 0) return false;
+  if (d->sh < 1 || d->sh > 2 || d->sw < 1 || d->sw > 2) return false;
+  g->cls_n = (64 + d->sw * 8 - 1) / (d->sw * 8);  // smallest class count with starts >= 64 elements apart
+  g->Hp = d->H + 2 * d->ph;
+  g->Wp = d->W + 2 * d->pw;
+  // the last pixel's row of 64 elements must end inside its image row
+  if ((d->Wo - 1) * d->sw + 8 > g->Wp) return false;
+  return encoder() != nullptr;
+}
+
+// Rows of 64 elements of the padded image: row (n, h2, j) starts at pixel (hp + sh * h2, (cls + cls_n * j) * sw).
+bool make_stem_map(CUtensorMap* out, const void* xpad, const b200_conv_t* d, const StemGeom& g, int hp, int cls, int tw,
+                   int th, int n_t) {
+  const int64_t Wc = (d->Wo - cls + g.cls_n - 1) / g.cls_n;
+  const int64_t Hs = (g.Hp - hp + d->sh - 1) / d->sh;
+  if (Wc <= 0 || Hs <= 0) return false;
+  const char* p = static_cast<const char*>(xpad) + ((int64_t)hp * g.Wp + (int64_t)cls * d->sw) * 8 * 2;
+  cuuint64_t dims[4] = {64, (cuuint64_t)Wc, (cuuint64_t)Hs, (cuuint64_t)d->N};
+  cuuint64_t strides[3] = {(cuuint64_t)(g.cls_n * d->sw * 8 * 2), (cuuint64_t)(d->sh * g.Wp * 8 * 2),
+                           (cuuint64_t)(g.Hp * g.Wp * 8 * 2)};
+  cuuint32_t box[4] = {64, (cuuint32_t)tw, (cuuint32_t)th, (cuuint32_t)n_t};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  return encoder()(out, map_dtype(d->dtype), 4, const_cast<char*>(p), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace convdev
+}  // namespace b200k
+
+extern "C" int b200_conv_stem_supported(const b200_conv_t* d) {
+  StemGeom g;
+  return stem_geom(d, &g) ? 1 : 0;
+}
+
+// y[N, Ho, Wo, K] from xpad[N, Hp, Wp, 8] and wpack[K][R][64] (element s * 8 + c of a row; the tail is zero).
+extern "C" int b200_conv_stem_fwd(const b200_conv_t* d, void* y, const void* xpad, const void* wpack, const void* bias,
+                                  int relu, cudaStream_t stream) {
+  StemGeom g;
+  if (!stem_geom(d, &g)) return (int)cudaErrorNotSupported;
+  for (int cls = 0; cls < g.cls_n; ++cls) {
+    const int Wc = (int)((d->Wo - cls + g.cls_n - 1) / g.cls_n);
+    if (Wc <= 0) continue;
+    Maps maps{};
+    PixParams p{};
+    int n_t, th, tw;
+    pick_rect(d->N, (int)d->Ho, Wc, BM, false, n_t, th, tw);
+    p.n_t = n_t, p.th = th, p.tw = tw, p.rows = n_t * th * tw;
+    p.tiles_n = (int)((d->N + n_t - 1) / n_t);
+    p.tiles_h = (int)((d->Ho + th - 1) / th);
+    p.tiles_w = (Wc + tw - 1) / tw;
+    p.tiles_c = (int)((d->K + BN - 1) / BN);
+    p.N = (int)d->N, p.Hg = (int)d->Ho, p.Wg = Wc;
+    p.k_chunks = 1;
+    p.a_bytes = p.rows * BK * 2;
+    p.out_sn = d->Ho * d->Wo * d->K, p.out_sh = d->Wo * d->K, p.out_sw = (long long)g.cls_n * d->K;
+    p.out_off = (long long)cls * d->K;
+    p.c_out = (int)d->K;
+    p.bias = bias, p.relu = relu;
+    p.idesc = make_idesc(d->dtype, true, true);
+    p.status = device_status();
+    bool have[2] = {false, false};
+    for (int r = 0; r < d->R; ++r) {
+      const int hp = r % d->sh;
+      if (!have[hp]) {
+        if (!make_stem_map(&maps.box[hp], xpad, d, g, hp, cls, tw, th, n_t)) return (int)cudaErrorInvalidValue;
+        have[hp] = true;
+      }
+      Tap t;
+      t.map = (short)hp, t.dh = (short)(r / d->sh), t.dw = 0, t.wrs = (short)r;
+      p.taps[p.n_taps++] = t;
+    }
+    if (!make_weight_map(&maps.other, wpack, d->dtype, d->K, d->R, 64, BN)) return (int)cudaErrorInvalidValue;
+    int e = launch_pix<true>(maps, p, d->dtype, y, stream);
+    if (e != 0) return e;
+  }
+  return 0;
+}
+
+// dwpack_f32[K][R][64] += sum over pixels of dy[N, Ho, Wo, K] x rows of xpad (fp32, zeroed by the caller).
+extern "C" int b200_conv_stem_wgrad(const b200_conv_t* d, float* dwpack_f32, const void* dy, const void* xpad,
+                                    cudaStream_t stream) {
+  StemGeom g;
+  if (!stem_geom(d, &g)) return (int)cudaErrorNotSupported;
+  if (!opt_in_smem(conv_wgrad_kernel)) return (int)cudaGetLastError();
+  for (int cls = 0; cls < g.cls_n; ++cls) {
+    const int Wc = (int)((d->Wo - cls + g.cls_n - 1) / g.cls_n);
+    if (Wc <= 0) continue;
+    Maps maps{};
+    WgradParams p{};
+    int n_t, th, tw;
+    pick_rect(d->N, (int)d->Ho, Wc, BK, true, n_t, th, tw);
+    p.n_t = n_t, p.th = th, p.tw = tw;
+    p.tiles_n = (int)((d->N + n_t - 1) / n_t);
+    p.tiles_h = (int)((d->Ho + th - 1) / th);
+    p.tiles_w = (Wc + tw - 1) / tw;
+    p.tiles_m = (int)((d->K + BM - 1) / BM);
+    p.tiles_nc = 1;
+    p.c_out = (int)d->K, p.c_in = 64, p.rs = d->R;
+    p.idesc = make_idesc(d->dtype, false, false);
+    p.status = device_status();
+    bool have[2] = {false, false};
+    for (int r = 0; r < d->R; ++r) {
+      const int hp = r % d->sh;
+      if (!have[hp]) {
+        if (!make_stem_map(&maps.box[hp], xpad, d, g, hp, cls, tw, th, n_t)) return (int)cudaErrorInvalidValue;
+        have[hp] = true;
+      }
+      Tap t;
+      t.map = (short)hp, t.dh = (short)(r / d->sh), t.dw = 0, t.wrs = (short)r;
+      p.taps[p.n_taps++] = t;
+    }
+    // dy of this class: columns cls, cls + cls_n, ...
+    if (!make_pixel_map(&maps.other, dy, d->dtype, d->N, d->Ho, d->Wo, d->K, 1, g.cls_n, 0, cls, 64, tw, th, n_t))
+      return (int)cudaErrorInvalidValue;
+    const int out_tiles = p.tiles_m * p.n_taps;
+    const int pix_tiles = p.tiles_n * p.tiles_h * p.tiles_w;
+    int splits = std::max(1, (2 * sm_count() + out_tiles - 1) / out_tiles);
+    splits = std::min(splits, pix_tiles);
+    p.steps_per_split = (pix_tiles + splits - 1) / splits;
+    p.splits = (pix_tiles + p.steps_per_split - 1) / p.steps_per_split;
+    const int grid = std::min(out_tiles * p.splits, sm_count());
+    conv_wgrad_kernel<<<grid, kThreads, kSmemBytes, stream>>>(maps, p, dwpack_f32);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+  }
+  return 0;
+}
