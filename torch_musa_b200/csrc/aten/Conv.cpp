@@ -20,6 +20,7 @@
 #include <torch/library.h>
 
 #include <atomic>
+#include <mutex>
 
 namespace b200 {
 namespace ops {
@@ -121,10 +122,39 @@ bool stem_eligible(const at::Tensor& input, const at::Tensor& weight, at::IntArr
   return d->Ho > 0 && d->Wo > 0 && b200_conv_stem_supported(d) != 0;
 }
 
-at::Tensor stem_padded_image(const at::Tensor& input, const b200_conv_t& d) {
+// The forward's padded image is kept for the backward of the same input (same storage, same version counter,
+// same geometry) and dropped when the backward has used it.
+struct StemCache {
+  const void* ptr = nullptr;
+  uint32_t version = 0;
+  int64_t N = 0, H = 0, W = 0, C = 0;
+  int ph = 0, pw = 0;
+  at::Tensor xp;
+};
+std::mutex g_stem_mu;
+StemCache g_stem_cache;  // backward runs on the autograd thread
+
+bool stem_cache_matches(const StemCache& c, const at::Tensor& input, const b200_conv_t& d) {
+  return c.xp.defined() && c.ptr == input.const_data_ptr() && c.version == input._version() && c.N == d.N &&
+         c.H == d.H && c.W == d.W && c.C == input.size(1) && c.ph == d.ph && c.pw == d.pw;
+}
+
+at::Tensor stem_padded_image(const at::Tensor& input, const b200_conv_t& d, bool forward) {
+  {
+    std::lock_guard<std::mutex> g(g_stem_mu);
+    if (!forward && stem_cache_matches(g_stem_cache, input, d)) {
+      at::Tensor xp = std::move(g_stem_cache.xp);
+      g_stem_cache = StemCache{};
+      return xp;
+    }
+  }
   at::Tensor xp = at::empty({d.N, d.H + 2 * d.ph, d.W + 2 * d.pw, 8}, input.options());
   xp.zero_();
   xp.narrow(1, d.ph, d.H).narrow(2, d.pw, d.W).narrow(3, 0, input.size(1)).copy_(input.permute({0, 2, 3, 1}));
+  if (forward && at::GradMode::is_enabled()) {
+    std::lock_guard<std::mutex> g(g_stem_mu);
+    g_stem_cache = StemCache{input.const_data_ptr(), input._version(), d.N, d.H, d.W, input.size(1), d.ph, d.pw, xp};
+  }
   return xp;
 }
 
@@ -139,7 +169,7 @@ at::Tensor implicit_forward(const at::Tensor& input, const at::Tensor& weight, c
                             at::IntArrayRef stride, at::IntArrayRef padding) {
   b200_conv_t sd;
   if (stem_eligible(input, weight, stride, padding, &sd)) {
-    const at::Tensor xp = stem_padded_image(input, sd);
+    const at::Tensor xp = stem_padded_image(input, sd, /*forward=*/true);
     const at::Tensor wp = stem_packed_filter(weight, sd);
     at::Tensor y = at::empty({sd.N, sd.K, sd.Ho, sd.Wo}, input.options().memory_format(at::MemoryFormat::ChannelsLast));
     at::Tensor b;
@@ -166,13 +196,15 @@ at::Tensor implicit_forward(const at::Tensor& input, const at::Tensor& weight, c
 std::tuple<at::Tensor, at::Tensor, at::Tensor> implicit_backward(const at::Tensor& grad_output, const at::Tensor& input,
                                                                  const at::Tensor& weight, at::IntArrayRef stride,
                                                                  at::IntArrayRef padding, std::array<bool, 3> mask) {
-  const at::Tensor x = nhwc_padded(input);
-  const at::Tensor w = nhwc_padded(weight);
   const at::Tensor gy = grad_output.contiguous(at::MemoryFormat::ChannelsLast);
-  b200_conv_t d = conv_desc(x, w, stride, padding);
-  auto stream = current_raw_stream(x);
   const int64_t C = input.size(1);
   at::Tensor gx, gw, gb;
+  b200_conv_t sd0;
+  const bool stem_only = !mask[0] && stem_eligible(input, weight, stride, padding, &sd0);
+  const at::Tensor x = stem_only ? input : nhwc_padded(input);
+  const at::Tensor w = stem_only ? weight : nhwc_padded(weight);
+  b200_conv_t d = conv_desc(x, w, stride, padding);
+  auto stream = current_raw_stream(input);
   if (mask[0]) {
     gx = at::empty(x.sizes(), x.options().memory_format(at::MemoryFormat::ChannelsLast));
     B200_KERNEL_CALL(b200_conv_dgrad(&d, gx.data_ptr(), gy.const_data_ptr(), w.const_data_ptr(), stream));
@@ -180,7 +212,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> implicit_backward(const at::Tenso
   }
   b200_conv_t sd;
   if (mask[1] && stem_eligible(input, weight, stride, padding, &sd)) {
-    const at::Tensor xp = stem_padded_image(input, sd);
+    const at::Tensor xp = stem_padded_image(input, sd, /*forward=*/false);
     at::Tensor acc = at::zeros({sd.K, sd.R, 8, 8}, input.options().dtype(at::kFloat));
     B200_KERNEL_CALL(b200_conv_stem_wgrad(&sd, acc.data_ptr<float>(), gy.const_data_ptr(), xp.const_data_ptr(), stream));
     gw = acc.narrow(2, 0, sd.S).narrow(3, 0, C).permute({0, 3, 1, 2}).to(weight.scalar_type());  // [K, C, R, S]

@@ -56,21 +56,24 @@ template <int NACC>
 __device__ __forceinline__ void reduce_over_y_and_add(float (&acc)[NACC], float* sh, int tx_n, int ty_n, float* out0,
                                                      float* out1, int c0) {
   const int tx = threadIdx.x % tx_n, ty = threadIdx.x / tx_n;
+  // accumulator-major layout: consecutive threads hit consecutive banks (a thread-major layout would put the
+  // whole warp on two banks and serialise every access sixteen-fold)
+  const int T = tx_n * ty_n, me = ty * tx_n + tx;
 #pragma unroll
-  for (int i = 0; i < NACC; ++i) sh[(ty * tx_n + tx) * NACC + i] = acc[i];
+  for (int i = 0; i < NACC; ++i) sh[i * T + me] = acc[i];
   __syncthreads();
   for (int s = ty_n >> 1; s > 0; s >>= 1) {
     if (ty < s) {
 #pragma unroll
-      for (int i = 0; i < NACC; ++i) sh[(ty * tx_n + tx) * NACC + i] += sh[((ty + s) * tx_n + tx) * NACC + i];
+      for (int i = 0; i < NACC; ++i) sh[i * T + me] += sh[i * T + me + s * tx_n];
     }
     __syncthreads();
   }
   if (ty == 0) {
 #pragma unroll
     for (int i = 0; i < NACC / 2; ++i) {
-      atomicAdd(out0 + c0 + i, sh[tx * NACC + i]);
-      atomicAdd(out1 + c0 + i, sh[tx * NACC + NACC / 2 + i]);
+      atomicAdd(out0 + c0 + i, sh[i * T + tx]);
+      atomicAdd(out1 + c0 + i, sh[(NACC / 2 + i) * T + tx]);
     }
   }
 }
