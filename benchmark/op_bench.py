@@ -8,6 +8,7 @@ the measured peaks of this machine (MEASURED_PEAKS.json if present).
   python benchmark/op_bench.py softmax|cross_entropy --rows 4096 --cols 32000
   python benchmark/op_bench.py swiglu --rows 4096 --cols 11008
   python benchmark/op_bench.py adamw --numel 268435456
+  python benchmark/op_bench.py conv [--rows BATCH]   (ResNet-50 filter shapes, ours vs library, fwd and bwd)
   python benchmark/op_bench.py all            (a Llama-7B shaped sweep; one JSON line per case)
 
 Every case prints one JSON line: {"op", "shape", "dtype", "us", "tflops" | "gbs", "frac_of_measured", ...}.
@@ -161,6 +162,40 @@ def bench_attention(dev, batch, heads, seq, dt=torch.bfloat16, iters=10):
     return out
 
 
+RESNET_CONVS = [   # (Cin, H, Cout, R, stride, pad): the distinct non-pointwise filters of ResNet-50 + strided 1x1
+    (3, 224, 64, 7, 2, 3), (64, 56, 64, 3, 1, 1), (128, 56, 128, 3, 2, 1), (128, 28, 128, 3, 1, 1),
+    (256, 28, 256, 3, 2, 1), (256, 14, 256, 3, 1, 1), (512, 14, 512, 3, 2, 1), (512, 7, 512, 3, 1, 1),
+    (256, 56, 512, 1, 2, 0), (1024, 14, 2048, 1, 2, 0),
+]
+
+
+def bench_conv(dev, batch, dt=torch.bfloat16, iters=10, cases=None):
+    """Implicit-GEMM convolution (forward, and data + weight gradients) against the library convolution on the same
+    tensors; channels-last.  FLOPs = 2 * N * Ho * Wo * K * C * R * S per pass."""
+    out = []
+    for (C, H, K, R, stride, pad) in (cases or RESNET_CONVS):
+        x = torch.randn(batch, C, H, H, device=dev, dtype=dt).contiguous(memory_format=torch.channels_last)
+        w = (torch.randn(K, C, R, R, device=dev, dtype=dt) * 0.05).contiguous(memory_format=torch.channels_last)
+        Ho = (H + 2 * pad - R) // stride + 1
+        flops = 2.0 * batch * Ho * Ho * K * C * R * R
+        g = torch.randn(batch, K, Ho, Ho, device=dev, dtype=dt).contiguous(memory_format=torch.channels_last)
+        shape = [batch, C, H, H, K, R, stride]
+        for impl, name in ((True, "tcgen05"), (False, "library")):
+            bw._C._set_implicit_conv_gemm(impl)
+            try:
+                with torch.no_grad():
+                    us = timeit(lambda: F.conv2d(x, w, None, stride, pad), dev, iters)
+                out.append(report("conv_fwd_" + name, shape, dt, us, flops=flops))
+                xg, wg = x.detach().requires_grad_(C > 3), w.detach().requires_grad_()
+                y = F.conv2d(xg, wg, None, stride, pad)
+                ins = (xg, wg) if C > 3 else (wg,)
+                us = timeit(lambda: torch.autograd.grad(y, ins, g, retain_graph=True), dev, iters)
+                out.append(report("conv_bwd_" + name, shape, dt, us, flops=flops * len(ins)))
+            finally:
+                bw._C._set_implicit_conv_gemm(True)
+    return out
+
+
 def bench_rmsnorm(dev, rows, cols, dt=torch.bfloat16, backward=False):
     x = torch.randn(rows, cols, device=dev, dtype=dt, requires_grad=backward)
     w = torch.ones(cols, device=dev, dtype=dt, requires_grad=backward)
@@ -238,6 +273,10 @@ def main():
         bench_gemm_fp8(dev, a.m, a.n, a.k, a.iters)
     elif a.op == "attention":
         bench_attention(dev, 1, 32, a.rows, dt, a.iters)
+    elif a.op == "conv":
+        bench_conv(dev, a.rows if a.rows != 4096 else 64, dt, a.iters)
+    elif a.op == "conv_small":      # one 3x3 layer on a small batch: the case used for profiler captures
+        bench_conv(dev, 32, dt, 3, cases=[(64, 56, 64, 3, 1, 1)])
     elif a.op == "gemm_sweep":
         bench_gemm_sweep(dev, a.iters)
     elif a.op == "rmsnorm":

@@ -259,3 +259,30 @@ def test_cpp_example_runs(bw):
     r = subprocess.run([os.path.join(root, "examples", "cpp", "rmsnorm_example")], capture_output=True, text=True, timeout=120)
     assert r.returncode == 0, r.stdout + r.stderr
     assert "max abs error" in r.stdout
+
+
+def test_stream_guards_and_event_cache(bw, dev):
+    """MultiStreamGuard / OptionalStreamGuard set and restore the current streams; finished events are reused."""
+    a, b = bw.Stream(), bw.Stream()
+    before = bw.current_stream().stream_id
+    inside, after = bw._C._multi_stream_guard_probe([(a.stream_id, a.device_index)])
+    assert inside == [a.stream_id] and after == [before]
+    hits0, _ = bw._C._event_cache_stats()
+    for _ in range(8):
+        e = bw.Event()
+        e.record()
+        e.synchronize()
+        del e
+        x = torch.ones(1024, device=dev)
+        with bw.stream(b):
+            y = x + 1
+        y.record_stream(bw.current_stream())     # the allocator's deferred free uses an event
+        del y
+    bw.synchronize()
+    torch.empty(1, device=dev)                   # lets the allocator process finished events
+    assert bw._C._event_cache_stats()[0] > hits0
+
+
+def test_current_blas_handle(bw, dev):
+    h = bw.current_blas_handle()
+    assert isinstance(h, int) and h != 0

@@ -73,14 +73,30 @@ def _collectives_body(rank, world):
     b = torch.tensor([True, False], device=dev) if rank == 0 else torch.tensor([False, False], device=dev)
     dist.all_reduce(b)
     assert b.cpu().tolist() == [True, False]
+    # scale-then-sum in one pass (gradient averaging with an arbitrary divisor)
+    x = torch.full((4096,), float(rank + 1), device=dev)
+    dist.all_reduce(x, op=dist._make_nccl_premul_sum(0.25))
+    assert torch.allclose(x.cpu(), torch.full((4096,), 0.25 * sum(range(1, world + 1))))
+    rs = torch.empty(256, dtype=torch.bfloat16, device=dev)
+    dist.reduce_scatter_tensor(rs, torch.ones(world * 256, dtype=torch.bfloat16, device=dev),
+                               op=dist._make_nccl_premul_sum(0.5))
+    assert torch.all(rs.float().cpu() == 0.5 * world)
+    # complex tensors travel as pairs of reals
+    z = torch.full((64,), complex(rank + 1, -(rank + 1)), dtype=torch.complex64, device=dev)
+    dist.all_reduce(z)
+    tot = sum(range(1, world + 1))
+    assert torch.allclose(torch.view_as_real(z).cpu(), torch.tensor([float(tot), -float(tot)]).repeat(64, 1))
     pg = dist.group.WORLD._get_backend(dev)
-    assert "all_gather_into_tensor" in bw._C._pg_dump_flight_recorder(pg)
+    dump = bw._C._pg_dump_flight_recorder(pg)
+    assert "all_gather_into_tensor" in dump
+    assert '"stack"' in dump                    # BCCL_TRACE_CPP_STACK=1: every record carries its caller's backtrace
+    assert bw._C._event_cache_stats()[0] > 0    # events of finished collectives were reused
 
 
 @pytest.mark.parametrize("world", WORLDS)
 def test_collectives_closed_form(world):
     _need(world)
-    run_ranks(_collectives_body, world, "bccl")
+    run_ranks(_collectives_body, world, "bccl", env={"BCCL_TRACE_CPP_STACK": "1"})
 
 
 def _fused_vs_nccl_body(rank, world):

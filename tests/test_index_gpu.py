@@ -154,3 +154,69 @@ def test_split_with_sizes_copy(bw, dev):
     for o, r in zip(outs, x.split([5, 10, 15], dim=1)):
         _same(o, r.contiguous())
     assert not bw.fallback_counts(), bw.fallback_counts()
+
+
+# ---------------------------------------------------------------- searchsorted / histc / nonzero / unique / group norm
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16, torch.int64])
+@pytest.mark.parametrize("right", [False, True])
+def test_searchsorted_and_bucketize(bw, dev, dt, right):
+    torch.manual_seed(0)
+    if dt == torch.int64:
+        b = torch.sort(torch.randint(-50, 50, (37,)))[0]
+        v = torch.randint(-60, 60, (5, 19))
+    else:
+        b = torch.sort(torch.randn(37))[0].to(dt)
+        v = torch.randn(5, 19).to(dt)
+        v[0, :5] = b[3:8]                                    # exact hits: left / right differ
+    bw.reset_fallback_counts()
+    assert torch.equal(torch.bucketize(v.to(dev), b.to(dev), right=right).cpu(), torch.bucketize(v, b, right=right))
+    out32 = torch.searchsorted(b.to(dev), v.to(dev), out_int32=True, right=right)
+    assert out32.dtype == torch.int32 and torch.equal(out32.cpu().long(), torch.searchsorted(b, v, right=right))
+    rows = torch.sort(torch.randn(5, 23), dim=-1)[0]         # one sorted row per row of values
+    vv = torch.randn(5, 7)
+    assert torch.equal(torch.searchsorted(rows.to(dev), vv.to(dev), right=right).cpu(),
+                       torch.searchsorted(rows, vv, right=right))
+    unsorted = torch.randn(31)
+    so = torch.argsort(unsorted)
+    assert torch.equal(torch.searchsorted(unsorted.to(dev), vv[0].to(dev), sorter=so.to(dev)).cpu(),
+                       torch.searchsorted(unsorted, vv[0], sorter=so))
+    assert not bw.fallback_counts(), bw.fallback_counts()
+
+
+def test_histc_nonzero_unique(bw, dev):
+    torch.manual_seed(1)
+    x = torch.randn(10007)
+    bw.reset_fallback_counts()
+    assert torch.equal(torch.histc(x.to(dev), bins=64, min=-3, max=3).cpu(), torch.histc(x, bins=64, min=-3, max=3))
+    assert torch.equal(torch.histc(x.to(dev), bins=10000).cpu(), torch.histc(x, bins=10000))   # range from the data
+    m = torch.randn(7, 11, 5) > 0.3
+    assert torch.equal(torch.nonzero(m.to(dev)).cpu(), torch.nonzero(m))
+    f = torch.randn(300).to(torch.bfloat16) * (torch.rand(300) > 0.5)
+    assert torch.equal(torch.nonzero(f.to(dev)).cpu(), torch.nonzero(f))
+    assert torch.nonzero(torch.zeros(5, 3, device=dev)).shape == (0, 2)
+    for t in (torch.randint(0, 40, (13, 29)), torch.randn(500).round(decimals=1), torch.randn(257).to(torch.bfloat16)):
+        u, inv, cnt = torch.unique(t.to(dev), return_inverse=True, return_counts=True)
+        ur, invr, cntr = torch.unique(t, return_inverse=True, return_counts=True)
+        assert torch.equal(u.cpu(), ur) and torch.equal(inv.cpu(), invr) and torch.equal(cnt.cpu(), cntr)
+    assert torch.equal(torch.unique(torch.tensor([3, 1, 3], device=dev)).cpu(), torch.tensor([1, 3]))
+    assert not bw.fallback_counts(), bw.fallback_counts()
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_group_norm(bw, dev, dt):
+    torch.manual_seed(2)
+    x = torch.randn(3, 32, 7, 5).to(dt)
+    w, b = torch.rand(32) + 0.5, torch.randn(32)
+    g = torch.randn(3, 32, 7, 5).to(dt)
+    xr, wr, br = x.float().requires_grad_(), w.clone().requires_grad_(), b.clone().requires_grad_()
+    yr = torch.nn.functional.group_norm(xr, 8, wr, br, 1e-5)
+    yr.backward(g.float())
+    xd = x.to(dev).requires_grad_()
+    wd, bd = w.to(dt).to(dev).requires_grad_(), b.to(dt).to(dev).requires_grad_()
+    bw.reset_fallback_counts()
+    y = torch.nn.functional.group_norm(xd, 8, wd, bd, 1e-5)
+    y.backward(g.to(dev))
+    assert not bw.fallback_counts(), bw.fallback_counts()
+    tol = 1e-4 if dt == torch.float32 else 3e-2
+    for a, r in ((y, yr), (xd.grad, xr.grad), (wd.grad, wr.grad), (bd.grad, br.grad)):
+        assert (a.float().cpu() - r).abs().max() <= tol * max(1.0, float(r.abs().max()))

@@ -106,3 +106,30 @@ def test_cpp_example_builds():
         pytest.skip("kernel library not built")
     r = subprocess.run(["make", "-C", os.path.join(root, "examples", "cpp"), "-B"], capture_output=True, text=True)
     assert r.returncode == 0, r.stdout + r.stderr
+
+
+def test_op_dumper_and_double_to_float(tmp_path):
+    import json
+    import torch
+    from torch_musa_b200.utils.op_debug import DoubleToFloat, OpDumper
+
+    x = torch.randn(4, 5)
+    with OpDumper(str(tmp_path), ops="aten::(mm|log)", device_type=None, save_tensors=True) as d:
+        y = x @ x.t()
+        z = torch.log(y - 100.0)          # NaNs appear here
+        _ = z + 1
+    assert d.summary() == {"aten::mm": 1, "aten::log": 1}
+    bad = d.first_non_finite()
+    assert bad is not None and bad["op"] == "aten::log" and bad["outputs"][0]["nan"] > 0
+    listed = json.load(open(tmp_path / "ops.json"))
+    assert [r["op"] for r in listed] == ["aten::mm", "aten::log"]
+    saved = torch.load(tmp_path / "000000_aten.mm.pt")
+    assert torch.equal(saved["out"], y)
+
+    a = torch.randn(8, 8, dtype=torch.float64)
+    with DoubleToFloat(device_type=None) as m:
+        b = a @ a
+        c = torch.sin(b)
+    assert b.dtype == torch.float64 and c.dtype == torch.float64
+    assert m.touched["aten::mm"] == 1 and m.touched["aten::sin"] == 1
+    assert not torch.equal(b, a @ a) and torch.allclose(b, a @ a, rtol=1e-4, atol=1e-4)   # computed in fp32

@@ -179,5 +179,15 @@ def get_sync_debug_mode() -> int:
 
 
 def current_blas_handle():
-    """There is no vendor BLAS handle: GEMMs are the backend's own tcgen05 kernels. Returns None."""
-    return None
+    """cuBLAS handle (a ``cublasHandle_t`` as an integer) bound to the current device and stream.
+
+    16-bit matrix products run on the backend's own tcgen05 kernels and never touch it; fp32 / fp64 / complex
+    products are library GEMMs that run over the same memory on the current blackwell stream, and this is the
+    handle they use."""
+    from ._lazy_init import _lazy_init
+
+    _lazy_init()
+    import torch
+
+    with torch.cuda.device(current_device()):
+        return torch.cuda.current_blas_handle()

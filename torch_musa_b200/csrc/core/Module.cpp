@@ -391,6 +391,22 @@ PYBIND11_MODULE(_C, m) {
     TORCH_CHECK(s.device().is_cpu() && host::is_managed_ptr(s.data()), "storage is not in managed host memory");
     return bridge::relabel_storage(s, make_device((c10::DeviceIndex)idx));
   });
+  m.def("_event_cache_stats", [] { return event_cache_stats(); });
+  m.def("_multi_stream_guard_probe", [](std::vector<std::tuple<int64_t, int64_t>> ids) {
+    // sets the given streams current on their devices inside a MultiStreamGuard and reports what was current
+    // inside and after the guard (used by the tests of the guard classes)
+    std::vector<Stream> streams;
+    for (auto& t : ids) streams.emplace_back(c10::Stream::unpack3(std::get<0>(t), (c10::DeviceIndex)std::get<1>(t), kDeviceType));
+    std::vector<int64_t> inside, after;
+    {
+      MultiStreamGuard g(streams);
+      OptionalStreamGuard og;
+      if (!streams.empty()) og.reset_stream(streams.front());
+      for (auto& s : streams) inside.push_back(get_current_stream(s.device_index()).id());
+    }
+    for (auto& s : streams) after.push_back(get_current_stream(s.device_index()).id());
+    return py::make_tuple(inside, after);
+  });
   m.def("_host_register", [](uintptr_t p, size_t n) {
     B200_CUDA_CHECK(cudaHostRegister(reinterpret_cast<void*>(p), n, cudaHostRegisterDefault));
   });

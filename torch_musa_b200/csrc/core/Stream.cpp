@@ -1,4 +1,7 @@
 #include "core/Stream.h"
+#include <cstdlib>
+#include <vector>
+#include <map>
 
 #include <c10/util/CallOnce.h>
 
@@ -147,10 +150,47 @@ Stream get_current_stream(c10::DeviceIndex device) {
 void set_current_stream(Stream s) { tl_current[s.device_index()] = s.id(); }
 
 // ------------------------------------------------------------------ Event
+// ---- event cache: creating and destroying a cudaEvent per collective / per freed block costs microseconds
+// each; finished events go back to a per-(device, flags) free list instead (B200_EVENT_CACHE=0 or
+// BCCL_ENABLE_EVENT_CACHE=0 switches it off).  Inter-process events are never cached: their handles were
+// given to other processes.  Parity: reference torch_musa/csrc/distributed/ProcessGroupMCCL.cpp (MUSAEventCache).
+namespace {
+struct EventCache {
+  std::mutex mu;
+  std::map<std::pair<int, unsigned>, std::vector<cudaEvent_t>> free_list;
+  std::atomic<int64_t> hits{0}, misses{0};
+  bool enabled = [] {
+    for (const char* n : {"B200_EVENT_CACHE", "BCCL_ENABLE_EVENT_CACHE"})
+      if (const char* e = std::getenv(n)) return std::atoi(e) != 0;
+    return true;
+  }();
+  static constexpr size_t kMaxPerKey = 1024;
+};
+EventCache& event_cache() {
+  static EventCache* c = new EventCache();  // leaked: events may be destroyed during static destruction
+  return *c;
+}
+}  // namespace
+
+std::pair<int64_t, int64_t> event_cache_stats() {
+  auto& c = event_cache();
+  return {c.hits.load(), c.misses.load()};
+}
+
 Event::~Event() { destroy(); }
 
 void Event::destroy() noexcept {
   if (created_) {
+    auto& c = event_cache();
+    if (c.enabled && !(flags_ & cudaEventInterprocess)) {
+      std::lock_guard<std::mutex> g(c.mu);
+      auto& v = c.free_list[{(int)device_, flags_}];
+      if (v.size() < EventCache::kMaxPerKey) {
+        v.push_back(ev_);
+        created_ = false;
+        return;
+      }
+    }
     int cur = -1;
     cudaGetDevice(&cur);
     if (cur != device_) cudaSetDevice(device_);
@@ -171,6 +211,21 @@ void Event::move_from(Event&& o) noexcept {
 }
 
 void Event::create(c10::DeviceIndex d) {
+  auto& c = event_cache();
+  if (c.enabled && !(flags_ & cudaEventInterprocess)) {
+    std::lock_guard<std::mutex> g(c.mu);
+    auto it = c.free_list.find({(int)d, flags_});
+    if (it != c.free_list.end() && !it->second.empty()) {
+      ev_ = it->second.back();
+      it->second.pop_back();
+      device_ = d;
+      created_ = true;
+      recorded_ = false;
+      c.hits.fetch_add(1, std::memory_order_relaxed);
+      return;
+    }
+  }
+  c.misses.fetch_add(1, std::memory_order_relaxed);
   DeviceSwitch sw(d);
   B200_CUDA_CHECK(cudaEventCreateWithFlags(&ev_, flags_));
   device_ = d;

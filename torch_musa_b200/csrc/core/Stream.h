@@ -11,6 +11,10 @@
 // priorities, id packing, external streams) and MUSAEvent.h:33-240.
 #pragma once
 
+#include <optional>
+#include <utility>
+#include <vector>
+
 #include "core/Device.h"
 
 #include <c10/core/Stream.h>
@@ -94,6 +98,9 @@ class B200_EXPORT Event {
   cudaEvent_t ev_ = nullptr;
 };
 
+// (reused, newly created) event counts of the event cache
+B200_EXPORT std::pair<int64_t, int64_t> event_cache_stats();
+
 // RAII: make `s` the current stream of its device (and that device current).
 struct B200_EXPORT StreamGuard {
   explicit StreamGuard(Stream s);
@@ -103,6 +110,47 @@ struct B200_EXPORT StreamGuard {
  private:
   c10::DeviceIndex prev_device_;
   Stream prev_stream_;
+};
+
+// A StreamGuard that may stay empty: reset_stream() arms it (or moves it to another stream), the destructor
+// restores whatever was current before the first arming.
+// Parity: reference torch_musa/csrc/core/MUSAGuard.h (OptionalMUSAStreamGuard, MUSAMultiStreamGuard).
+class OptionalStreamGuard {
+ public:
+  OptionalStreamGuard() = default;
+  explicit OptionalStreamGuard(Stream s) { reset_stream(s); }
+  explicit OptionalStreamGuard(std::optional<Stream> s) {
+    if (s.has_value()) reset_stream(*s);
+  }
+  void reset_stream(Stream s) {
+    guard_.reset();  // restore first: the guard below must remember the ORIGINAL stream of its device
+    guard_.emplace(s);
+  }
+  void reset() { guard_.reset(); }
+  bool armed() const { return guard_.has_value(); }
+
+ private:
+  std::optional<StreamGuard> guard_;
+};
+
+// Sets the current stream of several devices at once (at most one stream per device) and restores them all.
+class MultiStreamGuard {
+ public:
+  explicit MultiStreamGuard(const std::vector<Stream>& streams) {
+    prev_.reserve(streams.size());
+    for (const Stream& s : streams) {
+      prev_.push_back(get_current_stream(s.device_index()));
+      set_current_stream(s);
+    }
+  }
+  ~MultiStreamGuard() {
+    for (auto it = prev_.rbegin(); it != prev_.rend(); ++it) set_current_stream(*it);
+  }
+  MultiStreamGuard(const MultiStreamGuard&) = delete;
+  MultiStreamGuard& operator=(const MultiStreamGuard&) = delete;
+
+ private:
+  std::vector<Stream> prev_;
 };
 
 }  // namespace b200

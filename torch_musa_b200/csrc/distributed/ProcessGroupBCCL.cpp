@@ -63,6 +63,56 @@ ncclRedOp_t nccl_op(const c10d::ReduceOp& op, at::ScalarType t) {
   }
 }
 
+// Reduce operator for one NCCL call.  PREMUL_SUM (scale every contribution, then sum: gradient averaging with
+// an arbitrary divisor in one pass) needs a per-call custom operator that is destroyed after the enqueue.
+struct ReduceOpHolder {
+  ncclRedOp_t op;
+  ncclComm_t comm = nullptr;
+  bool custom = false;
+  at::Tensor factor_host;  // keeps the scalar alive until the call is enqueued
+  ReduceOpHolder(const c10d::ReduceOp& rop, at::ScalarType t, ncclComm_t c) {
+    if (rop == c10d::ReduceOp::PREMUL_SUM) {
+      TORCH_CHECK(t == at::kFloat || t == at::kDouble || t == at::kHalf || t == at::kBFloat16,
+                  "bccl: PREMUL_SUM needs a floating-point tensor");
+      auto* supp = static_cast<const c10d::NCCLPreMulSumSupplement*>(rop.supplement_.get());
+      TORCH_CHECK(supp, "bccl: PREMUL_SUM without a factor (use torch.distributed._make_nccl_premul_sum)");
+      if (supp->tensor_factor.defined()) {
+        const at::Tensor& f = supp->tensor_factor;
+        TORCH_CHECK(f.numel() == 1 && f.scalar_type() == t, "bccl: the PREMUL_SUM factor must be one element of the tensor's dtype");
+        BCCL_NCCL_CHECK(ncclRedOpCreatePreMulSum(&op, const_cast<void*>(f.const_data_ptr()), nccl_dtype(t),
+                                                 f.device().is_cpu() ? ncclScalarHostImmediate : ncclScalarDevice, c));
+      } else {
+        factor_host = at::scalar_tensor(supp->double_factor, at::TensorOptions().dtype(t).device(at::kCPU));
+        BCCL_NCCL_CHECK(ncclRedOpCreatePreMulSum(&op, factor_host.data_ptr(), nccl_dtype(t), ncclScalarHostImmediate, c));
+      }
+      comm = c;
+      custom = true;
+    } else {
+      op = nccl_op(rop, t);
+    }
+  }
+  ~ReduceOpHolder() {
+    if (custom) ncclRedOpDestroy(op, comm);
+  }
+  ReduceOpHolder(const ReduceOpHolder&) = delete;
+  ReduceOpHolder& operator=(const ReduceOpHolder&) = delete;
+};
+
+std::string json_escape(const std::string& in) {
+  std::string out;
+  out.reserve(in.size() + 8);
+  for (char ch : in) {
+    switch (ch) {
+      case '"': out += "\\\""; break;
+      case '\\': out += "\\\\"; break;
+      case '\n': out += "\\n"; break;
+      case '\t': out += "\\t"; break;
+      default: if ((unsigned char)ch >= 0x20) out += ch;
+    }
+  }
+  return out;
+}
+
 bool env_flag(const char* name, bool dflt) {
   const char* e = std::getenv(name);
   if (!e) return dflt;
@@ -107,7 +157,9 @@ std::string FlightRecorder::dump_json() const {
     os << "{\"id\": " << r.id << ", \"seq\": " << r.seq << ", \"op\": \"" << r.op << "\", \"in_numel\": " << r.in_numel
        << ", \"out_numel\": " << r.out_numel << ", \"dtype\": \"" << r.dtype << "\", \"state\": \"" << r.state
        << "\", \"fused\": " << (r.fused ? "true" : "false") << ", \"created_s\": " << r.created_s
-       << ", \"completed_s\": " << r.completed_s << ", \"duration_ms\": " << r.duration_ms << "}";
+       << ", \"completed_s\": " << r.completed_s << ", \"duration_ms\": " << r.duration_ms;
+    if (!r.stack.empty()) os << ", \"stack\": \"" << json_escape(r.stack) << "\"";
+    os << "}";
   }
   os << "]}";
   return os.str();
@@ -194,6 +246,11 @@ ProcessGroupBCCL::ProcessGroupBCCL(c10::intrusive_ptr<c10d::Store> store, int ra
   monitoring_ = env_flag("BCCL_ENABLE_MONITORING", true);
   propagate_error_ = env_flag("BCCL_PROPAGATE_ERROR", true);
   dump_on_timeout_ = env_flag("BCCL_DUMP_ON_TIMEOUT", false);
+  trace_stack_ = env_flag("BCCL_TRACE_CPP_STACK", false);
+  desync_debug_ = env_flag("BCCL_DESYNC_DEBUG", false);
+  // 0: a timed-out collective only raises on wait(); 1 (default): the group is also marked failed and the other
+  // ranks are told through the store; 2: the communicators are aborted as well so that blocked kernels return
+  async_error_handling_ = std::getenv("BCCL_ASYNC_ERROR_HANDLING") ? std::atoi(std::getenv("BCCL_ASYNC_ERROR_HANDLING")) : 1;
   if (const char* e = std::getenv("BCCL_HEARTBEAT_TIMEOUT_SEC")) heartbeat_timeout_s_ = std::max(1, std::atoi(e));
   // device-side waits on other ranks give up after the group's time-out (BCCL_DEVICE_WAIT_MS overrides)
   if (const char* e = std::getenv("BCCL_DEVICE_WAIT_MS")) b200_comm_set_wait_ms(std::atof(e));
@@ -303,6 +360,7 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupBCCL::collective(c10d::OpType type, c
   rec.dtype = c10::toString(ref.scalar_type());
   rec.state = "scheduled";
   rec.fused = fused;
+  if (trace_stack_) rec.stack = c10::get_backtrace(/*frames_to_skip=*/2, /*maximum_number_of_frames=*/24);
   work->record_id_ = recorder_.add(std::move(rec));
 
   // order the communication stream after the producer's stream
@@ -514,8 +572,9 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupBCCL::allreduce(std::vector<at::Tenso
   auto w = collective(c10d::OpType::ALLREDUCE, "allreduce", {t}, {tensors[0]}, [&](ncclComm_t comm, cudaStream_t s) {
     if (t.numel() == 0) return;
     if (try_fused_allreduce(t, o.reduceOp, s, dev)) { fused = true; return; }
+    ReduceOpHolder rop(o.reduceOp, t.scalar_type(), comm);
     BCCL_NCCL_CHECK(ncclAllReduce(t.const_data_ptr(), t.mutable_data_ptr(), (size_t)t.numel(), nccl_dtype(t.scalar_type()),
-                                  nccl_op(o.reduceOp, t.scalar_type()), comm, s));
+                                  rop.op, comm, s));
   });
   (void)fused;
   return w;
@@ -607,9 +666,9 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupBCCL::_reduce_scatter_base(at::Tensor
                       if (out.numel() == 0) return;
                       if (try_fused_reduce_scatter(out, in, o.reduceOp, s, dev)) return;
                       TORCH_CHECK(out.scalar_type() == in.scalar_type(), "bccl reduce_scatter_tensor: dtype mismatch");
+                      ReduceOpHolder rop(o.reduceOp, in.scalar_type(), comm);
                       BCCL_NCCL_CHECK(ncclReduceScatter(in.const_data_ptr(), out.mutable_data_ptr(), (size_t)out.numel(),
-                                                        nccl_dtype(in.scalar_type()), nccl_op(o.reduceOp, in.scalar_type()),
-                                                        comm, s));
+                                                        nccl_dtype(in.scalar_type()), rop.op, comm, s));
                     });
 }
 
@@ -850,12 +909,21 @@ void ProcessGroupBCCL::watchdog_loop() {
                        " ms on rank ", rank_)));
           w->set_exception(e);
           recorder_.complete(w->record_id_, "timed_out", -1.f);
-          error_ = c10d::ErrorType::TIMEOUT;
           LOG(ERROR) << "bccl watchdog: collective seq " << w->seq_ << " timed out on rank " << rank_
                      << "; flight recorder: " << recorder_.dump_json().substr(0, 2000);
-          try {
-            store_->set(std::string("bccl/remote_error"), std::to_string(rank_));
-          } catch (...) {
+          if (desync_debug_) report_desync(w->seq_);
+          if (dump_on_timeout_) dump_trace_file();
+          if (async_error_handling_ >= 1) {
+            error_ = c10d::ErrorType::TIMEOUT;
+            try {
+              store_->set(std::string("bccl/remote_error"), std::to_string(rank_));
+            } catch (...) {
+            }
+          }
+          if (async_error_handling_ >= 2) {
+            std::lock_guard<std::mutex> g(mu_);
+            for (auto& kv : comms_)
+              if (kv.second->comm) ncclCommAbort(kv.second->comm), kv.second->comm = nullptr;
           }
           retire = true;
         }
@@ -917,18 +985,40 @@ void ProcessGroupBCCL::monitor_loop() {
     if (std::chrono::duration_cast<std::chrono::seconds>(t - last_change).count() >= heartbeat_timeout_s_) {
       LOG(ERROR) << "bccl monitor: the watchdog of rank " << rank_ << " made no progress for " << heartbeat_timeout_s_
                  << " s; flight recorder: " << recorder_.dump_json().substr(0, 4000);
-      if (dump_on_timeout_) {
-        const char* prefix = std::getenv("BCCL_DEBUG_INFO_TEMP_FILE");
-        const std::string path = std::string(prefix ? prefix : "/tmp/bccl_trace_rank_") + std::to_string(rank_);
-        if (FILE* f = std::fopen(path.c_str(), "w")) {
-          const std::string js = recorder_.dump_json();
-          std::fwrite(js.data(), 1, js.size(), f);
-          std::fclose(f);
-        }
-      }
+      if (dump_on_timeout_) dump_trace_file();
       error_ = c10d::ErrorType::TIMEOUT;
       last_change = t;   // report once per time-out period
     }
+  }
+}
+
+void ProcessGroupBCCL::dump_trace_file() {
+  const char* prefix = std::getenv("BCCL_DEBUG_INFO_TEMP_FILE");
+  const std::string path = std::string(prefix ? prefix : "/tmp/bccl_trace_rank_") + std::to_string(rank_);
+  if (FILE* f = std::fopen(path.c_str(), "w")) {
+    const std::string js = recorder_.dump_json();
+    std::fwrite(js.data(), 1, js.size(), f);
+    std::fclose(f);
+  }
+}
+
+// Which collective did every rank reach?  Each rank publishes the sequence number it is stuck on; whoever
+// timed out logs the table, which names the rank that fell behind (or never called the collective).
+void ProcessGroupBCCL::report_desync(uint64_t seq) {
+  try {
+    store_->set("bccl/desync/" + std::to_string(rank_), std::to_string(seq));
+    std::ostringstream os;
+    for (int r = 0; r < size_; ++r) {
+      const std::string key = "bccl/desync/" + std::to_string(r);
+      if (store_->check({key})) {
+        auto v = store_->get(key);
+        os << " rank " << r << ": seq " << std::string(v.begin(), v.end()) << ";";
+      } else {
+        os << " rank " << r << ": no time-out reported;";
+      }
+    }
+    LOG(ERROR) << "bccl desync report from rank " << rank_ << " (stuck at seq " << seq << "):" << os.str();
+  } catch (...) {
   }
 }
 

@@ -45,6 +45,7 @@ struct FlightRecord {
   bool fused = false; // ran on the backend's own P2P kernel
   double created_s = 0, completed_s = 0;
   float duration_ms = -1.f;
+  std::string stack;  // C++ backtrace of the caller (BCCL_TRACE_CPP_STACK=1)
 };
 
 class FlightRecorder {
@@ -213,6 +214,10 @@ class B200_EXPORT ProcessGroupBCCL final : public c10d::Backend {
   std::mutex monitor_mu_;
   std::condition_variable monitor_cv_;
   bool monitoring_ = true, propagate_error_ = true, dump_on_timeout_ = false;
+  bool trace_stack_ = false, desync_debug_ = false;
+  int async_error_handling_ = 1;
+  void dump_trace_file();
+  void report_desync(uint64_t seq);
   int heartbeat_timeout_s_ = 480;
   std::mutex work_mu_;
   std::condition_variable work_cv_;

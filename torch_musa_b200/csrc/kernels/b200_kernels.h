@@ -139,6 +139,24 @@ B200_API int b200_topk_small(void* vals, int64_t* idxs, const void* in, int dtyp
 B200_API int b200_sort_rows(void* temp, size_t* temp_bytes, const void* keys_in, void* keys_out, int64_t* vals_out, int dtype,
                             int64_t rows, int64_t cols, int descending, cudaStream_t stream);
 
+/* ---- selection (kernels/select_ops.cu).  Entry points with `temp` follow the two-call convention: temp == NULL writes
+ * the scratch size to *temp_bytes. */
+/* out[r, j] = insertion point of vals[r, j] in the sorted row bounds[r (or 0 when shared), :]; sorter: optional permutation */
+B200_API int b200_searchsorted(void* out, int out_i32, const void* bounds, const void* vals, const int64_t* sorter, int dtype,
+                               int64_t rows, int64_t nv, int64_t nb, int shared_bounds, int right, cudaStream_t stream);
+/* counts[bins] (fp32, zeroed by the caller) += histogram of x over [lo, hi] */
+B200_API int b200_histc(float* counts, const void* x, int dtype, int64_t n, int bins, float lo, float hi, cudaStream_t stream);
+/* linear[n] (capacity) and count[1]: flat indices of the non-zero elements in order */
+B200_API int b200_nonzero_linear(void* temp, size_t* temp_bytes, int64_t* linear, int64_t* count, const void* x, int dtype,
+                                 int64_t n, cudaStream_t stream);
+/* coords[count, nd] from flat indices of a tensor of shape sizes[nd] (nd <= 8) */
+B200_API int b200_unravel(int64_t* coords, const int64_t* linear, const int64_t* count, int64_t capacity, const int64_t* sizes,
+                          int nd, cudaStream_t stream);
+/* keys sorted ascending (fp32 / int32 / int64): unique values, their counts, number of runs; run_id[n] (may be NULL) */
+B200_API int b200_unique_sorted(void* temp, size_t* temp_bytes, const void* keys, void* uniq, int64_t* counts,
+                                int64_t* num_runs, int64_t* run_id, int dtype, int64_t n, cudaStream_t stream);
+B200_API int b200_scatter_inverse(int64_t* inverse, const int64_t* run_id, const int64_t* perm, int64_t n, cudaStream_t stream);
+
 /* ---- 2-D pooling over [N, H, W, C] (kernels/pool.cu); idx = h * W + w of the maximum inside its image plane */
 typedef struct {
   int64_t N, H, W, C, Ho, Wo;
