@@ -208,7 +208,7 @@ def test_group_norm(bw, dev, dt):
     x = torch.randn(3, 32, 7, 5).to(dt)
     w, b = torch.rand(32) + 0.5, torch.randn(32)
     g = torch.randn(3, 32, 7, 5).to(dt)
-    xr, wr, br = x.float().requires_grad_(), w.clone().requires_grad_(), b.clone().requires_grad_()
+    xr, wr, br = x.clone().float().requires_grad_(), w.clone().requires_grad_(), b.clone().requires_grad_()
     yr = torch.nn.functional.group_norm(xr, 8, wr, br, 1e-5)
     yr.backward(g.float())
     xd = x.to(dev).requires_grad_()

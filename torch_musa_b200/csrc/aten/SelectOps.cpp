@@ -1,6 +1,7 @@
 // searchsorted / bucketize, histc, nonzero, unique and group norm on the backend's own kernels.
 // Data-dependent output sizes (nonzero, unique) read one count back from the device, as the operators' contracts
 // require.  Parity: reference torch_musa/csrc/aten/ops/{Bucketize,Unique,Nonzero,Histc,GroupNorm}.cpp.
+#include "aten/Loops.h"
 #include "aten/Ops.h"
 
 #include <ATen/Functions.h>
@@ -34,7 +35,7 @@ at::Tensor& searchsorted_out_impl(const at::Tensor& sorted, const at::Tensor& se
   at::native::resize_output(out, v.sizes());
   at::Tensor o = out.is_contiguous() ? out : at::empty(v.sizes(), out.options());
   B200_KERNEL_CALL(b200_searchsorted(o.data_ptr(), out_int32 ? 1 : 0, b.const_data_ptr(), v.const_data_ptr(),
-                                     so.defined() ? so.const_data_ptr<int64_t>() : nullptr, kdtype(dt), rows, nv, nb,
+                                     so.defined() ? so.const_data_ptr<int64_t>() : nullptr, loops::any_dtype(dt), rows, nv, nb,
                                      shared ? 1 : 0, right ? 1 : 0, current_raw_stream(self)));
   if (!o.is_same(out)) out.copy_(o);
   return out;
@@ -100,10 +101,10 @@ at::Tensor nonzero(const at::Tensor& self) {
   at::Tensor count = at::empty({1}, self.options().dtype(at::kLong));
   size_t bytes = 0;
   B200_KERNEL_CALL(b200_nonzero_linear(nullptr, &bytes, linear.data_ptr<int64_t>(), count.data_ptr<int64_t>(),
-                                       x.const_data_ptr(), kdtype(dt), n, stream));
+                                       x.const_data_ptr(), loops::any_dtype(dt), n, stream));
   at::Tensor temp = at::empty({(int64_t)bytes}, self.options().dtype(at::kByte));
   B200_KERNEL_CALL(b200_nonzero_linear(temp.data_ptr(), &bytes, linear.data_ptr<int64_t>(), count.data_ptr<int64_t>(),
-                                       x.const_data_ptr(), kdtype(dt), n, stream));
+                                       x.const_data_ptr(), loops::any_dtype(dt), n, stream));
   const int64_t nnz = count.item<int64_t>();  // the output shape depends on the data
   const int nd = (int)self.dim();
   at::Tensor coords = at::empty({nnz, nd}, self.options().dtype(at::kLong));
@@ -137,11 +138,11 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> unique2(const at::Tensor& self, b
   size_t bytes = 0;
   B200_KERNEL_CALL(b200_unique_sorted(nullptr, &bytes, keys.const_data_ptr(), uniq.data_ptr(), cnt.data_ptr<int64_t>(),
                                       runs.data_ptr<int64_t>(), run_id.defined() ? run_id.data_ptr<int64_t>() : nullptr,
-                                      kdtype(kd), n, stream));
+                                      loops::any_dtype(kd), n, stream));
   at::Tensor temp = at::empty({(int64_t)bytes}, self.options().dtype(at::kByte));
   B200_KERNEL_CALL(b200_unique_sorted(temp.data_ptr(), &bytes, keys.const_data_ptr(), uniq.data_ptr(), cnt.data_ptr<int64_t>(),
                                       runs.data_ptr<int64_t>(), run_id.defined() ? run_id.data_ptr<int64_t>() : nullptr,
-                                      kdtype(kd), n, stream));
+                                      loops::any_dtype(kd), n, stream));
   const int64_t m = runs.item<int64_t>();
   at::Tensor out = uniq.narrow(0, 0, m).to(dt);
   if (return_inverse) {
