@@ -280,3 +280,35 @@ def test_stream_guards_and_event_cache(bw, dev):
 def test_current_blas_handle(bw, dev):
     h = bw.current_blas_handle()
     assert isinstance(h, int) and h != 0
+
+
+def test_fft_plan_cache(bw, dev):
+    cache = torch.backends.blackwell.fft_plan_cache[bw.current_device()]
+    cache.clear()
+    x = torch.randn(8, 256, device=dev)
+    y = torch.fft.rfft(x)
+    assert torch.allclose(torch.view_as_real(y).cpu(), torch.view_as_real(torch.fft.rfft(x.cpu())), atol=1e-3)
+    assert cache.size >= 1
+    cache.max_size = 8
+    assert cache.max_size == 8
+
+
+def test_memory_snapshot_pickle_format(bw, dev, tmp_path):
+    """The dumped snapshot has the layout torch's memory visualiser reads: segments with blocks, device traces."""
+    import pickle
+
+    bw._record_memory_history(True, 1000, stacks="cpp")
+    keep = [torch.empty(1 << 20, device=dev) for _ in range(3)]
+    del keep[1]
+    path = str(tmp_path / "snap.pickle")
+    bw._dump_snapshot(path)
+    bw._record_memory_history(None)
+    snap = pickle.load(open(path, "rb"))
+    assert set(snap) >= {"segments", "device_traces"}
+    seg = snap["segments"][0]
+    assert {"address", "total_size", "allocated_size", "stream", "segment_type", "blocks"} <= set(seg)
+    assert {"size", "requested_size", "state"} <= set(seg["blocks"][0])
+    actions = {t["action"] for t in snap["device_traces"][bw.current_device()]}
+    assert {"alloc", "free_requested"} <= actions or {"alloc", "free_completed"} <= actions
+    allocs = [t for t in snap["device_traces"][bw.current_device()] if t["action"] == "alloc"]
+    assert allocs and "frames" in allocs[-1] and "alloc" in allocs[-1]["frames"].lower()   # symbolised call site

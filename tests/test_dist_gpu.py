@@ -448,3 +448,64 @@ def _dtensor_tp_body(rank, world):
 def test_dtensor_tensor_parallel_on_device(world):
     _need(world)
     run_ranks(_dtensor_tp_body, world, "bccl")
+
+
+def _fsdp1_body(rank, world):
+    import torch.distributed as dist
+    from torch.distributed.fsdp import FullyShardedDataParallel as FSDP
+    import torch_musa_b200 as bw  # noqa: F401
+
+    dev = torch.device("blackwell", rank)
+    torch.manual_seed(0)
+    ref = torch.nn.Sequential(torch.nn.Linear(64, 128), torch.nn.GELU(), torch.nn.Linear(128, 32))
+    model = torch.nn.Sequential(torch.nn.Linear(64, 128), torch.nn.GELU(), torch.nn.Linear(128, 32))
+    model.load_state_dict(ref.state_dict())
+    fsdp = FSDP(model.to(dev), device_id=dev, use_orig_params=True)
+    opt = torch.optim.SGD(fsdp.parameters(), lr=0.1)
+    ropt = torch.optim.SGD(ref.parameters(), lr=0.1)
+    for step in range(3):
+        torch.manual_seed(100 + step)
+        xs = torch.randn(world, 16, 64)
+        loss = fsdp(xs[rank].to(dev)).pow(2).mean()
+        loss.backward()
+        opt.step()
+        opt.zero_grad()
+        rloss = sum(ref(xs[r]).pow(2).mean() for r in range(world)) / world
+        rloss.backward()
+        ropt.step()
+        ropt.zero_grad()
+        tot = loss.detach().clone()
+        dist.all_reduce(tot)
+        assert abs(float(tot) / world - float(rloss)) < 1e-3, (step, float(tot) / world, float(rloss))
+    with FSDP.summon_full_params(fsdp):
+        for (n, p), (_, q) in zip(fsdp.named_parameters(), ref.named_parameters()):
+            assert torch.allclose(p.detach().cpu(), q.detach(), atol=1e-4), n
+
+
+def test_fsdp1_wrapper_trains_on_device():
+    """The flat-parameter FSDP wrapper (device handle, streams, all-gather / reduce-scatter on bccl) at 2 ranks."""
+    _need(2)
+    run_ranks(_fsdp1_body, 2, "bccl")
+
+
+def test_data_parallel_comm_on_devices(bw=None):
+    """broadcast / scatter / gather / reduce_add between two GPUs of one process, and the DataParallel wrapper."""
+    import torch_musa_b200 as bw
+    from torch_musa_b200.parallel import data_parallel as dp
+
+    _need(2)
+    d0, d1 = torch.device("blackwell", 0), torch.device("blackwell", 1)
+    x = torch.arange(24, dtype=torch.float32).view(6, 4)
+    copies = dp.broadcast(x.to(d0), [0, 1])
+    assert [c.device.index for c in copies] == [0, 1] and all(torch.equal(c.cpu(), x) for c in copies)
+    parts = dp.scatter(x.to(d0), [0, 1])
+    assert parts[1].device.index == 1 and torch.equal(parts[1].cpu(), x[3:])
+    assert torch.equal(dp.gather(parts, 0, destination=0).cpu(), x)
+    assert torch.equal(dp.reduce_add([x.to(d0), (2 * x).to(d1)], destination=1).cpu(), 3 * x)
+    torch.manual_seed(0)
+    m = torch.nn.Linear(4, 3)
+    wrapped = dp.DataParallel(torch.nn.Linear(4, 3).to(d0), device_ids=[0, 1])
+    wrapped.module.load_state_dict(m.state_dict())
+    out = wrapped(x.to(d0))
+    assert out.device.index == 0 and torch.allclose(out.cpu(), m(x), atol=1e-5)
+    bw.synchronize()

@@ -293,6 +293,13 @@ class _Backends:
     def version():
         return tuple(int(x) for x in (torch.version.cuda or "0.0").split("."))
 
+    @property
+    def fft_plan_cache(self):
+        """FFT plan caches, one per device (``[i].size``, ``[i].max_size``, ``[i].clear()``).  Transforms run as library
+        FFTs over the same memory, so the cache that matters is the library's cache of the device with the same
+        ordinal.  Parity: reference torch_musa/csrc/aten/mufft (plan cache of its FFT library)."""
+        return torch.backends.cuda.cufft_plan_cache
+
     class flags:
         """Context manager that sets ``allow_tf32`` for a block."""
 

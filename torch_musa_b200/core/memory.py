@@ -117,10 +117,12 @@ def memory_snapshot(device: Any = None):
     return _C()._snapshot(-1 if device is None else _get_device_index(device))
 
 
-def _record_memory_history(enabled: Optional[Union[str, bool]] = "all", max_entries: int = 100000, **kwargs) -> None:
-    """Start/stop recording allocator events (alloc/free/segment/oom) into a ring buffer."""
+def _record_memory_history(enabled: Optional[Union[str, bool]] = "all", max_entries: int = 100000,
+                           stacks: Optional[str] = None, **kwargs) -> None:
+    """Start/stop recording allocator events (alloc/free/segment/oom) into a ring buffer.  ``stacks="cpp"`` (or
+    ``"all"``) also stores the symbolised C++ frames of every allocation site in the trace (key ``frames``)."""
     _lazy_init()
-    _C()._record_memory_history(bool(enabled) and enabled != "none", int(max_entries))
+    _C()._record_memory_history(bool(enabled) and enabled != "none", int(max_entries), stacks in ("cpp", "all"))
 
 
 def _snapshot(device: Any = None) -> Dict[str, Any]:

@@ -1,5 +1,6 @@
 #include "core/CachingAllocator.h"
 
+#include <c10/util/Backtrace.h>
 #include <c10/util/Exception.h>
 #include <c10/util/irange.h>
 
@@ -789,8 +790,9 @@ class DeviceAllocatorImpl {
     return it == private_.end() ? 0 : it->second->use_count;
   }
 
-  void set_history(bool on, size_t max_entries) {
+  void set_history(bool on, size_t max_entries, bool stacks = false) {
     std::lock_guard<std::mutex> lk(mu_);
+    history_stacks_ = on && stacks;
     history_ = on;
     history_max_ = max_entries ? max_entries : 1;
     if (!on) trace_.clear();
@@ -822,7 +824,10 @@ class DeviceAllocatorImpl {
   void trace(TraceEntry::Action a, void* p, size_t n, cudaStream_t s) {
     if (!history_) return;
     if (trace_.size() >= history_max_) trace_.pop_front();
-    trace_.push_back(TraceEntry{a, device_, (uintptr_t)p, n, s, now_ns()});
+    trace_.push_back(TraceEntry{a, device_, (uintptr_t)p, n, s, now_ns(), {}});
+    // symbolised C++ frames of the caller (allocation sites); only while asked for: it costs tens of microseconds
+    if (history_stacks_ && (a == TraceEntry::ALLOC || a == TraceEntry::SEGMENT_ALLOC || a == TraceEntry::OOM))
+      trace_.back().stack = c10::get_backtrace(/*frames_to_skip=*/3, /*maximum_number_of_frames=*/20);
   }
 
   PrivatePool* ensure_pool(MempoolId id) {
@@ -1391,7 +1396,7 @@ class DeviceAllocatorImpl {
   bool limited_ = false;
   double fraction_ = 1.0;
   size_t allowed_ = 0;
-  bool history_ = false;
+  bool history_ = false, history_stacks_ = false;
   size_t history_max_ = 1;
   std::deque<TraceEntry> trace_;
 };
@@ -1678,8 +1683,8 @@ int CachingAllocator::pool_use_count(int device, MempoolId pool) {
 }
 
 void CachingAllocator::attach_oom_observer(OomObserver o) { g_observers.push_back(std::move(o)); }
-void CachingAllocator::record_history(bool enabled, size_t max_entries) {
-  for (auto& d : devs_) d->set_history(enabled, max_entries);
+void CachingAllocator::record_history(bool enabled, size_t max_entries, bool stacks) {
+  for (auto& d : devs_) d->set_history(enabled, max_entries, stacks);
 }
 std::vector<TraceEntry> CachingAllocator::trace(int device) {
   if ((int)devs_.size() <= device) return {};

@@ -148,6 +148,7 @@ struct TraceEntry {
   size_t size;
   cudaStream_t stream;
   uint64_t time_ns;
+  std::string stack;  // symbolised caller frames (record_history(..., stacks=true))
 };
 
 using OomObserver = std::function<void(int device, size_t requested, size_t total, size_t free_b)>;
@@ -212,7 +213,7 @@ class B200_EXPORT CachingAllocator final : public c10::Allocator {
   void refresh_peer_access(int device);
 
   void attach_oom_observer(OomObserver o);
-  void record_history(bool enabled, size_t max_entries);
+  void record_history(bool enabled, size_t max_entries, bool stacks = false);
   std::vector<TraceEntry> trace(int device);
   static MempoolId new_pool_id(bool user_created);
 

@@ -124,6 +124,7 @@ py::list trace(int device) {
     d["stream"] = (uintptr_t)t.stream;
     d["device"] = t.device;
     d["time_us"] = t.time_ns / 1000;
+    if (!t.stack.empty()) d["frames"] = t.stack;
     out.append(d);
   }
   return out;
@@ -336,7 +337,9 @@ PYBIND11_MODULE(_C, m) {
   m.def("_get_memory_fraction", [](int d) { return alloc::get()->get_memory_fraction(d); });
   m.def("_snapshot", &snapshot, py::arg("device") = -1);
   m.def("_trace", &trace);
-  m.def("_record_memory_history", [](bool on, size_t max_entries) { alloc::get()->record_history(on, max_entries); });
+  m.def("_record_memory_history", [](bool on, size_t max_entries, bool stacks) {
+    alloc::get()->record_history(on, max_entries, stacks);
+  }, py::arg("enabled"), py::arg("max_entries"), py::arg("stacks") = false);
   m.def("_allocator_backend", [] { return alloc::backend_name(); });
   m.def("_set_allocator_settings", [](const std::string& s) { alloc::set_config_string(s); });
   m.def("_allocator_config", [] {
