@@ -61,6 +61,20 @@ def test_sharded_adamw_single_process_matches_torch():
         o.step()
         r.step()
     assert max(float((p.float() - q).abs().max()) for p, q in zip(ps, ref)) < 4e-3
+    # checkpoint round trip: a fresh optimizer over fresh parameters continues exactly where this one stands
+    sd = o.state_dict()
+    ps2 = [torch.nn.Parameter(torch.zeros_like(p)) for p in ps]
+    o2 = ShardedFusedAdamW(ps2, lr=1.0, weight_decay=0.0, bucket_mb=1)
+    o2.load_state_dict(sd)
+    assert all(torch.equal(a, b) for a, b in zip(ps, ps2))
+    for opt, params in ((o, ps), (o2, ps2)):
+        opt.zero_grad()
+        for p in params:
+            p.grad.copy_(torch.ones_like(p) * 0.25)
+        opt.step()
+    assert all(torch.equal(a, b) for a, b in zip(ps, ps2))
+    full = o.full_state_dict()
+    assert full["state"][0]["exp_avg"].shape == ps[0].shape and full["param_groups"][0]["lr"] == 1e-2
 
 
 def test_comm_helpers_on_cpu_tensors():

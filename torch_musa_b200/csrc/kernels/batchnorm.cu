@@ -12,6 +12,8 @@
 // Conv+BN+activation fused modules in torch_musa/core/ao.
 #include "common.cuh"
 
+#include <cstdlib>
+
 namespace b200k {
 namespace {
 
@@ -30,7 +32,11 @@ inline BnGeom bn_geom(int64_t P, int C) {
   while (g.tx * 2 <= cv && g.tx < 32 && cv % (g.tx * 2) == 0) g.tx *= 2;
   g.ty = kBnThreads / g.tx;
   g.gx = cv / g.tx;
-  int64_t want = (int64_t)kSMs * 8 / g.gx;
+  static const int mult = [] {
+    const char* e = std::getenv("B200_BN_GRID_MULT");
+    return e ? std::max(1, std::atoi(e)) : 8;
+  }();
+  int64_t want = (int64_t)kSMs * mult / g.gx;
   if (want < 1) want = 1;
   const int64_t max_y = cdiv(P, (int64_t)g.ty);
   g.gy = (int)std::min<int64_t>(std::max<int64_t>(want, 1), std::max<int64_t>(max_y, 1));

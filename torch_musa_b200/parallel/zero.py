@@ -120,3 +120,54 @@ class ShardedFusedAdamW:
             st = self.sm.take_status()
             if st:
                 raise RuntimeError(f"a sharded-optimizer kernel gave up on a bounded wait (status {st})")
+
+    # ------------------------------------------------------------------ checkpointing
+    def state_dict(self) -> dict:
+        """This rank's shard of the optimizer state (fp32 master weights and both moments, bucket-major as the step
+        uses them) plus the hyper-parameters; save one per rank, or gather with ``full_state_dict``."""
+        return {"step": float(self.step_t), "lr": self.lr, "betas": tuple(self.betas), "eps": self.eps,
+                "weight_decay": self.wd, "world": self.world, "rank": self.rank, "bucket_elems": self.bs,
+                "master": self.p32.detach().cpu(), "exp_avg": self.m.detach().cpu(), "exp_avg_sq": self.v.detach().cpu()}
+
+    def load_state_dict(self, sd: dict) -> None:
+        if sd["world"] != self.world or sd["rank"] != self.rank or sd["bucket_elems"] != self.bs:
+            raise ValueError("optimizer shard was saved for a different world size, rank or bucket size")
+        self.lr, self.betas, self.eps, self.wd = sd["lr"], tuple(sd["betas"]), sd["eps"], sd["weight_decay"]
+        self.step_t.fill_(sd["step"])
+        with torch.no_grad():
+            self.p32.copy_(sd["master"])
+            self.m.copy_(sd["exp_avg"])
+            self.v.copy_(sd["exp_avg_sq"])
+            # parameters follow the restored master weights
+            chunk = self.bs * self.world
+            for b in range(self.n_buckets):
+                self.p16.copy_(self.p32[b * self.bs:(b + 1) * self.bs])
+                out = self.flat_p[b * chunk:(b + 1) * chunk]
+                if self.world > 1:
+                    dist.all_gather_into_tensor(out, self.p16, group=self.group)
+                else:
+                    out.copy_(self.p16)
+
+    def full_state_dict(self) -> dict:
+        """Per-parameter ``exp_avg`` / ``exp_avg_sq`` / fp32 master tensors in the parameters' shapes, assembled from
+        every rank's shard (a collective call).  The layout torch's AdamW uses, for tools that expect it."""
+        def gather(shard: torch.Tensor) -> torch.Tensor:
+            chunk = self.bs * self.world
+            full = torch.empty(self.n_buckets * chunk, dtype=shard.dtype, device=shard.device)
+            for b in range(self.n_buckets):
+                out = full[b * chunk:(b + 1) * chunk]
+                piece = shard[b * self.bs:(b + 1) * self.bs].contiguous()
+                if self.world > 1:
+                    dist.all_gather_into_tensor(out, piece, group=self.group)
+                else:
+                    out.copy_(piece)
+            return full
+        flats = {"master": gather(self.p32), "exp_avg": gather(self.m), "exp_avg_sq": gather(self.v)}
+        state, off = {}, 0
+        for i, p in enumerate(self.params):
+            n = p.numel()
+            state[i] = {k: v[off:off + n].view_as(p).cpu() for k, v in flats.items()}
+            state[i]["step"] = float(self.step_t)
+            off += n
+        return {"state": state, "param_groups": [{"lr": self.lr, "betas": tuple(self.betas), "eps": self.eps,
+                                                  "weight_decay": self.wd, "params": list(range(len(self.params)))}]}
