@@ -229,3 +229,31 @@ def test_pooling_forward_backward(bw, dev, cl, dt):
         o.backward(g.to(dt).to(dev))
         assert torch.allclose(xd.grad.float().cpu(), xr.grad, atol=tol * 4, rtol=tol * 4)
     assert not any("pool" in k for k in bw.fallback_counts()), bw.fallback_counts()
+
+
+def test_deterministic_mode(bw, dev):
+    """With deterministic algorithms on, the weight gradient is bit-identical from run to run (no split over pixels),
+    and index_put_ with accumulate leaves its atomic kernel for the sort-based route."""
+    torch.manual_seed(0)
+    x = torch.randn(8, 64, 28, 28, dtype=torch.bfloat16, device=dev).contiguous(memory_format=torch.channels_last)
+    w = (torch.randn(64, 64, 3, 3, dtype=torch.bfloat16, device=dev) * 0.05).contiguous(memory_format=torch.channels_last)
+    g = torch.randn(8, 64, 28, 28, dtype=torch.bfloat16, device=dev).contiguous(memory_format=torch.channels_last)
+
+    def wgrad():
+        wd = w.detach().requires_grad_()
+        F.conv2d(x, wd, None, 1, 1).backward(g)
+        return wd.grad.float()
+
+    base = wgrad()
+    torch.use_deterministic_algorithms(True)
+    try:
+        a, b = wgrad(), wgrad()
+        assert torch.equal(a, b)
+        assert rel_err(a, base) < 1e-2
+        t = torch.zeros(16, device=dev)
+        bw.reset_fallback_counts()
+        t.index_put_((torch.tensor([1, 1, 3], device=dev),), torch.ones(3, device=dev), accumulate=True)
+        assert t.cpu().tolist()[:4] == [0.0, 2.0, 0.0, 1.0]
+        assert any("index_put" in k for k in bw.fallback_counts())
+    finally:
+        torch.use_deterministic_algorithms(False)

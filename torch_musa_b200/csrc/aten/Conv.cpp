@@ -16,6 +16,7 @@
 #include "aten/FallbackCall.h"
 #include "aten/Ops.h"
 
+#include <ATen/Context.h>
 #include <ATen/Functions.h>
 #include <torch/library.h>
 
@@ -214,12 +215,15 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> implicit_backward(const at::Tenso
   if (mask[1] && stem_eligible(input, weight, stride, padding, &sd)) {
     const at::Tensor xp = stem_padded_image(input, sd, /*forward=*/false);
     at::Tensor acc = at::zeros({sd.K, sd.R, 8, 8}, input.options().dtype(at::kFloat));
+    if (at::globalContext().deterministicAlgorithms())
+      at::globalContext().alertNotDeterministic("the row-packed first-layer weight gradient (fp32 atomics over pixel splits)");
     B200_KERNEL_CALL(b200_conv_stem_wgrad(&sd, acc.data_ptr<float>(), gy.const_data_ptr(), xp.const_data_ptr(), stream));
     gw = acc.narrow(2, 0, sd.S).narrow(3, 0, C).permute({0, 3, 1, 2}).to(weight.scalar_type());  // [K, C, R, S]
     const bool cl = weight.is_contiguous(at::MemoryFormat::ChannelsLast) && !weight.is_contiguous();
     gw = gw.contiguous(cl ? at::MemoryFormat::ChannelsLast : at::MemoryFormat::Contiguous);
   } else if (mask[1]) {
     at::Tensor acc = at::zeros({d.K, d.R, d.S, d.C}, x.options().dtype(at::kFloat));
+    b200_conv_set_deterministic(at::globalContext().deterministicAlgorithms() ? 1 : 0);
     B200_KERNEL_CALL(b200_conv_wgrad(&d, acc.data_ptr<float>(), gy.const_data_ptr(), x.const_data_ptr(), stream));
     gw = acc.to(weight.scalar_type()).permute({0, 3, 1, 2});  // [K, C, R, S] with channels-last strides
     if (x.size(1) != C) gw = gw.narrow(1, 0, C);

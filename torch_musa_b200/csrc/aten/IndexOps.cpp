@@ -8,6 +8,7 @@
 #include "aten/Loops.h"
 #include "core/DeviceAssert.h"
 
+#include <ATen/Context.h>
 #include <ATen/ExpandUtils.h>
 #include <ATen/Functions.h>
 #include <ATen/TensorOperators.h>
@@ -295,7 +296,11 @@ at::Tensor& index_put_impl_(at::Tensor& self, const c10::List<std::optional<at::
     if (shapes_ok) {
       at::Tensor target = self.is_contiguous() ? self : self.contiguous();
       const int64_t J = a.flat.numel();
-      if (J > 0 && outer * inner > 0) {
+      // accumulating floating-point values with atomics adds in an order that varies between runs: with
+      // deterministic algorithms requested the sort-based library path below runs instead
+      const bool atomics_unwanted = accumulate && at::isFloatingType(self.scalar_type()) &&
+                                    at::globalContext().deterministicAlgorithms();
+      if (J > 0 && outer * inner > 0 && !atomics_unwanted) {
         DeviceSwitch sw(self.device().index());
         int e = b200_index_put(target.mutable_data_ptr(), v.const_data_ptr(), a.flat.const_data_ptr(), B200_I64,
                                loops::any_dtype(self.scalar_type()), accumulate ? 1 : 0, outer, block, inner, J, inner,
@@ -305,7 +310,7 @@ at::Tensor& index_put_impl_(at::Tensor& self, const c10::List<std::optional<at::
           if (!target.is_same(self)) self.copy_(target);
           return self;
         }
-      } else {
+      } else if (!atomics_unwanted) {
         return self;
       }
     }

@@ -1,5 +1,7 @@
 #include "distributed/ProcessGroupBCCL.h"
 
+#include <ATen/record_function.h>
+
 #include <cstdio>
 
 #include "aten/Ops.h"
@@ -345,6 +347,8 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupBCCL::collective(c10d::OpType type, c
               "bccl: this process group is in an error state (a previous collective timed out or failed)");
   const at::Tensor& ref = !outputs.empty() ? outputs[0] : inputs[0];
   const c10::DeviceIndex dev = ref.device().index();
+  // a profiler range per collective, with the tensors as its inputs (sizes and dtypes show up in traces)
+  RECORD_FUNCTION(std::string("bccl:") + name, std::vector<c10::IValue>(inputs.begin(), inputs.end()));
   DeviceSwitch sw(dev);
   Comm& c = get_comm(dev);
   const uint64_t seq = ++seq_;

@@ -182,6 +182,8 @@ B200_API int b200_conv_fwd(const b200_conv_t* d, void* y, const void* x, const v
                            int relu, cudaStream_t stream);
 B200_API int b200_conv_dgrad(const b200_conv_t* d, void* dx, const void* dy, const void* w, cudaStream_t stream);
 B200_API int b200_conv_wgrad(const b200_conv_t* d, float* dw_f32, const void* dy, const void* x, cudaStream_t stream);
+/* on: the weight gradient is not split over pixels (one CTA per output tile, fixed order): bit-reproducible, slower */
+B200_API void b200_conv_set_deterministic(int on);
 /* Few-channel first layers (C == 8 after padding, S * 8 <= 64): xpad[N, H + 2 ph, W + 2 pw, 8] is the image with its
  * zero border written out, wpack[K][R][64] holds filter row r as element s * 8 + c (zero tail); one K step covers a
  * whole filter row.  wgrad adds into dwpack_f32[K][R][64]. */

@@ -638,6 +638,11 @@ extern "C" int b200_conv_dgrad(const b200_conv_t* d, void* dx, const void* dy, c
   return 0;
 }
 
+namespace b200k { namespace convdev { bool g_wgrad_deterministic = false; } }
+// With `on`, every output tile of the weight gradient is produced by ONE CTA in a fixed pixel order (no split over
+// pixels, so no fp32 atomics whose order varies from run to run): slower, bit-reproducible.
+extern "C" void b200_conv_set_deterministic(int on) { g_wgrad_deterministic = on != 0; }
+
 extern "C" int b200_conv_wgrad(const b200_conv_t* d, float* dw_f32, const void* dy, const void* x,
                                cudaStream_t stream) {
   if (!supported(d)) return (int)cudaErrorNotSupported;
@@ -677,7 +682,7 @@ extern "C" int b200_conv_wgrad(const b200_conv_t* d, float* dw_f32, const void* 
     return (int)cudaErrorInvalidValue;
   const int out_tiles = p.tiles_m * p.n_taps * p.tiles_nc;
   const int pix_tiles = p.tiles_n * p.tiles_h * p.tiles_w;
-  int splits = std::max(1, (2 * sm_count() + out_tiles - 1) / out_tiles);
+  int splits = g_wgrad_deterministic ? 1 : std::max(1, (2 * sm_count() + out_tiles - 1) / out_tiles);
   splits = std::min(splits, pix_tiles);
   p.steps_per_split = (pix_tiles + splits - 1) / splits;
   p.splits = (pix_tiles + p.steps_per_split - 1) / p.steps_per_split;
