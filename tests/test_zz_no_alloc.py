@@ -82,3 +82,24 @@ def test_static_l2norm_rejects_oversize_lists(bw, dev):
     assert rc == 1  # cudaErrorInvalidValue: refused before anything is launched
     bw.synchronize()
     assert float(out) == 0.0
+
+
+@pytest.mark.parametrize("n_tensors", [300, 1024])
+def test_static_l2norm_many_tensors_without_per_tensor_output(bw, dev, n_tensors):
+    """The cases that depend on the fixed sizing: several clean-up batches (more than 128 tensors), the 1024-tensor
+    boundary, and no per-tensor output (the per-tensor norms then live in the array's last n floats)."""
+    lib = _lib()
+    bw.set_device(0)
+    stream = bw.current_stream().cuda_stream
+    torch.manual_seed(n_tensors)
+    sizes = [1 + (i * 37) % 513 for i in range(n_tensors)]
+    sizes[7] = 300001                                   # one tensor that spans many chunks
+    tensors = [torch.randn(s, device=dev) for s in sizes]
+    n, ptrs, numels = _args(tensors)
+    for _ in range(2):
+        tot = torch.zeros(1, device=dev)
+        rc = lib.b200_multi_tensor_l2norm_static(n, B200_F32, ptrs, numels, tot.data_ptr(), None, stream)
+        assert rc == 0, rc
+        bw.synchronize()
+        ref = torch.cat([t.cpu().double().reshape(-1) for t in tensors]).norm()
+        assert float(tot) == pytest.approx(float(ref), rel=1e-5)

@@ -15,7 +15,9 @@
  *             cudaErrorInvalidValue and nothing is launched.  The array is 1024 * 321 + 8 floats
  *             (about 1.3 MB) and stays resident on each device until the process exits.
  *   Set-up    the first call on a device looks up the array's device address (with that device
- *             current) and caches it; make that first call before starting any stream capture.
+ *             current) and caches it; make that first call before starting any stream capture.  The
+ *             first call on a device may come from any thread: concurrent first calls all store the
+ *             same address into the cache, so no lock is taken.
  *   Sharing   every call on a device uses the same array and leaves its partial sums behind.  Each
  *             call overwrites every slot it later reads, so nothing has to be cleared between calls,
  *             but two calls that overlap on the GPU (different streams, no ordering) race on the
