@@ -3,6 +3,8 @@
 replayed from a device graph.
 
   python benchmark/decode_bench.py [--batch 32] [--kv 2048] [--layers 32] [--tokens 32]
+  python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 benchmark/decode_bench.py   (tensor parallel:
+      every rank holds 1/W of the heads and of the KV cache, two all-reduces per layer inside the captured step)
 
 One JSON line: {"op": "decode", "batch", "kv_len", "eager_ms_per_token", "graph_ms_per_token", "graph_tokens_per_s", ...}.
 Random-init bf16 weights, random prompt; CUDA-event times after warm-up.
@@ -22,7 +24,7 @@ import torch  # noqa: E402
 
 import torch_musa_b200 as bw  # noqa: E402
 from torch_musa_b200.models import Llama, LlamaConfig  # noqa: E402
-from torch_musa_b200.models.decode import LlamaDecoder  # noqa: E402
+from torch_musa_b200.models.decode import LlamaDecoder, shard_for_tensor_parallel  # noqa: E402
 
 
 def main():
@@ -32,8 +34,18 @@ def main():
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--tokens", type=int, default=32)
     a = ap.parse_args()
-    dev = torch.device("blackwell:0")
-    cfg = LlamaConfig(n_layers=a.layers, max_seq_len=a.kv + a.tokens * 3 + 8)
+    world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("blackwell", local)
+    group = None
+    if world > 1:
+        import torch.distributed as dist
+
+        bw.set_device(local)
+        dist.init_process_group("bccl", rank=rank, world_size=world)
+        group = dist.group.WORLD
+    cfg = LlamaConfig(n_layers=a.layers, max_seq_len=a.kv + a.tokens * 3 + 8, fused_qkv=world == 1,
+                      fused_gate_up=world == 1)
     torch.manual_seed(0)
     with torch.device(dev):
         model = Llama(cfg).to(torch.bfloat16).eval()
@@ -42,8 +54,11 @@ def main():
         for p in model.parameters():
             if p.dim() >= 2:
                 p.normal_(0.0, 0.02)
-    prompt = torch.randint(0, cfg.vocab_size, (a.batch, a.kv), device=dev)
-    dec = LlamaDecoder(model, a.batch, cfg.max_seq_len, device=dev)
+    if world > 1:
+        shard_for_tensor_parallel(model, rank, world)
+    torch.manual_seed(1)
+    prompt = torch.randint(0, cfg.vocab_size, (a.batch, a.kv)).to(dev)
+    dec = LlamaDecoder(model, a.batch, cfg.max_seq_len, device=dev, tp_group=group)
     dec.prefill(prompt)
 
     def timed(n):
@@ -60,9 +75,18 @@ def main():
     dec.capture()
     dec.decode(4)
     graph = timed(a.tokens)
-    print(json.dumps({"op": "decode", "model": f"llama-7b dims, {a.layers} layers", "batch": a.batch, "kv_len": a.kv,
+    if world > 1:
+        t = torch.tensor([eager, graph], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)          # max over ranks
+        eager, graph = float(t[0]), float(t[1])
+        if rank != 0:
+            dist.destroy_process_group()
+            return
+    print(json.dumps({"op": "decode", "tp": world, "model": f"llama-7b dims, {a.layers} layers", "batch": a.batch, "kv_len": a.kv,
                       "eager_ms_per_token": round(eager, 3), "graph_ms_per_token": round(graph, 3),
                       "graph_tokens_per_s": round(a.batch / graph * 1e3, 1), "speedup": round(eager / graph, 2)}))
+    if world > 1:
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

@@ -223,3 +223,29 @@ def test_custom_op_sharding_rules_are_registered():
     table = DTensor._op_dispatcher.sharding_propagator.op_strategy_funcs
     for name in ("silu_mul", "swiglu", "rope", "rms_norm_residual", "cross_entropy_fwd"):
         assert getattr(torch.ops.blackwell, name).default in table, name
+
+
+def _tp_decode_body(rank, world):
+    import copy
+    from torch_musa_b200.models import Llama, llama_tiny_config
+    from torch_musa_b200.models.decode import LlamaDecoder, shard_for_tensor_parallel
+
+    cfg = llama_tiny_config(fused_qkv=False, fused_gate_up=False, n_kv_heads=2)
+    torch.manual_seed(0)
+    full = Llama(cfg).eval()
+    prompt = torch.randint(0, cfg.vocab_size, (3, 6))
+    single = LlamaDecoder(copy.deepcopy(full), 3, 32)
+    single.prefill(prompt)
+    want = single.decode(6)
+    shard = shard_for_tensor_parallel(copy.deepcopy(full), rank, world)
+    assert shard.layers[0].attn.wq.weight.shape[0] == full.layers[0].attn.wq.weight.shape[0] // world
+    dec = LlamaDecoder(shard, 3, 32, tp_group=dist.group.WORLD)
+    assert dec.k_cache.shape[2] == cfg.kv_heads // world        # each rank caches its own heads only
+    dec.prefill(prompt)
+    got = dec.decode(6)
+    assert torch.equal(got, want), (got, want)
+
+
+def test_tensor_parallel_decode_matches_single_process():
+    """KV-cache decode with heads and cache sharded over 2 ranks produces the tokens of the unsharded decoder."""
+    run_ranks(_tp_decode_body, 2, "gloo")

@@ -115,6 +115,8 @@ std::string json_escape(const std::string& in) {
   return out;
 }
 
+bool capturing(cudaStream_t s);  // defined with the fused-collective helpers below
+
 bool env_flag(const char* name, bool dflt) {
   const char* e = std::getenv(name);
   if (!e) return dflt;
@@ -175,7 +177,7 @@ WorkBCCL::WorkBCCL(int rank, c10d::OpType op, uint64_t seq, c10::DeviceIndex dev
       end_(timing ? cudaEventDefault : cudaEventDisableTiming), timing_(timing) {}
 
 bool WorkBCCL::isCompleted() {
-  if (aborted_.load()) return true;
+  if (aborted_.load() || captured_) return true;
   {
     std::lock_guard<std::mutex> g(mutex_);
     if (exception_) return true;
@@ -204,6 +206,7 @@ bool WorkBCCL::wait(std::chrono::milliseconds timeout) {
     if (exception_) std::rethrow_exception(exception_);
   }
   blockCurrentStream();
+  if (captured_) return true;  // the wait above became an edge of the graph; events of a capture cannot be queried
   if (blocking_wait_ || timeout != ::kNoTimeout) {
     // host-side wait with a deadline: poll so a stuck collective turns into an exception, not a hang
     auto limit = timeout != ::kNoTimeout ? timeout : timeout_;
@@ -399,6 +402,13 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupBCCL::collective(c10d::OpType type, c
     if (it != symm_.end()) work->symm_ = it->second;
   }
   work->end_.record(c.stream);
+  if (capturing(cur.stream())) {
+    // Recorded into a graph: the communication stream forked from the capturing stream at `ready` and joins it
+    // again when the caller waits on the work.  The watchdog must not poll events that belong to a capture.
+    work->captured_ = true;
+    recorder_.complete(work->record_id_, "captured", -1.f);
+    return work;
+  }
   {
     // future completes on the communication stream
     StreamGuard sg(c.stream);

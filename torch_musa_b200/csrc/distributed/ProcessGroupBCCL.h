@@ -100,6 +100,7 @@ class WorkBCCL final : public c10d::Work {
   uint64_t record_id_ = 0;
   std::atomic<bool> aborted_{false};
   bool test_only_ = false;
+  bool captured_ = false;  // issued while a graph was being captured: ordering is the graph's, nothing to poll
   // set when the collective ran on a peer-memory kernel: its bounded waits report through this arena's status word
   std::shared_ptr<SymmetricMemory> symm_;
 };

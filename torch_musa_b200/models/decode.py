@@ -19,13 +19,55 @@ from ..ops import functional as BF
 from .llama import Llama
 
 
+def shard_for_tensor_parallel(model: Llama, rank: int, world: int) -> Llama:
+    """Keeps this rank's slice of every projection, in place: q/k/v and gate/up by output rows (whole heads), output
+    and down projections by input columns.  Norms, embedding and LM head stay replicated.  The model must use
+    separate q/k/v and gate/up projections."""
+    cfg = model.cfg
+    assert not cfg.fused_qkv and not cfg.fused_gate_up, "tensor-parallel decode needs fused_qkv=False, fused_gate_up=False"
+    assert cfg.n_heads % world == 0 and cfg.kv_heads % world == 0 and cfg.ffn_dim % world == 0
+
+    def rows(lin, n):
+        per = n // world
+        lin.weight = torch.nn.Parameter(lin.weight.detach()[rank * per:(rank + 1) * per].clone(), requires_grad=False)
+        lin.out_features = per
+
+    def cols(lin, n):
+        per = n // world
+        lin.weight = torch.nn.Parameter(lin.weight.detach()[:, rank * per:(rank + 1) * per].clone(), requires_grad=False)
+        lin.in_features = per
+
+    hd = cfg.head_dim
+    for layer in model.layers:
+        a, f = layer.attn, layer.ffn
+        rows(a.wq, cfg.n_heads * hd)
+        rows(a.wk, cfg.kv_heads * hd)
+        rows(a.wv, cfg.kv_heads * hd)
+        cols(a.wo, cfg.n_heads * hd)
+        rows(f.w1, cfg.ffn_dim)
+        rows(f.w3, cfg.ffn_dim)
+        cols(f.w2, cfg.ffn_dim)
+    return model
+
+
 class LlamaDecoder:
-    def __init__(self, model: Llama, batch: int, max_len: int, device=None, dtype: Optional[torch.dtype] = None):
+    """``tp_group``: the model was sharded with ``shard_for_tensor_parallel`` over this process group; every rank then
+    holds 1/W of the heads and of the KV cache, and the two row-parallel projections of a layer end in an all-reduce
+    (recorded into the graph like every other operation of the step)."""
+
+    def __init__(self, model: Llama, batch: int, max_len: int, device=None, dtype: Optional[torch.dtype] = None,
+                 tp_group=None):
         cfg = model.cfg
         self.model, self.cfg, self.B, self.max_len = model, cfg, batch, max_len
         self.device = torch.device(device) if device is not None else next(model.parameters()).device
         dt = dtype or next(model.parameters()).dtype
-        L, kv, hd = cfg.n_layers, cfg.kv_heads, cfg.head_dim
+        self.tp_group = tp_group
+        self.tp = 1
+        if tp_group is not None:
+            import torch.distributed as dist
+
+            self.tp = dist.get_world_size(tp_group)
+        L, kv, hd = cfg.n_layers, cfg.kv_heads // self.tp, cfg.head_dim
         self.k_cache = torch.zeros(L, batch, kv, max_len, hd, device=self.device, dtype=dt)
         self.v_cache = torch.zeros_like(self.k_cache)
         self.tokens = torch.zeros(batch, 1, dtype=torch.long, device=self.device)      # input of the next step
@@ -37,6 +79,13 @@ class LlamaDecoder:
         self._graph = None
         self._fused_decode = (self.device.type == "blackwell" and hd == 128 and dt in (torch.bfloat16, torch.float16))
 
+    def _reduce(self, t: torch.Tensor) -> torch.Tensor:
+        if self.tp > 1:
+            import torch.distributed as dist
+
+            dist.all_reduce(t, group=self.tp_group)
+        return t
+
     # ------------------------------------------------------------------ prefill (eager, whole prompt at once)
     @torch.no_grad()
     def prefill(self, prompt: torch.Tensor) -> None:
@@ -45,7 +94,7 @@ class LlamaDecoder:
         B, S0 = prompt.shape
         assert B == self.B and S0 < self.max_len
         m, cfg = self.model, self.cfg
-        hd, h, kv = cfg.head_dim, cfg.n_heads, cfg.kv_heads
+        hd, h, kv = cfg.head_dim, cfg.n_heads // self.tp, cfg.kv_heads // self.tp
         x = m.tok_emb(prompt)
         for li, layer in enumerate(m.layers):
             hn = layer.attn_norm(x)
@@ -59,8 +108,8 @@ class LlamaDecoder:
             self.v_cache[li, :, :, :S0] = v.transpose(1, 2)
             o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True,
                                                enable_gqa=(kv != h))
-            x = x + a.wo(o.transpose(1, 2).reshape(B, S0, h * hd))
-            x = x + layer.ffn(layer.ffn_norm(x))
+            x = x + self._reduce(a.wo(o.transpose(1, 2).reshape(B, S0, h * hd)))
+            x = x + self._reduce(layer.ffn(layer.ffn_norm(x)))
         logits = m.lm_head(m.norm(x[:, -1:]))
         self.tokens.copy_(logits.argmax(-1))
         self.pos.fill_(S0)
@@ -69,7 +118,7 @@ class LlamaDecoder:
     @torch.no_grad()
     def _step(self) -> None:
         m, cfg, B = self.model, self.cfg, self.B
-        hd, h, kv = cfg.head_dim, cfg.n_heads, cfg.kv_heads
+        hd, h, kv = cfg.head_dim, cfg.n_heads // self.tp, cfg.kv_heads // self.tp
         positions = self.pos.expand(B, 1)
         # keys at index <= pos are visible (additive mask, broadcast over batch and heads)
         mask = torch.where(self._arange <= self.pos, 0.0, float("-inf")).to(self.k_cache.dtype).view(1, 1, 1, self.max_len)
@@ -92,8 +141,8 @@ class LlamaDecoder:
             else:
                 o = F.scaled_dot_product_attention(q.transpose(1, 2), self.k_cache[li], self.v_cache[li], attn_mask=mask,
                                                    enable_gqa=(kv != h)).transpose(1, 2).reshape(B, 1, h * hd)
-            x = x + a.wo(o)
-            x = x + layer.ffn(layer.ffn_norm(x))
+            x = x + self._reduce(a.wo(o))
+            x = x + self._reduce(layer.ffn(layer.ffn_norm(x)))
         logits = m.lm_head(m.norm(x))
         self.next_tokens.copy_(logits.argmax(-1))
         self.tokens.copy_(self.next_tokens)
