@@ -165,3 +165,31 @@ def test_gemm_switch(bw, dev):
     finally:
         bw._C._set_tensor_core_gemm(True)
     assert torch.allclose(y1.float().cpu(), y2.float().cpu(), atol=0.25, rtol=2e-2)
+
+
+def test_fp32_matmul_as_tf32_on_tensor_cores(bw, dev):
+    """fp32 operands run on the tcgen05 kernel as tf32 when that precision is allowed, on the library GEMM otherwise."""
+    torch.manual_seed(0)
+    a, b = torch.randn(300, 520), torch.randn(520, 264)
+    bias = torch.randn(264)
+    ref = (a.double() @ b.double()).float()
+    ad, bd = a.to(dev), b.to(dev)
+    prev = torch.backends.blackwell.allow_tf32
+    try:
+        torch.backends.blackwell.allow_tf32 = False
+        bw.reset_fallback_counts()
+        strict = ad @ bd
+        assert any("mm" in k for k in bw.fallback_counts())
+        assert (strict.cpu() - ref).abs().max() < 1e-3
+        torch.backends.blackwell.allow_tf32 = True
+        bw.reset_fallback_counts()
+        fast = ad @ bd                                     # b is [K, N] row-major: re-laid out K-major first
+        lin = torch.nn.functional.linear(ad, bd.t().contiguous(), bias.to(dev))    # both operands K-major as stored
+        assert not any("mm" in k for k in bw.fallback_counts()), bw.fallback_counts()
+        scale = float(ref.abs().max())
+        assert (fast.cpu() - ref).abs().max() < 4e-3 * scale        # 10-bit mantissa
+        assert (fast.cpu() - ref).abs().max() > 1e-6 * scale        # ... so really not fp32 arithmetic
+        assert (lin.cpu() - (ref + bias)).abs().max() < 4e-3 * scale
+        assert bw._C._gemm_status() == 0
+    finally:
+        torch.backends.blackwell.allow_tf32 = prev

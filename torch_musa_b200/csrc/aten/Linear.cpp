@@ -8,6 +8,7 @@
 #include "aten/Ops.h"
 
 #include <ATen/ExpandUtils.h>
+#include <ATen/Context.h>
 #include <ATen/Functions.h>
 #include <ATen/native/Resize.h>
 #include <torch/library.h>
@@ -57,7 +58,13 @@ bool gemm_eligible(const at::Tensor& a, const at::Tensor& b) {
   if (!g_use_tc_gemm.load(std::memory_order_relaxed)) return false;
   auto dt = a.scalar_type();
   if (dt != b.scalar_type()) return false;
-  if (dt != at::kBFloat16 && dt != at::kHalf) return false;
+  // fp32 operands multiply on the tensor cores as tf32 when the caller allows that precision
+  // (torch.backends.blackwell.allow_tf32 / torch.set_float32_matmul_precision); strict fp32 is a library GEMM
+  if (dt == at::kFloat) {
+    if (!at::globalContext().allowTF32CuBLAS()) return false;
+  } else if (dt != at::kBFloat16 && dt != at::kHalf) {
+    return false;
+  }
   if (a.is_conj() || b.is_conj() || a.is_neg() || b.is_neg()) return false;
   if (!on_device(a) || !on_device(b) || a.device() != b.device()) return false;  // the generic route reports the mismatch
   return true;
@@ -70,6 +77,16 @@ bool run_gemm(const at::Tensor& out, const at::Tensor& a, const at::Tensor& b, c
   Operand A, B;
   if (!describe(a, nd - 1, &A)) return false;
   if (!describe(b, nd - 2, &B)) return false;
+  if (a.scalar_type() == at::kFloat) {
+    // the tf32 kernel reads both operands with the reduction dimension contiguous: re-lay out what is not
+    if (out.scalar_type() != at::kFloat || accumulate) return false;
+    if (!A.kmajor && !describe(a.contiguous(), nd - 1, &A)) return false;
+    if (!B.kmajor) {
+      const at::Tensor bt = b.transpose(nd - 2, nd - 1).contiguous().transpose(nd - 2, nd - 1);
+      if (!describe(bt, nd - 2, &B)) return false;
+    }
+    if (!A.kmajor || !B.kmajor) return false;
+  }
   b200_gemm_desc_t g{};
   g.m = (int)a.size(nd - 2);
   g.k = (int)a.size(nd - 1);

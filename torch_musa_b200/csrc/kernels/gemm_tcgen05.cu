@@ -39,7 +39,8 @@ constexpr int kStageBytes = kATileBytes + kBTileBytes;
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 constexpr uint32_t kTmemCols = 512;
 
-template <typename OutT, bool A_KMAJOR, bool B_KMAJOR>
+// TF32: fp32 operands (K-major only), 32 elements = 128 bytes per K block, kind::tf32.
+template <typename OutT, bool A_KMAJOR, bool B_KMAJOR, bool TF32 = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, OutT* __restrict__ d,
             const Params p) {
@@ -58,7 +59,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int k_blocks = (p.k + BK - 1) / BK;
+  constexpr int BKE = TF32 ? 32 : BK;  // elements per K block (always 128 bytes)
+  const int k_blocks = (p.k + BKE - 1) / BKE;
   const int tiles_per_batch = p.tiles_m * p.tiles_n;
   const int tiles_all_batches = tiles_per_batch * p.batch;
   const int total_tiles = tiles_all_batches * p.splits;
@@ -108,7 +110,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           mbar_expect_tx(&full_bar[stage], kStageBytes);
           uint8_t* sa = smem_a + stage * kATileBytes;
           uint8_t* sb = smem_b + stage * kBTileBytes;
-          const int k0 = kb * BK;
+          const int k0 = kb * BKE;
           if constexpr (A_KMAJOR) {
             tma_load_3d(sa, &tmap_a, &full_bar[stage], k0, m0, b);
           } else {
@@ -150,7 +152,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             // MN-major: 16 k-rows of 128 B = 2048 B; LBO = next 64-wide MN box (8 KB), SBO = 8 k-rows.
             const uint64_t adesc = A_KMAJOR ? make_desc(sa + kk * 32, 16, 1024) : make_desc(sa + kk * 2048, 8192, 1024);
             const uint64_t bdesc = B_KMAJOR ? make_desc(sb + kk * 32, 16, 1024) : make_desc(sb + kk * 2048, 8192, 1024);
-            umma_f16(tmem_d, adesc, bdesc, p.idesc, (kb > kb0 || kk != 0) ? 1u : 0u);
+            if constexpr (TF32) umma_tf32(tmem_d, adesc, bdesc, p.idesc, (kb > kb0 || kk != 0) ? 1u : 0u);
+            else umma_f16(tmem_d, adesc, bdesc, p.idesc, (kb > kb0 || kk != 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);  // slot reusable once these MMAs have read it
           if (++stage == kStages) { stage = 0; phase ^= 1; }
@@ -294,7 +297,9 @@ bool make_map(CUtensorMap* out, const void* ptr, int dtype, uint64_t inner, uint
   cuuint64_t strides[2] = {outer_stride_bytes, batch_stride_bytes ? batch_stride_bytes : outer_stride_bytes * outer};
   cuuint32_t box[3] = {box_inner, box_outer, 1};
   cuuint32_t estr[3] = {1, 1, 1};
-  CUtensorMapDataType dt = dtype == B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUtensorMapDataType dt = dtype == B200_BF16  ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                           : dtype == B200_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                               : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   CUresult r = enc(out, dt, 3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return false;
@@ -322,19 +327,22 @@ template <typename OutT>
 int launch(const b200_gemm_desc_t* g, void* d, const void* a, const void* b, cudaStream_t stream,
            const GemmPlan& plan) {
   CUtensorMap ma, mb;
-  const uint64_t esz = 2;
+  const bool tf32 = g->in_dtype == B200_F32;
+  const uint64_t esz = tf32 ? 4 : 2;
+  const uint32_t BKH = tf32 ? 32 : BK;  // elements per 128-byte K block
   const uint64_t batch = (uint64_t)std::max(g->batch, 1);
   bool ok;
+  if (tf32 && !(g->a_kmajor && g->b_kmajor)) return (int)cudaErrorNotSupported;
   if (g->a_kmajor)
     ok = make_map(&ma, a, g->in_dtype, (uint64_t)g->k, (uint64_t)g->m, batch, (uint64_t)g->lda * esz,
-                  (uint64_t)g->stride_a * esz, BK, BM);
+                  (uint64_t)g->stride_a * esz, BKH, BM);
   else
     ok = make_map(&ma, a, g->in_dtype, (uint64_t)g->m, (uint64_t)g->k, batch, (uint64_t)g->lda * esz,
                   (uint64_t)g->stride_a * esz, 64, BK);
   if (!ok) return (int)cudaErrorNotSupported;
   if (g->b_kmajor)
     ok = make_map(&mb, b, g->in_dtype, (uint64_t)g->k, (uint64_t)g->n, batch, (uint64_t)g->ldb * esz,
-                  (uint64_t)g->stride_b * esz, BK, BN);
+                  (uint64_t)g->stride_b * esz, BKH, BN);
   else
     ok = make_map(&mb, b, g->in_dtype, (uint64_t)g->n, (uint64_t)g->k, batch, (uint64_t)g->ldb * esz,
                   (uint64_t)g->stride_b * esz, 64, BK);
@@ -353,7 +361,7 @@ int launch(const b200_gemm_desc_t* g, void* d, const void* a, const void* b, cud
   p.accumulate = g->accumulate;
   p.alpha = g->alpha;
   // instruction descriptor: fp32 accumulate, A/B format, majors, N>>3, M>>4
-  const uint32_t fmt = g->in_dtype == B200_BF16 ? 1u : 0u;
+  const uint32_t fmt = g->in_dtype == B200_BF16 ? 1u : (g->in_dtype == B200_F32 ? 2u : 0u);  // f16 0, bf16 1, tf32 2
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((g->a_kmajor ? 0u : 1u) << 15) | ((g->b_kmajor ? 0u : 1u) << 16) |
             ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
   int* host_status = status_word();
@@ -392,6 +400,21 @@ int launch(const b200_gemm_desc_t* g, void* d, const void* a, const void* b, cud
     kern<<<grid, kThreads, kSmemBytes, stream>>>(ma, mb, (OutT*)d, p);                                           \
   } while (0)
 
+  if (tf32) {
+    if constexpr (std::is_same<OutT, float>::value) {
+      static bool attr_set = false;
+      auto kern = gemm_kernel<float, true, true, true>;
+      if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+      }
+      kern<<<grid, kThreads, kSmemBytes, stream>>>(ma, mb, (float*)d, p);
+      B200K_LAUNCH_RET();
+    } else {
+      return (int)cudaErrorNotSupported;
+    }
+  }
   if (g->a_kmajor && g->b_kmajor) GEMM_GO(true, true);
   else if (g->a_kmajor && !g->b_kmajor) GEMM_GO(true, false);
   else if (!g->a_kmajor && g->b_kmajor) GEMM_GO(false, true);
@@ -444,7 +467,8 @@ int b200_gemm_status(int clear) {
 
 static int gemm_validate(const b200_gemm_desc_t* g, const void* a, const void* b) {
   if (g->k <= 0) return (int)cudaErrorNotSupported;
-  if (g->in_dtype != B200_BF16 && g->in_dtype != B200_F16) return (int)cudaErrorNotSupported;
+  if (g->in_dtype != B200_BF16 && g->in_dtype != B200_F16 && g->in_dtype != B200_F32) return (int)cudaErrorNotSupported;
+  if (g->in_dtype == B200_F32 && (!g->a_kmajor || !g->b_kmajor || g->out_dtype != B200_F32)) return (int)cudaErrorNotSupported;
   // TMA: base 16-byte aligned, byte strides multiples of 16
   auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
   if (!al(a) || !al(b) || g->lda % 8 != 0 || g->ldb % 8 != 0) return (int)cudaErrorNotSupported;

@@ -769,10 +769,12 @@ GemmPlan gemm_plan(const b200_gemm_desc_t* g) {
   GemmPlan plan;
   plan.pair = choice == 2 || choice == 3;
   plan.dynamic = choice == 3;
-  const int k_blocks = (g->k + BK - 1) / BK;
+  const bool tf32 = g->in_dtype == B200_F32;  // fp32 operands: single-CTA kernel, 32 elements per K block, no split
+  if (tf32) plan.pair = plan.dynamic = false;
+  const int k_blocks = (g->k + (tf32 ? 32 : BK) - 1) / (tf32 ? 32 : BK);
   plan.splits = 1;
   plan.kb_per_split = k_blocks;
-  if (batch == 1 && g_splitk.load(std::memory_order_relaxed)) {
+  if (batch == 1 && !tf32 && g_splitk.load(std::memory_order_relaxed)) {
     const long long tiles = ceil_div_ll(g->m, plan.pair ? 256 : 128) * ceil_div_ll(g->n, 256);
     const long long units = plan.pair ? pairs : sms;
     if (tiles * 2 <= units && k_blocks >= 32) {
