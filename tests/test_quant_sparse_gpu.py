@@ -40,3 +40,21 @@ def test_sparse_coo_tensor(bw, dev):
     v2 = torch.randn(5, 2)
     s2 = torch.sparse_coo_tensor(i.to(dev), v2.to(dev), (4, 3, 2))
     assert torch.allclose(s2.to_dense().cpu(), torch.sparse_coo_tensor(i, v2, (4, 3, 2)).to_dense())
+
+
+def test_jagged_nested_tensor(bw, dev):
+    """Jagged nested tensors are a wrapper over one packed values tensor: their operators land on this device's
+    dense kernels (linear on the GEMM, element-wise and reductions on the substrate)."""
+    torch.manual_seed(2)
+    parts = [torch.randn(n, 64) for n in (5, 1, 9)]
+    w = torch.randn(32, 64)
+    nt = torch.nested.nested_tensor([p.to(dev) for p in parts], layout=torch.jagged)
+    assert nt.device.type == "blackwell" and nt.is_nested
+    out = torch.nn.functional.linear(nt, w.to(dev))
+    act = torch.nn.functional.gelu(out) * 2.0
+    for got, p in zip(act.unbind(), parts):
+        ref = torch.nn.functional.gelu(p @ w.t()) * 2.0
+        assert torch.allclose(got.cpu(), ref, atol=2e-2, rtol=2e-2)
+    padded = torch.nested.to_padded_tensor(act, 0.0)
+    assert tuple(padded.shape) == (3, 9, 32)
+    assert torch.allclose(padded[1, 1:].cpu(), torch.zeros(8, 32))
