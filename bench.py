@@ -589,6 +589,9 @@ def measure(args, env: Env, wl: Workload) -> dict:
     out.update(extra)
     if env.ours:
         out["fallback_ops"] = len(env.bw.fallback_counts())
+        if out["fallback_ops"]:
+            # which operators ran on a library kernel instead of one of this repository's (name: calls)
+            out["fallback_op_names"] = dict(sorted(env.bw.fallback_counts().items(), key=lambda kv: -kv[1])[:12])
         if os.environ.get("B200_BENCH_VERBOSE") and rank == 0:
             sys.stderr.write("fallbacks: " + json.dumps(sorted(env.bw.fallback_counts().items(), key=lambda kv: -kv[1])) + "\n")
     else:
