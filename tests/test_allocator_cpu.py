@@ -223,3 +223,24 @@ def test_pool_checkpoint_restore(h):
     assert snap[0]["blocks"] == [(20 * MiB, False)]
     h.release_pool(pid)
     assert h.stats()["reserved_bytes"]["all"]["current"] == 0
+
+
+def test_canary_reports_a_write_past_the_end(bw):
+    bw._C._set_allocator_settings("canary:True")
+    try:
+        h = bw._C._HostCacheHarness()
+        a = h.alloc(1000)
+        b = h.alloc(4096)
+        h.write_read(a, 1000, 1)                      # stays inside: fine
+        h.write_read(b, 4096 + 8, 2)                  # 8 bytes too many
+        h.free(a)
+        assert h.canary_violations() == 0
+        h.free(b)                                     # logs a warning and counts the violation
+        assert h.canary_violations() == 1
+        assert "4096-byte allocation" in h.last_canary_report()
+        # the guard bytes count towards the block size: 512 B requested no longer fits a 512 B block
+        c = h.alloc(512)
+        assert h.stats()["allocated_bytes"]["all"]["current"] == 1024
+        h.free(c)
+    finally:
+        bw._C._set_allocator_settings("canary:False")

@@ -313,6 +313,8 @@ Config parse_config(const std::string& s, Config c) {
       c.pinned_num_register_threads = (int)n;
     } else if (k == "pinned_use_background_threads") {
       c.pinned_use_background_threads = parse_bool(k, v);
+    } else if (k == "canary") {
+      c.canary = parse_bool(k, v);
     } else if (k == "cpu") {
       TORCH_CHECK(v == "unified" || v == "default", "allocator config: cpu must be 'unified' or 'default'");
       c.cpu_unified = (v == "unified");
@@ -354,6 +356,7 @@ struct Block {
   Block *prev = nullptr, *next = nullptr;
   int event_count = 0;
   int gc_count = 0;
+  bool has_canary = false;   // guard bytes sit behind `requested`
   XSegment* xseg = nullptr;  // expandable segment this block lies in
   bool mapped = true;        // false: address space only (never in Pool::blocks)
   bool is_split() const { return prev || next; }
@@ -428,10 +431,52 @@ class DeviceAllocatorImpl {
     return (size + kRoundLarge - 1) / kRoundLarge * kRoundLarge;
   }
 
+  // ---- guard bytes (debug option `canary:True`): kCanaryBytes of a fixed pattern directly behind the requested
+  // bytes of every allocation, checked when the allocation is freed.  An out-of-bounds write of a kernel then
+  // shows up at the free of the block it overran, with the block's size, instead of as silent corruption of a
+  // neighbour.  Costs a memset per allocation and a synchronous 64-byte read-back per free.
+  static constexpr size_t kCanaryBytes = 64;
+  static constexpr unsigned char kCanaryByte = 0xA5;
+
+  void write_canary(Block* b) {
+    char* at = static_cast<char*>(b->ptr) + b->requested;
+    if (be_->device_events) {
+      DeviceSwitch sw(device_);
+      B200_CUDA_WARN(cudaMemsetAsync(at, kCanaryByte, kCanaryBytes, b->stream));
+    } else {
+      std::memset(at, kCanaryByte, kCanaryBytes);
+    }
+  }
+  void check_canary(Block* b) {
+    unsigned char host[kCanaryBytes];
+    const char* at = static_cast<const char*>(b->ptr) + b->requested;
+    if (be_->device_events) {
+      DeviceSwitch sw(device_);
+      if (cudaMemcpy(host, at, kCanaryBytes, cudaMemcpyDeviceToHost) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return;
+      }
+    } else {
+      std::memcpy(host, at, kCanaryBytes);
+    }
+    for (size_t i = 0; i < kCanaryBytes; ++i) {
+      if (host[i] != kCanaryByte) {
+        ++canary_violations_;
+        std::ostringstream os;
+        os << "blackwell allocator: the " << b->requested << "-byte allocation at " << b->ptr << " (device " << device_
+           << ") was written " << (i + 1) << " or more bytes past its end";
+        canary_report_ = os.str();
+        TORCH_WARN(canary_report_);
+        return;
+      }
+    }
+  }
+
   Block* malloc(size_t orig, cudaStream_t stream) {
     std::unique_lock<std::mutex> lk(mu_);
     process_events();
-    size_t size = round_size(orig);
+    const bool canary = config().canary;
+    size_t size = round_size(orig + (canary ? kCanaryBytes : 0));
     Pool& pool = pool_for(size, stream);
     Block* b = find_free(pool, size, stream);
     if (!b) {
@@ -466,6 +511,8 @@ class DeviceAllocatorImpl {
       bump([&](int t) { stats_.inactive_split[t].inc(1); stats_.inactive_split_bytes[t].inc(rem->size); }, pool);
     }
     mark_allocated(b, orig);
+    b->has_canary = canary;
+    if (canary) write_canary(b);
     return b;
   }
 
@@ -493,6 +540,10 @@ class DeviceAllocatorImpl {
 
   void free_locked(Block* b, bool ignore_stream_uses) {
     if (ignore_stream_uses) b->stream_uses.clear();
+    if (b->has_canary) {
+      check_canary(b);
+      b->has_canary = false;
+    }
     b->allocated = false;
     live_.erase(b->ptr);
     Pool& pool = *b->pool;
@@ -803,6 +854,14 @@ class DeviceAllocatorImpl {
   }
 
   std::vector<OomObserver>* observers = nullptr;
+  int64_t canary_violations() {
+    std::lock_guard<std::mutex> lk(mu_);
+    return canary_violations_;
+  }
+  std::string canary_report() {
+    std::lock_guard<std::mutex> lk(mu_);
+    return canary_report_;
+  }
 
  private:
   template <class F>
@@ -1396,6 +1455,8 @@ class DeviceAllocatorImpl {
   bool limited_ = false;
   double fraction_ = 1.0;
   size_t allowed_ = 0;
+  int64_t canary_violations_ = 0;
+  std::string canary_report_;
   bool history_ = false, history_stacks_ = false;
   size_t history_max_ = 1;
   std::deque<TraceEntry> trace_;
@@ -1680,6 +1741,19 @@ void CachingAllocator::create_or_incref_pool(int device, MempoolId pool) {
 int CachingAllocator::pool_use_count(int device, MempoolId pool) {
   if ((int)devs_.size() <= device) return 0;
   return devs_[device]->pool_use_count(pool);
+}
+
+int64_t CachingAllocator::canary_violations() const {
+  int64_t n = 0;
+  for (auto& d : devs_) n += d->canary_violations();
+  return n;
+}
+std::string CachingAllocator::last_canary_report() const {
+  for (auto& d : devs_) {
+    std::string r = d->canary_report();
+    if (!r.empty()) return r;
+  }
+  return {};
 }
 
 void CachingAllocator::attach_oom_observer(OomObserver o) { g_observers.push_back(std::move(o)); }

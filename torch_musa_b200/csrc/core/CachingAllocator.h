@@ -87,6 +87,7 @@ struct Config {
   std::string backend = "native";            // native | unified | cudaMallocAsync | host
   bool cpu_unified = false;                  // "cpu:unified": CPU allocator hands out managed memory
   bool no_caching = false;                   // PYTORCH_NO_BLACKWELL_MEMORY_CACHING
+  bool canary = false;                       // debug: guard bytes behind every allocation, verified when it is freed
 };
 
 // Parses "key:value,key:value" (the PYTORCH_BLACKWELL_ALLOC_CONF syntax); throws on unknown keys.
@@ -211,6 +212,10 @@ class B200_EXPORT CachingAllocator final : public c10::Allocator {
   void unmap_imported(void* va, size_t chunk_bytes, int device, const std::vector<uint64_t>& handles);
   // Re-grants read/write on `device`'s mapped chunks to the GPUs that now have peer access to it.
   void refresh_peer_access(int device);
+
+  // Number of allocations whose guard bytes were found overwritten (option `canary:True`), and the last report.
+  int64_t canary_violations() const;
+  std::string last_canary_report() const;
 
   void attach_oom_observer(OomObserver o);
   void record_history(bool enabled, size_t max_entries, bool stacks = false);

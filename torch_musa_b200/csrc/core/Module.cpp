@@ -350,6 +350,7 @@ PYBIND11_MODULE(_C, m) {
     d["roundup_power2_divisions"] = c.roundup_power2_divisions;
     d["large_segment_bytes"] = c.large_segment_bytes;
     d["expandable_segments"] = c.expandable_segments;
+    d["canary"] = c.canary;
     d["backend"] = c.backend;
     d["cpu_unified"] = c.cpu_unified;
     d["no_caching"] = c.no_caching;
@@ -365,6 +366,7 @@ PYBIND11_MODULE(_C, m) {
     d["roundup_power2_divisions"] = c.roundup_power2_divisions;
     d["large_segment_bytes"] = c.large_segment_bytes;
     d["expandable_segments"] = c.expandable_segments;
+    d["canary"] = c.canary;
     d["backend"] = c.backend;
     d["cpu_unified"] = c.cpu_unified;
     d["pinned_use_host_register"] = c.pinned_use_host_register;
@@ -394,6 +396,8 @@ PYBIND11_MODULE(_C, m) {
     TORCH_CHECK(s.device().is_cpu() && host::is_managed_ptr(s.data()), "storage is not in managed host memory");
     return bridge::relabel_storage(s, make_device((c10::DeviceIndex)idx));
   });
+  m.def("_allocator_canary_violations", [] { return alloc::get()->canary_violations(); });
+  m.def("_allocator_last_canary_report", [] { return alloc::get()->last_canary_report(); });
   m.def("_event_cache_stats", [] { return event_cache_stats(); });
   m.def("_multi_stream_guard_probe", [](std::vector<std::tuple<int64_t, int64_t>> ids) {
     // sets the given streams current on their devices inside a MultiStreamGuard and reports what was current
@@ -561,6 +565,8 @@ PYBIND11_MODULE(_C, m) {
         std::memset(reinterpret_cast<void*>(p), value, n);
         return (int)reinterpret_cast<unsigned char*>(p)[n - 1];
       })
+      .def("canary_violations", [](HostCacheHarness& h) { return h.a->canary_violations(); })
+      .def("last_canary_report", [](HostCacheHarness& h) { return h.a->last_canary_report(); })
       .def("record_history", [](HostCacheHarness& h, bool on, size_t n) { h.a->record_history(on, n); })
       .def("trace", [](HostCacheHarness& h) {
         py::list out;
