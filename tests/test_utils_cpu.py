@@ -147,3 +147,31 @@ def test_op_dumper_and_double_to_float(tmp_path):
     assert b.dtype == torch.float64 and c.dtype == torch.float64
     assert m.touched["aten::mm"] == 1 and m.touched["aten::sin"] == 1
     assert not torch.equal(b, a @ a) and torch.allclose(b, a @ a, rtol=1e-4, atol=1e-4)   # computed in fp32
+
+
+def _isolated_probe(x):
+    import os
+
+    return {"pid": os.getpid(), "twice": 2 * x}
+
+
+def _rank_sum_body(rank, world, offset):
+    import torch
+    import torch.distributed as dist
+
+    t = torch.tensor([float(rank + offset)])
+    dist.all_reduce(t)
+    assert float(t) == sum(r + offset for r in range(world))
+
+
+def test_multi_process_harness():
+    import os
+    from torch_musa_b200.testing.distributed import MultiProcessTestCase, spawn_isolated_test
+
+    out = spawn_isolated_test(_isolated_probe, 21)
+    assert out["twice"] == 42 and out["pid"] != os.getpid()
+
+    class Suite(MultiProcessTestCase):
+        world_size = 3
+
+    Suite().run_on_ranks(_rank_sum_body, 10)
