@@ -312,3 +312,17 @@ def test_memory_snapshot_pickle_format(bw, dev, tmp_path):
     assert {"alloc", "free_requested"} <= actions or {"alloc", "free_completed"} <= actions
     allocs = [t for t in snap["device_traces"][bw.current_device()] if t["action"] == "alloc"]
     assert allocs and len(allocs[-1].get("frames", "")) > 20        # the call site's frames were recorded
+
+
+def test_telemetry_and_legacy_storage(bw, dev):
+    s = bw.FloatStorage(16)
+    assert s.device.type == "blackwell" and s.dtype == torch.float32 and len(s) == 16
+    assert bw.current_blaslt_handle() != 0
+    assert bw.cudart().cudaMemGetInfo(0)[1] > (100 << 30)
+    try:
+        t, p, c = bw.temperature(), bw.power_draw(), bw.clock_rate()
+    except (RuntimeError, ModuleNotFoundError):
+        pytest.skip("NVML is not reachable in this container")
+    assert 0 < t < 120 and p > 0 and 0 < c <= 2500
+    assert 0 <= bw.utilization() <= 100
+    assert "GPU:0" in bw.list_gpu_processes()

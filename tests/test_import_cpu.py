@@ -91,3 +91,13 @@ def test_legacy_typed_tensor_classes(bw):
         assert cls.dtype == dt and cls.is_blackwell
         assert not isinstance(torch.zeros(1, dtype=dt), cls)        # a CPU tensor is not a device tensor
     assert repr(bw.FloatTensor) == "<class 'torch.blackwell.FloatTensor'>"
+
+
+def test_small_api_surface(bw):
+    import torch
+
+    assert bw.get_gencode_flags() == "-gencode arch=compute_100a,code=sm_100a"
+    assert bw.FloatStorage.dtype == torch.float32 and bw.BFloat16Storage.dtype == torch.bfloat16
+    for name in ("utilization", "temperature", "power_draw", "clock_rate", "memory_usage", "list_gpu_processes",
+                 "current_blas_handle", "current_blaslt_handle", "cudart", "ipc_collect", "get_pool_checkpoint"):
+        assert callable(getattr(bw, name)), name

@@ -182,6 +182,22 @@ from .core.tensor_types import make_types as _make_tensor_types  # noqa: E402
 
 globals().update(_make_tensor_types())  # FloatTensor, HalfTensor, BFloat16Tensor, ... (legacy typed classes)
 
+from .core.monitoring import (  # noqa: E402
+    clock_rate,
+    cudart,
+    current_blaslt_handle,
+    get_gencode_flags,
+    list_gpu_processes,
+    make_storage_types as _make_storage_types,
+    memory_usage,
+    power_draw,
+    temperature,
+    utilization,
+)
+
+globals().update(_make_storage_types())  # FloatStorage, HalfStorage, ... (legacy typed storages)
+runtime = cudart
+
 
 from .core import reductions as _reductions  # noqa: E402
 
