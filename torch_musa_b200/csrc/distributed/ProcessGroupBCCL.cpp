@@ -866,6 +866,12 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupBCCL::make_test_work(std::chrono::mil
 
 // ------------------------------------------------------------------ watchdog
 void ProcessGroupBCCL::watchdog_loop() {
+  {
+    // This thread polls events while other threads may be capturing graphs in the global capture mode, under which
+    // an event query from ANY thread invalidates the capture.  Polling is harmless to a capture: opt this thread out.
+    cudaStreamCaptureMode mode = cudaStreamCaptureModeRelaxed;
+    if (cudaThreadExchangeStreamCaptureMode(&mode) != cudaSuccess) (void)cudaGetLastError();
+  }
   const auto period = std::chrono::milliseconds(std::getenv("BCCL_WATCHDOG_MS") ? std::atoi(std::getenv("BCCL_WATCHDOG_MS")) : 100);
   while (!stop_.load()) {
     {
