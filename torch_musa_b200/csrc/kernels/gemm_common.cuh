@@ -6,6 +6,8 @@
 
 #include <cuda.h>
 
+#include <cstdlib>
+
 namespace b200k {
 namespace gemmdev {
 
@@ -152,17 +154,31 @@ struct Params {
   int group_m;   // row tiles per L2 group (see decode_tile)
 };
 
-// Row tiles per L2 group.  While all of A (M x K elements of 2 bytes) fits in about three quarters of the 126 MB L2
-// one group covers every row tile (A stays resident, B streams once); beyond that a group's A rows take about 48 MB.
-inline int gemm_group_m(int tile_rows, int m, int k) {
+// Row tiles per L2 group (see decode_tile).  Measured on the Llama-7B shapes (us, 74 SM pairs):
+//   * both operands MN-major (weight gradients): one group over all row tiles re-reads the operands from DRAM
+//     several times (1.06 GB against 134 MB of algorithmic bytes at 4096 x 12288 x 4096; L2 hit rate 57 % against
+//     85 % for the K-major layout): groups of 4 row tiles bring 302 -> 265 at that shape, 110 -> 102 at 4096^3;
+//   * K-major: while A (M x K x 2 bytes) is at most 64 MB one group covers every row tile (A stays resident, B
+//     streams once); beyond that (K = 11008) groups of about 24 MB of A rows: 303 -> 291.
+inline int gemm_group_m(int tile_rows, int m, int k, bool both_mn_major = false) {
+  static const int forced = [] {   // experiment knob
+    const char* e = std::getenv("B200_GEMM_GROUP_M");
+    return e ? std::atoi(e) : 0;
+  }();
+  if (forced > 0) return forced;
   const long long per_tile = (long long)tile_rows * k * 2;
   const int tiles_m = (m + tile_rows - 1) / tile_rows;
-  if ((long long)m * k * 2 <= (96ll << 20)) return tiles_m > 0 ? tiles_m : 1;
-  long long g = (48ll << 20) / (per_tile > 0 ? per_tile : 1);
-  if (g < 2) g = 2;
-  if (g > 32) g = 32;
-  return (int)g;
+  int g;
+  if ((long long)m * k * 2 <= (64ll << 20)) {
+    g = tiles_m > 0 ? tiles_m : 1;
+  } else {
+    long long q = (24ll << 20) / (per_tile > 0 ? per_tile : 1);
+    g = (int)(q < 2 ? 2 : (q > 32 ? 32 : q));
+  }
+  if (both_mn_major && g > 4) g = 4;
+  return g;
 }
+
 
 
 

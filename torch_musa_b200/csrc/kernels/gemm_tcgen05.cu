@@ -300,8 +300,17 @@ bool make_map(CUtensorMap* out, const void* ptr, int dtype, uint64_t inner, uint
   CUtensorMapDataType dt = dtype == B200_BF16  ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                            : dtype == B200_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                                : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  // experiment knob: L2 promotion size of the operand maps (0 none, 1 64 B, 2 128 B, 3 256 B = default)
+  static const int promo = [] {
+    const char* e = std::getenv("B200_GEMM_L2_PROMOTION");
+    return e ? std::atoi(e) : 3;
+  }();
+  const CUtensorMapL2promotion pr = promo == 0   ? CU_TENSOR_MAP_L2_PROMOTION_NONE
+                                    : promo == 1 ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B
+                                    : promo == 2 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B
+                                                 : CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
   CUresult r = enc(out, dt, 3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                   CU_TENSOR_MAP_SWIZZLE_128B, pr, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return false;
   std::lock_guard<std::mutex> g(mu);
   if (cache.size() > 4096) cache.clear();
@@ -376,7 +385,7 @@ int launch(const b200_gemm_desc_t* g, void* d, const void* a, const void* b, cud
   p.splits = plan.splits;
   p.kb_per_split = plan.kb_per_split;
   p.split_stride = (int64_t)g->m * g->n;
-  p.group_m = gemm_group_m(BM, g->m, plan.splits > 1 ? plan.kb_per_split * BK : g->k);
+  p.group_m = gemm_group_m(BM, g->m, plan.splits > 1 ? plan.kb_per_split * BK : g->k, !g->a_kmajor && !g->b_kmajor);
 
   const int total = p.tiles_m * p.tiles_n * p.batch * p.splits;
   int dev = 0, sms = kSMs;

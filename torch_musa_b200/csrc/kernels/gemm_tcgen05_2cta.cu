@@ -689,7 +689,7 @@ int launch_pair(const b200_gemm_desc_t* g, void* d, const void* a, const void* b
   p.splits = plan.splits;
   p.kb_per_split = plan.kb_per_split;
   p.split_stride = (int64_t)g->m * g->n;
-  p.group_m = gemm_group_m(BM2, g->m, plan.splits > 1 ? plan.kb_per_split * BK : g->k);
+  p.group_m = gemm_group_m(BM2, g->m, plan.splits > 1 ? plan.kb_per_split * BK : g->k, !g->a_kmajor && !g->b_kmajor);
 
   const int total = p.tiles_m * p.tiles_n * p.batch * p.splits;
   const int pairs = std::max(1, gemm_sm_count() / 2);
