@@ -97,7 +97,7 @@ def test_library_routes_still_work(bw, dev):
         bw._C._set_sdp_impl(prev)
 
 
-@pytest.mark.parametrize("H,Hkv,pos", [(4, 4, 0), (8, 2, 37), (4, 4, 255), (4, 1, 100)])
+@pytest.mark.parametrize("H,Hkv,pos", [(4, 4, 0), (8, 2, 37), (4, 4, 255), (4, 1, 100), (4, 4, 31), (4, 2, 63), (4, 4, 64)])
 def test_decode_attention(bw, dev, H, Hkv, pos):
     torch.manual_seed(0)
     B, L = 3, 256

@@ -1,12 +1,13 @@
 // Single-query ("decode") attention over a static KV cache, head_dim 128.
 //
-// One CTA per (batch, query head), eight warps; warp w owns every eighth block of 32 keys in [0, *pos], the
-// lanes split the 128 dimensions four each.  Per key: 4 FMAs + a warp sum for the score, online softmax in the
-// log2 domain, 4 FMAs into the output slice; four keys are in flight per iteration.  The eight partial (max, sum,
-// output) triples are merged through shared memory.  The visible length is read from device memory, so the
-// kernel can sit inside a captured graph and follow the position counter without any host involvement.
-// Memory-bound by design: K and V are read exactly once per query head (grouped-query heads re-read their
-// shared KV head through L2).
+// One CTA per (batch, query head), eight warps.  A warp is four independent groups of eight lanes; a group owns
+// every 32nd key of [0, *pos] and its lanes split the 128 dimensions sixteen each (two 16-byte loads per row), so
+// a score needs three shuffles instead of a full warp reduction and the probability never has to be broadcast:
+// every group runs its own online softmax (log2 domain) and accumulates its own output slice.  Two keys per group
+// are in flight per iteration.  The 32 partial (max, sum, output) triples of a CTA are merged through shared memory.
+// The visible length is read from device memory, so the kernel can sit inside a captured graph and follow the
+// position counter without any host involvement.  Memory-bound by design: K and V are read exactly once per query
+// head (grouped-query heads re-read their shared KV head through L2).
 // Parity: the reference has no decode kernel; it relies on the vendor SDPA (reference
 // torch_musa/csrc/aten/ops/attention/mudnn/SDP.cpp).
 #include "common.cuh"
@@ -16,80 +17,110 @@ namespace {
 
 constexpr int DD = 128;
 constexpr int kDecWarps = 8;
+constexpr int kGroups = 4;              // lane groups per warp
+constexpr int kDimsPerLane = 16;        // 128 dims / 8 lanes
+constexpr int kParts = kDecWarps * kGroups;
 
 template <typename T>
-__global__ void __launch_bounds__(kDecWarps * 32)
+__device__ __forceinline__ void load16(const T* p, float (&out)[kDimsPerLane]) {
+  const uint4 a = *reinterpret_cast<const uint4*>(p);
+  const uint4 b = *reinterpret_cast<const uint4*>(p + 8);
+  const T* pa = reinterpret_cast<const T*>(&a);
+  const T* pb = reinterpret_cast<const T*>(&b);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    out[i] = ToF<T>::to(pa[i]);
+    out[8 + i] = ToF<T>::to(pb[i]);
+  }
+}
+
+// One lane's sixteen elements of a cache row, kept packed (two 16-byte words) until use.
+template <typename T>
+struct Row {
+  uint4 a, b;
+  __device__ __forceinline__ void load(const T* p, bool valid) {
+    if (valid) {
+      a = *reinterpret_cast<const uint4*>(p);
+      b = *reinterpret_cast<const uint4*>(p + 8);
+    } else {
+      a = make_uint4(0, 0, 0, 0);
+      b = a;
+    }
+  }
+  __device__ __forceinline__ float get(int i) const {
+    const T* pa = reinterpret_cast<const T*>(&a);
+    const T* pb = reinterpret_cast<const T*>(&b);
+    return ToF<T>::to(i < 8 ? pa[i] : pb[i - 8]);
+  }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kDecWarps * 32, 2)
 decode_attn_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __restrict__ kc, const T* __restrict__ vc,
                    const long long* __restrict__ pos_ptr, int H, int Hkv, int max_len, float scale_log2) {
-  __shared__ float sh_m[kDecWarps], sh_l[kDecWarps], sh_o[kDecWarps][DD];
+  __shared__ float sh_m[kParts], sh_l[kParts];
+  __shared__ float sh_o[kParts][DD];
   const int b = blockIdx.x / H, h = blockIdx.x - b * H;
   const int hk = h / (H / Hkv);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int grp = lane >> 3, gl = lane & 7;
+  const int part = warp * kGroups + grp;
   long long n_keys = *pos_ptr + 1;
   if (n_keys > max_len) n_keys = max_len;
   if (n_keys < 0) n_keys = 0;
-  const T* kbase = kc + ((long long)(b * Hkv + hk) * max_len) * DD + lane * 4;
-  const T* vbase = vc + ((long long)(b * Hkv + hk) * max_len) * DD + lane * 4;
-  float qv[4];
-  {
-    const T* qp = q + ((long long)b * H + h) * DD + lane * 4;
+  const T* kbase = kc + ((long long)(b * Hkv + hk) * max_len) * DD + gl * kDimsPerLane;
+  const T* vbase = vc + ((long long)(b * Hkv + hk) * max_len) * DD + gl * kDimsPerLane;
+  float qv[kDimsPerLane];
+  load16(q + ((long long)b * H + h) * DD + gl * kDimsPerLane, qv);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) qv[i] = ToF<T>::to(qp[i]) * scale_log2;
-  }
-  float m = -INFINITY, l = 0.f, o[4] = {0.f, 0.f, 0.f, 0.f};
-  // keys warp, warp + 8, ... in steps of 4 keys
-  for (long long k0 = (long long)warp * 4; k0 < n_keys; k0 += kDecWarps * 4) {
-    float s[4], vv[4][4];
+  for (int i = 0; i < kDimsPerLane; ++i) qv[i] *= scale_log2;
+  float m = -INFINITY, l = 0.f, o[kDimsPerLane];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const long long key = k0 + u;
-      float d = 0.f;
-      if (key < n_keys) {
-        const uint2 kr = *reinterpret_cast<const uint2*>(kbase + key * DD);
-        const uint2 vr = *reinterpret_cast<const uint2*>(vbase + key * DD);
-        const T* kp = reinterpret_cast<const T*>(&kr);
-        const T* vp = reinterpret_cast<const T*>(&vr);
+  for (int i = 0; i < kDimsPerLane; ++i) o[i] = 0.f;
+
+  auto consume = [&](const Row<T>& kr, const Row<T>& vr, bool valid) {
+    float d = 0.f;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          d = fmaf(qv[i], ToF<T>::to(kp[i]), d);
-          vv[u][i] = ToF<T>::to(vp[i]);
-        }
-      } else {
+    for (int i = 0; i < kDimsPerLane; ++i) d = fmaf(qv[i], kr.get(i), d);
+    d += __shfl_xor_sync(0xffffffffu, d, 4);
+    d += __shfl_xor_sync(0xffffffffu, d, 2);
+    d += __shfl_xor_sync(0xffffffffu, d, 1);
+    if (!valid) return;
+    const float m_new = fmaxf(m, d);
+    const float alpha = exp2f(m - m_new);    // m = -inf on the first key: alpha = 0, the empty state vanishes
+    const float pz = exp2f(d - m_new);
+    l = fmaf(l, alpha, pz);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) vv[u][i] = 0.f;
-      }
-      s[u] = d;
-    }
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      s[u] = warp_sum(s[u]);
-      if (k0 + u >= n_keys) s[u] = -INFINITY;
-    }
-    const float m_new = fmaxf(fmaxf(fmaxf(s[0], s[1]), fmaxf(s[2], s[3])), m);
-    const float alpha = exp2f(m - m_new);      // m_new is finite here: key k0 is always valid
-    l *= alpha;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) o[i] *= alpha;
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const float pz = exp2f(s[u] - m_new);
-      l += pz;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) o[i] = fmaf(pz, vv[u][i], o[i]);
-    }
+    for (int i = 0; i < kDimsPerLane; ++i) o[i] = fmaf(pz, vr.get(i), o[i] * alpha);
     m = m_new;
+  };
+
+  // keys part, part + 32, ...; two in flight, kept packed until they are consumed.  The shuffles inside `consume`
+  // are executed by every lane of the warp: a group without a key left feeds zeros through them and skips the update.
+  const long long span = 2 * kParts;
+  const long long k_end = ((n_keys + span - 1) / span) * span;
+  for (long long k0 = part; k0 < k_end; k0 += span) {
+    const long long ka = k0, kb = k0 + kParts;
+    const bool va = ka < n_keys, vb = kb < n_keys;
+    Row<T> k_a, v_a, k_b, v_b;
+    k_a.load(kbase + ka * DD, va);
+    v_a.load(vbase + ka * DD, va);
+    k_b.load(kbase + kb * DD, vb);
+    v_b.load(vbase + kb * DD, vb);
+    consume(k_a, v_a, va);
+    consume(k_b, v_b, vb);
   }
-  if (lane == 0) { sh_m[warp] = m; sh_l[warp] = l; }
+  if (gl == 0) { sh_m[part] = m; sh_l[part] = l; }
 #pragma unroll
-  for (int i = 0; i < 4; ++i) sh_o[warp][lane * 4 + i] = o[i];
+  for (int i = 0; i < kDimsPerLane; ++i) sh_o[part][gl * kDimsPerLane + i] = o[i];
   __syncthreads();
   if (threadIdx.x < DD) {
     float mm = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < kDecWarps; ++w) mm = fmaxf(mm, sh_m[w]);
+    for (int w = 0; w < kParts; ++w) mm = fmaxf(mm, sh_m[w]);
     float ll = 0.f, acc = 0.f;
 #pragma unroll
-    for (int w = 0; w < kDecWarps; ++w) {
+    for (int w = 0; w < kParts; ++w) {
       const float f = sh_m[w] == -INFINITY ? 0.f : exp2f(sh_m[w] - mm);
       ll += sh_l[w] * f;
       acc += sh_o[w][threadIdx.x] * f;
@@ -107,7 +138,7 @@ extern "C" int b200_decode_attention(int dtype, void* out, const void* q, const 
                                      const long long* pos, int B, int H, int Hkv, int max_len, int head_dim, float scale,
                                      cudaStream_t stream) {
   if (head_dim != DD || B <= 0 || H <= 0 || Hkv <= 0 || H % Hkv != 0 || max_len <= 0) return (int)cudaErrorNotSupported;
-  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 7)
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 15)
     return (int)cudaErrorNotSupported;
   const float sl2 = scale * 1.4426950408889634f;
   if (dtype == B200_BF16)
