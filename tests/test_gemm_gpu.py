@@ -193,3 +193,38 @@ def test_fp32_matmul_as_tf32_on_tensor_cores(bw, dev):
         assert bw._C._gemm_status() == 0
     finally:
         torch.backends.blackwell.allow_tf32 = prev
+
+
+@pytest.mark.parametrize("counts,R", [([130, 0, 77, 256], 520), ([64, 64], 128), ([5], 64), ([200, 300, 1, 63, 129], 1024)])
+def test_grouped_gemm_device_side_counts(bw, dev, counts, R):
+    """The three grouped products (forward, input gradient, per-group weight gradient) against fp32 loops; the
+    group lengths are only ever read on the device, rows past their sum stay untouched."""
+    from torch_musa_b200.ops import grouped_linear
+
+    torch.manual_seed(0)
+    G, K, N = len(counts), 192, 328
+    x = (torch.randn(R, K) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(G, N, K) * 0.1).to(torch.bfloat16)
+    dy = (torch.randn(R, N) * 0.5).to(torch.bfloat16)
+    cnt = torch.tensor(counts, dtype=torch.int32)
+    used = sum(counts)
+    # fp32 oracle
+    y_ref, dx_ref, dw_ref, s = torch.zeros(R, N), torch.zeros(R, K), torch.zeros(G, N, K), 0
+    for g, n in enumerate(counts):
+        y_ref[s:s + n] = x[s:s + n].float() @ w[g].float().t()
+        dx_ref[s:s + n] = dy[s:s + n].float() @ w[g].float()
+        dw_ref[g] = dy[s:s + n].float().t() @ x[s:s + n].float()
+        s += n
+    xd, wd = x.to(dev).requires_grad_(), w.to(dev).requires_grad_()
+    out = torch.full((R, N), 7.0, dtype=torch.bfloat16, device=dev)
+    bw.reset_fallback_counts()
+    y = grouped_linear(xd, wd, cnt.to(dev), out)
+    y.backward(dy.to(dev))
+    assert bw._C._gemm_status() == 0
+    assert (y[:used].float().cpu() - y_ref[:used]).abs().max() < 3e-2 * max(1.0, float(y_ref.abs().max()))
+    assert bool((y[used:] == 7.0).all())                       # rows of no group are not written
+    assert (xd.grad[:used].float().cpu() - dx_ref[:used]).abs().max() < 3e-2 * max(1.0, float(dx_ref.abs().max()))
+    assert (wd.grad.float().cpu() - dw_ref).abs().max() < 3e-2 * max(1.0, float(dw_ref.abs().max()))
+    # the host implementation of the same contract (any device) agrees
+    y_cpu = grouped_linear(x.float(), w.float(), cnt)
+    assert torch.allclose(y_cpu[:used], y_ref[:used], atol=1e-4)

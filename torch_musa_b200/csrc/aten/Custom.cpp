@@ -230,6 +230,66 @@ at::Tensor decode_attention(const at::Tensor& q, const at::Tensor& k_cache, cons
   return out;
 }
 
+// mode 0: a [R, K] x b [G, N, K] -> [R, N];  mode 1: a [R, N] x b [G, N, K] -> [R, K];  mode 2: a [R, M], b [R, N] -> [G, M, N].
+// The rows of group g are the next counts[g] packed rows; counts stays on the device.
+at::Tensor grouped_mm_impl(const at::Tensor& a, const at::Tensor& b, const at::Tensor& counts, int64_t mode,
+                           const std::optional<at::Tensor>& out) {
+  check_fast(a, "grouped_mm");
+  check_devices("grouped_mm", a, b, counts);
+  TORCH_CHECK(counts.scalar_type() == at::kInt && counts.dim() == 1 && counts.is_contiguous(), "grouped_mm: counts must be int32 [groups]");
+  TORCH_CHECK(a.dim() == 2 && a.scalar_type() == b.scalar_type() && (a.scalar_type() == at::kBFloat16 || a.scalar_type() == at::kHalf),
+              "grouped_mm: bf16 / fp16 operands, a two-dimensional");
+  at::Tensor ac = a.contiguous(), bc = b.contiguous();
+  const int64_t G = counts.size(0), R = ac.size(0);
+  b200_grouped_gemm_t g{};
+  g.rows = (int)R;
+  g.groups = (int)G;
+  g.counts = counts.const_data_ptr<int>();
+  g.in_dtype = g.out_dtype = kdtype(a.scalar_type());
+  std::vector<int64_t> oshape;
+  if (mode == 0 || mode == 1) {
+    TORCH_CHECK(bc.dim() == 3 && bc.size(0) == G && ac.size(1) == bc.size(mode == 0 ? 2 : 1), "grouped_mm: b must be [groups, N, K]");
+    g.ragged_depth = 0;
+    g.b_kmajor = mode == 0;
+    g.k = (int)ac.size(1);
+    g.n = (int)bc.size(mode == 0 ? 1 : 2);
+    g.lda = ac.size(1);
+    g.ldb = bc.size(2);
+    g.stride_b = bc.size(1) * bc.size(2);
+    oshape = {R, (int64_t)g.n};
+  } else {
+    TORCH_CHECK(mode == 2 && bc.dim() == 2 && bc.size(0) == R, "grouped_mm: mode 2 takes a [R, M] and b [R, N]");
+    g.ragged_depth = 1;
+    g.m = (int)ac.size(1);
+    g.n = (int)bc.size(1);
+    g.lda = ac.size(1);
+    g.ldb = bc.size(1);
+    g.stride_d = (int64_t)g.m * g.n;
+    oshape = {G, (int64_t)g.m, (int64_t)g.n};
+  }
+  at::Tensor o;
+  if (out.has_value() && out->defined()) {
+    o = *out;
+    TORCH_CHECK(o.is_contiguous() && o.scalar_type() == a.scalar_type() && o.sizes().equals(oshape), "grouped_mm: out has the wrong shape");
+  } else {
+    o = at::empty(oshape, a.options());
+  }
+  g.ldd = g.n;
+  DeviceSwitch sw(a.device().index());
+  int e = b200_grouped_gemm(&g, o.mutable_data_ptr(), ac.const_data_ptr(), bc.const_data_ptr(), current_raw_stream(a));
+  TORCH_CHECK(e != (int)cudaErrorNotSupported, "grouped_mm: unsupported problem (at most 64 groups, widths multiples of 8)");
+  B200_KERNEL_CALL(e);
+  return o;
+}
+
+at::Tensor grouped_mm(const at::Tensor& a, const at::Tensor& b, const at::Tensor& counts, int64_t mode) {
+  return grouped_mm_impl(a, b, counts, mode, std::nullopt);
+}
+at::Tensor& grouped_mm_out(const at::Tensor& a, const at::Tensor& b, const at::Tensor& counts, int64_t mode, at::Tensor& out) {
+  grouped_mm_impl(a, b, counts, mode, out);
+  return out;
+}
+
 void sleep_cycles(int64_t cycles) {
   B200_KERNEL_CALL(b200_sleep(cycles, get_current_stream().stream()));
 }
@@ -253,11 +313,15 @@ TORCH_LIBRARY(blackwell, m) {
   m.def("multi_tensor_axpby_(Tensor(a!)[] out, Tensor[] x, Tensor[] y, float a, float b) -> ()");
   m.def("multi_tensor_lamb_(Tensor(a!)[] params, Tensor[] grads, Tensor(b!)[] exp_avg, Tensor(c!)[] exp_avg_sq, float lr, float beta1, float beta2, float eps, float weight_decay, int step, bool bias_correction, bool grad_averaging, bool adam_w_mode, float max_grad_norm, bool use_nvlamb, Tensor? global_grad_norm) -> ()");
   m.def("decode_attention(Tensor q, Tensor k_cache, Tensor v_cache, Tensor pos, float? scale=None) -> Tensor");
+  m.def("grouped_mm(Tensor a, Tensor b, Tensor counts, int mode) -> Tensor");
+  m.def("grouped_mm_out(Tensor a, Tensor b, Tensor counts, int mode, Tensor(a!) out) -> Tensor(a!)");
   m.def("_sleep(int cycles) -> ()");
 }
 
 TORCH_LIBRARY_IMPL(blackwell, PrivateUse1, m) {
   m.impl("decode_attention", TORCH_FN(decode_attention));
+  m.impl("grouped_mm", TORCH_FN(grouped_mm));
+  m.impl("grouped_mm_out", TORCH_FN(grouped_mm_out));
   m.impl("rope", TORCH_FN(rope));
   m.impl("swiglu", TORCH_FN(swiglu));
   m.impl("swiglu_backward", TORCH_FN(swiglu_backward));

@@ -360,6 +360,22 @@ typedef struct {
   size_t workspace_bytes;
 } b200_gemm_desc_t;
 B200_API int b200_gemm(const b200_gemm_desc_t* desc, void* d, const void* a, const void* b, cudaStream_t stream);
+/* Grouped GEMM whose per-group lengths are read from device memory (`counts`, int32 [groups], groups <= 64).
+ *   ragged_depth = 0: d[r, 0:n] = a[r, 0:k] * b[g(r)]^T for the packed rows r of group g; a [rows, k] (lda), d [rows, n]
+ *                     (ldd); b [groups, n, k] when b_kmajor, else [groups, k, n] (ldb, stride_b per group).
+ *   ragged_depth = 1: d[g] [m, n] (ldd, stride_d) = a[rows of g, 0:m]^T * b[rows of g, 0:n]; a [rows, m] (lda), b [rows, n].
+ * Rows past the sum of the counts are neither read into a result nor written; an empty group's d[g] is zero. */
+typedef struct {
+  int ragged_depth;
+  int rows, m, n, k;
+  int groups;
+  const int* counts;
+  int b_kmajor;
+  int in_dtype, out_dtype;
+  int64_t lda, ldb, ldd;
+  int64_t stride_b, stride_d;
+} b200_grouped_gemm_t;
+B200_API int b200_grouped_gemm(const b200_grouped_gemm_t* desc, void* d, const void* a, const void* b, cudaStream_t stream);
 /* Scratch a split-K run of this problem wants (few output tiles, long K); 0 when the problem is not split. */
 B200_API size_t b200_gemm_workspace_bytes(const b200_gemm_desc_t* desc);
 /* 1 when the running driver exposes the tensor-map encoder the kernel needs */

@@ -61,7 +61,11 @@ class Experts(nn.Module):
         for w in (self.w13, self.w2):
             nn.init.normal_(w, std=0.02)
 
-    def forward(self, rows: torch.Tensor, rows_per_expert: List[int]) -> torch.Tensor:
+    def forward(self, rows: torch.Tensor, rows_per_expert, y_out=None, dx_out=None) -> torch.Tensor:
+        if isinstance(rows_per_expert, torch.Tensor):
+            # counts on the device: one grouped GEMM per projection over the packed rows, nothing read on the host
+            h = BF.grouped_linear(rows, self.w13, rows_per_expert, None, dx_out)
+            return BF.grouped_linear(BF.swiglu(h), self.w2, rows_per_expert, y_out)
         outs, start = [], 0
         for e, n in enumerate(rows_per_expert):
             n = min(n, rows.shape[0] - start)
@@ -93,7 +97,7 @@ class MoEFeedForward(nn.Module):
         gates = torch.softmax(top, dim=-1)                 # softmax over the selected logits (Mixtral)
         ex = self._exchange[0]
         recv, rows_per_expert, ctx = ex.dispatch(flat, idx, self.slot)
-        y = self.experts(recv, rows_per_expert)
+        y = self.experts(recv, rows_per_expert, *ex.expert_buffers(self.slot))
         out = ex.combine(y, gates, ctx, self.slot)
         return out.view(B, S, D)
 

@@ -14,6 +14,7 @@ from .functional import (  # noqa: F401
     rope,
     precompute_rope_cache,
     swiglu,
+    grouped_linear,
     silu_mul,
     gated_silu,
     fused_cross_entropy,

@@ -106,3 +106,15 @@ def _(x, e5m2=False):
 @_reg("decode_attention")
 def _(q, k_cache, v_cache, pos, scale=None):
     return torch.empty_like(q)
+
+
+@_reg("grouped_mm")
+def _(a, b, counts, mode):
+    if mode == 2:
+        return a.new_empty((counts.shape[0], a.shape[1], b.shape[1]))
+    return a.new_empty((a.shape[0], b.shape[1] if mode == 0 else b.shape[2]))
+
+
+@_reg("grouped_mm_out")
+def _(a, b, counts, mode, out):
+    return out

@@ -201,6 +201,60 @@ def swiglu(x: torch.Tensor) -> torch.Tensor:
 gated_silu = swiglu
 
 
+# ------------------------------------------------------------------------- grouped linear (expert GEMMs)
+def _grouped_rows(counts: torch.Tensor, rows: int):
+    out, start = [], 0
+    for n in counts.tolist():
+        n = max(0, min(int(n), rows - start))
+        out.append((start, n))
+        start += n
+    return out
+
+
+class _GroupedLinear(torch.autograd.Function):
+    """``y[r] = x[r] @ w[g(r)].T`` over packed row groups whose lengths (``counts``, int32) stay on the device: one
+    grouped tensor-core GEMM each for the product, the input gradient and the per-group weight gradients."""
+
+    @staticmethod
+    def forward(ctx, x, w, counts, out, grad_input_out):
+        ctx.save_for_backward(x, w, counts)
+        ctx.grad_input_out = grad_input_out
+        if out is not None:
+            ctx.mark_dirty(out)
+            return torch.ops.blackwell.grouped_mm_out(x, w, counts, 0, out)
+        return torch.ops.blackwell.grouped_mm(x, w, counts, 0)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, counts = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = None
+        if ctx.needs_input_grad[0]:
+            if ctx.grad_input_out is not None:
+                dx = torch.ops.blackwell.grouped_mm_out(dy, w, counts, 1, ctx.grad_input_out)
+            else:
+                dx = torch.ops.blackwell.grouped_mm(dy, w, counts, 1)
+        dw = torch.ops.blackwell.grouped_mm(dy, x, counts, 2) if ctx.needs_input_grad[1] else None
+        return dx, dw, None, None, None
+
+
+def grouped_linear(x: torch.Tensor, w: torch.Tensor, counts: torch.Tensor, out: Optional[torch.Tensor] = None,
+                   grad_input_out: Optional[torch.Tensor] = None):
+    """Rows of ``x`` [R, K] are packed group after group (``counts[g]`` rows for group g); ``w`` is [G, N, K].
+    Returns [R, N]; rows past ``counts.sum()`` are left as they are (uninitialised without ``out``).  On the
+    blackwell device nothing reads ``counts`` on the host.  ``out`` / ``grad_input_out`` name buffers the product /
+    the input gradient are written into (an exchange arena, so that no copy follows)."""
+    if _on_device(x) and x.dtype in (torch.bfloat16, torch.float16):
+        return _GroupedLinear.apply(x, w, counts.to(torch.int32), out, grad_input_out)
+    parts = [F.linear(x[s:s + n], w[g]) for g, (s, n) in enumerate(_grouped_rows(counts, x.shape[0]))]
+    used = sum(p.shape[0] for p in parts)
+    y = torch.cat(parts + [x.new_zeros((x.shape[0] - used, w.shape[1]))], 0)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
 class _SiluMul(torch.autograd.Function):
     @staticmethod
     def forward(ctx, gate, up):

@@ -7,6 +7,9 @@ Two interchangeable implementations of the same contract
 
 ``recv`` holds the rows this rank's experts must process, grouped by local expert (all rows of local
 expert 0, then expert 1, ...); ``y`` is what the experts computed for those rows, in the same order.
+``rows_per_local_expert`` is a list, or -- fused exchange, the default -- an int32 device tensor: ``recv`` is then
+the whole capacity-sized receive buffer and the grouped expert GEMMs (``ops.grouped_linear``) read the counts on
+the device, so that no host synchronisation sits in the layer.
 
 * ``FusedExpertExchange`` (blackwell device): the kernels of ``csrc/kernels/moe.cu``.  Dispatch is ONE
   kernel that exchanges the per-expert counts through peer memory, derives every row's destination and
@@ -21,6 +24,8 @@ Parity: the reference has no expert parallelism; its all_to_all is a loop of sen
 (reference torch_musa/csrc/distributed/ProcessGroupMCCL.cpp:4022-4117).
 """
 from __future__ import annotations
+
+import os
 
 from typing import List, Optional, Tuple
 
@@ -79,6 +84,10 @@ class ReferenceExpertExchange:
         ctx = (order, regroup, in_splits, out_splits, T, K)
         return recv[regroup], rows_per_expert, ctx
 
+    def expert_buffers(self, slot: int = 0):
+        """(output buffer, input-gradient buffer) the expert GEMMs may write into directly: none here."""
+        return None, None
+
     def combine(self, y: torch.Tensor, gates: torch.Tensor, ctx, slot: int = 0) -> torch.Tensor:
         order, regroup, in_splits, out_splits, T, K = ctx
         back = torch.empty_like(y)
@@ -119,7 +128,8 @@ class _Receive(torch.autograd.Function):
     def backward(ctx, d_recv):
         ex = ctx.ex
         idx, pos = ctx.saved_tensors
-        ex.drecv_view()[: ctx.rows].copy_(d_recv)
+        if d_recv.data_ptr() != ex.drecv_view().data_ptr():       # the grouped input-gradient GEMM wrote it in place
+            ex.drecv_view()[: ctx.rows].copy_(d_recv)
         dx = ex.sm.moe_gather(idx, pos, None, ex.d, ex.E, ex.drecv_off())
         return dx, None, None, None, None, None
 
@@ -128,7 +138,8 @@ class _Combine(torch.autograd.Function):
     @staticmethod
     def forward(ctx, y, gates, idx, pos, ex, slot):
         rows = y.shape[0]
-        ex.y_view(slot)[:rows].copy_(y)
+        if y.data_ptr() != ex.y_view(slot).data_ptr():             # the grouped down projection wrote it in place
+            ex.y_view(slot)[:rows].copy_(y)
         out = ex.sm.moe_gather(idx, pos, gates, ex.d, ex.E, ex.y_off(slot))
         ctx.ex, ctx.slot, ctx.rows = ex, slot, rows
         ctx.save_for_backward(gates, idx, pos)
@@ -141,7 +152,9 @@ class _Combine(torch.autograd.Function):
         d_out = d_out.contiguous()
         d_gates = ex.sm.moe_gather_dot(d_out, idx, pos, ex.E, ex.y_off(ctx.slot))
         ex.sm.moe_scatter(d_out, idx, pos, gates, ex.E, ex.dy_off())
-        d_y = ex.dy_view()[: ctx.rows].clone()
+        # with device-side counts the rows go to the expert GEMMs where they are (their consumers run before the
+        # next layer's backward scatters into this buffer again: its input depends on them)
+        d_y = ex.dy_view() if ctx.rows == ex.cap_rows else ex.dy_view()[: ctx.rows].clone()
         return d_y, d_gates, None, None, None, None
 
 
@@ -154,6 +167,7 @@ class FusedExpertExchange:
 
         self.E, self.d, self.cap_rows, self.slots = num_experts, d_model, int(cap_rows), slots
         self.group = group
+        self.host_counts = os.environ.get("B200_MOE_HOST_COUNTS", "0") == "1"
         self.rank, self.world = _group_info(group)
         assert num_experts % self.world == 0 and d_model % 8 == 0
         self.E_local = num_experts // self.world
@@ -180,12 +194,26 @@ class FusedExpertExchange:
     def drecv_view(self): return self._view(self.drecv_off())
 
     def dispatch(self, x: torch.Tensor, idx: torch.Tensor, slot: int = 0):
+        """Returns (received rows, rows per local expert, context for `combine`).  By default the counts stay on
+        the device (an int32 tensor; the received rows are the whole capacity-sized buffer and the grouped expert
+        GEMMs read the counts themselves); ``host_counts`` brings them to the host as a list, which costs a
+        synchronisation per layer."""
         idx32 = idx.to(torch.int32).contiguous()
         pos, recv_counts = _Dispatch.apply(x.contiguous(), idx32, self, slot)
-        rows_per_expert = recv_counts.tolist()          # the one host read: the expert GEMMs need their row counts
+        if not self.host_counts:
+            recv = _Receive.apply(x, idx32, pos, self, slot, self.cap_rows)
+            return recv, recv_counts, (idx32, pos)
+        rows_per_expert = recv_counts.tolist()
         rows = min(sum(rows_per_expert), self.cap_rows)
         recv = _Receive.apply(x, idx32, pos, self, slot, rows)
         return recv, rows_per_expert, (idx32, pos)
+
+    def expert_buffers(self, slot: int = 0):
+        """(output buffer, input-gradient buffer) for the grouped expert GEMMs: this slot's combine source and the
+        buffer the dispatch backward gathers from."""
+        if self.host_counts:
+            return None, None
+        return self.y_view(slot), self.drecv_view()
 
     def combine(self, y: torch.Tensor, gates: torch.Tensor, ctx, slot: int = 0) -> torch.Tensor:
         idx32, pos = ctx
