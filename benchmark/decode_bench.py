@@ -80,12 +80,14 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)          # max over ranks
         eager, graph = float(t[0]), float(t[1])
         if rank != 0:
+            del dec          # the captured graph references the communicator: release it before the group goes
             dist.destroy_process_group()
             return
     print(json.dumps({"op": "decode", "tp": world, "model": f"llama-7b dims, {a.layers} layers", "batch": a.batch, "kv_len": a.kv,
                       "eager_ms_per_token": round(eager, 3), "graph_ms_per_token": round(graph, 3),
                       "graph_tokens_per_s": round(a.batch / graph * 1e3, 1), "speedup": round(eager / graph, 2)}))
     if world > 1:
+        del dec
         dist.destroy_process_group()
 
 

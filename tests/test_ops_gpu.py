@@ -298,8 +298,16 @@ def test_cat_and_strided_copy(bw, dev, dt):
         ref = torch.cat(shapes, dim=d)
         bw.reset_kernel_launch_count()
         out = torch.cat([s.to(dev) for s in shapes], dim=d)
-        assert bw.kernel_launch_count() >= len(shapes)
+        assert bw.kernel_launch_count() >= (1 if d == 0 else len(shapes))   # outermost dim: one launch for all pieces
         assert torch.equal(out.cpu(), ref)
+    # many small pieces of an integer type (what data-parallel wrappers flatten every step), odd byte counts,
+    # more pieces than one launch takes
+    pieces = [torch.arange(n, dtype=torch.int64) + 1000 * i for i, n in enumerate([1] * 140 + [3, 0, 5, 17])]
+    bw.reset_fallback_counts()
+    got = torch.cat([p.to(dev) for p in pieces])
+    assert torch.equal(got.cpu(), torch.cat(pieces)) and not bw.fallback_counts()
+    odd = [torch.randint(0, 255, (n,), dtype=torch.uint8) for n in (1, 15, 16, 33, 70001)]
+    assert torch.equal(torch.cat([o.to(dev) for o in odd]).cpu(), torch.cat(odd))
     # legacy: 1-D empty tensors are skipped
     out = torch.cat([torch.empty(0, device=dev, dtype=dt), xs[0].to(dev)], dim=1)
     assert torch.equal(out.cpu(), xs[0])

@@ -24,10 +24,11 @@ namespace {
 bool legacy_skip(const at::Tensor& t) { return t.dim() == 1 && t.numel() == 0; }
 
 bool cat_native_ok(const at::ITensorListRef& tensors, const at::Tensor& out) {
-  if (!on_device(out) || kdtype(out.scalar_type()) < 0) return false;
+  // any element type: pieces of a type the cast-copy kernel does not know go through copy_ (a device-side
+  // strided copy as well), e.g. the int64 step counters that DistributedDataParallel flattens every step
+  if (!on_device(out)) return false;
   for (const at::Tensor& t : tensors) {
     if (!on_device(t) || t.device() != out.device()) return false;
-    if (kdtype(t.scalar_type()) < 0) return false;
     if (t.is_conj() || t.is_neg()) return false;
   }
   return true;
@@ -64,6 +65,25 @@ at::Tensor& cat_out(const at::ITensorListRef& tensors, int64_t dim, at::Tensor& 
   if (out.sizes() != at::IntArrayRef(shape)) out.resize_(shape);
   if (out.numel() == 0) return out;
   auto stream = current_raw_stream(out);
+  // outermost-dimension concatenation of contiguous pieces of the output's type: one byte-copy launch per 128 pieces
+  int64_t outer = 1;
+  for (int64_t i = 0; i < d; ++i) outer *= shape[i];
+  bool bytes_ok = outer == 1 && out.is_contiguous() && out.scalar_type() == first->scalar_type();
+  if (bytes_ok)
+    for (const at::Tensor& t : tensors)
+      if (!legacy_skip(t) && !t.is_contiguous()) bytes_ok = false;
+  if (bytes_ok) {
+    std::vector<const void*> srcs;
+    std::vector<int64_t> nbytes;
+    for (const at::Tensor& t : tensors) {
+      if (legacy_skip(t) || t.numel() == 0) continue;
+      srcs.push_back(t.const_data_ptr());
+      nbytes.push_back((int64_t)t.numel() * (int64_t)t.element_size());
+    }
+    DeviceSwitch sw(out.device().index());
+    B200_KERNEL_CALL(b200_cat_bytes(out.mutable_data_ptr(), srcs.data(), nbytes.data(), (int)srcs.size(), stream));
+    return out;
+  }
   int64_t off = 0;
   for (const at::Tensor& t : tensors) {
     if (legacy_skip(t) || t.size(d) == 0) continue;
@@ -78,7 +98,7 @@ at::Tensor cat(const at::ITensorListRef& tensors, int64_t dim) {
   const at::Tensor* first = nullptr;
   for (const at::Tensor& t : tensors)
     if (!legacy_skip(t)) { first = &t; break; }
-  bool plain_case = first != nullptr && on_device(*first) && kdtype(first->scalar_type()) >= 0;
+  bool plain_case = first != nullptr && on_device(*first);
   if (plain_case)
     for (const at::Tensor& t : tensors)
       if (!legacy_skip(t) && (t.scalar_type() != first->scalar_type() || !on_device(t))) plain_case = false;

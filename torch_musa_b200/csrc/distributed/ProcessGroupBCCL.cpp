@@ -274,7 +274,7 @@ ProcessGroupBCCL::~ProcessGroupBCCL() {
   symm_.clear();
   for (auto& kv : comms_) {
     if (kv.second->comm) {
-      if (error_.load() == c10d::ErrorType::SUCCESS) ncclCommDestroy(kv.second->comm);
+      if (error_.load() == c10d::ErrorType::SUCCESS && !graph_captured_.load()) ncclCommDestroy(kv.second->comm);
       else ncclCommAbort(kv.second->comm);
     }
   }
@@ -406,6 +406,7 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupBCCL::collective(c10d::OpType type, c
     // Recorded into a graph: the communication stream forked from the capturing stream at `ready` and joins it
     // again when the caller waits on the work.  The watchdog must not poll events that belong to a capture.
     work->captured_ = true;
+    graph_captured_ = true;
     recorder_.complete(work->record_id_, "captured", -1.f);
     return work;
   }
@@ -1060,7 +1061,10 @@ void ProcessGroupBCCL::shutdown() {
   symm_.clear();
   for (auto& kv : comms_)
     if (kv.second->comm) {
-      ncclCommDestroy(kv.second->comm);
+      // Graphs that recorded collectives may still be alive (their owner decides when they go): destroying the
+      // communicator would block until they are released, so such a communicator is torn down without waiting.
+      if (graph_captured_.load()) ncclCommAbort(kv.second->comm);
+      else ncclCommDestroy(kv.second->comm);
       kv.second->comm = nullptr;
     }
 }

@@ -224,6 +224,9 @@ class B200_EXPORT ProcessGroupBCCL final : public c10d::Backend {
   std::condition_variable work_cv_;
   std::list<c10::intrusive_ptr<WorkBCCL>> works_;
   std::atomic<bool> stop_{false};
+  // a collective of this group was recorded into a device graph: the communicator library keeps such a
+  // communicator alive until every graph that references it is gone, and a blocking destroy would wait for that
+  std::atomic<bool> graph_captured_{false};
   std::atomic<c10d::ErrorType> error_{c10d::ErrorType::SUCCESS};
   FlightRecorder recorder_;
   std::atomic<int64_t> fused_count_{0};

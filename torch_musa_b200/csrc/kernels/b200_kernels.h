@@ -41,6 +41,8 @@ B200_API int b200_binary(int op, int dtype, void* out, const void* a, const void
                          int64_t n, cudaStream_t stream);
 B200_API int b200_unary(int op, int dtype, void* out, const void* a, int64_t n, cudaStream_t stream);
 /* dtype-converting / strided copy. ndim <= 8; strides in elements. */
+/* dst = the n_pieces byte ranges (srcs[i], nbytes[i]) one after the other; the ranges may not overlap dst */
+B200_API int b200_cat_bytes(void* dst, const void* const* srcs, const int64_t* nbytes, int n_pieces, cudaStream_t stream);
 B200_API int b200_cast_copy(void* dst, int dst_dtype, const void* src, int src_dtype, int ndim, const int64_t* sizes,
                             const int64_t* dst_strides, const int64_t* src_strides, cudaStream_t stream);
 B200_API int b200_fill(void* out, int dtype, double value, int64_t n, cudaStream_t stream);
