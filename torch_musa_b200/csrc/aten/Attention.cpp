@@ -217,6 +217,84 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> sdpa_fused_bwd(
   return {st[0].toTensor(), st[1].toTensor(), st[2].toTensor(), at::Tensor()};
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------
+// Packed variable-length attention: q [total_q, H, 128], k / v [total_k, Hkv, 128], cu_seqlens int32 [B + 1] on the
+// device.  ONE launch of the tcgen05 forward (and of the backward) covers every sequence: a CTA reads its sequence's
+// bounds from cu_seqlens and offsets its tile coordinates; nothing is read on the host.  lse is [H, total_q].
+// Parity: reference torch_musa/csrc/aten/ops/attention/mudnn/SDP.cpp:678-845 (varlen entry of the vendor flash kernel).
+void varlen_desc(b200_attn_t& a, const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& cu_q,
+                 const at::Tensor& cu_k, int64_t max_q, int64_t max_k, bool causal, std::optional<double> scale) {
+  TORCH_CHECK(q.dim() == 3 && k.dim() == 3 && v.dim() == 3 && q.size(2) == 128 && k.size(2) == 128 && v.sizes() == k.sizes(),
+              "varlen_attention: q [total_q, H, 128], k / v [total_k, Hkv, 128]");
+  TORCH_CHECK((q.scalar_type() == at::kBFloat16 || q.scalar_type() == at::kHalf) && k.scalar_type() == q.scalar_type() &&
+              v.scalar_type() == q.scalar_type(), "varlen_attention: bf16 / fp16 only");
+  TORCH_CHECK(cu_q.scalar_type() == at::kInt && cu_k.scalar_type() == at::kInt && cu_q.dim() == 1 && cu_q.sizes() == cu_k.sizes() &&
+              cu_q.numel() >= 2 && cu_q.is_contiguous() && cu_k.is_contiguous(), "varlen_attention: cu_seqlens must be int32 [B + 1]");
+  TORCH_CHECK(q.size(1) % k.size(1) == 0 && max_q > 0 && max_k > 0, "varlen_attention: bad head counts or lengths");
+  a.B = (int)cu_q.numel() - 1;
+  a.H = (int)q.size(1); a.Hkv = (int)k.size(1);
+  a.Sq = (int)max_q; a.Sk = (int)max_k; a.head_dim = 128;
+  a.dtype = kdtype(q.scalar_type());
+  a.causal = causal ? 1 : 0;
+  a.scale = (float)scale.value_or(1.0 / std::sqrt(128.0));
+  a.q_ss = q.stride(0); a.q_sh = q.stride(1);
+  a.k_ss = k.stride(0); a.k_sh = k.stride(1);
+  a.v_ss = v.stride(0); a.v_sh = v.stride(1);
+  a.cu_seqlens_q = cu_q.const_data_ptr<int>();
+  a.cu_seqlens_k = cu_k.const_data_ptr<int>();
+  a.total_q = (int)q.size(0);
+  a.total_k = (int)k.size(0);
+}
+
+std::tuple<at::Tensor, at::Tensor> varlen_attention(const at::Tensor& q_, const at::Tensor& k_, const at::Tensor& v_,
+                                                    const at::Tensor& cu_q, const at::Tensor& cu_k, int64_t max_q,
+                                                    int64_t max_k, bool causal, std::optional<double> scale) {
+  check_devices("varlen_attention", q_, k_, v_, cu_q, cu_k);
+  at::Tensor q = q_.stride(2) == 1 ? q_ : q_.contiguous(), k = k_.stride(2) == 1 ? k_ : k_.contiguous(),
+             v = v_.stride(2) == 1 ? v_ : v_.contiguous();
+  b200_attn_t a{};
+  varlen_desc(a, q, k, v, cu_q, cu_k, max_q, max_k, causal, scale);
+  at::Tensor o = at::empty({q.size(0), q.size(1), 128}, q.options());
+  at::Tensor lse = at::empty({q.size(1), q.size(0)}, q.options().dtype(at::kFloat));
+  a.o_ss = o.stride(0); a.o_sh = o.stride(1);
+  DeviceSwitch sw(q.device().index());
+  int e = b200_flash_attn_fwd(&a, o.mutable_data_ptr(), lse.data_ptr<float>(), q.const_data_ptr(), k.const_data_ptr(),
+                              v.const_data_ptr(), current_raw_stream(q));
+  TORCH_CHECK(e != (int)cudaErrorNotSupported, "varlen_attention: unsupported strides or alignment");
+  B200_KERNEL_CALL(e);
+  g_native_fwd_calls.fetch_add(1, std::memory_order_relaxed);
+  return {o, lse};
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor> varlen_attention_backward(
+    const at::Tensor& grad_out, const at::Tensor& q_, const at::Tensor& k_, const at::Tensor& v_, const at::Tensor& out,
+    const at::Tensor& lse, const at::Tensor& cu_q, const at::Tensor& cu_k, int64_t max_q, int64_t max_k, bool causal,
+    std::optional<double> scale) {
+  check_devices("varlen_attention_backward", grad_out, q_, k_, v_, out, lse, cu_q, cu_k);
+  at::Tensor q = q_.contiguous(), k = k_.contiguous(), v = v_.contiguous(), go = grad_out.contiguous(), o = out.contiguous(),
+             l = lse.contiguous();
+  b200_attn_t a{};
+  varlen_desc(a, q, k, v, cu_q, cu_k, max_q, max_k, causal, scale);
+  TORCH_CHECK(l.scalar_type() == at::kFloat && l.numel() == q.size(0) * q.size(1), "varlen_attention_backward: lse must be [H, total_q]");
+  a.o_ss = o.stride(0); a.o_sh = o.stride(1);
+  at::Tensor dq32 = at::empty({q.size(1), q.size(0), 128}, q.options().dtype(at::kFloat));
+  at::Tensor delta = at::empty({q.size(1), q.size(0)}, q.options().dtype(at::kFloat));
+  at::Tensor gk = at::empty_like(k), gv = at::empty_like(v);
+  const int64_t extra[9] = {0, go.stride(1), go.stride(0), 0, gk.stride(1), gk.stride(0), 0, gv.stride(1), gv.stride(0)};
+  DeviceSwitch sw(q.device().index());
+  int e = b200_flash_attn_bwd(&a, dq32.data_ptr<float>(), gk.mutable_data_ptr(), gv.mutable_data_ptr(),
+                              delta.data_ptr<float>(), q.const_data_ptr(), k.const_data_ptr(), v.const_data_ptr(),
+                              o.const_data_ptr(), go.const_data_ptr(), l.const_data_ptr<float>(), extra,
+                              current_raw_stream(q));
+  TORCH_CHECK(e != (int)cudaErrorNotSupported, "varlen_attention_backward: unsupported strides or alignment");
+  B200_KERNEL_CALL(e);
+  g_native_bwd_calls.fetch_add(1, std::memory_order_relaxed);
+  at::Tensor gq = at::empty_like(q);
+  gq.copy_(dq32.transpose(0, 1));       // fp32 [H, total, 128] accumulator -> [total, H, 128] in the input type
+  return {gq, gk, gv};
+}
+
 }  // namespace
 
 int64_t native_sdp_forward_calls() { return g_native_fwd_calls.load(); }
@@ -236,6 +314,16 @@ REGISTER_PRIVATEUSE1_DISPATCH(_fused_sdp_choice_stub, &b200::ops::fused_sdp_choi
 
 namespace b200 {
 namespace ops {
+
+TORCH_LIBRARY_FRAGMENT(blackwell, m) {
+  m.def("varlen_attention(Tensor q, Tensor k, Tensor v, Tensor cu_seqlens_q, Tensor cu_seqlens_k, int max_seqlen_q, int max_seqlen_k, bool causal=False, float? scale=None) -> (Tensor, Tensor)");
+  m.def("varlen_attention_backward(Tensor grad_out, Tensor q, Tensor k, Tensor v, Tensor out, Tensor lse, Tensor cu_seqlens_q, Tensor cu_seqlens_k, int max_seqlen_q, int max_seqlen_k, bool causal=False, float? scale=None) -> (Tensor, Tensor, Tensor)");
+}
+
+TORCH_LIBRARY_IMPL(blackwell, PrivateUse1, m) {
+  m.impl("varlen_attention", TORCH_FN(varlen_attention));
+  m.impl("varlen_attention_backward", TORCH_FN(varlen_attention_backward));
+}
 
 TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
   m.impl("_fused_sdp_choice", TORCH_FN(fused_sdp_choice));

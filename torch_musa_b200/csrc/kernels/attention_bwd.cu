@@ -45,6 +45,11 @@ struct BwdParams {
   int64_t dk_sb, dk_sh, dk_ss, dv_sb, dv_sh, dv_ss;
   int kv_blocks, q_blocks;
   int* status;
+  // packed variable-length sequences (NULL: dense batch), as in the forward kernel; lse / delta are then [H, total_q]
+  // and dq [H, total_q, 128]
+  const int* cu_q;
+  const int* cu_k;
+  int total_q;
 };
 
 // adds a [128 rows x 32 floats] box of shared memory (128B-swizzled) into global memory at (x, y) of the tensor map
@@ -94,8 +99,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   const int b = bh / p.Hkv, hk = bh - b * p.Hkv;
   const int G = p.H / p.Hkv;
   const int k0 = kb * BK;
-  const int i0 = p.causal ? min(p.q_blocks, k0 / BQ) : 0;   // first query block that sees these keys
-  const int n_i = p.q_blocks - i0;
+  // this instance's sequence (see the forward kernel): rows past a packed sequence's end are loaded, masked by index
+  // (their probabilities and score gradients are exact zeros) and never stored
+  int Sq = p.Sq, Sk = p.Sk, qoff = 0, koff = 0, bt = b, q_blocks = p.q_blocks;
+  if (p.cu_q) {
+    qoff = p.cu_q[b];
+    Sq = p.cu_q[b + 1] - qoff;
+    koff = p.cu_k[b];
+    Sk = p.cu_k[b + 1] - koff;
+    bt = 0;
+    q_blocks = (Sq + BQ - 1) / BQ;
+  }
+  const int i0 = p.causal ? min(q_blocks, k0 / BQ) : 0;   // first query block that sees these keys
+  const int n_i = k0 < Sk ? q_blocks - i0 : 0;            // a key block past the sequence's end has nothing to do
   const int n_it = n_i * G;
 
   if (threadIdx.x == 0) {
@@ -134,10 +150,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     // ------------------------------------------------------------ TMA producer
     if (lane == 0 && n_it > 0) {
       mbar_expect_tx(kv_full, 2 * kTile);
-      tma_load_4d(sK, &tmap_k, kv_full, 0, k0, hk, b);
-      tma_load_4d(sK + kTile / 2, &tmap_k, kv_full, 64, k0, hk, b);
-      tma_load_4d(sV, &tmap_v, kv_full, 0, k0, hk, b);
-      tma_load_4d(sV + kTile / 2, &tmap_v, kv_full, 64, k0, hk, b);
+      tma_load_4d(sK, &tmap_k, kv_full, 0, koff + k0, hk, bt);
+      tma_load_4d(sK + kTile / 2, &tmap_k, kv_full, 64, koff + k0, hk, bt);
+      tma_load_4d(sV, &tmap_v, kv_full, 0, koff + k0, hk, bt);
+      tma_load_4d(sV + kTile / 2, &tmap_v, kv_full, 64, koff + k0, hk, bt);
       for (int n = 0; n < 2 * n_it; ++n) {
         const int st = n % kRing;
         if (!mbar_wait(&r_empty[st], (uint32_t)(((n / kRing) & 1) ^ 1), abort_flag)) break;
@@ -146,8 +162,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         const int h = hk * G + it / n_i;
         const int q0 = (i0 + it % n_i) * BQ;
         const CUtensorMap* map = (n & 1) ? &tmap_do : &tmap_q;
-        tma_load_4d(sR + st * kTile, map, &r_full[st], 0, q0, h, b);
-        tma_load_4d(sR + st * kTile + kTile / 2, map, &r_full[st], 64, q0, h, b);
+        tma_load_4d(sR + st * kTile, map, &r_full[st], 0, qoff + q0, h, bt);
+        tma_load_4d(sR + st * kTile + kTile / 2, map, &r_full[st], 64, qoff + q0, h, bt);
       }
     }
     __syncwarp();
@@ -248,19 +264,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       // ds_ready, i.e. all reads of the previous values.
       {
         const int which = tid >> 7, q = tid & 127, qi = q0 + q;
-        const int64_t idx = ((int64_t)b * p.H + h) * p.Sq + qi;
+        const int64_t idx = p.cu_q ? (int64_t)h * p.total_q + qoff + qi : ((int64_t)b * p.H + h) * p.Sq + qi;
         if (which == 0) {
-          float l = qi < p.Sq ? p.lse[idx] : -INFINITY;
+          float l = qi < Sq ? p.lse[idx] : -INFINITY;
           s_lse[q] = l > -INFINITY ? -l * 1.4426950408889634f : -INFINITY;   // negated: an addend of the exponent
         } else {
-          s_dlt[q] = qi < p.Sq ? -p.delta[idx] * p.scale : 0.f;              // negated and scaled likewise
+          s_dlt[q] = qi < Sq ? -p.delta[idx] * p.scale : 0.f;              // negated and scaled likewise
         }
       }
       named_bar_sync(1, 256);
       const float4* nlse4 = reinterpret_cast<const float4*>(s_lse + wg * 64);
       const float4* ndlt4 = reinterpret_cast<const float4*>(s_dlt + wg * 64);
       const bool diag = p.causal && q0 < k0 + BK;       // only then can a query be older than a key of this block
-      const bool key_off = kj >= p.Sk;
+      const bool key_off = kj >= Sk;
       if (!wait_all(s_full, par)) { ok = false; break; }
       // the staged dQ of the previous pair must have left the shared memory that P^T is written to
       if (it > 0 && !wait_all(stage_free, par ^ 1u)) { ok = false; break; }
@@ -377,7 +393,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       if (lane == 0) mbar_arrive(dq_drained);
       named_bar_sync(2, 256);
       if (tid == 0) {
-        const int row0 = (int)(((int64_t)b * p.H + h) * p.Sq + q0);
+        const int row0 = p.cu_q ? (int)((int64_t)h * p.total_q + qoff + q0) : (int)(((int64_t)b * p.H + h) * p.Sq + q0);
 #pragma unroll
         for (int c = 0; c < 4; ++c)
           tma_reduce_add_2d(&tmap_dq, sP + (size_t)c * (kTile / 2), c * 32, row0);
@@ -392,9 +408,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     // ---- dK, dV of this key block (all pairs have completed: the last mma2_done was waited for above)
     if (ok) {
       tc_fence_after();
-      const bool row_ok = kj < p.Sk;
-      T* dk_row = dk + (int64_t)b * p.dk_sb + (int64_t)hk * p.dk_sh + (int64_t)kj * p.dk_ss + wg * 64;
-      T* dv_row = dv + (int64_t)b * p.dv_sb + (int64_t)hk * p.dv_sh + (int64_t)kj * p.dv_ss + wg * 64;
+      const bool row_ok = kj < Sk;
+      T* dk_row = dk + (int64_t)bt * p.dk_sb + (int64_t)hk * p.dk_sh + (int64_t)(koff + kj) * p.dk_ss + wg * 64;
+      T* dv_row = dv + (int64_t)bt * p.dv_sb + (int64_t)hk * p.dv_sh + (int64_t)(koff + kj) * p.dv_ss + wg * 64;
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
 #pragma unroll
@@ -493,21 +509,32 @@ extern "C" int b200_flash_attn_bwd(const b200_attn_t* a, float* dq_accum, void* 
   for (int64_t s : strides)
     if (s % 8 != 0) return (int)cudaErrorNotSupported;
   if (!al(q) || !al(k) || !al(v) || !al(o) || !al(d_o) || !al(dk) || !al(dv) || !al(dq_accum)) return (int)cudaErrorNotSupported;
-  if ((a->B > 1 && (a->q_sb == 0 || a->k_sb == 0 || a->v_sb == 0 || x[0] == 0)) ||
+  const bool packed = a->cu_seqlens_q != nullptr;
+  if (packed && (!a->cu_seqlens_k || a->total_q <= 0 || a->total_k <= 0)) return (int)cudaErrorNotSupported;
+  if ((a->B > 1 && !packed && (a->q_sb == 0 || a->k_sb == 0 || a->v_sb == 0 || x[0] == 0)) ||
       (a->H > 1 && (a->q_sh == 0 || x[1] == 0)) || (a->Hkv > 1 && (a->k_sh == 0 || a->v_sh == 0)) || a->q_ss == 0 ||
       a->k_ss == 0 || a->v_ss == 0 || x[2] == 0)
     return (int)cudaErrorNotSupported;
   const int bf16 = a->dtype == B200_BF16;
   CUtensorMap mq, mk, mv, mdo;
   auto nz = [](int64_t s, int64_t fallback) { return s ? s : fallback; };
-  if (!make_attn_map(&mq, q, bf16, a->B, a->H, a->Sq, nz(a->q_sb, 8), nz(a->q_sh, 8), a->q_ss) ||
-      !make_attn_map(&mk, k, bf16, a->B, a->Hkv, a->Sk, nz(a->k_sb, 8), nz(a->k_sh, 8), a->k_ss) ||
-      !make_attn_map(&mv, v, bf16, a->B, a->Hkv, a->Sk, nz(a->v_sb, 8), nz(a->v_sh, 8), a->v_ss) ||
-      !make_attn_map(&mdo, d_o, bf16, a->B, a->H, a->Sq, nz(x[0], 8), nz(x[1], 8), x[2]))
+  if (packed) {
+    // one "batch" of total rows: the kernel adds each sequence's first row to its tile coordinates
+    if (!make_attn_map(&mq, q, bf16, 1, a->H, a->total_q, (int64_t)a->total_q * a->q_ss, nz(a->q_sh, 8), a->q_ss) ||
+        !make_attn_map(&mk, k, bf16, 1, a->Hkv, a->total_k, (int64_t)a->total_k * a->k_ss, nz(a->k_sh, 8), a->k_ss) ||
+        !make_attn_map(&mv, v, bf16, 1, a->Hkv, a->total_k, (int64_t)a->total_k * a->v_ss, nz(a->v_sh, 8), a->v_ss) ||
+        !make_attn_map(&mdo, d_o, bf16, 1, a->H, a->total_q, (int64_t)a->total_q * x[2], nz(x[1], 8), x[2]))
+      return (int)cudaErrorNotSupported;
+  } else if (!make_attn_map(&mq, q, bf16, a->B, a->H, a->Sq, nz(a->q_sb, 8), nz(a->q_sh, 8), a->q_ss) ||
+             !make_attn_map(&mk, k, bf16, a->B, a->Hkv, a->Sk, nz(a->k_sb, 8), nz(a->k_sh, 8), a->k_ss) ||
+             !make_attn_map(&mv, v, bf16, a->B, a->Hkv, a->Sk, nz(a->v_sb, 8), nz(a->v_sh, 8), a->v_ss) ||
+             !make_attn_map(&mdo, d_o, bf16, a->B, a->H, a->Sq, nz(x[0], 8), nz(x[1], 8), x[2]))
     return (int)cudaErrorNotSupported;
-  // dq_accum as a [B * H * Sq, 128] fp32 matrix; one box = 32 columns (128 bytes) of 128 rows
+  // dq_accum as a [B * H * Sq, 128] ([H * total_q, 128] when packed) fp32 matrix; one box = 32 columns of 128 rows
+  const long long rows = packed ? (long long)a->H * a->total_q : (long long)a->B * a->H * a->Sq;
+  const int dB = packed ? 1 : a->B, dS = packed ? a->total_q : a->Sq;     // the row-dot kernel's view of o and d_o
   CUtensorMap mdq;
-  if (!make_dq_map(&mdq, dq_accum, (int64_t)a->B * a->H * a->Sq)) return (int)cudaErrorNotSupported;
+  if (!make_dq_map(&mdq, dq_accum, rows)) return (int)cudaErrorNotSupported;
   BwdParams p{};
   p.B = a->B; p.H = a->H; p.Hkv = a->Hkv; p.Sq = a->Sq; p.Sk = a->Sk;
   p.causal = a->causal;
@@ -521,14 +548,16 @@ extern "C" int b200_flash_attn_bwd(const b200_attn_t* a, float* dq_accum, void* 
   p.kv_blocks = (a->Sk + BK - 1) / BK;
   p.q_blocks = (a->Sq + BQ - 1) / BQ;
   p.status = gemm_status_word_device();
-  const long long rows = (long long)a->B * a->H * a->Sq;
+  p.cu_q = a->cu_seqlens_q;
+  p.cu_k = a->cu_seqlens_k;
+  p.total_q = a->total_q;
   const long long grid = (long long)a->B * a->Hkv * p.kv_blocks;
   if (grid > 2147483647ll || rows / 8 + 1 > 2147483647ll) return (int)cudaErrorNotSupported;
   cudaError_t e = cudaMemsetAsync(dq_accum, 0, (size_t)rows * BD * sizeof(float), stream);
   if (e != cudaSuccess) return (int)e;
   if (bf16) {
     attn_delta_kernel<__nv_bfloat16><<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>(
-        (const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, delta, a->B, a->H, a->Sq, a->o_sb, a->o_sh, a->o_ss, x[0], x[1], x[2]);
+        (const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, delta, dB, a->H, dS, a->o_sb, a->o_sh, a->o_ss, x[0], x[1], x[2]);
     static bool set = false;
     auto kern = attn_bwd_kernel<__nv_bfloat16>;
     if (!set) {
@@ -539,7 +568,7 @@ extern "C" int b200_flash_attn_bwd(const b200_attn_t* a, float* dq_accum, void* 
     kern<<<(unsigned)grid, kBwdThreads, kBwdSmem, stream>>>(mq, mk, mv, mdo, mdq, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, p);
   } else {
     attn_delta_kernel<__half><<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>(
-        (const __half*)o, (const __half*)d_o, delta, a->B, a->H, a->Sq, a->o_sb, a->o_sh, a->o_ss, x[0], x[1], x[2]);
+        (const __half*)o, (const __half*)d_o, delta, dB, a->H, dS, a->o_sb, a->o_sh, a->o_ss, x[0], x[1], x[2]);
     static bool set = false;
     auto kern = attn_bwd_kernel<__half>;
     if (!set) {

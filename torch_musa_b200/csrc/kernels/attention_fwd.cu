@@ -25,8 +25,13 @@ struct AttnParams {
   int causal;
   float scale_log2;           // softmax scale * log2(e)
   int64_t o_sb, o_sh, o_ss;   // output strides in elements (last dim contiguous)
-  float* lse;                 // [B, H, Sq]
+  float* lse;                 // [B, H, Sq]; packed sequences: [H, total_q]
   int q_blocks, q_pairs;
+  // packed variable-length sequences (NULL: dense batch): sequence b holds rows [cu_q[b], cu_q[b + 1]) of the packed
+  // q / out [total_q, H, 128] and rows [cu_k[b], cu_k[b + 1]) of k / v; Sq / Sk are then the longest lengths
+  const int* cu_q;
+  const int* cu_k;
+  int total_q;
   int* status;
 };
 
@@ -67,13 +72,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   const int bh = (int)(blockIdx.x % n_bh);
   const int b = bh / p.H, h = bh - b * p.H;
   const int hk = h / (p.H / p.Hkv);
+  // this instance's sequence: lengths, first packed rows and the batch coordinate of the tensor maps.  Rows past a
+  // packed sequence's end belong to the next sequence: they are loaded, masked by index and never stored.
+  int Sq = p.Sq, Sk = p.Sk, qoff = 0, koff = 0, bt = b;
+  if (p.cu_q) {
+    qoff = p.cu_q[b];
+    Sq = p.cu_q[b + 1] - qoff;
+    koff = p.cu_k[b];
+    Sk = p.cu_k[b + 1] - koff;
+    bt = 0;
+  }
   int nb[2];
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
     const int q0 = (2 * qp + t) * AQ;
-    int k_end = p.Sk;
-    if (p.causal) k_end = min(p.Sk, q0 + AQ);
-    nb[t] = q0 < p.Sq ? (k_end + AK - 1) / AK : 0;
+    int k_end = Sk;
+    if (p.causal) k_end = min(Sk, q0 + AQ);
+    nb[t] = q0 < Sq ? (k_end + AK - 1) / AK : 0;
   }
   const int nbmax = max(nb[0], nb[1]);
 
@@ -111,8 +126,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         if (nb[t] == 0) continue;
         const int q0 = (2 * qp + t) * AQ;
         mbar_expect_tx(&q_full[t], kTile);
-        tma_load_4d(sQ + t * kTile, &tmap_q, &q_full[t], 0, q0, h, b);                 // d 0..63
-        tma_load_4d(sQ + t * kTile + kTile / 2, &tmap_q, &q_full[t], 64, q0, h, b);    // d 64..127
+        tma_load_4d(sQ + t * kTile, &tmap_q, &q_full[t], 0, qoff + q0, h, bt);                 // d 0..63
+        tma_load_4d(sQ + t * kTile + kTile / 2, &tmap_q, &q_full[t], 64, qoff + q0, h, bt);    // d 64..127
       }
       for (int n = 0; n < 2 * nbmax; ++n) {
         const int st = n % kRing;
@@ -120,8 +135,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         mbar_expect_tx(&r_full[st], kTile);
         const int k0 = (n >> 1) * AK;
         const CUtensorMap* map = (n & 1) ? &tmap_v : &tmap_k;   // V is read as an MN-major B operand: same boxes
-        tma_load_4d(sR + st * kTile, map, &r_full[st], 0, k0, hk, b);
-        tma_load_4d(sR + st * kTile + kTile / 2, map, &r_full[st], 64, k0, hk, b);
+        tma_load_4d(sR + st * kTile, map, &r_full[st], 0, koff + k0, hk, bt);
+        tma_load_4d(sR + st * kTile + kTile / 2, map, &r_full[st], 64, koff + k0, hk, bt);
       }
     }
     __syncwarp();
@@ -214,7 +229,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       tc_fence_after();
       const int k0 = j * AK;
       // the row's visible keys: [0, lim)
-      int lim = p.Sk - k0;
+      int lim = Sk - k0;
       if (p.causal) lim = min(lim, qi - k0 + 1);
       lim = max(0, min(lim, AK));
       const bool full = __all_sync(0xffffffffu, lim == AK);
@@ -326,13 +341,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     if (ok && n_blocks > 0) {
       tc_fence_after();
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      T* orow = out + (int64_t)b * p.o_sb + (int64_t)h * p.o_sh + (int64_t)qi * p.o_ss;
+      T* orow = out + (int64_t)bt * p.o_sb + (int64_t)h * p.o_sh + (int64_t)(qoff + qi) * p.o_ss;
 #pragma unroll
       for (int c = 0; c < AD / 32; ++c) {
         uint32_t raw[32];
         tmem_ld32(o_addr + (uint32_t)(c * 32), raw);
         tmem_ld_wait();
-        if (qi < p.Sq) {
+        if (qi < Sq) {
 #pragma unroll
           for (int g8 = 0; g8 < 4; ++g8) {
             Vec16<T> v;
@@ -342,8 +357,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           }
         }
       }
-      if (qi < p.Sq && p.lse)
-        p.lse[((int64_t)b * p.H + h) * p.Sq + qi] = l_run > 0.f ? (m_ref + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
+      if (qi < Sq && p.lse)
+        p.lse[p.cu_q ? (int64_t)h * p.total_q + qoff + qi : ((int64_t)b * p.H + h) * p.Sq + qi] = l_run > 0.f ? (m_ref + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
     }
   }
 
@@ -373,15 +388,23 @@ extern "C" int b200_flash_attn_fwd(const b200_attn_t* a, void* out, float* lse, 
       !st_ok(a->o_sh) || !st_ok(a->o_ss))
     return (int)cudaErrorNotSupported;
   // a broadcast (zero) stride cannot be a tensor-map stride
-  if ((a->B > 1 && (a->q_sb == 0 || a->k_sb == 0 || a->v_sb == 0)) || (a->H > 1 && a->q_sh == 0) ||
+  if ((a->B > 1 && !a->cu_seqlens_q && (a->q_sb == 0 || a->k_sb == 0 || a->v_sb == 0)) || (a->H > 1 && a->q_sh == 0) ||
       (a->Hkv > 1 && (a->k_sh == 0 || a->v_sh == 0)) || a->q_ss == 0 || a->k_ss == 0 || a->v_ss == 0)
     return (int)cudaErrorNotSupported;
   const int bf16 = a->dtype == B200_BF16;
   CUtensorMap mq, mk, mv;
   auto nz = [](int64_t s, int64_t fallback) { return s ? s : fallback; };
-  if (!make_attn_map(&mq, q, bf16, a->B, a->H, a->Sq, nz(a->q_sb, 8), nz(a->q_sh, 8), a->q_ss) ||
-      !make_attn_map(&mk, k, bf16, a->B, a->Hkv, a->Sk, nz(a->k_sb, 8), nz(a->k_sh, 8), a->k_ss) ||
-      !make_attn_map(&mv, v, bf16, a->B, a->Hkv, a->Sk, nz(a->v_sb, 8), nz(a->v_sh, 8), a->v_ss))
+  const bool packed = a->cu_seqlens_q != nullptr;
+  if (packed) {
+    if (!a->cu_seqlens_k || a->total_q <= 0 || a->total_k <= 0) return (int)cudaErrorNotSupported;
+    // one "batch" of total rows: the kernel adds each sequence's first row to its tile coordinates
+    if (!make_attn_map(&mq, q, bf16, 1, a->H, a->total_q, (int64_t)a->total_q * a->q_ss, nz(a->q_sh, 8), a->q_ss) ||
+        !make_attn_map(&mk, k, bf16, 1, a->Hkv, a->total_k, (int64_t)a->total_k * a->k_ss, nz(a->k_sh, 8), a->k_ss) ||
+        !make_attn_map(&mv, v, bf16, 1, a->Hkv, a->total_k, (int64_t)a->total_k * a->v_ss, nz(a->v_sh, 8), a->v_ss))
+      return (int)cudaErrorNotSupported;
+  } else if (!make_attn_map(&mq, q, bf16, a->B, a->H, a->Sq, nz(a->q_sb, 8), nz(a->q_sh, 8), a->q_ss) ||
+             !make_attn_map(&mk, k, bf16, a->B, a->Hkv, a->Sk, nz(a->k_sb, 8), nz(a->k_sh, 8), a->k_ss) ||
+             !make_attn_map(&mv, v, bf16, a->B, a->Hkv, a->Sk, nz(a->v_sb, 8), nz(a->v_sh, 8), a->v_ss))
     return (int)cudaErrorNotSupported;
   AttnParams p{};
   p.B = a->B; p.H = a->H; p.Hkv = a->Hkv; p.Sq = a->Sq; p.Sk = a->Sk;
@@ -389,6 +412,9 @@ extern "C" int b200_flash_attn_fwd(const b200_attn_t* a, void* out, float* lse, 
   p.scale_log2 = a->scale * 1.4426950408889634f;
   p.o_sb = a->o_sb; p.o_sh = a->o_sh; p.o_ss = a->o_ss;
   p.lse = lse;
+  p.cu_q = a->cu_seqlens_q;
+  p.cu_k = a->cu_seqlens_k;
+  p.total_q = a->total_q;
   p.q_blocks = (a->Sq + AQ - 1) / AQ;
   p.q_pairs = (p.q_blocks + 1) / 2;
   p.status = gemm_status_word_device();

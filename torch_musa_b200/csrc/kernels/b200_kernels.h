@@ -534,6 +534,13 @@ typedef struct {
   int causal;
   float scale;
   int64_t q_sb, q_sh, q_ss, k_sb, k_sh, k_ss, v_sb, v_sh, v_ss, o_sb, o_sh, o_ss;
+  /* Packed variable-length sequences (both NULL: dense batch).  Device int32 [B + 1] prefix sums of the sequence
+   * lengths; q / out / d_o are [total_q, H, 128], k / v (and dk / dv) [total_k, Hkv, 128] addressed with the *_sh and
+   * *_ss strides (the *_sb strides are ignored); Sq / Sk are the longest lengths; lse and delta are [H, total_q],
+   * dq_accum [H, total_q, 128].  Causal masks compare positions inside a sequence. */
+  const int* cu_seqlens_q;
+  const int* cu_seqlens_k;
+  int total_q, total_k;
 } b200_attn_t;
 B200_API int b200_flash_attn_fwd(const b200_attn_t* desc, void* out, float* lse, const void* q, const void* k,
                                  const void* v, cudaStream_t stream);

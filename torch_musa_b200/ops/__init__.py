@@ -20,6 +20,7 @@ from .functional import (  # noqa: F401
     fused_cross_entropy,
     multi_tensor_l2norm,
     scaled_dot_product_attention,
+    flash_attn_varlen_func,
 )
 from .modules import RMSNorm, RoPE, SwishGLU, FusedCrossEntropyLoss, BatchNormAct2d  # noqa: F401
 from . import fake  # noqa: F401  (FakeTensor / meta rules for torch.compile)

@@ -118,3 +118,14 @@ def _(a, b, counts, mode):
 @_reg("grouped_mm_out")
 def _(a, b, counts, mode, out):
     return out
+
+
+@_reg("varlen_attention")
+def _(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, causal=False, scale=None):
+    return torch.empty_like(q, memory_format=torch.contiguous_format), q.new_empty((q.shape[1], q.shape[0]), dtype=torch.float32)
+
+
+@_reg("varlen_attention_backward")
+def _(grad_out, q, k, v, out, lse, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, causal=False, scale=None):
+    return (torch.empty_like(q, memory_format=torch.contiguous_format), torch.empty_like(k, memory_format=torch.contiguous_format),
+            torch.empty_like(v, memory_format=torch.contiguous_format))

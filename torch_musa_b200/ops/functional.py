@@ -338,3 +338,50 @@ def scaled_dot_product_attention(q, k, v, attn_mask=None, dropout_p: float = 0.0
     """``F.scaled_dot_product_attention``; on the device it is routed to the backend's attention kernels."""
     return F.scaled_dot_product_attention(q, k, v, attn_mask=attn_mask, dropout_p=dropout_p, is_causal=is_causal,
                                           scale=scale, enable_gqa=enable_gqa)
+
+
+# ------------------------------------------------------------------------- packed variable-length attention
+class _VarlenAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, cu_q, cu_k, max_q, max_k, causal, scale):
+        out, lse = torch.ops.blackwell.varlen_attention(q, k, v, cu_q, cu_k, max_q, max_k, causal, scale)
+        ctx.save_for_backward(q, k, v, out, lse, cu_q, cu_k)
+        ctx.args = (max_q, max_k, causal, scale)
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        q, k, v, out, lse, cu_q, cu_k = ctx.saved_tensors
+        dq, dk, dv = torch.ops.blackwell.varlen_attention_backward(d_out, q, k, v, out, lse, cu_q, cu_k, *ctx.args)
+        return dq, dk, dv, None, None, None, None, None, None
+
+
+def flash_attn_varlen_func(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens_q: torch.Tensor,
+                           cu_seqlens_k: torch.Tensor, max_seqlen_q: int, max_seqlen_k: int,
+                           softmax_scale: Optional[float] = None, causal: bool = False) -> torch.Tensor:
+    """Attention over sequences of different lengths packed without padding: ``q`` [total_q, H, D], ``k`` / ``v``
+    [total_k, Hkv, D]; sequence i owns rows ``cu_seqlens[i]:cu_seqlens[i + 1]`` (int32 prefix sums, on the device of
+    the tensors).  Returns [total_q, H, D].  On the blackwell device with D = 128 and bf16 / fp16 the whole batch is
+    one launch of the tensor-core forward (one more for the backward) and the lengths are never read on the host;
+    otherwise the sequences are processed one by one with ``scaled_dot_product_attention``.  A causal mask compares
+    positions inside a sequence (key index <= query index)."""
+    if (_on_device(q) and q.shape[-1] == 128 and q.dtype in (torch.bfloat16, torch.float16)
+            and k.dtype == q.dtype and v.dtype == q.dtype):
+        return _VarlenAttention.apply(q, k, v, cu_seqlens_q.to(torch.int32), cu_seqlens_k.to(torch.int32),
+                                      int(max_seqlen_q), int(max_seqlen_k), bool(causal), softmax_scale)
+    cq, ck = cu_seqlens_q.tolist(), cu_seqlens_k.tolist()
+    rep = q.shape[1] // k.shape[1]
+    outs = []
+    for i in range(len(cq) - 1):
+        qi = q[cq[i]:cq[i + 1]].transpose(0, 1).unsqueeze(0)
+        ki = k[ck[i]:ck[i + 1]].transpose(0, 1).unsqueeze(0)
+        vi = v[ck[i]:ck[i + 1]].transpose(0, 1).unsqueeze(0)
+        if rep > 1:
+            ki, vi = ki.repeat_interleave(rep, 1), vi.repeat_interleave(rep, 1)
+        mask = None
+        if causal:
+            sq, sk = qi.shape[2], ki.shape[2]
+            mask = torch.ones(sq, sk, dtype=torch.bool, device=q.device).tril()
+        o = F.scaled_dot_product_attention(qi, ki, vi, attn_mask=mask, scale=softmax_scale)
+        outs.append(o.squeeze(0).transpose(0, 1))
+    return torch.cat(outs, 0)
