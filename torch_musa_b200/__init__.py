@@ -337,6 +337,7 @@ torch.backends.blackwell = _Backends()
 if not hasattr(torch.version, DEVICE_TYPE):
     setattr(torch.version, DEVICE_TYPE, "sm_100a / CUDA " + str(torch.version.cuda))
 from . import utils, profiler, testing  # noqa: E402,F401
+from . import ao  # noqa: E402,F401  (publishes the fused SiLU blocks under torch.ao.nn.intrinsic*, adds the fusion rules)
 
 
 def _autoload():
