@@ -118,3 +118,23 @@ def test_aot_package_roundtrip_on_cpu(bw, tmp_path):
     assert int(out["n"]) == int(exp["n"]) + 1
     with pytest.raises(TypeError):
         loaded(x)
+
+
+def test_dynamo_traces_device_module_calls_without_graph_breaks(bw):
+    """Device queries fold into the graph as constants, the device module's autocast class is a context manager Dynamo
+    knows, the stream accessors are in-graph functions: a function that uses them compiles as ONE graph."""
+    from torch._dynamo import trace_rules
+    from torch._dynamo.variables import TorchInGraphFunctionVariable
+
+    rule_map = trace_rules.get_torch_obj_rule_map()
+    for fn in (bw.current_stream, bw.default_stream, bw.stream, bw.is_available, bw.current_device):
+        assert rule_map.get(fn) is TorchInGraphFunctionVariable, fn
+
+    def f(x):
+        with bw.amp.autocast(dtype=torch.bfloat16):
+            y = x @ x
+        return y + (1 if bw.is_available() else 2) + bw.device_count()
+
+    x = torch.randn(4, 4)
+    compiled = torch.compile(f, backend="eager", fullgraph=True)      # fullgraph: any graph break raises
+    assert torch.allclose(compiled(x), f(x))

@@ -84,6 +84,8 @@ def install() -> None:
     except Exception:  # pragma: no cover
         pass
 
+    _install_trace_rules(bw)
+
     from .compile_backend import register as _register_backend
 
     _register_backend()
@@ -91,3 +93,68 @@ def install() -> None:
     from .compile.backend import register as _register_compiler
 
     _register_compiler()
+
+
+# Functions of the device module that Dynamo may call while tracing and keep in the graph as calls (the same
+# treatment torch.cuda's stream accessors get), and the autocast class it may enter as a context manager.
+_IN_GRAPH_FUNCTIONS = ("current_stream", "default_stream", "stream")
+# Queries whose answer Dynamo may bake into the graph as a constant (the second group under a guard that re-checks it),
+# the treatment the same functions of torch.cuda get.
+_CONSTANT_FUNCTIONS = ("is_available", "get_device_properties", "is_bf16_supported", "device_count")
+_GUARDED_CONSTANT_FUNCTIONS = ("current_device", "is_initialized")
+
+
+def _install_trace_rules(bw) -> None:
+    """Parity: reference torch_musa/_dynamo/trace_rules.py:20-42 (in-graph functions) and
+    torch_musa/_dynamo/variables/torch.py:7-13 (autocast as a supported context-manager class)."""
+    try:
+        from torch._dynamo import trace_rules
+        from torch._dynamo.variables import TorchInGraphFunctionVariable
+        from torch._dynamo.variables.torch import supported_ctx_manager_classes
+    except Exception:  # pragma: no cover - Dynamo is optional in a PyTorch build
+        return
+    from torch._dynamo.variables import torch as torch_vars
+
+    names = _IN_GRAPH_FUNCTIONS + _CONSTANT_FUNCTIONS + _GUARDED_CONSTANT_FUNCTIONS
+    rules = {f"torch.blackwell.{name}": TorchInGraphFunctionVariable for name in names if hasattr(bw, name)}
+    for name in _CONSTANT_FUNCTIONS + _GUARDED_CONSTANT_FUNCTIONS:
+        torch_vars.constant_fold_functions[getattr(bw, name)] = None
+    for name in _GUARDED_CONSTANT_FUNCTIONS:
+        torch_vars.constant_fold_functions_need_guards[getattr(bw, name)] = None
+    try:
+        trace_rules.get_torch_obj_rule_map.cache_clear()          # the object -> rule map is built once and cached
+        trace_rules.torch_name_rule_map[-1].update(rules)          # the table of Python (non C-binding) functions
+    except Exception:  # pragma: no cover
+        pass
+    try:
+        supported_ctx_manager_classes[bw.amp.autocast] = None
+        _teach_autocast(bw)
+    except Exception:  # pragma: no cover
+        pass
+
+
+def _teach_autocast(bw) -> None:
+    """Dynamo models autocast regions with one variable class that is built from ``torch.autocast``'s arguments; the
+    device module's ``autocast(enabled, dtype, cache_enabled)`` is translated into that form (device type fixed)."""
+    import inspect
+
+    from torch._dynamo.variables.ctx_manager import AutocastModeVariable
+    from torch._dynamo.variables.torch import TorchCtxManagerClassVariable
+
+    if getattr(TorchCtxManagerClassVariable.call_function, "_blackwell_autocast", False):
+        return
+    original = TorchCtxManagerClassVariable.call_function
+    own_signature = inspect.signature(bw.amp.autocast)
+
+    def call_function(self, tx, args, kwargs):
+        if self.value is bw.amp.autocast:
+            bound = own_signature.bind(*args, **kwargs)
+            bound.apply_defaults()
+            a = bound.arguments
+            return AutocastModeVariable.create(
+                torch.amp.autocast_mode.autocast, [],
+                {"device_type": "blackwell", "dtype": a["dtype"], "enabled": a["enabled"], "cache_enabled": a["cache_enabled"]})
+        return original(self, tx, args, kwargs)
+
+    call_function._blackwell_autocast = True
+    TorchCtxManagerClassVariable.call_function = call_function
