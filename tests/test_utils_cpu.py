@@ -175,3 +175,13 @@ def test_multi_process_harness():
         world_size = 3
 
     Suite().run_on_ranks(_rank_sum_body, 10)
+
+
+def test_op_coverage_report_reads_the_dispatcher():
+    from torch_musa_b200.utils import op_coverage
+
+    r = op_coverage.report()
+    assert r["native_base_operators"] > 150 and "mm" in r["native_by_base"] and "convolution_overrideable" in r["native_by_base"]
+    assert any(n.startswith("blackwell::") for n in r["custom_operators"])
+    assert r["covered_of_cuda"] <= r["cuda_base_operators"] and "mm" not in r["fallback_base_operators"]
+    assert op_coverage.main(["--missing", "3"]) == 0
