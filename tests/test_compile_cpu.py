@@ -138,3 +138,19 @@ def test_dynamo_traces_device_module_calls_without_graph_breaks(bw):
     x = torch.randn(4, 4)
     compiled = torch.compile(f, backend="eager", fullgraph=True)      # fullgraph: any graph break raises
     assert torch.allclose(compiled(x), f(x))
+
+
+def test_aot_c_shim_is_exported_and_reports_errors(bw):
+    """The C ABI for ahead-of-time compiled code: device-type code, and a failure that comes back as a status plus a
+    message instead of a C++ exception (no device here, so every index is out of range)."""
+    import ctypes
+
+    lib = ctypes.CDLL(bw._C.__file__)
+    assert lib.aoti_torch_device_type_blackwell() == torch._C._autograd.DeviceType.PrivateUse1.value
+    lib.b200_shim_last_error.restype = ctypes.c_char_p
+    handle = ctypes.c_void_p()
+    if not bw.is_available():
+        assert lib.aoti_torch_create_blackwell_guard(0, ctypes.byref(handle)) == 1
+        assert b"out of range" in lib.b200_shim_last_error()
+    assert lib.aoti_torch_create_blackwell_guard(0, None) == 1 and b"null" in lib.b200_shim_last_error()
+    assert lib.aoti_torch_delete_blackwell_guard(None) == 0          # deleting nothing is fine

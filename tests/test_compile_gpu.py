@@ -140,3 +140,29 @@ def test_aot_package_on_device(bw, tmp_path):
     out = loaded(x.to(DEV))
     assert (out.cpu().float() - ref(x).float()).abs().max() < 0.06
     assert loaded.runner.fused_launches >= 1
+
+
+def test_aot_c_shim_guards_and_streams(bw):
+    """The C ABI for ahead-of-time compiled code on a device: a stream guard makes a raw stream current and restores
+    the previous one, the device guard restores its device, the current-stream query returns the raw handle."""
+    import ctypes
+
+    lib = ctypes.CDLL(bw._C.__file__)
+    dev = bw.current_device()
+    cur = ctypes.c_void_p()
+    assert lib.aoti_torch_get_current_blackwell_stream(dev, ctypes.byref(cur)) == 0
+    assert (cur.value or 0) == bw.current_stream(dev).cuda_stream
+    side = bw.Stream(dev)
+    guard = ctypes.c_void_p()
+    assert lib.aoti_torch_create_blackwell_stream_guard(ctypes.c_void_p(side.cuda_stream), dev, ctypes.byref(guard)) == 0
+    assert bw.current_stream(dev).cuda_stream == side.cuda_stream
+    x = torch.ones(1024, device=DEV) * 3                       # work issued under the guard runs on `side`
+    assert lib.aoti_torch_delete_blackwell_stream_guard(guard) == 0
+    assert bw.current_stream(dev).cuda_stream == (cur.value or 0)
+    side.synchronize()
+    assert float(x.sum()) == 3072.0
+    dguard = ctypes.c_void_p()
+    assert lib.aoti_torch_create_blackwell_guard(dev, ctypes.byref(dguard)) == 0
+    assert lib.aoti_torch_blackwell_guard_set_index(dguard, dev) == 0
+    assert lib.aoti_torch_blackwell_guard_set_index(dguard, 1 << 20) == 1       # refused, status instead of a throw
+    assert lib.aoti_torch_delete_blackwell_guard(dguard) == 0 and bw.current_device() == dev
