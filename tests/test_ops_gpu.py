@@ -353,3 +353,24 @@ def test_mixed_device_arguments_raise(bw, dev):
     with pytest.raises(RuntimeError, match="same device"):
         torch.ops.blackwell.cross_entropy_fwd(h.float(), torch.zeros(4, dtype=torch.long))
     bw.synchronize()
+
+
+def test_swiglu_limited_to_live_rows(bw, dev):
+    """Packed row groups with device-side lengths: only the first sum(counts) rows are computed / get a gradient."""
+    from torch_musa_b200.ops import swiglu
+
+    torch.manual_seed(0)
+    x = torch.randn(40, 256).to(torch.bfloat16)
+    counts = torch.tensor([7, 0, 12], dtype=torch.int32)
+    live = int(counts.sum())
+    xd = x.to(dev).requires_grad_()
+    y = swiglu(xd, counts.to(dev))
+    g, u = x.float().chunk(2, -1)
+    ref = torch.nn.functional.silu(g) * u
+    assert (y[:live].float().cpu() - ref[:live]).abs().max() < 2e-2
+    dy = torch.randn(40, 128).to(torch.bfloat16)
+    y.backward(dy.to(dev))
+    xr = x.float().requires_grad_()
+    gr, ur = xr.chunk(2, -1)
+    (torch.nn.functional.silu(gr) * ur)[:live].backward(dy.float()[:live])
+    assert (xd.grad[:live].float().cpu() - xr.grad[:live]).abs().max() < 3e-2

@@ -56,7 +56,16 @@ at::Tensor rope(const at::Tensor& x, const at::Tensor& cos, const at::Tensor& si
   return out;
 }
 
-at::Tensor swiglu(const at::Tensor& x) {
+const int* counts_ptr(const std::optional<at::Tensor>& counts, int* n, const char* what) {
+  *n = 0;
+  if (!counts.has_value() || !counts->defined()) return nullptr;
+  TORCH_CHECK(counts->scalar_type() == at::kInt && counts->dim() == 1 && counts->is_contiguous() && on_device(*counts), what,
+              ": row counts must be a contiguous int32 vector on the device");
+  *n = (int)counts->numel();
+  return counts->const_data_ptr<int>();
+}
+
+at::Tensor swiglu_rows(const at::Tensor& x, const std::optional<at::Tensor>& row_counts) {
   check_fast(x, "swiglu");
   TORCH_CHECK(x.dim() >= 1 && x.size(-1) % 2 == 0, "swiglu: last dimension must be even");
   at::Tensor xc = x.contiguous();
@@ -64,23 +73,30 @@ at::Tensor swiglu(const at::Tensor& x) {
   std::vector<int64_t> shape(x.sizes().begin(), x.sizes().end());
   shape.back() = h;
   at::Tensor out = at::empty(shape, x.options());
+  int n = 0;
+  const int* cp = counts_ptr(row_counts, &n, "swiglu");
   DeviceSwitch sw(x.device().index());
-  B200_KERNEL_CALL(b200_swiglu_fwd(kdtype(x.scalar_type()), out.mutable_data_ptr(), xc.const_data_ptr(), rows, h,
-                                   current_raw_stream(x)));
+  B200_KERNEL_CALL(b200_swiglu_fwd_rows(kdtype(x.scalar_type()), out.mutable_data_ptr(), xc.const_data_ptr(), rows, h, cp, n,
+                                        current_raw_stream(x)));
   return out;
 }
 
-at::Tensor swiglu_backward(const at::Tensor& dy, const at::Tensor& x) {
+at::Tensor swiglu_rows_backward(const at::Tensor& dy, const at::Tensor& x, const std::optional<at::Tensor>& row_counts) {
   check_fast(x, "swiglu_backward");
   check_devices("swiglu_backward", x, dy);
   at::Tensor xc = x.contiguous(), dyc = dy.contiguous();
   const int64_t h = x.size(-1) / 2, rows = h ? x.numel() / (2 * h) : 0;
   at::Tensor dx = at::empty_like(xc);
+  int n = 0;
+  const int* cp = counts_ptr(row_counts, &n, "swiglu_backward");
   DeviceSwitch sw(x.device().index());
-  B200_KERNEL_CALL(b200_swiglu_bwd(kdtype(x.scalar_type()), dx.mutable_data_ptr(), dyc.const_data_ptr(),
-                                   xc.const_data_ptr(), rows, h, current_raw_stream(x)));
+  B200_KERNEL_CALL(b200_swiglu_bwd_rows(kdtype(x.scalar_type()), dx.mutable_data_ptr(), dyc.const_data_ptr(),
+                                        xc.const_data_ptr(), rows, h, cp, n, current_raw_stream(x)));
   return dx;
 }
+
+at::Tensor swiglu(const at::Tensor& x) { return swiglu_rows(x, std::nullopt); }
+at::Tensor swiglu_backward(const at::Tensor& dy, const at::Tensor& x) { return swiglu_rows_backward(dy, x, std::nullopt); }
 
 at::Tensor silu_mul(const at::Tensor& gate, const at::Tensor& up) {
   check_fast(gate, "silu_mul");
@@ -300,6 +316,8 @@ TORCH_LIBRARY(blackwell, m) {
   m.def("rope(Tensor x, Tensor cos, Tensor sin, Tensor? positions=None, bool interleaved=False, bool conj=False) -> Tensor");
   m.def("swiglu(Tensor x) -> Tensor");
   m.def("swiglu_backward(Tensor dy, Tensor x) -> Tensor");
+  m.def("swiglu_rows(Tensor x, Tensor? row_counts) -> Tensor");
+  m.def("swiglu_rows_backward(Tensor dy, Tensor x, Tensor? row_counts) -> Tensor");
   m.def("silu_mul(Tensor gate, Tensor up) -> Tensor");
   m.def("silu_mul_backward(Tensor dy, Tensor gate, Tensor up) -> (Tensor, Tensor)");
   m.def("cross_entropy_fwd(Tensor logits, Tensor target, int ignore_index=-100, float label_smoothing=0.0) -> (Tensor, Tensor)");
@@ -325,6 +343,8 @@ TORCH_LIBRARY_IMPL(blackwell, PrivateUse1, m) {
   m.impl("rope", TORCH_FN(rope));
   m.impl("swiglu", TORCH_FN(swiglu));
   m.impl("swiglu_backward", TORCH_FN(swiglu_backward));
+  m.impl("swiglu_rows", TORCH_FN(swiglu_rows));
+  m.impl("swiglu_rows_backward", TORCH_FN(swiglu_rows_backward));
   m.impl("silu_mul", TORCH_FN(silu_mul));
   m.impl("silu_mul_backward", TORCH_FN(silu_mul_backward));
   m.impl("cross_entropy_fwd", TORCH_FN(cross_entropy_fwd));

@@ -244,6 +244,12 @@ B200_API int b200_rope(int dtype, void* out, const void* x, const float* cos, co
                        int interleaved, int conj, cudaStream_t stream);
 /* x [rows, 2*h] -> out [rows, h] = silu(x[:, :h]) * x[:, h:]  (gate_first=1) */
 B200_API int b200_swiglu_fwd(int dtype, void* out, const void* x, int64_t rows, int64_t h, cudaStream_t stream);
+/* Same, limited to the first sum(row_counts[0..n_counts)) rows (device int32 counts of packed row groups; NULL: all rows);
+ * the other rows of out / dx are left untouched. */
+B200_API int b200_swiglu_fwd_rows(int dtype, void* out, const void* x, int64_t rows, int64_t h, const int* row_counts,
+                                  int n_counts, cudaStream_t stream);
+B200_API int b200_swiglu_bwd_rows(int dtype, void* dx, const void* dy, const void* x, int64_t rows, int64_t h,
+                                  const int* row_counts, int n_counts, cudaStream_t stream);
 B200_API int b200_swiglu_bwd(int dtype, void* dx, const void* dy, const void* x, int64_t rows, int64_t h,
                              cudaStream_t stream);
 /* two-tensor form: out = silu(gate) * up */

@@ -76,12 +76,22 @@ __device__ __forceinline__ float silu_f(float g) { return g / (1.f + __expf(-g))
 constexpr int kSwU = 4;
 constexpr int kSwThreads = 128;
 
+// Packed row groups whose lengths live on the device (the rows a mixture-of-experts layer received): only the
+// first sum(counts) rows carry data.  Every thread adds the few counts itself (they sit in L2).
+__device__ __forceinline__ int64_t live_rows(const int* __restrict__ counts, int n) {
+  int64_t s = 0;
+  for (int i = 0; i < n; ++i) s += max(__ldg(counts + i), 0);
+  return s;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kSwThreads) swiglu_fwd_kernel(T* __restrict__ out, const T* __restrict__ x,
-                                                                int64_t rows, int64_t h) {
+                                                                int64_t rows, int64_t h,
+                                                                const int* __restrict__ row_counts, int n_counts) {
   constexpr int V = Vec16<T>::N;
   const int vh = (int)(h / V);
   const int64_t r = blockIdx.x;
+  if (row_counts && r >= live_rows(row_counts, n_counts)) return;   // rows of no group: left untouched
   const T* gp = x + r * 2 * h;
   const T* up = gp + h;
   T* op = out + r * h;
@@ -106,10 +116,12 @@ __global__ void __launch_bounds__(kSwThreads) swiglu_fwd_kernel(T* __restrict__ 
 
 template <typename T>
 __global__ void __launch_bounds__(kSwThreads) swiglu_bwd_kernel(T* __restrict__ dx, const T* __restrict__ dy,
-                                                                const T* __restrict__ x, int64_t rows, int64_t h) {
+                                                                const T* __restrict__ x, int64_t rows, int64_t h,
+                                                                const int* __restrict__ row_counts, int n_counts) {
   constexpr int V = Vec16<T>::N;
   const int vh = (int)(h / V);
   const int64_t r = blockIdx.x;
+  if (row_counts && r >= live_rows(row_counts, n_counts)) return;
   const T* gp = x + r * 2 * h;
   const T* up = gp + h;
   const T* dp = dy + r * h;
@@ -370,25 +382,35 @@ int b200_rope(int dtype, void* out, const void* x, const float* cosv, const floa
 }
 
 int b200_swiglu_fwd(int dtype, void* out, const void* x, int64_t rows, int64_t h, cudaStream_t stream) {
+  return b200_swiglu_fwd_rows(dtype, out, x, rows, h, nullptr, 0, stream);
+}
+
+int b200_swiglu_bwd(int dtype, void* dx, const void* dy, const void* x, int64_t rows, int64_t h, cudaStream_t stream) {
+  return b200_swiglu_bwd_rows(dtype, dx, dy, x, rows, h, nullptr, 0, stream);
+}
+
+int b200_swiglu_fwd_rows(int dtype, void* out, const void* x, int64_t rows, int64_t h, const int* row_counts, int n_counts,
+                         cudaStream_t stream) {
   if (rows == 0 || h == 0) return 0;
   B200K_DISPATCH_FLOAT(dtype, T, {
     if (h % Vec16<T>::N != 0 || !aligned16((const T*)x) || !aligned16((T*)out)) return (int)cudaErrorNotSupported;
     const unsigned chunks = (unsigned)cdiv(h / Vec16<T>::N, (int64_t)kSwThreads * kSwU);
     if (rows > 2147483647ll || chunks > 65535u) return (int)cudaErrorNotSupported;
-    swiglu_fwd_kernel<T><<<dim3((unsigned)rows, chunks), kSwThreads, 0, stream>>>((T*)out, (const T*)x, rows, h);
+    swiglu_fwd_kernel<T><<<dim3((unsigned)rows, chunks), kSwThreads, 0, stream>>>((T*)out, (const T*)x, rows, h, row_counts, n_counts);
     B200K_LAUNCH_RET();
   })
   return (int)cudaErrorNotSupported;
 }
 
-int b200_swiglu_bwd(int dtype, void* dx, const void* dy, const void* x, int64_t rows, int64_t h, cudaStream_t stream) {
+int b200_swiglu_bwd_rows(int dtype, void* dx, const void* dy, const void* x, int64_t rows, int64_t h, const int* row_counts,
+                         int n_counts, cudaStream_t stream) {
   if (rows == 0 || h == 0) return 0;
   B200K_DISPATCH_FLOAT(dtype, T, {
     if (h % Vec16<T>::N != 0 || !aligned16((const T*)x) || !aligned16((T*)dx) || !aligned16((const T*)dy))
       return (int)cudaErrorNotSupported;
     const unsigned chunks = (unsigned)cdiv(h / Vec16<T>::N, (int64_t)kSwThreads * kSwU);
     if (rows > 2147483647ll || chunks > 65535u) return (int)cudaErrorNotSupported;
-    swiglu_bwd_kernel<T><<<dim3((unsigned)rows, chunks), kSwThreads, 0, stream>>>((T*)dx, (const T*)dy, (const T*)x, rows, h);
+    swiglu_bwd_kernel<T><<<dim3((unsigned)rows, chunks), kSwThreads, 0, stream>>>((T*)dx, (const T*)dy, (const T*)x, rows, h, row_counts, n_counts);
     B200K_LAUNCH_RET();
   })
   return (int)cudaErrorNotSupported;

@@ -65,7 +65,7 @@ class Experts(nn.Module):
         if isinstance(rows_per_expert, torch.Tensor):
             # counts on the device: one grouped GEMM per projection over the packed rows, nothing read on the host
             h = BF.grouped_linear(rows, self.w13, rows_per_expert, None, dx_out)
-            return BF.grouped_linear(BF.swiglu(h), self.w2, rows_per_expert, y_out)
+            return BF.grouped_linear(BF.swiglu(h, rows_per_expert), self.w2, rows_per_expert, y_out)
         outs, start = [], 0
         for e, n in enumerate(rows_per_expert):
             n = min(n, rows.shape[0] - start)

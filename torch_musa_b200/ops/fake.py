@@ -129,3 +129,13 @@ def _(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, causal=Fa
 def _(grad_out, q, k, v, out, lse, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, causal=False, scale=None):
     return (torch.empty_like(q, memory_format=torch.contiguous_format), torch.empty_like(k, memory_format=torch.contiguous_format),
             torch.empty_like(v, memory_format=torch.contiguous_format))
+
+
+@_reg("swiglu_rows")
+def _(x, row_counts):
+    return x.new_empty(x.shape[:-1] + (x.shape[-1] // 2,))
+
+
+@_reg("swiglu_rows_backward")
+def _(dy, x, row_counts):
+    return torch.empty_like(x, memory_format=torch.contiguous_format)

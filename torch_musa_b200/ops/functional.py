@@ -190,9 +190,25 @@ class _SwiGLU(torch.autograd.Function):
         return torch.ops.blackwell.swiglu_backward(dy, x)
 
 
-def swiglu(x: torch.Tensor) -> torch.Tensor:
-    """``silu(x[..., :h]) * x[..., h:]`` for a packed gate|up tensor."""
+class _SwiGLURows(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, counts):
+        ctx.save_for_backward(x, counts)
+        return torch.ops.blackwell.swiglu_rows(x, counts)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, counts = ctx.saved_tensors
+        return torch.ops.blackwell.swiglu_rows_backward(dy, x, counts), None
+
+
+def swiglu(x: torch.Tensor, row_counts: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``silu(x[..., :h]) * x[..., h:]`` for a packed gate|up tensor.  ``row_counts`` (int32, on the device): the
+    lengths of the packed row groups of a 2-D ``x``; only the first ``row_counts.sum()`` rows are computed (and get a
+    gradient), the others are left as they are -- the sum is taken on the device."""
     if _on_device(x):
+        if row_counts is not None:
+            return _SwiGLURows.apply(x, row_counts.to(torch.int32))
         return _SwiGLU.apply(x)
     g, u = x.chunk(2, dim=-1)
     return F.silu(g) * u
