@@ -246,6 +246,38 @@ at::Tensor decode_attention(const at::Tensor& q, const at::Tensor& k_cache, cons
   return out;
 }
 
+// q / k / v: [B, 1, heads, 128] or [B, heads, 128] (views with a contiguous last dimension are fine)
+at::Tensor decode_rope_cache(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& cos,
+                             const at::Tensor& sin, const at::Tensor& pos, at::Tensor& k_cache, at::Tensor& v_cache) {
+  check_fast(q, "decode_rope_cache");
+  check_devices("decode_rope_cache", q, k, v, cos, sin, pos, k_cache, v_cache);
+  auto rows = [](const at::Tensor& t, const char* name) {
+    TORCH_CHECK((t.dim() == 3 || (t.dim() == 4 && t.size(1) == 1)) && t.size(-1) == 128 && t.stride(-1) == 1, "decode_rope_cache: ",
+                name, " must be [B, 1, heads, 128] or [B, heads, 128] with a contiguous last dimension");
+  };
+  rows(q, "q"); rows(k, "k"); rows(v, "v");
+  const int64_t B = q.size(0), H = q.size(-2), Hkv = k.size(-2);
+  TORCH_CHECK(k.size(0) == B && v.size(0) == B && v.size(-2) == Hkv && k_cache.dim() == 4 && k_cache.size(0) == B &&
+              k_cache.size(1) == Hkv && k_cache.size(3) == 128 && v_cache.sizes() == k_cache.sizes() && k_cache.is_contiguous() &&
+              v_cache.is_contiguous(), "decode_rope_cache: caches must be contiguous [B, Hkv, max_len, 128]");
+  TORCH_CHECK(k.scalar_type() == q.scalar_type() && v.scalar_type() == q.scalar_type() && k_cache.scalar_type() == q.scalar_type() &&
+              v_cache.scalar_type() == q.scalar_type(), "decode_rope_cache: one dtype");
+  TORCH_CHECK(cos.scalar_type() == at::kFloat && sin.scalar_type() == at::kFloat && cos.is_contiguous() && sin.is_contiguous() &&
+              cos.size(-1) == 64 && sin.sizes() == cos.sizes(), "decode_rope_cache: cos / sin must be contiguous float32 [positions, 64]");
+  TORCH_CHECK(pos.scalar_type() == at::kLong && pos.numel() == 1, "decode_rope_cache: pos must be one int64 element");
+  at::Tensor out = at::empty({B, H, 128}, q.options());
+  const int64_t strides[6] = {q.stride(0), q.stride(-2), k.stride(0), k.stride(-2), v.stride(0), v.stride(-2)};
+  DeviceSwitch sw(q.device().index());
+  int e = b200_decode_rope_cache(kdtype(q.scalar_type()), out.mutable_data_ptr(), q.const_data_ptr(), k.const_data_ptr(),
+                                 v.const_data_ptr(), strides, cos.const_data_ptr<float>(), sin.const_data_ptr<float>(),
+                                 reinterpret_cast<const long long*>(pos.const_data_ptr<int64_t>()), k_cache.mutable_data_ptr(),
+                                 v_cache.mutable_data_ptr(), (int)B, (int)H, (int)Hkv, (int)k_cache.size(2), 128,
+                                 (int)(cos.numel() / 64), current_raw_stream(q));
+  TORCH_CHECK(e != (int)cudaErrorNotSupported, "decode_rope_cache: head_dim 128, bf16 / fp16, even strides only");
+  B200_KERNEL_CALL(e);
+  return out;
+}
+
 // mode 0: a [R, K] x b [G, N, K] -> [R, N];  mode 1: a [R, N] x b [G, N, K] -> [R, K];  mode 2: a [R, M], b [R, N] -> [G, M, N].
 // The rows of group g are the next counts[g] packed rows; counts stays on the device.
 at::Tensor grouped_mm_impl(const at::Tensor& a, const at::Tensor& b, const at::Tensor& counts, int64_t mode,
@@ -333,11 +365,13 @@ TORCH_LIBRARY(blackwell, m) {
   m.def("decode_attention(Tensor q, Tensor k_cache, Tensor v_cache, Tensor pos, float? scale=None) -> Tensor");
   m.def("grouped_mm(Tensor a, Tensor b, Tensor counts, int mode) -> Tensor");
   m.def("grouped_mm_out(Tensor a, Tensor b, Tensor counts, int mode, Tensor(a!) out) -> Tensor(a!)");
+  m.def("decode_rope_cache(Tensor q, Tensor k, Tensor v, Tensor cos, Tensor sin, Tensor pos, Tensor(a!) k_cache, Tensor(b!) v_cache) -> Tensor");
   m.def("_sleep(int cycles) -> ()");
 }
 
 TORCH_LIBRARY_IMPL(blackwell, PrivateUse1, m) {
   m.impl("decode_attention", TORCH_FN(decode_attention));
+  m.impl("decode_rope_cache", TORCH_FN(decode_rope_cache));
   m.impl("grouped_mm", TORCH_FN(grouped_mm));
   m.impl("grouped_mm_out", TORCH_FN(grouped_mm_out));
   m.impl("rope", TORCH_FN(rope));

@@ -564,6 +564,13 @@ B200_API int b200_decode_attention(int dtype, void* out, const void* q, const vo
                                    const long long* pos, int B, int H, int Hkv, int max_len, int head_dim, float scale,
                                    cudaStream_t stream);
 
+/* One decode step's rotary embedding + cache update: q_out [B, H, 128] = rope(q), k_cache[b, hk, *pos] = rope(k),
+ * v_cache[b, hk, *pos] = v.  q / k / v rows of 128 contiguous elements addressed by strides = {q batch, q head, k batch,
+ * k head, v batch, v head} (elements); cos / sin float [table_len, 64] (rotate-half layout); caches [B, Hkv, max_len, 128]. */
+B200_API int b200_decode_rope_cache(int dtype, void* q_out, const void* q, const void* k, const void* v, const int64_t* strides,
+                                    const float* cosv, const float* sinv, const long long* pos, void* k_cache, void* v_cache,
+                                    int B, int H, int Hkv, int max_len, int head_dim, int table_len, cudaStream_t stream);
+
 /* ---------------------------------------------------------------- expert-parallel MoE token exchange (bf16 rows)
  * E experts, E / world per rank in rank order; idx / slot / pos are int32 [T*K]; receive buffers hold cap_rows
  * rows of d elements at a byte offset of every rank's arena; counts_off points at world*E int32 of scratch in the

@@ -129,6 +129,62 @@ decode_attn_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __rest
   }
 }
 
+// One decode step's rotary embedding and cache update in ONE launch: the new query rows are rotated into q_out, the
+// new key rows are rotated straight into the key cache at position *pos, the new value rows are copied into the value
+// cache.  One warp per (batch, head) row of 128 elements: a lane owns two adjacent dims of the first half and their
+// partners in the second half (rotate-half layout).  The position is read from device memory (graph-capturable).
+template <typename T>
+__global__ void __launch_bounds__(256)
+decode_rope_cache_kernel(T* __restrict__ q_out, const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
+                         long long q_sb, long long q_sh, long long k_sb, long long k_sh, long long v_sb, long long v_sh,
+                         const float* __restrict__ cosv, const float* __restrict__ sinv, const long long* __restrict__ pos_ptr,
+                         T* __restrict__ k_cache, T* __restrict__ v_cache, int B, int H, int Hkv, int max_len, int table_len) {
+  const int per_b = H + 2 * Hkv;
+  const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= (long long)B * per_b) return;
+  const int lane = threadIdx.x & 31;
+  const int b = (int)(row / per_b), j = (int)(row - (long long)b * per_b);
+  long long p = *pos_ptr;
+  p = p < 0 ? 0 : (p >= max_len ? max_len - 1 : p);
+  const long long pt = p < table_len ? p : table_len - 1;
+  const T* src;
+  T* dst;
+  bool rotate = true;
+  if (j < H) {
+    src = q + b * q_sb + j * q_sh;
+    dst = q_out + ((long long)b * H + j) * DD;
+  } else if (j < H + Hkv) {
+    const int hk = j - H;
+    src = k + b * k_sb + hk * k_sh;
+    dst = k_cache + (((long long)b * Hkv + hk) * max_len + p) * DD;
+  } else {
+    const int hk = j - H - Hkv;
+    src = v + b * v_sb + hk * v_sh;
+    dst = v_cache + (((long long)b * Hkv + hk) * max_len + p) * DD;
+    rotate = false;
+  }
+  // two adjacent elements (4 bytes) of each half
+  const uint32_t lo = *reinterpret_cast<const uint32_t*>(src + lane * 2);
+  const uint32_t hi = *reinterpret_cast<const uint32_t*>(src + DD / 2 + lane * 2);
+  if (!rotate) {
+    *reinterpret_cast<uint32_t*>(dst + lane * 2) = lo;
+    *reinterpret_cast<uint32_t*>(dst + DD / 2 + lane * 2) = hi;
+    return;
+  }
+  const T* l2 = reinterpret_cast<const T*>(&lo);
+  const T* h2 = reinterpret_cast<const T*>(&hi);
+  const float2 c = *reinterpret_cast<const float2*>(cosv + pt * (DD / 2) + lane * 2);
+  const float2 sn = *reinterpret_cast<const float2*>(sinv + pt * (DD / 2) + lane * 2);
+  const float x0a = ToF<T>::to(l2[0]), x0b = ToF<T>::to(l2[1]), x1a = ToF<T>::to(h2[0]), x1b = ToF<T>::to(h2[1]);
+  T ol[2], oh[2];
+  ol[0] = ToF<T>::from(x0a * c.x - x1a * sn.x);
+  ol[1] = ToF<T>::from(x0b * c.y - x1b * sn.y);
+  oh[0] = ToF<T>::from(x1a * c.x + x0a * sn.x);
+  oh[1] = ToF<T>::from(x1b * c.y + x0b * sn.y);
+  *reinterpret_cast<uint32_t*>(dst + lane * 2) = *reinterpret_cast<const uint32_t*>(ol);
+  *reinterpret_cast<uint32_t*>(dst + DD / 2 + lane * 2) = *reinterpret_cast<const uint32_t*>(oh);
+}
+
 }  // namespace
 }  // namespace b200k
 
@@ -147,6 +203,33 @@ extern "C" int b200_decode_attention(int dtype, void* out, const void* q, const 
   else if (dtype == B200_F16)
     decode_attn_kernel<__half><<<B * H, kDecWarps * 32, 0, stream>>>((__half*)out, (const __half*)q, (const __half*)k_cache,
         (const __half*)v_cache, pos, H, Hkv, max_len, sl2);
+  else
+    return (int)cudaErrorNotSupported;
+  B200K_LAUNCH_RET();
+}
+
+extern "C" int b200_decode_rope_cache(int dtype, void* q_out, const void* q, const void* k, const void* v, const int64_t* strides,
+                                      const float* cosv, const float* sinv, const long long* pos, void* k_cache, void* v_cache,
+                                      int B, int H, int Hkv, int max_len, int head_dim, int table_len, cudaStream_t stream) {
+  // strides (elements): q batch, q head, k batch, k head, v batch, v head; rows of 128 contiguous elements, 4-byte aligned
+  if (head_dim != DD || B <= 0 || H <= 0 || Hkv <= 0 || max_len <= 0 || table_len <= 0) return (int)cudaErrorNotSupported;
+  for (int i = 0; i < 6; ++i)
+    if (strides[i] % 2 != 0) return (int)cudaErrorNotSupported;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+       reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 3)
+    return (int)cudaErrorNotSupported;
+  if ((reinterpret_cast<uintptr_t>(cosv) | reinterpret_cast<uintptr_t>(sinv)) & 7) return (int)cudaErrorNotSupported;
+  const long long rows = (long long)B * (H + 2 * Hkv);
+  const unsigned grid = (unsigned)((rows + 7) / 8);
+  if (dtype == B200_BF16)
+    decode_rope_cache_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(
+        (__nv_bfloat16*)q_out, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, strides[0], strides[1],
+        strides[2], strides[3], strides[4], strides[5], cosv, sinv, pos, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, B, H,
+        Hkv, max_len, table_len);
+  else if (dtype == B200_F16)
+    decode_rope_cache_kernel<__half><<<grid, 256, 0, stream>>>(
+        (__half*)q_out, (const __half*)q, (const __half*)k, (const __half*)v, strides[0], strides[1], strides[2], strides[3],
+        strides[4], strides[5], cosv, sinv, pos, (__half*)k_cache, (__half*)v_cache, B, H, Hkv, max_len, table_len);
   else
     return (int)cudaErrorNotSupported;
   B200K_LAUNCH_RET();

@@ -130,15 +130,18 @@ class LlamaDecoder:
                 q, k, v = a.wqkv(hn).view(B, 1, h + 2 * kv, hd).split([h, kv, kv], dim=2)
             else:
                 q, k, v = a.wq(hn).view(B, 1, h, hd), a.wk(hn).view(B, 1, kv, hd), a.wv(hn).view(B, 1, kv, hd)
-            q = BF.rope(q, self.cos, self.sin, positions)
-            k = BF.rope(k, self.cos, self.sin, positions)
-            self.k_cache[li].index_copy_(2, self.pos, k.transpose(1, 2))
-            self.v_cache[li].index_copy_(2, self.pos, v.transpose(1, 2))
             if self._fused_decode:
-                # one memory-bound kernel over the cache; the visible length comes from the device counter
-                o = torch.ops.blackwell.decode_attention(q.reshape(B, h, hd), self.k_cache[li], self.v_cache[li], self.pos)
+                # one launch rotates q and k, writes the new key / value rows into the caches at the device-side position;
+                # one memory-bound kernel then reads the cache, its visible length from the same counter
+                qr = torch.ops.blackwell.decode_rope_cache(q, k, v, self.cos, self.sin, self.pos, self.k_cache[li],
+                                                           self.v_cache[li])
+                o = torch.ops.blackwell.decode_attention(qr, self.k_cache[li], self.v_cache[li], self.pos)
                 o = o.view(B, 1, h * hd)
             else:
+                q = BF.rope(q, self.cos, self.sin, positions)
+                k = BF.rope(k, self.cos, self.sin, positions)
+                self.k_cache[li].index_copy_(2, self.pos, k.transpose(1, 2))
+                self.v_cache[li].index_copy_(2, self.pos, v.transpose(1, 2))
                 o = F.scaled_dot_product_attention(q.transpose(1, 2), self.k_cache[li], self.v_cache[li], attn_mask=mask,
                                                    enable_gqa=(kv != h)).transpose(1, 2).reshape(B, 1, h * hd)
             x = x + self._reduce(a.wo(o))

@@ -139,3 +139,8 @@ def _(x, row_counts):
 @_reg("swiglu_rows_backward")
 def _(dy, x, row_counts):
     return torch.empty_like(x, memory_format=torch.contiguous_format)
+
+
+@_reg("decode_rope_cache")
+def _(q, k, v, cos, sin, pos, k_cache, v_cache):
+    return q.new_empty((q.shape[0], q.shape[-2], q.shape[-1]))
