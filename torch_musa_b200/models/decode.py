@@ -114,6 +114,17 @@ class LlamaDecoder:
         self.tokens.copy_(logits.argmax(-1))
         self.pos.fill_(S0)
 
+    def _add_norm(self, norm, x, delta):
+        """(norm(x + delta), x + delta); residual add and RMS norm are one kernel on the device."""
+        if delta is None:
+            return norm(x), x
+        if self._fused_decode and isinstance(norm, torch.nn.RMSNorm) and norm.weight is not None:
+            eps = norm.eps if norm.eps is not None else torch.finfo(x.dtype).eps
+            y, res, _ = torch.ops.blackwell.rms_norm_residual(delta, x, norm.weight, eps)
+            return y, res
+        x = x + delta
+        return norm(x), x
+
     # ------------------------------------------------------------------ one decode step on fixed buffers
     @torch.no_grad()
     def _step(self) -> None:
@@ -123,8 +134,9 @@ class LlamaDecoder:
         # keys at index <= pos are visible (additive mask, broadcast over batch and heads)
         mask = torch.where(self._arange <= self.pos, 0.0, float("-inf")).to(self.k_cache.dtype).view(1, 1, 1, self.max_len)
         x = m.tok_emb(self.tokens)
+        delta = None          # the previous block's output, added to the residual stream inside the next norm kernel
         for li, layer in enumerate(m.layers):
-            hn = layer.attn_norm(x)
+            hn, x = self._add_norm(layer.attn_norm, x, delta)
             a = layer.attn
             if cfg.fused_qkv:
                 q, k, v = a.wqkv(hn).view(B, 1, h + 2 * kv, hd).split([h, kv, kv], dim=2)
@@ -144,9 +156,10 @@ class LlamaDecoder:
                 self.v_cache[li].index_copy_(2, self.pos, v.transpose(1, 2))
                 o = F.scaled_dot_product_attention(q.transpose(1, 2), self.k_cache[li], self.v_cache[li], attn_mask=mask,
                                                    enable_gqa=(kv != h)).transpose(1, 2).reshape(B, 1, h * hd)
-            x = x + self._reduce(a.wo(o))
-            x = x + self._reduce(layer.ffn(layer.ffn_norm(x)))
-        logits = m.lm_head(m.norm(x))
+            hn, x = self._add_norm(layer.ffn_norm, x, self._reduce(a.wo(o)))
+            delta = self._reduce(layer.ffn(hn))
+        hn, x = self._add_norm(m.norm, x, delta)
+        logits = m.lm_head(hn)
         self.next_tokens.copy_(logits.argmax(-1))
         self.tokens.copy_(self.next_tokens)
         self.pos.add_(1)
