@@ -248,6 +248,56 @@ def bench_adamw(dev, numel):
     return report("fused_adamw", [numel], torch.float32, us, nbytes=28 * numel)
 
 
+def bench_grouped_gemm(dev, rows_per_group=(4300, 3900, 4200, 3984), n=28672, k=4096, dt=torch.bfloat16, iters=10):
+    """MoE expert projection (Mixtral dims: 4096 -> 2 x 14336, four local experts, uneven rows): the grouped kernel
+    with device-side counts (forward, input gradient, weight gradient) against one dense GEMM per expert after a
+    host read of the counts."""
+    G, R = len(rows_per_group), sum(rows_per_group)
+    cap = 2 * R                                      # capacity-sized buffers, as the exchange hands them over
+    x = torch.randn(cap, k, device=dev, dtype=dt)
+    w = torch.randn(G, n, k, device=dev, dtype=dt) * 0.02
+    dy = torch.randn(cap, n, device=dev, dtype=dt)
+    counts = torch.tensor(rows_per_group, dtype=torch.int32, device=dev)
+    flops = 2.0 * R * n * k
+    out = []
+    for mode, a, b, name in ((0, x, w, "fwd"), (1, dy, w, "dgrad"), (2, dy, x, "wgrad")):
+        us = timeit(lambda: torch.ops.blackwell.grouped_mm(a, b, counts, mode), dev, iters)
+        out.append(report("grouped_gemm_" + name, [list(rows_per_group), n, k], dt, us, flops=flops, launches=1))
+
+    def loop_fwd():
+        rows, s = counts.tolist(), 0                  # the host read the grouped kernel does without
+        for g, r in enumerate(rows):
+            x[s:s + r] @ w[g].t()
+            s += r
+    us = timeit(loop_fwd, dev, iters)
+    out.append(report("expert_loop_fwd", [list(rows_per_group), n, k], dt, us, flops=flops, launches=G))
+    return out
+
+
+def bench_varlen_attention(dev, lens=(4096, 1024, 3000, 72), heads=32, dt=torch.bfloat16, iters=10):
+    """Packed variable-length causal attention (one launch per pass) against the same sequences padded to the longest
+    one and run as a dense batch."""
+    from torch_musa_b200.ops import flash_attn_varlen_func
+
+    total, mx = sum(lens), max(lens)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=dev)
+    q, k, v = (torch.randn(total, heads, 128, device=dev, dtype=dt, requires_grad=True) for _ in range(3))
+    flops_f = sum(4.0 * heads * L * L * 128 / 2 for L in lens)
+    us = timeit(lambda: flash_attn_varlen_func(q, k, v, cu, cu, mx, mx, causal=True), dev, iters)
+    report("varlen_attention_fwd", [list(lens), heads, 128], dt, us, flops=flops_f, launches=1)
+    g = torch.randn(total, heads, 128, device=dev, dtype=dt)
+
+    def fb():
+        o = flash_attn_varlen_func(q, k, v, cu, cu, mx, mx, causal=True)
+        o.backward(g)
+        q.grad = k.grad = v.grad = None
+    us_fb = timeit(fb, dev, iters)
+    report("varlen_attention_fwd_bwd", [list(lens), heads, 128], dt, us_fb, flops=3.5 * flops_f, launches=2)
+    qp, kp, vp = (torch.randn(len(lens), mx, heads, 128, device=dev, dtype=dt).transpose(1, 2) for _ in range(3))
+    us_pad = timeit(lambda: F.scaled_dot_product_attention(qp, kp, vp, is_causal=True), dev, iters)
+    report("padded_dense_attention_fwd", [len(lens), heads, mx, 128], dt, us_pad, flops=flops_f, launches=1)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("op")
@@ -277,6 +327,10 @@ def main():
         bench_conv(dev, a.rows if a.rows != 4096 else 64, dt, a.iters)
     elif a.op == "conv_small":      # one 3x3 layer (103 MB activations, larger than L2): the case used for profiler captures
         bench_conv(dev, 256, dt, 3, cases=[(64, 56, 64, 3, 1, 1)])
+    elif a.op == "grouped_gemm":
+        bench_grouped_gemm(dev, dt=dt, iters=a.iters)
+    elif a.op == "varlen_attention":
+        bench_varlen_attention(dev, dt=dt, iters=a.iters)
     elif a.op == "gemm_sweep":
         bench_gemm_sweep(dev, a.iters)
     elif a.op == "rmsnorm":
