@@ -172,7 +172,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     int stage = 0, acc = 0;
     uint32_t phase = 0, acc_phase = 0;
     bool ok = true;
-    // lane 0 waits, the warp takes its verdict: the lanes can never disagree about leaving the loop
+    // lane 0 waits, the warp takes its answer: the lanes can never disagree about leaving the loop
     auto warp_wait = [&](uint64_t* bar, uint32_t parity) {
       int w = 1;
       if (lane == 0) w = mbar_wait(bar, parity, abort_flag) ? 1 : 0;
