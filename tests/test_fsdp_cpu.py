@@ -110,3 +110,8 @@ def test_fused_fsdp_matches_stock_two_ranks(mode, low):
 
 def test_fused_fsdp_single_rank_aliases_shadow():
     run_ranks(_body, 1, "gloo", args=("adamw", False))
+
+
+def test_fused_fsdp_matches_stock_eight_ranks():
+    """The engine's layouts at the largest world size of one node (shards of 1/8, padded tails, eight staging slots)."""
+    run_ranks(_body, 8, "gloo", args=("adamw", True))
