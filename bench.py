@@ -250,7 +250,13 @@ class LlamaFSDP(Workload):
         if mode != "stock_collectives":
             from torch_musa_b200.parallel import fsdp as bw_fsdp
 
-            self.engine = bw_fsdp.install_fused_collectives(model, fused_adamw=dict(hp, eps=1e-8) if mode == "fused_adamw" else None)
+            try:
+                self.engine = bw_fsdp.install_fused_collectives(model, fused_adamw=dict(hp, eps=1e-8) if mode == "fused_adamw" else None)
+            except (RuntimeError, ValueError) as e:
+                # the peer-mapped arena could not be set up (the same on every rank: its creation is collective); the
+                # step then runs on the process group's all_gather / reduce_scatter and says so in its record
+                self.install_error = f"{type(e).__name__}: {e}"[:300]
+                mode = "stock_collectives"
         if self.engine is not None and self.engine.optimizer is not None:
             opt = self.engine.optimizer
         else:
@@ -284,6 +290,8 @@ class LlamaFSDP(Workload):
 
     def extra(self):
         out = {}
+        if getattr(self, "install_error", None):
+            out["fused_install_error"] = self.install_error
         if self.engine is not None:
             self.engine.check()
             out["fused_collective_count"] = self.engine.fused_collective_count
