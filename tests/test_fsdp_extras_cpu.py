@@ -170,3 +170,51 @@ def _pipeline_body(rank, world):
 
 def test_two_stage_pipeline_over_send_recv():
     run_ranks(_pipeline_body, 2, "gloo")
+
+
+def _fsdp_suite_body(rank, world):
+    import copy
+
+    import torch
+    import torch.distributed as dist
+    from torch.distributed.fsdp import fully_shard
+    from torch_musa_b200.testing.distributed import FSDPTest
+
+    seen = []
+
+    def one(lr, hybrid):
+        torch.manual_seed(0)
+        ref = torch.nn.Sequential(torch.nn.Linear(12, 20), torch.nn.ReLU(), torch.nn.Linear(20, 6))
+        model = copy.deepcopy(ref)
+        mesh = FSDPTest.device_mesh_plan(hybrid_shard=hybrid)
+        for layer in model:
+            fully_shard(layer, mesh=mesh)
+        fully_shard(model, mesh=mesh)
+        torch.manual_seed(100 + rank)
+        x = torch.randn(4, 12)
+        for m in (ref, model):
+            m(x).pow(2).mean().backward()
+        for p in ref.parameters():                       # what data parallelism averages
+            dist.all_reduce(p.grad)
+            p.grad /= world
+        FSDPTest.check_sharded_parity(ref, model, atol=1e-5)
+        seen.append((lr, hybrid))
+
+    FSDPTest.run_subtests({"lr": [0.1], "hybrid": [False, True]}, one)
+    assert seen == [(0.1, False), (0.1, True)]
+    # a failing combination is reported with its parameters
+    try:
+        FSDPTest.run_subtests({"k": [1]}, lambda k: (_ for _ in ()).throw(ValueError("boom")))
+    except AssertionError as e:
+        assert "{'k': 1}" in str(e) and "boom" in str(e)
+    else:
+        raise AssertionError("run_subtests swallowed a failure")
+
+
+def test_fsdp_suite_helpers_on_cpu_ranks():
+    from torch_musa_b200.testing.distributed import FSDPTest
+
+    class Suite(FSDPTest):
+        world_size = 4
+
+    Suite().run_on_ranks(_fsdp_suite_body)
