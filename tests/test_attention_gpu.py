@@ -163,3 +163,40 @@ def test_packed_variable_length_attention(bw, dev, lens, H, Hkv, causal):
     # the host-side composition of the same contract agrees with the oracle too
     cpu = flash_attn_varlen_func(q0.float(), k0.float(), v0.float(), cu, cu, max(lens), max(lens), causal=causal)
     assert (cpu - ref.detach()).abs().max() < 1e-3
+
+
+@pytest.mark.parametrize("fused_qkv", [True, False])
+def test_decode_rope_and_cache_update_in_one_launch(bw, dev, fused_qkv):
+    """q rotated into a fresh buffer, k rotated into the key cache at the device-side position, v copied into the
+    value cache; packed qkv views (strided) and separate tensors; against the fp32 rotate-half formula."""
+    from torch_musa_b200.ops import precompute_rope_cache
+
+    torch.manual_seed(0)
+    B, H, Hkv, L, pos = 3, 4, 2, 32, 17
+    cos, sin = precompute_rope_cache(L, 128)
+    if fused_qkv:
+        qkv = torch.randn(B, 1, H + 2 * Hkv, 128).to(torch.bfloat16)
+        q, k, v = qkv.split([H, Hkv, Hkv], dim=2)
+        qd, kd, vd = qkv.to(dev).split([H, Hkv, Hkv], dim=2)
+    else:
+        q, k, v = (torch.randn(B, 1, n, 128).to(torch.bfloat16) for n in (H, Hkv, Hkv))
+        qd, kd, vd = q.to(dev), k.to(dev), v.to(dev)
+    kc = torch.full((B, Hkv, L, 128), 9.0, dtype=torch.bfloat16, device=dev)
+    vc = torch.full((B, Hkv, L, 128), 9.0, dtype=torch.bfloat16, device=dev)
+    p = torch.tensor([pos], dtype=torch.long, device=dev)
+    bw.reset_kernel_launch_count()
+    qr = torch.ops.blackwell.decode_rope_cache(qd, kd, vd, cos.to(dev), sin.to(dev), p, kc, vc)
+    assert bw.kernel_launch_count() == 1
+
+    def rot(x):                                   # [B, 1, n, 128] -> rotate-half at position pos, fp32
+        x = x.float()
+        a, b = x[..., :64], x[..., 64:]
+        c, s = cos[pos], sin[pos]
+        return torch.cat([a * c - b * s, b * c + a * s], -1)
+
+    assert (qr.float().cpu() - rot(q).squeeze(1)).abs().max() < 3e-2
+    assert (kc[:, :, pos].float().cpu() - rot(k).squeeze(1)).abs().max() < 3e-2
+    assert torch.equal(vc[:, :, pos].cpu(), v.squeeze(1))
+    untouched = torch.ones(L, dtype=torch.bool)
+    untouched[pos] = False
+    assert bool((kc[:, :, untouched.to(dev)] == 9.0).all()) and bool((vc[:, :, untouched.to(dev)] == 9.0).all())
