@@ -218,3 +218,50 @@ def test_fsdp_suite_helpers_on_cpu_ranks():
         world_size = 4
 
     Suite().run_on_ranks(_fsdp_suite_body)
+
+
+def _pipeline_schedule_body(rank, world, schedule):
+    import torch
+    import torch.nn.functional as F
+    from torch_musa_b200.parallel.pipeline import PipelineStage, split_into_stages
+
+    torch.manual_seed(0)
+    layers = [torch.nn.Linear(16, 16) if i % 2 == 0 else torch.nn.Tanh() for i in range(9)] + [torch.nn.Linear(16, 5)]
+    full = torch.nn.Sequential(*layers)
+    stages = split_into_stages(layers, world)           # the same modules: stage r trains its slice in place
+    n_micro = 5
+    xs = [torch.randn(3, 16) for _ in range(n_micro)]
+    ys = [torch.randint(0, 5, (3,)) for _ in range(n_micro)]
+    # single-process oracle on a copy
+    import copy
+
+    ref = copy.deepcopy(full)
+    ref_loss = sum(F.cross_entropy(ref(x), y) for x, y in zip(xs, ys)) / n_micro
+    ref_loss.backward()
+    stage = PipelineStage(stages[rank], rank, world)
+    for _ in range(2):                                   # the second round reuses the announced shapes
+        for p in stages[rank].parameters():
+            p.grad = None
+        loss = stage.run(schedule, micro_inputs=xs if stage.is_first else None, micro_targets=ys if stage.is_last else None,
+                         loss_fn=F.cross_entropy, n_micro=n_micro)
+        if stage.is_last:
+            assert abs(float(loss) - float(ref_loss)) < 1e-5
+        else:
+            assert loss is None
+        mine = dict(stages[rank].named_parameters())
+        offset = sum(len(s) for s in stages[:rank])
+        for name, p in mine.items():
+            idx, leaf = name.split(".", 1)
+            want = dict(ref.named_parameters())[f"{offset + int(idx)}.{leaf}"].grad
+            assert torch.allclose(p.grad, want, atol=1e-6), name
+
+
+def test_pipeline_schedules_match_single_process():
+    import pytest as _pytest
+
+    for schedule, world in (("gpipe", 2), ("1f1b", 4), ("1f1b", 3)):
+        run_ranks(_pipeline_schedule_body, world, "gloo", args=(schedule,))
+    from torch_musa_b200.parallel.pipeline import split_into_stages
+
+    with _pytest.raises(ValueError):
+        split_into_stages([torch.nn.ReLU()], 2)
