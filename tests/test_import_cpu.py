@@ -28,7 +28,7 @@ def test_api_surface(bw):
                  "set_per_process_memory_fraction", "memory_summary", "memory_snapshot", "MemPool",
                  "use_mem_pool", "change_current_allocator", "manual_seed", "manual_seed_all", "get_rng_state",
                  "set_rng_state", "seed", "initial_seed", "BlackwellGraph", "graph", "graph_pool_handle",
-                 "make_graphed_callables", "is_current_stream_capturing", "amp", "_lazy_init", "_sleep",
+                 "make_graphed_callables", "update_graph_with_profile", "is_current_stream_capturing", "amp", "_lazy_init", "_sleep",
                  "use_unified_cpu_allocator", "get_allocator_backend", "ipc_collect", "OutOfMemoryError"]:
         assert hasattr(bw, name), name
     assert bw.get_arch_list() == ["sm_100a"]

@@ -60,6 +60,14 @@ def test_graph_capture_replay(bw, dev):
     pool = g.pool()
     assert isinstance(pool, tuple) and len(pool) == 2
     g.reset()
+    # a graph that kept its captured graph can be instantiated again (what a profiler attached later needs)
+    k = bw.BlackwellGraph(keep_graph=True)
+    with bw.graph(k):
+        static_z = lin(static_x) * 2
+    assert bw.update_graph_with_profile() >= 1
+    k.replay()
+    bw.synchronize()
+    assert torch.allclose(static_z.float().cpu(), (lin(static_x) * 2).float().cpu(), atol=1e-2, rtol=1e-2)
 
 
 def test_graph_rng_advances(bw, dev):

@@ -172,6 +172,7 @@ from .graphs import (  # noqa: E402
     graph,
     graph_pool_handle,
     make_graphed_callables,
+    update_graph_with_profile,
 )
 from .core import serialization as _serialization  # noqa: E402
 from .core import attrs as _attrs  # noqa: E402

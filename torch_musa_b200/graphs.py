@@ -8,6 +8,8 @@ Parity: reference torch_musa/musa_graph/graphs.py:12-516.
 """
 from __future__ import annotations
 
+import weakref
+
 import gc
 from typing import Any, Callable, Optional, Tuple, Union
 
@@ -28,10 +30,14 @@ def graph_pool_handle() -> Tuple[int, int]:
 class BlackwellGraph:
     """Wrapper around a captured CUDA graph for the blackwell device."""
 
+    _instances = weakref.WeakSet()     # live graphs, for update_graph_with_profile()
+
     def __init__(self, keep_graph: bool = False):
         self._g = _bw()._C._Graph()
+        self._keeps_graph = bool(keep_graph)
         if keep_graph:
             self._g.enable_debug_mode()
+        BlackwellGraph._instances.add(self)
 
     def capture_begin(self, pool: Optional[Tuple[int, int]] = None, capture_error_mode: str = "global") -> None:
         self._g.capture_begin(pool, capture_error_mode)
@@ -49,6 +55,7 @@ class BlackwellGraph:
         return tuple(self._g.pool())
 
     def enable_debug_mode(self) -> None:
+        self._keeps_graph = True
         self._g.enable_debug_mode()
 
     def debug_dump(self, debug_path: str) -> None:
@@ -220,3 +227,20 @@ def make_graphed_callables(callables, sample_args, num_warmup_iters: int = 3, al
         else:
             ret.append(graphed)
     return ret[0] if just_one else tuple(ret)
+
+
+def update_graph_with_profile() -> int:
+    """Re-instantiates the executable of every live graph that kept its captured graph (``keep_graph=True`` or
+    ``enable_debug_mode()`` before the capture).  A profiler that attaches after a graph was instantiated does not
+    see the kernels inside it; instantiating again under the profiler makes them visible.  Returns the number of
+    graphs that were re-instantiated; graphs that did not keep their captured graph are left alone.
+    Parity: reference torch_musa/musa_graph/graphs.py:21-28."""
+    n = 0
+    for g in list(BlackwellGraph._instances):
+        if g._keeps_graph:
+            try:
+                g.reinstantiate_graph()
+                n += 1
+            except RuntimeError:
+                pass        # nothing captured yet
+    return n
