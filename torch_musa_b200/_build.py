@@ -178,6 +178,14 @@ def build(verbose: bool = True, jobs: int | None = None) -> dict:
         cxx_flags += ["-isystem", i]
     for i in _nccl_include():
         cxx_flags += ["-isystem", i]
+    # developer builds of the host runtime: B200_BUILD_ASAN=1 / B200_BUILD_TSAN=1 (the device code is unaffected; an
+    # instrumented _C.so needs the sanitizer runtime preloaded into python: LD_PRELOAD=$(g++ -print-file-name=libasan.so))
+    sanitize = []
+    if os.environ.get("B200_BUILD_ASAN", "0") == "1":
+        sanitize = ["-fsanitize=address", "-fno-omit-frame-pointer", "-g"]
+    elif os.environ.get("B200_BUILD_TSAN", "0") == "1":
+        sanitize = ["-fsanitize=thread", "-fno-omit-frame-pointer", "-g"]
+    cxx_flags += sanitize
     cjobs = []
     for s in cpp_srcs:
         o = OBJ / "cpp" / (s.relative_to(CSRC).as_posix().replace("/", "__") + ".o")
@@ -201,7 +209,7 @@ def build(verbose: bool = True, jobs: int | None = None) -> dict:
     cobjs = [str(j[1]) for j in cjobs]
     if n1 or not clib.exists() or any(os.stat(o).st_mtime > clib.stat().st_mtime for o in cobjs) \
             or klib.stat().st_mtime > clib.stat().st_mtime:
-        cmd = [CXX, "-shared", "-o", str(clib), *cobjs, "-L", str(PKG), "-lb200_kernels",
+        cmd = [CXX, "-shared", "-o", str(clib), *cobjs, *sanitize[:1], "-L", str(PKG), "-lb200_kernels",
                "-Wl,-rpath,$ORIGIN", "-Wl,--no-as-needed"]
         for l in tlib:
             cmd += ["-L", l, f"-Wl,-rpath,{l}"]

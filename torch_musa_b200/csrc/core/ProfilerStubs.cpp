@@ -3,6 +3,7 @@
 // run a callback on every device, synchronise.  NVTX-style marks and ranges go to torch's own NVTX path and are
 // no-ops here.  (Kineto/CUPTI traces need none of this: the kernels are CUDA kernels.)
 // Parity: reference torch_musa/csrc/profiler/stubs.cpp:39-102.
+#include <nvtx3/nvToolsExt.h>
 #include "core/Device.h"
 #include "core/Stream.h"
 
@@ -46,9 +47,11 @@ struct BlackwellProfilerStubs : public torch::profiler::impl::ProfilerStubs {
     return ms * 1000.f;  // microseconds
   }
 
-  void mark(const char*) const override {}
-  void rangePush(const char*) const override {}
-  void rangePop() const override {}
+  // NVTX (header-only v3: the calls are no-ops until a tool injects its library), so that ranges emitted through
+  // torch.autograd.profiler.emit_nvtx / record_function show up on the timeline of an attached profiler
+  void mark(const char* name) const override { nvtxMarkA(name ? name : ""); }
+  void rangePush(const char* name) const override { nvtxRangePushA(name ? name : ""); }
+  void rangePop() const override { nvtxRangePop(); }
   bool enabled() const override { return true; }
 
   void onEachDevice(std::function<void(int)> op) const override {
