@@ -31,6 +31,21 @@ import torch.nn.functional as F  # noqa: E402
 import torch_musa_b200 as bw  # noqa: E402
 
 
+def env_info():
+    """Software stack and device of this run, as one JSON line (first line of a log that should stay interpretable).
+    Parity: reference benchmark/operator_benchmark/README.md:86-165 (records its SDK versions beside the numbers)."""
+    info = {"env": True, "torch": torch.__version__, "cuda": torch.version.cuda, "backend": bw.__version__,
+            "nccl": ".".join(map(str, bw.bccl.version())), "python": sys.version.split()[0]}
+    if bw.is_available():
+        p = bw.get_device_properties(0)
+        info.update({"device": bw.get_device_name(0), "sms": getattr(p, "multi_processor_count", None),
+                     "memory_gb": round(getattr(p, "total_memory", 0) / 2**30, 1), "arch": bw.get_arch_list()})
+    pk = peaks()
+    info["roofline"] = {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["tflops"], "source": pk["src"]}
+    print(json.dumps(info), flush=True)
+    return info
+
+
 def peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -311,8 +326,13 @@ def main():
     ap.add_argument("--dtype", default="bfloat16")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--backward", action="store_true")
+    ap.add_argument("--env", action="store_true", help="print the software stack and device as a first JSON line")
     ap.add_argument("--gemm-config", type=int, default=None, help="pin the GEMM tile configuration (1 single CTA, 2 SM pair)")
     a = ap.parse_args()
+    if a.env:
+        env_info()
+        if a.op == "env":
+            return
     if a.gemm_config is not None:
         bw._C._gemm_force_config(a.gemm_config)
     dev = torch.device("blackwell:0")
