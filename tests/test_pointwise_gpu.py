@@ -84,7 +84,7 @@ def test_type_promotion_and_division(bw, dev):
 
 
 UNARY_F = ["floor", "ceil", "round", "trunc", "frac", "sign", "exp2", "expm1", "sin", "cos", "tan", "erf", "exp", "tanh",
-           "sigmoid", "neg", "abs", "isnan"]
+           "sigmoid", "neg", "abs", "isnan", "atan", "sinh", "cosh", "asinh", "erfc"]
 UNARY_POS = ["log", "log2", "log10", "log1p", "sqrt", "rsqrt", "reciprocal"]
 
 
@@ -97,6 +97,9 @@ def test_unary_float(bw, dev, dt):
     for name in UNARY_POS:
         _check(getattr(torch, name), (_rand((5, 7), dt, positive=True)[:, ::2],), dev)
     x = _rand((6, 6), dt)
+    for name in ("asin", "acos", "atanh"):                                # domain (-1, 1)
+        _check(lambda t, f=getattr(torch, name): f(t.clamp(-0.9, 0.9)), (x,), dev)
+    _check(lambda t: torch.acosh(t.abs() + 1.25), (x,), dev)              # domain [1, inf)
     _check(lambda t: torch.nn.functional.gelu(t.t()), (x,), dev)
     _check(lambda t: torch.nn.functional.leaky_relu(t, 0.1), (x,), dev)
     _check(lambda t: torch.nn.functional.elu(t), (x,), dev)

@@ -217,6 +217,15 @@ B200_PW_UNARY(sin, "sin", B200_EW_SIN, kFloat)
 B200_PW_UNARY(cos, "cos", B200_EW_COS, kFloat)
 B200_PW_UNARY(tan, "tan", B200_EW_TAN, kFloat)
 B200_PW_UNARY(erf, "erf", B200_EW_ERF, kFloat)
+B200_PW_UNARY(asin, "asin", B200_EW_ASIN, kFloat)
+B200_PW_UNARY(acos, "acos", B200_EW_ACOS, kFloat)
+B200_PW_UNARY(atan, "atan", B200_EW_ATAN, kFloat)
+B200_PW_UNARY(sinh, "sinh", B200_EW_SINH, kFloat)
+B200_PW_UNARY(cosh, "cosh", B200_EW_COSH, kFloat)
+B200_PW_UNARY(asinh, "asinh", B200_EW_ASINH, kFloat)
+B200_PW_UNARY(acosh, "acosh", B200_EW_ACOSH, kFloat)
+B200_PW_UNARY(atanh, "atanh", B200_EW_ATANH, kFloat)
+B200_PW_UNARY(erfc, "erfc", B200_EW_ERFC, kFloat)
 B200_PW_UNARY(bitwise_not, "bitwise_not", B200_EW_BITWISE_NOT, kSame)
 // .out forms of the operators whose functional / in-place forms live in Elementwise.cpp
 B200_PW_UNARY(exp_g, "exp", B200_EW_EXP, kFloat)
@@ -457,6 +466,15 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
   REG3(cos, "cos", "", "", ".out")
   REG3(tan, "tan", "", "", ".out")
   REG3(erf, "erf", "", "", ".out")
+  REG3(asin, "asin", "", "", ".out")
+  REG3(acos, "acos", "", "", ".out")
+  REG3(atan, "atan", "", "", ".out")
+  REG3(sinh, "sinh", "", "", ".out")
+  REG3(cosh, "cosh", "", "", ".out")
+  REG3(asinh, "asinh", "", "", ".out")
+  REG3(acosh, "acosh", "", "", ".out")
+  REG3(atanh, "atanh", "", "", ".out")
+  REG3(erfc, "erfc", "", "", ".out")
   REG3(bitwise_not, "bitwise_not", "", "", ".out")
   m.impl("exp.out", TORCH_FN(exp_g_out));
   m.impl("sqrt.out", TORCH_FN(sqrt_g_out));

@@ -69,7 +69,9 @@ enum {
   B200_EW_SQRT, B200_EW_RSQRT, B200_EW_RECIPROCAL, B200_EW_SQUARE, B200_EW_SIN, B200_EW_COS, B200_EW_TAN,
   B200_EW_TANH, B200_EW_SIGMOID, B200_EW_ERF, B200_EW_RELU, B200_EW_SILU, B200_EW_GELU_ERF, B200_EW_GELU_TANH,
   B200_EW_ISNAN, B200_EW_ISINF, B200_EW_ISFINITE, B200_EW_LOGICAL_NOT, B200_EW_BITWISE_NOT, B200_EW_COPY, B200_EW_FILL,
-  B200_EW_LOG_SIGMOID
+  B200_EW_LOG_SIGMOID,
+  B200_EW_ASIN, B200_EW_ACOS, B200_EW_ATAN, B200_EW_SINH, B200_EW_COSH, B200_EW_ASINH, B200_EW_ACOSH, B200_EW_ATANH,
+  B200_EW_ERFC
 };
 typedef struct {
   int ndim;                 /* 1..8 coalesced dimensions, innermost first */

@@ -97,6 +97,15 @@ template <> struct Math<float> {
   static __device__ __forceinline__ float fm(float a, float b) { return fmodf(a, b); }
   static __device__ __forceinline__ float ab(float a) { return fabsf(a); }
   static __device__ __forceinline__ float at2(float a, float b) { return atan2f(a, b); }
+  static __device__ __forceinline__ float asn(float a) { return asinf(a); }
+  static __device__ __forceinline__ float acs(float a) { return acosf(a); }
+  static __device__ __forceinline__ float atn(float a) { return atanf(a); }
+  static __device__ __forceinline__ float snh(float a) { return sinhf(a); }
+  static __device__ __forceinline__ float csh(float a) { return coshf(a); }
+  static __device__ __forceinline__ float asnh(float a) { return asinhf(a); }
+  static __device__ __forceinline__ float acsh(float a) { return acoshf(a); }
+  static __device__ __forceinline__ float atnh(float a) { return atanhf(a); }
+  static __device__ __forceinline__ float erc(float a) { return erfcf(a); }
 };
 template <> struct Math<double> {
   static __device__ __forceinline__ double pw(double a, double b) { return pow(a, b); }
@@ -116,6 +125,15 @@ template <> struct Math<double> {
   static __device__ __forceinline__ double fm(double a, double b) { return fmod(a, b); }
   static __device__ __forceinline__ double ab(double a) { return fabs(a); }
   static __device__ __forceinline__ double at2(double a, double b) { return atan2(a, b); }
+  static __device__ __forceinline__ double asn(double a) { return asin(a); }
+  static __device__ __forceinline__ double acs(double a) { return acos(a); }
+  static __device__ __forceinline__ double atn(double a) { return atan(a); }
+  static __device__ __forceinline__ double snh(double a) { return sinh(a); }
+  static __device__ __forceinline__ double csh(double a) { return cosh(a); }
+  static __device__ __forceinline__ double asnh(double a) { return asinh(a); }
+  static __device__ __forceinline__ double acsh(double a) { return acosh(a); }
+  static __device__ __forceinline__ double atnh(double a) { return atanh(a); }
+  static __device__ __forceinline__ double erc(double a) { return erfc(a); }
 };
 
 // floating compute types
@@ -192,6 +210,15 @@ __device__ __forceinline__ C apply_float(int op, C a, C b, C c, double s0, doubl
     case B200_EW_GELU_ERF: return (C)0.5 * a * ((C)1 + M::er(a * (C)0.70710678118654752));
     case B200_EW_GELU_TANH: { C in = (C)0.7978845608028654 * (a + (C)0.044715 * a * a * a); return (C)0.5 * a * ((C)1 + M::th(in)); }
     case B200_EW_LOG_SIGMOID: return (a < (C)0 ? a : (C)0) - M::l1p(M::ex(-M::ab(a)));
+    case B200_EW_ASIN: return M::asn(a);
+    case B200_EW_ACOS: return M::acs(a);
+    case B200_EW_ATAN: return M::atn(a);
+    case B200_EW_SINH: return M::snh(a);
+    case B200_EW_COSH: return M::csh(a);
+    case B200_EW_ASINH: return M::asnh(a);
+    case B200_EW_ACOSH: return M::acsh(a);
+    case B200_EW_ATANH: return M::atnh(a);
+    case B200_EW_ERFC: return M::erc(a);
     case B200_EW_ISNAN: return (C)(a != a);
     case B200_EW_ISINF: return (C)(a == (C)INFINITY || a == -(C)INFINITY);
     case B200_EW_ISFINITE: return (C)(a == a && a != (C)INFINITY && a != -(C)INFINITY);
