@@ -185,3 +185,46 @@ def test_op_coverage_report_reads_the_dispatcher():
     assert any(n.startswith("blackwell::") for n in r["custom_operators"])
     assert r["covered_of_cuda"] <= r["cuda_base_operators"] and "mm" not in r["fallback_base_operators"]
     assert op_coverage.main(["--missing", "3"]) == 0
+
+
+def test_integration_run_with_strategies_and_gates():
+    """The end-to-end harness: a small classifier trained under autocast + channels-last must pass its accuracy gates;
+    an unreachable gate is reported by name; evaluators compute what they say."""
+    from torch import nn
+    from torch_musa_b200.testing import integration as it
+
+    torch.manual_seed(0)
+    centres = torch.randn(4, 3, 4, 4) * 2.0
+
+    def batches(n, seed):
+        g = torch.Generator().manual_seed(seed)
+        out = []
+        for _ in range(n):
+            y = torch.randint(0, 4, (32,), generator=g)
+            out.append((centres[y] + 0.3 * torch.randn(32, 3, 4, 4, generator=g), y))
+        return out
+
+    def make():
+        return nn.Sequential(nn.Conv2d(3, 8, 3, padding=1), nn.ReLU(), nn.Flatten(), nn.Linear(8 * 16, 4))
+
+    lines = []
+    run = it.IntegrationRun(model=make(), loss_fn=nn.CrossEntropyLoss(), train_batches=batches(30, 1), test_batches=batches(5, 2),
+                            optimizer=lambda p: torch.optim.Adam(p, lr=1e-2), epochs=2, device="cpu",
+                            strategies=[it.TF32(False), it.AMP(torch.bfloat16), it.ChannelsLast()],
+                            evaluators={"top": it.TopKAccuracy((1, 2))},
+                            gates={"top.top1": it.GreaterThan(0.9), "top.top2": it.GreaterThan(0.95), "train_loss": it.LessThan(0.5)},
+                            log=lines.append)
+    report = run.run()
+    assert report["gates_passed"] and report["top.top1"] > 0.9 and report["seconds_per_epoch"] > 0
+    assert "amp" in lines[0] and "channels_last" in lines[0] and len(lines) == 3
+    bad = it.IntegrationRun(model=make(), loss_fn=nn.CrossEntropyLoss(), test_batches=batches(2, 3),
+                            evaluators={"top": it.TopKAccuracy((1,))}, gates={"top.top1": it.GreaterThan(0.99), "nope": it.LessThan(1)})
+    with pytest.raises(AssertionError, match="top.top1.*not greater than.*nope: no such metric"):
+        bad.run()
+    f1 = it.F1Score()
+    f1.append(torch.tensor([0.9, 0.8, 0.1, 0.7]), torch.tensor([1, 0, 0, 1]))
+    assert abs(f1.evaluate()["f1"] - 0.8) < 1e-9                      # tp 2, fp 1, fn 0
+    j = it.JaccardIndex()
+    j.append(torch.tensor([True, True, False, False]), torch.tensor([True, False, True, False]))
+    assert abs(j.evaluate()["iou"] - 1 / 3) < 1e-9
+    assert len(it.default_strategy_sets()) == 4
