@@ -228,3 +228,22 @@ def test_integration_run_with_strategies_and_gates():
     j.append(torch.tensor([True, True, False, False]), torch.tensor([True, False, True, False]))
     assert abs(j.evaluate()["iou"] - 1 / 3) < 1e-9
     assert len(it.default_strategy_sets()) == 4
+
+
+def test_cmake_description_configures(tmp_path):
+    """The CMake build of the kernel library (an alternative to the package's own build script) configures: the
+    compiler is found, the options parse, every kernel source is picked up.  (Compiling all kernels takes minutes and is
+    what the package build already does.)"""
+    import os
+    import shutil
+    import subprocess
+
+    if not shutil.which("cmake") or not os.path.exists("/usr/local/cuda/bin/nvcc"):
+        pytest.skip("cmake or nvcc not available")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run(["cmake", "-S", root, "-B", str(tmp_path), "-DCMAKE_CUDA_COMPILER=/usr/local/cuda/bin/nvcc",
+                        "-DB200_USE_ASAN=ON", "-DB200_WERROR=ON"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    made = open(os.path.join(str(tmp_path), "CMakeFiles", "b200_kernels.dir", "build.make")).read()
+    for name in ("gemm_tcgen05.cu", "gemm_grouped.cu", "attention_bwd.cu", "conv_tcgen05.cu", "decode_attn.cu"):
+        assert name in made, name
