@@ -247,3 +247,35 @@ def test_cmake_description_configures(tmp_path):
     made = open(os.path.join(str(tmp_path), "CMakeFiles", "b200_kernels.dir", "build.make")).read()
     for name in ("gemm_tcgen05.cu", "gemm_grouped.cu", "attention_bwd.cu", "conv_tcgen05.cu", "decode_attn.cu"):
         assert name in made, name
+
+
+def test_host_paths_of_grouped_linear_and_varlen_attention():
+    """The device-independent compositions behind `grouped_linear`, `swiglu(row_counts=...)` and `flash_attn_varlen_func`
+    (what runs on any other device, and the oracle of the GPU tests) against explicit per-group / per-sequence loops."""
+    import torch.nn.functional as F
+    from torch_musa_b200.ops import flash_attn_varlen_func, grouped_linear, swiglu
+
+    torch.manual_seed(0)
+    x, w = torch.randn(20, 6, requires_grad=True), torch.randn(3, 4, 6, requires_grad=True)
+    counts = torch.tensor([5, 0, 9], dtype=torch.int32)
+    y = grouped_linear(x, w, counts)
+    assert y.shape == (20, 4) and torch.allclose(y[:5], x[:5] @ w[0].t()) and torch.allclose(y[5:14], x[5:14] @ w[2].t())
+    assert bool((y[14:] == 0).all())
+    y.sum().backward()
+    assert torch.allclose(w.grad[1], torch.zeros(4, 6)) and bool((x.grad[14:] == 0).all())
+    out = torch.full((20, 4), 7.0)
+    assert grouped_linear(x.detach(), w.detach(), counts, out) is out and bool((out[14:] == 0).all())
+    g = torch.randn(4, 8)
+    assert torch.allclose(swiglu(g, counts), F.silu(g[:, :4]) * g[:, 4:])          # the host path computes every row
+    lens = [3, 7, 1]
+    cu = torch.tensor([0, 3, 10, 11], dtype=torch.int32)
+    q, k, v = torch.randn(11, 4, 8), torch.randn(11, 2, 8), torch.randn(11, 2, 8)
+    got = flash_attn_varlen_func(q, k, v, cu, cu, max(lens), max(lens), causal=True)
+    s = 0
+    for n in lens:
+        qi, ki, vi = (t[s:s + n].transpose(0, 1) for t in (q, k, v))
+        ki, vi = ki.repeat_interleave(2, 0), vi.repeat_interleave(2, 0)
+        att = (qi @ ki.transpose(-1, -2)) / 8 ** 0.5
+        att = att.masked_fill(~torch.ones(n, n, dtype=torch.bool).tril(), float("-inf")).softmax(-1)
+        assert torch.allclose(got[s:s + n].transpose(0, 1), att @ vi, atol=1e-5)
+        s += n
