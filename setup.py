@@ -30,7 +30,7 @@ setup(
     version="0.2.0",
     description="Blackwell-native (sm_100a) out-of-tree PyTorch device backend: device `blackwell`, collective backend `bccl`",
     packages=find_packages(include=["torch_musa_b200", "torch_musa_b200.*"]),
-    package_data={"torch_musa_b200": ["*.so", "csrc/kernels/*.h"]},
+    package_data={"torch_musa_b200": ["*.so", "csrc/kernels/*.h", "csrc/compile/AotShim.h"]},
     python_requires=">=3.10",
     install_requires=["torch>=2.6"],
     cmdclass={"build_py": BuildWithKernels},
