@@ -279,3 +279,30 @@ def test_host_paths_of_grouped_linear_and_varlen_attention():
         att = att.masked_fill(~torch.ones(n, n, dtype=torch.bool).tril(), float("-inf")).softmax(-1)
         assert torch.allclose(got[s:s + n].transpose(0, 1), att @ vi, atol=1e-5)
         s += n
+
+
+def test_sharded_adamw_dynamic_loss_scaling():
+    """Scaled gradients give the same update as unscaled ones; a non-finite gradient skips the step and backs the
+    scale off; good steps grow it again."""
+    from torch_musa_b200.parallel.zero import ShardedFusedAdamW
+
+    torch.manual_seed(0)
+    base = [torch.randn(40, 16) * 0.1, torch.randn(16) * 0.1]
+    a = [torch.nn.Parameter(b.to(torch.bfloat16)) for b in base]
+    b = [torch.nn.Parameter(b.to(torch.bfloat16)) for b in base]
+    oa = ShardedFusedAdamW(a, lr=1e-2, bucket_mb=1)
+    ob = ShardedFusedAdamW(b, lr=1e-2, bucket_mb=1)
+    scaler = torch.amp.GradScaler("cpu", init_scale=256.0, growth_interval=2)
+    grads = [(torch.randn(p.shape) * 0.05).to(torch.bfloat16) for p in a]
+    for p, q, g in zip(a, b, grads):
+        p.grad.copy_(g)
+        q.grad.copy_((g.float() * 256.0).to(torch.bfloat16))      # what backward of a scaled loss produces
+    oa.step()
+    assert ob.step_with_scaler(scaler) is True
+    assert all(torch.allclose(p.float(), q.float(), atol=1e-2) for p, q in zip(a, b))
+    before = [q.detach().clone() for q in b]
+    b[0].grad[0, 0] = float("inf")
+    assert ob.step_with_scaler(scaler) is False and scaler.get_scale() == 128.0
+    assert all(torch.equal(x, q) for x, q in zip(before, b)) and float(ob.step_t) == 1.0
+    ob.zero_grad()
+    assert ob.step_with_scaler(scaler) and ob.step_with_scaler(scaler) and scaler.get_scale() == 256.0

@@ -83,24 +83,58 @@ class ShardedFusedAdamW:
             yield self.flat_g[off:off + n].view_as(p)
             off += n
 
+    def _grads_finite(self) -> bool:
+        """True when no gradient element on any rank is inf / nan (one small all-reduce and one host read)."""
+        ok = torch.isfinite(self.flat_g).all().to(torch.float32).reshape(1)
+        if self.world > 1:
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
+        return bool(ok.item() > 0)
+
+    def step_with_scaler(self, scaler) -> bool:
+        """One step under dynamic loss scaling (``torch.amp.GradScaler`` used as the holder of the scale and of its
+        growth / backoff policy): gradients are divided by the scale inside the update kernel; a step whose gradients
+        are not finite on some rank is skipped on every rank and the scale backs off; after ``growth_interval`` good
+        steps in a row the scale grows.  Returns whether the update was applied."""
+        scale = float(scaler.get_scale())
+        applied = self.step(grad_scale=scale, check_finite=True)
+        self._good_steps = getattr(self, "_good_steps", 0) + 1 if applied else 0
+        def set_scale(value: float) -> None:
+            try:
+                scaler.update(value)
+            except AssertionError:      # the scaler creates its state on the first `scale()` call: make that call
+                scaler.scale(torch.zeros((), device=self.device))
+                scaler.update(value)
+
+        if not applied:
+            set_scale(scale * scaler.get_backoff_factor())
+        elif self._good_steps >= scaler.get_growth_interval():
+            set_scale(scale * scaler.get_growth_factor())
+            self._good_steps = 0
+        return applied
+
     @torch.no_grad()
-    def step(self) -> None:
+    def step(self, grad_scale: float = 1.0, check_finite: bool = False) -> bool:
+        """``grad_scale``: the factor the loss was multiplied by (the gradients are divided by it on the fly);
+        ``check_finite``: leave parameters and state untouched and return False when a gradient is inf / nan."""
+        if check_finite and not self._grads_finite():
+            return False
         self.step_t += 1
         chunk = self.bs * self.world
         b1, b2 = self.betas
+        inv = 1.0 / float(grad_scale)
         for b in range(self.n_buckets):
             g = self.flat_g[b * chunk:(b + 1) * chunk]
             sl = slice(b * self.bs, (b + 1) * self.bs)
             if self.fused:
                 self.sm.reduce_scatter_adamw(g, self.p32[sl], self.m[sl], self.v[sl], self.p16, self.step_t, self.lr, b1,
-                                             b2, self.eps, self.wd, 1.0 / self.world)
+                                             b2, self.eps, self.wd, inv / self.world)
             else:
                 if self.world > 1:
                     gs = torch.empty(self.bs, dtype=torch.float32, device=self.device)
                     dist.reduce_scatter_tensor(gs, g.float(), op=dist.ReduceOp.SUM, group=self.group)
-                    gs /= self.world
+                    gs *= inv / self.world
                 else:
-                    gs = g.float()
+                    gs = g.float() * inv if inv != 1.0 else g.float()
                 p, m, v = self.p32[sl], self.m[sl], self.v[sl]
                 step = float(self.step_t)
                 p.mul_(1 - self.lr * self.wd)
@@ -114,6 +148,7 @@ class ShardedFusedAdamW:
                 dist.all_gather_into_tensor(out, self.p16, group=self.group)
             else:
                 out.copy_(self.p16)
+        return True
 
     def check(self) -> None:
         if self.sm is not None:
