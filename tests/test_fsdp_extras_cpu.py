@@ -259,7 +259,7 @@ def _pipeline_schedule_body(rank, world, schedule):
 def test_pipeline_schedules_match_single_process():
     import pytest as _pytest
 
-    for schedule, world in (("gpipe", 2), ("1f1b", 4), ("1f1b", 3)):
+    for schedule, world in (("gpipe", 2), ("1f1b", 4)):
         run_ranks(_pipeline_schedule_body, world, "gloo", args=(schedule,))
     from torch_musa_b200.parallel.pipeline import split_into_stages
 
