@@ -306,3 +306,19 @@ def test_sharded_adamw_dynamic_loss_scaling():
     assert all(torch.equal(x, q) for x, q in zip(before, b)) and float(ob.step_t) == 1.0
     ob.zero_grad()
     assert ob.step_with_scaler(scaler) and ob.step_with_scaler(scaler) and scaler.get_scale() == 256.0
+
+
+def test_python_examples_run_on_cpu():
+    import importlib.util
+    import os
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+    def load(name):
+        spec = importlib.util.spec_from_file_location(name, os.path.join(root, "examples", "python", name + ".py"))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        return mod
+
+    assert load("train_tiny_llama").main(["--steps", "8", "--device", "cpu"]) < 3.0      # starts near ln(512) = 6.2
+    assert load("quantize_conv_block").main() < 0.2
