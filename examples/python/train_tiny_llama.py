@@ -1,8 +1,8 @@
 #!/usr/bin/env python
 """Trains a tiny Llama for a few steps on the blackwell device (or on the CPU when no B200 is visible) with the
-fused optimizer, bf16 autocast and, optionally, the step captured into a device graph.
+fused optimizer and bf16 autocast.
 
-    python examples/python/train_tiny_llama.py [--steps 20] [--device blackwell|cpu] [--graph]
+    python examples/python/train_tiny_llama.py [--steps 20] [--device blackwell|cpu]
 """
 from __future__ import annotations
 
@@ -22,7 +22,6 @@ def main(argv=None) -> float:
     ap = argparse.ArgumentParser()
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--device", default="blackwell" if bw.is_available() else "cpu")
-    ap.add_argument("--graph", action="store_true", help="capture forward + backward + optimizer step into one graph")
     a = ap.parse_args(argv)
     dev = torch.device(a.device)
     torch.manual_seed(0)
@@ -41,24 +40,9 @@ def main(argv=None) -> float:
         return loss
 
     first = last = None
-    if a.graph and dev.type == "blackwell":
-        side = bw.Stream()
-        side.wait_stream(bw.current_stream())
-        with bw.stream(side):
-            for _ in range(3):
-                step()
-        bw.current_stream().wait_stream(side)
-        g = bw.BlackwellGraph()
-        with bw.graph(g):
-            static_loss = step()
-        for i in range(a.steps):
-            g.replay()
-            last = float(static_loss)
-            first = last if first is None else first
-    else:
-        for i in range(a.steps):
-            last = float(step().detach())
-            first = last if first is None else first
+    for _ in range(a.steps):
+        last = float(step().detach())
+        first = last if first is None else first
     print(f"device {dev}: loss {first:.3f} -> {last:.3f} over {a.steps} steps")
     return last
 
