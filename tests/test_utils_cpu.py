@@ -322,3 +322,17 @@ def test_python_examples_run_on_cpu():
 
     assert load("train_tiny_llama").main(["--steps", "8", "--device", "cpu"]) < 3.0      # starts near ln(512) = 6.2
     assert load("quantize_conv_block").main() < 0.2
+
+
+def test_experts_accept_device_side_counts():
+    """The expert block gives the same rows whether the per-expert counts arrive as a list (host) or as an int32 tensor
+    (the form the fused exchange hands over, with a capacity-sized row buffer)."""
+    from torch_musa_b200.models.moe import Experts
+
+    torch.manual_seed(0)
+    ex = Experts(3, 16, 24)
+    rows = torch.randn(20, 16)
+    counts = [6, 0, 9]
+    want = ex(rows[:15], counts)
+    got = ex(rows, torch.tensor(counts, dtype=torch.int32))          # 5 rows of slack past the last expert
+    assert got.shape == (20, 16) and torch.allclose(got[:15], want, atol=1e-6)
