@@ -244,3 +244,40 @@ def test_canary_reports_a_write_past_the_end(bw):
         h.free(c)
     finally:
         bw._C._set_allocator_settings("canary:False")
+
+
+def test_snapshot_renderings(tmp_path):
+    """Segment map, event trace and folded stacks from a snapshot dictionary (the layout `_snapshot()` returns)."""
+    import pickle
+
+    from torch_musa_b200.core import memory_viz as mv
+
+    snap = {
+        "segments": [
+            {"device": 0, "address": 0x7000000, "total_size": 2 << 20, "allocated_size": 1 << 20, "segment_type": "small",
+             "segment_pool_id": (0, 0), "is_expandable": False,
+             "blocks": [{"address": 0x7000000, "size": 1 << 20, "requested_size": 1000000, "state": "active_allocated"},
+                        {"address": 0x7100000, "size": 1 << 20, "requested_size": 0, "state": "inactive"}]},
+            {"device": 0, "address": 0x9000000, "total_size": 20 << 20, "allocated_size": 0, "segment_type": "large",
+             "segment_pool_id": (0, 3), "is_expandable": True, "blocks": []}],
+        "device_traces": [[
+            {"action": "segment_alloc", "addr": 0x7000000, "size": 2 << 20, "stream": 0, "device": 0, "time_us": 10},
+            {"action": "alloc", "addr": 0x7000000, "size": 1 << 20, "stream": 0, "device": 0, "time_us": 11,
+             "frames": "alloc_fn()\nat::empty()\nmodel_forward()\nmain"},
+            {"action": "alloc", "addr": 0x7100000, "size": 1 << 20, "stream": 0, "device": 0, "time_us": 12,
+             "frames": "alloc_fn()\nat::empty()\ntemp_buffer()\nmain"},
+            {"action": "free_requested", "addr": 0x7100000, "size": 1 << 20, "stream": 0, "device": 0, "time_us": 13},
+            {"action": "free_completed", "addr": 0x7100000, "size": 1 << 20, "stream": 0, "device": 0, "time_us": 14}]],
+    }
+    text = mv.segments_text(snap)
+    assert "segment 0x7000000" in text and "expandable, pool (0, 3)" in text and "active_allocated (requested 976.6 KiB)" in text
+    assert text.endswith("total: reserved 22.0 MiB, allocated 1.0 MiB, cached 21.0 MiB in 2 segments")
+    assert mv.trace_text(snap).count("\n") == 4 and "free_completed" in mv.trace_text(snap, last=1)
+    assert [e["addr"] for e in mv.live_allocations(snap)] == [0x7000000]
+    assert mv.flamegraph_lines(snap) == ["main;model_forward();at::empty();alloc_fn() 1048576"]
+    assert len(mv.flamegraph_lines(snap, live_only=False)) == 2
+    p = tmp_path / "s.pickle"
+    p.write_bytes(pickle.dumps(snap))
+    assert mv.main([str(p), "--flamegraph", str(tmp_path / "o.folded")]) == 0
+    assert (tmp_path / "o.folded").read_text().strip().endswith("1048576")
+    assert mv.main([str(p)]) == 0 and mv.main([str(p), "--trace"]) == 0
