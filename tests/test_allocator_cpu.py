@@ -281,3 +281,63 @@ def test_snapshot_renderings(tmp_path):
     assert mv.main([str(p), "--flamegraph", str(tmp_path / "o.folded")]) == 0
     assert (tmp_path / "o.folded").read_text().strip().endswith("1048576")
     assert mv.main([str(p)]) == 0 and mv.main([str(p), "--trace"]) == 0
+
+
+@pytest.mark.parametrize("seed,expandable", [(0, False), (1, False), (2, True), (3, True)])
+def test_randomised_alloc_free_keeps_invariants(bw, seed, expandable):
+    """A few thousand random allocator operations (several streams, sizes from 1 byte to 40 MiB, frees in random order,
+    cache flushes) on the host backend: live allocations never overlap, every one lies inside a segment of the
+    snapshot, the statistics equal what the snapshot shows, and everything goes back to the system at the end."""
+    import random
+
+    prev = bw._C._allocator_config()["expandable_segments"]
+    bw._C._set_allocator_settings(f"expandable_segments:{'True' if expandable else 'False'}")
+    try:
+        h = bw._C._HostCacheHarness()
+        rng = random.Random(seed)
+        live = {}                                  # ptr -> (nbytes, stream)
+        sizes = [1, 17, 512, 4000, 70_000, 900_000, 3 * MiB, 11 * MiB, 40 * MiB]
+
+        def check():
+            spans = sorted((p, p + n) for p, (n, _) in live.items())
+            for (a0, a1), (b0, b1) in zip(spans, spans[1:]):
+                assert a1 <= b0, "two live allocations overlap"
+            snap = h.snapshot()
+            segs = [(s["address"], s["address"] + s["total_size"]) for s in snap]
+            for p, (n, _) in live.items():
+                assert any(lo <= p and p + n <= hi for lo, hi in segs), "a live allocation lies outside every segment"
+            st = h.stats()
+            in_blocks = sum(size for s in snap for size, allocated in s["blocks"] if allocated)
+            assert st["allocated_bytes"]["all"]["current"] == in_blocks
+            assert st["allocated_bytes"]["all"]["current"] >= sum(n for n, _ in live.values())
+            assert st["allocation"]["all"]["current"] == len(live)
+            assert st["reserved_bytes"]["all"]["current"] >= st["allocated_bytes"]["all"]["current"]
+
+        for step in range(1500):
+            r = rng.random()
+            if r < 0.55 or not live:
+                n = max(1, int(rng.choice(sizes) * rng.uniform(0.5, 1.5)))
+                stream = rng.choice([0, 0, 0x10, 0x20])
+                p = h.alloc(n, stream=stream)
+                assert p and p not in live
+                live[p] = (n, stream)
+            elif r < 0.95:
+                p = rng.choice(list(live))
+                if rng.random() < 0.2:
+                    h.record_stream(p, rng.choice([0x10, 0x20, 0x30]))       # a use on another stream delays its reuse
+                h.free(p)
+                del live[p]
+            else:
+                h.empty_cache()
+            if step % 100 == 0:
+                check()
+        check()
+        for p in list(live):
+            h.free(p)
+        live.clear()
+        h.empty_cache()
+        st = h.stats()
+        assert st["allocated_bytes"]["all"]["current"] == 0 and st["allocation"]["all"]["current"] == 0
+        assert st["reserved_bytes"]["all"]["current"] == 0, "memory left cached after freeing everything and flushing"
+    finally:
+        bw._C._set_allocator_settings(f"expandable_segments:{'True' if prev else 'False'}")
