@@ -171,14 +171,18 @@ def test_every_generated_operator_compiles_without_a_gpu(bw):
         a = torch.exp(x) + torch.exp2(x) + torch.expm1(x) + torch.log(x.abs() + 1) + torch.log2(x.abs() + 1) + torch.log1p(x.abs())
         b = torch.sqrt(x.abs()) + torch.rsqrt(x.abs() + 1) + torch.reciprocal(x + 3) + torch.tanh(x) + torch.sigmoid(x) + torch.relu(x)
         c = F.silu(x) + torch.erf(x) + torch.sin(x) + torch.cos(x) + (-x) + F.gelu(x) + F.gelu(x, approximate="tanh") + F.leaky_relu(x, 0.2)
-        return a + b + c
+        d = torch.tan(x) + torch.asin(x.clamp(-0.9, 0.9)) + torch.acos(x.clamp(-0.9, 0.9)) + torch.atan(x) + torch.sinh(x) + torch.cosh(x)
+        e = torch.asinh(x) + torch.acosh(x.abs() + 1.5) + torch.atanh(x.clamp(-0.9, 0.9)) + torch.erfc(x) + torch.log10(x.abs() + 1)
+        f = torch.floor(x) + torch.ceil(x) + torch.trunc(x) + torch.round(x) + torch.sign(x) + torch.isnan(x).to(x.dtype)
+        return a + b + c + d + e + f
 
     def binary(x, y):
         a = torch.maximum(x, y) + torch.minimum(x, y) + x.pow(2) + x.abs().pow(y) + torch.where(x > y, x, y) - torch.sub(x, y, alpha=2)
         b = (x < y).to(x.dtype) + (x >= 0.5).to(x.dtype) + (x <= y).to(x.dtype) + (x == y).to(x.dtype) + (x != 1.0).to(x.dtype)
         c = torch.logical_and(x > 0, y > 0).to(x.dtype) + torch.logical_or(x > 0, y > 0).to(x.dtype) + torch.logical_not(x > 0).to(x.dtype)
         d = torch.clamp(x, -1.0, 1.0) + torch.clamp_min(x, 0.1) + torch.clamp_max(y, 0.9) + (2.0 - x) + x / (y.abs() + 1) * 3.0
-        return a + b + c + d
+        e = torch.atan2(x, y) + torch.fmod(x, y.abs() + 1)
+        return a + b + c + d + e
 
     def backward_forms(g, y):
         return (aten.sigmoid_backward(g, y) + aten.tanh_backward(g, y) + aten.threshold_backward(g, y, 0.0) + aten.silu_backward(g, y)

@@ -171,6 +171,25 @@ _reg(aten.silu.default)(lambda a, n: f"({a[0]} * sigmoidf({a[0]}))")
 _reg(aten.erf.default)(lambda a, n: f"erff({a[0]})")
 _reg(aten.sin.default)(lambda a, n: f"sinf({a[0]})")
 _reg(aten.cos.default)(lambda a, n: f"cosf({a[0]})")
+_reg(aten.tan.default)(lambda a, n: f"tanf({a[0]})")
+_reg(aten.asin.default)(lambda a, n: f"asinf({a[0]})")
+_reg(aten.acos.default)(lambda a, n: f"acosf({a[0]})")
+_reg(aten.atan.default)(lambda a, n: f"atanf({a[0]})")
+_reg(aten.sinh.default)(lambda a, n: f"sinhf({a[0]})")
+_reg(aten.cosh.default)(lambda a, n: f"coshf({a[0]})")
+_reg(aten.asinh.default)(lambda a, n: f"asinhf({a[0]})")
+_reg(aten.acosh.default)(lambda a, n: f"acoshf({a[0]})")
+_reg(aten.atanh.default)(lambda a, n: f"atanhf({a[0]})")
+_reg(aten.erfc.default)(lambda a, n: f"erfcf({a[0]})")
+_reg(aten.log10.default)(lambda a, n: f"log10f({a[0]})")
+_reg(aten.floor.default)(lambda a, n: f"floorf({a[0]})")
+_reg(aten.ceil.default)(lambda a, n: f"ceilf({a[0]})")
+_reg(aten.trunc.default)(lambda a, n: f"truncf({a[0]})")
+_reg(aten.round.default)(lambda a, n: f"nearbyintf({a[0]})")
+_reg(aten.sign.default)(lambda a, n: f"(float)(({a[0]} > 0.0f) - ({a[0]} < 0.0f))")
+_reg(aten.atan2.default)(lambda a, n: f"atan2f({a[0]}, {a[1]})")
+_reg(aten.fmod.Tensor, aten.fmod.Scalar)(lambda a, n: f"fmodf({a[0]}, {a[1]})")
+_reg(aten.isnan.default)(lambda a, n: _b(f"{a[0]} != {a[0]}"))
 _reg(aten.maximum.default)(lambda a, n: f"fmaxf({a[0]}, {a[1]})")
 _reg(aten.minimum.default)(lambda a, n: f"fminf({a[0]}, {a[1]})")
 _reg(aten.pow.Tensor_Tensor, aten.pow.Tensor_Scalar)(
