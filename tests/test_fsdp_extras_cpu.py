@@ -265,3 +265,34 @@ def test_pipeline_schedules_match_single_process():
 
     with _pytest.raises(ValueError):
         split_into_stages([torch.nn.ReLU()], 2)
+
+
+def _sharded_scaler_body(rank, world):
+    """A non-finite gradient on ONE rank skips the step on EVERY rank (and only the scale changes)."""
+    from torch_musa_b200.parallel.zero import ShardedFusedAdamW
+
+    torch.manual_seed(0)
+    ps = [torch.nn.Parameter((torch.randn(64, 8) * 0.1).to(torch.bfloat16)), torch.nn.Parameter(torch.zeros(8, dtype=torch.bfloat16))]
+    opt = ShardedFusedAdamW(ps, lr=1e-2, bucket_mb=1)
+    scaler = torch.amp.GradScaler("cpu", init_scale=64.0, growth_interval=100)
+    before = [p.detach().clone() for p in ps]
+    for p in ps:
+        p.grad.fill_(0.5 * 64.0)
+    if rank == 1:
+        ps[0].grad[3, 3] = float("nan")
+    assert opt.step_with_scaler(scaler) is False and scaler.get_scale() == 32.0
+    assert all(torch.equal(a, b) for a, b in zip(before, ps))
+    opt.zero_grad()
+    for p in ps:
+        p.grad.fill_(0.5 * 32.0)
+    assert opt.step_with_scaler(scaler) is True
+    assert all(not torch.equal(a, b) for a, b in zip(before, ps))
+    # every rank holds the same updated parameters
+    flat = torch.cat([p.detach().float().reshape(-1) for p in ps])
+    ref = flat.clone()
+    torch.distributed.broadcast(ref, src=0)
+    assert torch.equal(flat, ref)
+
+
+def test_sharded_adamw_loss_scaling_skips_on_every_rank():
+    run_ranks(_sharded_scaler_body, 2, "gloo")
